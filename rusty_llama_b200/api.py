@@ -1,0 +1,114 @@
+"""The Python entry point: load a model folder, generate from token ids.
+
+Names follow the reference where it has them: `generate` with a `steps` count that
+includes the prompt (src/model.rs:1640-1706), `temperature`, `top_p`, `seed` as its
+`-t -p -s` (src/main.rs:24-32).  Text never enters: prompts are lists of token ids.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Mapping, Optional, Sequence, Union
+
+import torch
+
+from .config.llama import read_config_json
+from .engine import Engine, GenerationResult, GenerationStats, StepEntry, generate
+from .errors import StepError
+from .models.model import Model
+from .sampling import Sampler, SamplingParams
+from .weights import load_model, random_model
+
+DEFAULT_STEPS = 256  # the reference's `-n` default (src/main.rs:30)
+
+
+class LLM:
+    """A loaded model with its cache, step function and sampler."""
+
+    def __init__(self, model: Model, max_tokens: Optional[int] = None, max_seqs: Optional[int] = None, use_graphs: bool = True):
+        self.model = model
+        if max_tokens is None:
+            max_tokens = 8 * model.spec.max_positions
+        self.engine = Engine(model, max_tokens, max_seqs, use_graphs=use_graphs)
+        self.sampler = Sampler(model.rt.device, self.engine.cache.max_seqs, model.spec.vocab_size, model.rt.workspace)
+        self.last_stats: Optional[GenerationStats] = None
+
+    # -- the step function, for callers that schedule by themselves
+    def open_sequence(self) -> int:
+        return self.engine.open_sequence()
+
+    def close_sequence(self, slot: int) -> None:
+        self.engine.close_sequence(slot)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        return self.engine.step(entries)
+
+    # -- generation
+    def generate(
+        self,
+        prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+        max_new_tokens: Optional[int] = None,
+        temperature: float = 1.0,
+        top_p: float = 0.9,
+        seed: Optional[int] = None,
+        steps: Optional[int] = None,
+        stop_token_ids: Optional[Sequence[int]] = None,
+        include_stop: bool = False,
+        max_batch: Optional[int] = None,
+        on_token: Optional[Callable[[int, int], None]] = None,
+        return_results: bool = False,
+    ):
+        """Token ids generated after each prompt.
+
+        prompts: one list of ids, or a list of them (then a list of lists comes back).
+        max_new_tokens: tokens to produce per prompt.  `steps` is the reference's count
+        instead: positions in total, prompt included, clamped to the model's limit
+        (src/model.rs:1668); give one of the two (neither: steps = 256).
+        temperature 0 is greedy; top_p outside (0, 1) turns the nucleus off; seed None
+        takes the wall clock."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        batch: List[Sequence[int]] = [prompts] if single else list(prompts)  # type: ignore[list-item]
+        if max_new_tokens is not None and steps is not None:
+            raise StepError("give max_new_tokens or steps, not both")
+        params = SamplingParams(temperature, top_p, seed)
+        stats = GenerationStats()
+        if max_new_tokens is None:
+            total = min(DEFAULT_STEPS if steps is None else steps, self.engine.max_positions)
+            budget = [max(total - len(p), 0) for p in batch]
+        else:
+            budget = max_new_tokens
+        results = generate(
+            self.engine, self.sampler, batch, budget, params, stop_token_ids, include_stop, max_batch, on_token, stats
+        )
+        self.last_stats = stats
+        if return_results:
+            return results[0] if single else results
+        toks = [r.tokens for r in results]
+        return toks[0] if single else toks
+
+
+def load(
+    model_dir: str,
+    dtype: str = "bfloat16",
+    device: str = "cuda:0",
+    max_tokens: Optional[int] = None,
+    max_seqs: Optional[int] = None,
+    use_graphs: bool = True,
+) -> LLM:
+    """A model folder (config.json + model.safetensors) -> LLM.  config.json picks the architecture."""
+    return LLM(load_model(model_dir, dtype=dtype, device=device), max_tokens, max_seqs, use_graphs)
+
+
+def load_random(
+    config: Union[str, Mapping],
+    seed: int = 0,
+    dtype: str = "bfloat16",
+    device: str = "cuda:0",
+    max_tokens: Optional[int] = None,
+    max_seqs: Optional[int] = None,
+    use_graphs: bool = True,
+    std: float = 0.02,
+    norm_jitter: float = 0.0,
+) -> LLM:
+    """An LLM with random weights made on the device from a configuration (a dict or a folder with config.json)."""
+    cfg = read_config_json(config) if isinstance(config, str) else config
+    return LLM(random_model(cfg, seed, dtype, device, std, norm_jitter), max_tokens, max_seqs, use_graphs)

@@ -1,0 +1,105 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions
+// and the convention of the exported launchers.
+//
+// Every launcher is `extern "C"`, takes raw device pointers, sizes and the
+// stream to launch on, allocates nothing and returns 0 or an error code:
+// a positive code is a CUDA error (cudaError_t) seen right after the launch,
+// a negative one means the launcher refused its arguments before launching;
+// `rl_error_text()` then holds the reason.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define RL_API extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+
+// dtype codes shared with the Python side
+#define RL_F32 0
+#define RL_BF16 1
+
+static thread_local char rl_error_buf[512] = {0};
+
+#define RL_REFUSE(code, ...)                                         \
+  do {                                                               \
+    snprintf(rl_error_buf, sizeof(rl_error_buf), __VA_ARGS__);       \
+    return -(code);                                                  \
+  } while (0)
+
+#define RL_LAUNCH_RESULT()                                                         \
+  do {                                                                             \
+    cudaError_t rl_e = cudaGetLastError();                                         \
+    if (rl_e != cudaSuccess) {                                                     \
+      snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(rl_e)); \
+      return (int)rl_e;                                                            \
+    }                                                                              \
+    return 0;                                                                      \
+  } while (0)
+
+#define RL_DEFINE_ERROR_TEXT() \
+  RL_API const char* rl_error_text() { return rl_error_buf; }
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block whose size is a multiple of 32 and at most 1024.  The order
+// of the additions depends on the block size only, so equal inputs give equal
+// bits.  `red` is 32 floats of shared memory.  Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nwarps; ++w) t += red[w];
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = red[0];
+  for (int w = 1; w < nwarps; ++w) t = fmaxf(t, red[w]);
+  return t;
+}
+
+// 8 bf16 values (16 bytes) to 8 floats.
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = __bfloat1622float2(p[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}

@@ -1,0 +1,128 @@
+// Row-wise kernels around the residual stream: embedding rows, the fused
+// residual sum + RMSNorm, and the gated activation of the feed-forward.
+//
+// The residual stream is kept in 32-bit in both precisions.  What a mixer or a
+// feed-forward returns (in the activation type, possibly as several partial
+// sums of a split matrix product) is added to it in 32-bit inside the norm
+// kernel, which then writes the normalised row in the activation type: one
+// pass over the row instead of the reference's separate `add_kernel` and
+// `rmsnorm_kernel` (src/backend/cuda.rs:90-116).
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[tokens[t], :] widened to 32-bit, no scale (src/model.rs:1237-1242).
+template <typename TW>
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                    float* __restrict__ out, int d) {
+  const int t = blockIdx.x;
+  const TW* row = table + (size_t)tokens[t] * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+RL_API int rl_embed_gather(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens,
+                           int d, cudaStream_t stream) {
+  if (n_tokens <= 0 || d <= 0) RL_REFUSE(1, "embed_gather: n_tokens=%d d=%d", n_tokens, d);
+  if (table_dtype == RL_BF16)
+    embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>(tokens, (const bf16*)table, out, d);
+  else if (table_dtype == RL_F32)
+    embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, out, d);
+  else
+    RL_REFUSE(2, "embed_gather: unknown table dtype %d", table_dtype);
+  RL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- residual sum + RMSNorm
+// For output row r (stream row t = rows ? rows[r] : r):
+//   v = x[t] + delta[0][t] + delta[1][t] + ...        (32-bit, in this order)
+//   if write_x: x[t] = v
+//   if w: out[r] = v * (1 / sqrt(sum(v^2)/d + eps)) * w   (src/backend/cpu.rs:96-105)
+// The row is held in shared memory between the two passes.
+template <typename TA, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, int n_parts,
+                                   long long part_stride, const TW* __restrict__ w, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int d, float eps, int write_x) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float* xr = x + (size_t)t * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = xr[i];
+    for (int p = 0; p < n_parts; ++p) v += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
+    row[i] = v;
+    if (write_x) xr[i] = v;
+    ss += v * v;
+  }
+  if (w == nullptr) return;
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)d + eps);
+  TA* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>(row[i] * inv * to_f32(w[i]));
+}
+
+template <typename TA, typename TW>
+static int launch_add_rmsnorm(float* x, const void* delta, int n_parts, long long part_stride, const void* w,
+                              void* out, const int* rows, int n_rows, int d, float eps, int write_x,
+                              cudaStream_t stream) {
+  const size_t smem = (size_t)d * sizeof(float);
+  auto kern = add_rmsnorm_kernel<TA, TW>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) RL_REFUSE(3, "add_rmsnorm: a row of %d values does not fit shared memory", d);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) RL_REFUSE(4, "add_rmsnorm: cannot get %zu bytes of shared memory", smem);
+  }
+  kern<<<n_rows, 256, smem, stream>>>(x, (const TA*)delta, n_parts, part_stride, (const TW*)w, (TA*)out, rows, d,
+                                      eps, write_x);
+  RL_LAUNCH_RESULT();
+}
+
+RL_API int rl_add_rmsnorm(float* x, const void* delta, int n_parts, long long part_stride, const void* w,
+                          int w_dtype, void* out, int act_dtype, const int* rows, int n_rows, int d, float eps,
+                          int write_x, cudaStream_t stream) {
+  if (n_rows <= 0 || d <= 0 || n_parts < 0) RL_REFUSE(1, "add_rmsnorm: n_rows=%d d=%d n_parts=%d", n_rows, d, n_parts);
+  if (n_parts > 0 && delta == nullptr) RL_REFUSE(2, "add_rmsnorm: %d parts but no delta", n_parts);
+  if (w != nullptr && out == nullptr) RL_REFUSE(2, "add_rmsnorm: a weight but no output");
+  if (act_dtype == RL_BF16 && w_dtype == RL_BF16)
+    return launch_add_rmsnorm<bf16, bf16>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
+  if (act_dtype == RL_BF16 && w_dtype == RL_F32)
+    return launch_add_rmsnorm<bf16, float>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
+  if (act_dtype == RL_F32 && w_dtype == RL_F32)
+    return launch_add_rmsnorm<float, float>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
+  if (act_dtype == RL_F32 && w_dtype == RL_BF16)
+    return launch_add_rmsnorm<float, bf16>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
+  RL_REFUSE(5, "add_rmsnorm: unknown dtypes act=%d w=%d", act_dtype, w_dtype);
+}
+
+// ---------------------------------------------------------------- gated activation
+// h[t, i] = silu(g) * u with g = gu[t, i], u = gu[t, ff + i], silu(z) = z / (1 + exp(-z))
+// in 32-bit (src/math.rs:25-27, src/backend/cuda.rs:94-97).
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ h, int ff, long long total) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += step) {
+    const long long t = idx / ff;
+    const int i = (int)(idx - t * ff);
+    const float g = to_f32(gu[t * 2 * ff + i]);
+    const float u = to_f32(gu[t * 2 * ff + ff + i]);
+    h[idx] = from_f32<TA>(g * (1.0f / (1.0f + expf(-g))) * u);
+  }
+}
+
+RL_API int rl_swiglu(const void* gate_up, void* h, int act_dtype, int n_tokens, int ff, cudaStream_t stream) {
+  if (n_tokens <= 0 || ff <= 0) RL_REFUSE(1, "swiglu: n_tokens=%d ff=%d", n_tokens, ff);
+  const long long total = (long long)n_tokens * ff;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (act_dtype == RL_BF16)
+    swiglu_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)h, ff, total);
+  else if (act_dtype == RL_F32)
+    swiglu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)h, ff, total);
+  else
+    RL_REFUSE(2, "swiglu: unknown dtype %d", act_dtype);
+  RL_LAUNCH_RESULT();
+}

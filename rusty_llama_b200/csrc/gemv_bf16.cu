@@ -1,0 +1,135 @@
+// Matrix products of the decode step in bfloat16: out[M, N] = x[M, K] . w[N, K]^T
+// for a handful of rows (M <= 64), where every weight is read from HBM exactly
+// once and the arithmetic is free.  Counterpart of the reference's warp-per-row
+// GEMV family (src/backend/cuda.rs:354-442), with tensor cores instead of dp4a.
+//
+// A block owns 16 output features; its 8 warps take the 32-wide k blocks in
+// turn, so the block streams 512 contiguous bytes of each of its 16 weight rows
+// per round.  Inside a warp the weights are the A operand of
+// mma.sync.m16n8k16 (16 features x 16 k) and the activations the B operand
+// (16 k x 8 batch rows), accumulated in 32-bit.  A lane loads 16 contiguous
+// bytes of a weight row and uses them as its k elements of two consecutive
+// MMAs; the activations are loaded with the same rule, so both operands agree
+// on which k sits where and the sum over k is unchanged.  The eight partial
+// sums of a block are added in warp order through shared memory: no atomics,
+// no scratch, the same bits every run.
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define WARPS 8
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const bf16* p) {
+  uint4 v;
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <typename TO>
+__device__ __forceinline__ void store_out(TO* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int NT, typename TO>
+__global__ void __launch_bounds__(WARPS * 32)
+gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, int ldw, TO* __restrict__ out,
+                 int ldo, int M, int N, int K) {
+  __shared__ float red[WARPS][NT * 128];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const bool row0_ok = n0 + g < N, row1_ok = n0 + g + 8 < N;
+  const bf16* w0 = w + (size_t)(row0_ok ? n0 + g : 0) * ldw;
+  const bf16* w1 = w + (size_t)(row1_ok ? n0 + g + 8 : 0) * ldw;
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  const int n_blocks = (K + 31) / 32;
+  // U k blocks of weights are requested before the first is used, so that each
+  // lane keeps 2 * U 16-byte loads in flight.
+  constexpr int U = 4;
+  for (int kb = warp; kb < n_blocks; kb += WARPS * U) {
+    uint4 a0[U], a1[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (kb + u * WARPS) * 32 + 8 * t4;
+      const bool k_ok = k + 8 <= K;
+      a0[u] = (k_ok && row0_ok) ? ld_stream(w0 + k) : zero;
+      a1[u] = (k_ok && row1_ok) ? ld_stream(w1 + k) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (kb + u * WARPS) * 32 + 8 * t4;
+      const bool k_ok = k + 8 <= K;
+      uint4 b[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int m = nt * 8 + g;
+        b[nt] = (k_ok && m < M) ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k)) : zero;
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        mma_bf16(acc[nt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b[nt].x, b[nt].y);
+        mma_bf16(acc[nt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[nt].z, b[nt].w);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) red[warp][nt * 128 + lane * 4 + c] = acc[nt][c];
+  __syncthreads();
+  for (int e = tid; e < NT * 128; e += WARPS * 32) {
+    float sum = 0.f;
+#pragma unroll
+    for (int wq = 0; wq < WARPS; ++wq) sum += red[wq][e];
+    const int nt = e >> 7, l = (e & 127) >> 2, c = e & 3;
+    const int n = n0 + (l >> 2) + 8 * (c >> 1);
+    const int m = nt * 8 + 2 * (l & 3) + (c & 1);
+    if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, sum);
+  }
+}
+
+template <int NT>
+static int launch_gemv(const bf16* x, int ldx, const bf16* w, int ldw, void* out, int out_dtype, int ldo, int M,
+                       int N, int K, cudaStream_t stream) {
+  const int blocks = (N + 15) / 16;
+  if (out_dtype == RL_F32)
+    gemv_bf16_kernel<NT, float><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (float*)out, ldo, M, N, K);
+  else
+    gemv_bf16_kernel<NT, bf16><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (bf16*)out, ldo, M, N, K);
+  RL_LAUNCH_RESULT();
+}
+
+RL_API int rl_gemv_bf16_max_rows() { return 64; }
+
+RL_API int rl_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M,
+                        int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_bf16: M=%d N=%d K=%d", M, N, K);
+  if (M > 64) RL_REFUSE(2, "gemv_bf16: %d rows, this kernel takes at most 64", M);
+  if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_bf16: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte loads)", K, ldx, ldw);
+  if (ldx < K || ldw < K || ldo < N) RL_REFUSE(4, "gemv_bf16: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
+  if (out_dtype != RL_F32 && out_dtype != RL_BF16) RL_REFUSE(5, "gemv_bf16: unknown output dtype %d", out_dtype);
+  const bf16* xx = (const bf16*)x;
+  const bf16* ww = (const bf16*)w;
+  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
+  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
+  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
+  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
+}

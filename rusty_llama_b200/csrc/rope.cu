@@ -1,0 +1,105 @@
+// Rotary position encoding fused with the write of keys and values into the
+// paged cache: one kernel where the reference runs a projection into the cache
+// span, `rope_kernel` and `kv_append` (src/backend/cuda.rs:119-149, :1511-1512).
+//
+// Input: the fused projection qkv[T, row_stride] holding, per token, H query
+// heads, then K key heads, then K value heads, each of `hd` values.
+//   - q is rotated in place;
+//   - k is rotated and stored, v is stored, at (page, slot in page) of the
+//     token's position in its sequence's page table.
+// Angle of pair j at position p: (float)p * inv_freq[j], one 32-bit multiply,
+// then sincosf (src/backend/cpu.rs:337-352).  Pairs are neighbours (2j, 2j+1)
+// when `interleaved`, else halves (j, j + rot/2); dimensions from `rot` on pass
+// through unrotated (partial rotary, src/backend/cpu.rs:319-341).
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                     int table_width, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     const float* __restrict__ inv_freq, int H, int K, int hd, int rot,
+                                     int interleaved, int page_size, int write_kv) {
+  extern __shared__ float trig[];  // cos[rot/2], sin[rot/2]
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = rot >> 1;
+  float* cs = trig;
+  float* sn = trig + half;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const float a = (float)pos * inv_freq[j];
+    float s, c;
+    sincosf(a, &s, &c);
+    cs[j] = c;
+    sn[j] = s;
+  }
+  __syncthreads();
+
+  T* row = qkv + (size_t)t * row_stride;
+  // query heads, in place
+  const int q_pairs = H * half;
+  for (int idx = threadIdx.x; idx < q_pairs; idx += blockDim.x) {
+    const int h = idx / half, j = idx - h * half;
+    const int i0 = interleaved ? 2 * j : j;
+    const int i1 = interleaved ? 2 * j + 1 : j + half;
+    T* head = row + (size_t)h * hd;
+    const float x0 = to_f32(head[i0]), x1 = to_f32(head[i1]);
+    head[i0] = from_f32<T>(x0 * cs[j] - x1 * sn[j]);
+    head[i1] = from_f32<T>(x0 * sn[j] + x1 * cs[j]);
+  }
+  if (!write_kv) return;
+
+  const int seq = tok_seq[t];
+  const int page = block_table[(size_t)seq * table_width + pos / page_size];
+  const int in_page = pos % page_size;
+  const T* krow = row + (size_t)H * hd;
+  const T* vrow = krow + (size_t)K * hd;
+  // key heads: rotated pairs, then the unrotated tail
+  const int k_pairs = K * half;
+  for (int idx = threadIdx.x; idx < k_pairs; idx += blockDim.x) {
+    const int h = idx / half, j = idx - h * half;
+    const int i0 = interleaved ? 2 * j : j;
+    const int i1 = interleaved ? 2 * j + 1 : j + half;
+    const T* head = krow + (size_t)h * hd;
+    T* dst = k_pages + (((size_t)page * K + h) * page_size + in_page) * hd;
+    const float x0 = to_f32(head[i0]), x1 = to_f32(head[i1]);
+    dst[i0] = from_f32<T>(x0 * cs[j] - x1 * sn[j]);
+    dst[i1] = from_f32<T>(x0 * sn[j] + x1 * cs[j]);
+  }
+  const int tail = hd - rot;
+  for (int idx = threadIdx.x; idx < K * tail; idx += blockDim.x) {
+    const int h = idx / tail, i = rot + (idx - h * tail);
+    k_pages[(((size_t)page * K + h) * page_size + in_page) * hd + i] = krow[(size_t)h * hd + i];
+  }
+  for (int idx = threadIdx.x; idx < K * hd; idx += blockDim.x) {
+    const int h = idx / hd, i = idx - h * hd;
+    v_pages[(((size_t)page * K + h) * page_size + in_page) * hd + i] = vrow[idx];
+  }
+}
+
+RL_API int rl_rope_kv_write(void* qkv, int dtype, int row_stride, const int* tok_pos, const int* tok_seq,
+                            const int* block_table, int table_width, void* k_pages, void* v_pages,
+                            const float* inv_freq, int n_tokens, int H, int K, int hd, int rot, int interleaved,
+                            int page_size, int write_kv, cudaStream_t stream) {
+  if (n_tokens <= 0 || H <= 0 || K < 0 || hd <= 0) RL_REFUSE(1, "rope_kv_write: T=%d H=%d K=%d hd=%d", n_tokens, H, K, hd);
+  if (rot < 0 || rot > hd || (rot & 1)) RL_REFUSE(2, "rope_kv_write: rotary size %d does not fit a head of %d", rot, hd);
+  if (row_stride < (H + (write_kv ? 2 * K : 0)) * hd) RL_REFUSE(3, "rope_kv_write: row stride %d too small", row_stride);
+  if (write_kv && (page_size <= 0 || !block_table || !k_pages || !v_pages || table_width <= 0))
+    RL_REFUSE(4, "rope_kv_write: a cache write needs pages and a page table");
+  if (rot > 0 && inv_freq == nullptr) RL_REFUSE(5, "rope_kv_write: no frequency table");
+  const size_t smem = (size_t)rot * sizeof(float);
+  if (smem > 48 * 1024) RL_REFUSE(6, "rope_kv_write: rotary size %d too large", rot);
+  if (dtype == RL_BF16)
+    rope_kv_write_kernel<bf16><<<n_tokens, 128, smem, stream>>>((bf16*)qkv, row_stride, tok_pos, tok_seq, block_table,
+                                                               table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq,
+                                                               H, K, hd, rot, interleaved, page_size, write_kv);
+  else if (dtype == RL_F32)
+    rope_kv_write_kernel<float><<<n_tokens, 128, smem, stream>>>((float*)qkv, row_stride, tok_pos, tok_seq,
+                                                                 block_table, table_width, (float*)k_pages,
+                                                                 (float*)v_pages, inv_freq, H, K, hd, rot,
+                                                                 interleaved, page_size, write_kv);
+  else
+    RL_REFUSE(7, "rope_kv_write: unknown dtype %d", dtype);
+  RL_LAUNCH_RESULT();
+}

@@ -1,0 +1,408 @@
+"""The kernels as Python functions on torch tensors.
+
+Each function checks what the kernel cannot check for itself (device, dtype,
+contiguity, sizes that index arithmetic relies on), passes raw pointers and the
+current stream to the launcher and raises KernelError when the launcher refuses
+or the launch fails.  Nothing here computes with torch: if the extension cannot
+be built or loaded, every call fails.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from ..errors import KernelError
+from . import build
+
+PAGE_SIZE = 64  # tokens per cache page; the attention kernels' key tile
+
+_F32, _BF16 = 0, 1
+_DT = {torch.float32: _F32, torch.bfloat16: _BF16}
+
+c_int, c_ll, c_float, c_void_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def _dt(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is neither float32 nor bfloat16") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(t: torch.Tensor, what: str, dtype=None, contiguous=True) -> torch.Tensor:
+    _need(isinstance(t, torch.Tensor), f"{what}: not a tensor")
+    _need(t.is_cuda, f"{what}: tensor is on {t.device}, the kernels run on CUDA only")
+    if dtype is not None:
+        _need(t.dtype == dtype, f"{what}: dtype {t.dtype}, expected {dtype}")
+    if contiguous:
+        _need(t.is_contiguous(), f"{what}: tensor is not contiguous")
+    return t
+
+
+def _rows(t: torch.Tensor, what: str) -> int:
+    """Row stride of a 2-D tensor whose rows are dense."""
+    _need(t.dim() == 2 and t.stride(1) == 1, f"{what}: expected a 2-D tensor with dense rows")
+    return t.stride(0)
+
+
+def _p(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(lib, rc: int, name: str) -> None:
+    if rc != 0:
+        text = lib.rl_error_text().decode("utf-8", "replace")
+        kind = "refused its arguments" if rc < 0 else f"failed to launch (CUDA error {rc})"
+        raise KernelError(f"{name} {kind}: {text}")
+
+
+# ------------------------------------------------------------------ row kernels
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[tokens[t]] as float32.  Token ids must already be known to lie in the table."""
+    _cuda(tokens, "embed_gather tokens", torch.int32)
+    _cuda(table, "embed_gather table")
+    _need(tokens.dim() == 1 and table.dim() == 2, "embed_gather: tokens[T] and table[V, d] expected")
+    T, d = tokens.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((T, d), dtype=torch.float32, device=table.device)
+    _cuda(out, "embed_gather out", torch.float32)
+    _need(tuple(out.shape) == (T, d), "embed_gather: out has the wrong shape")
+    lib = build.load("elementwise")
+    rc = lib.rl_embed_gather(_p(tokens), _p(table), c_int(_dt(table, "embed_gather table")), _p(out), c_int(T), c_int(d), _stream())
+    _check(lib, rc, "embed_gather")
+    return out
+
+
+def add_rmsnorm(
+    x: torch.Tensor,
+    delta: Optional[torch.Tensor],
+    weight: Optional[torch.Tensor],
+    eps: float,
+    act_dtype: torch.dtype,
+    rows: Optional[torch.Tensor] = None,
+    write_x: bool = True,
+    out: Optional[torch.Tensor] = None,
+) -> Optional[torch.Tensor]:
+    """x (float32 [T, d]) += sum of delta parts; returns rmsnorm(x) * weight in `act_dtype`.
+
+    delta: None, [T, d] or [parts, T, d] in `act_dtype`.  weight None: only the sum.
+    rows: int32 indices of the rows to produce (all rows if None).
+    """
+    _cuda(x, "add_rmsnorm x", torch.float32)
+    _need(x.dim() == 2, "add_rmsnorm: x must be [T, d]")
+    T, d = x.shape
+    n_parts, part_stride = 0, 0
+    if delta is not None:
+        _cuda(delta, "add_rmsnorm delta", act_dtype)
+        if delta.dim() == 2:
+            _need(tuple(delta.shape) == (T, d), f"add_rmsnorm: delta {tuple(delta.shape)} does not match x {(T, d)}")
+            n_parts = 1
+        else:
+            _need(delta.dim() == 3 and tuple(delta.shape[1:]) == (T, d), f"add_rmsnorm: delta {tuple(delta.shape)} does not match x {(T, d)}")
+            n_parts, part_stride = delta.shape[0], T * d
+    n_rows = T
+    if rows is not None:
+        _cuda(rows, "add_rmsnorm rows", torch.int32)
+        n_rows = rows.numel()
+    w_dt = _F32
+    if weight is not None:
+        _cuda(weight, "add_rmsnorm weight")
+        _need(tuple(weight.shape) == (d,), f"add_rmsnorm: weight {tuple(weight.shape)} does not match d={d}")
+        w_dt = _dt(weight, "add_rmsnorm weight")
+        if out is None:
+            out = torch.empty((n_rows, d), dtype=act_dtype, device=x.device)
+        _cuda(out, "add_rmsnorm out", act_dtype)
+        _need(tuple(out.shape) == (n_rows, d), "add_rmsnorm: out has the wrong shape")
+    else:
+        _need(delta is not None, "add_rmsnorm: neither a delta nor a weight, nothing to do")
+        out = None
+    if n_rows == 0:
+        return out
+    lib = build.load("elementwise")
+    rc = lib.rl_add_rmsnorm(
+        _p(x), _p(delta), c_int(n_parts), c_ll(part_stride), _p(weight), c_int(w_dt), _p(out),
+        c_int(_DT[act_dtype]), _p(rows), c_int(n_rows), c_int(d), c_float(eps), c_int(1 if write_x else 0), _stream(),
+    )
+    _check(lib, rc, "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h[t, i] = silu(gate_up[t, i]) * gate_up[t, ff + i]."""
+    _cuda(gate_up, "swiglu input")
+    _need(gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0, "swiglu: input must be [T, 2*ff]")
+    T, ff = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((T, ff), dtype=gate_up.dtype, device=gate_up.device)
+    _cuda(out, "swiglu out", gate_up.dtype)
+    _need(tuple(out.shape) == (T, ff), "swiglu: out has the wrong shape")
+    lib = build.load("elementwise")
+    rc = lib.rl_swiglu(_p(gate_up), _p(out), c_int(_dt(gate_up, "swiglu")), c_int(T), c_int(ff), _stream())
+    _check(lib, rc, "swiglu")
+    return out
+
+
+# ------------------------------------------------------------------ position encoding + cache write
+def rope_kv_write(
+    qkv: torch.Tensor,
+    tok_pos: torch.Tensor,
+    tok_seq: torch.Tensor,
+    block_table: Optional[torch.Tensor],
+    k_pages: Optional[torch.Tensor],
+    v_pages: Optional[torch.Tensor],
+    inv_freq: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    rotary_dim: int,
+    interleaved: bool,
+    write_kv: bool = True,
+) -> None:
+    """Rotate q (in place) and k, store k and v at each token's place in the paged cache.
+
+    qkv: [T, >= (H + 2K) * hd] rows holding q heads, k heads, v heads.
+    k_pages, v_pages: [pages, K, PAGE_SIZE, hd] of qkv's dtype.
+    """
+    _cuda(qkv, "rope_kv_write qkv", contiguous=False)
+    stride = _rows(qkv, "rope_kv_write qkv")
+    T = qkv.shape[0]
+    _cuda(tok_pos, "rope_kv_write tok_pos", torch.int32)
+    _cuda(tok_seq, "rope_kv_write tok_seq", torch.int32)
+    _need(tok_pos.numel() == T and tok_seq.numel() == T, "rope_kv_write: one position and one sequence index per token")
+    width = 0
+    if write_kv:
+        _cuda(block_table, "rope_kv_write block_table", torch.int32)
+        _need(block_table.dim() == 2, "rope_kv_write: block_table must be [S, width]")
+        width = block_table.shape[1]
+        for name, pages in (("k_pages", k_pages), ("v_pages", v_pages)):
+            _cuda(pages, f"rope_kv_write {name}", qkv.dtype)
+            _need(
+                pages.dim() == 4 and tuple(pages.shape[1:]) == (num_kv_heads, PAGE_SIZE, head_dim),
+                f"rope_kv_write: {name} {tuple(pages.shape)} is not [pages, {num_kv_heads}, {PAGE_SIZE}, {head_dim}]",
+            )
+        _need(qkv.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim, "rope_kv_write: qkv rows too short")
+    if rotary_dim:
+        _cuda(inv_freq, "rope_kv_write inv_freq", torch.float32)
+        _need(inv_freq.numel() == rotary_dim // 2, "rope_kv_write: inv_freq must hold rotary_dim/2 values")
+    lib = build.load("rope")
+    rc = lib.rl_rope_kv_write(
+        _p(qkv), c_int(_dt(qkv, "rope_kv_write")), c_int(stride), _p(tok_pos), _p(tok_seq), _p(block_table), c_int(width),
+        _p(k_pages), _p(v_pages), _p(inv_freq), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(rotary_dim), c_int(1 if interleaved else 0), c_int(PAGE_SIZE), c_int(1 if write_kv else 0), _stream(),
+    )
+    _check(lib, rc, "rope_kv_write")
+
+
+# ------------------------------------------------------------------ attention
+def _check_pages(k_pages, v_pages, dtype, K, hd, what):
+    for name, pages in (("k_pages", k_pages), ("v_pages", v_pages)):
+        _cuda(pages, f"{what} {name}", dtype)
+        _need(
+            pages.dim() == 4 and tuple(pages.shape[1:]) == (K, PAGE_SIZE, hd),
+            f"{what}: {name} {tuple(pages.shape)} is not [pages, {K}, {PAGE_SIZE}, {hd}]",
+        )
+
+
+def attn_generic(
+    q: torch.Tensor, k_pages, v_pages, block_table, tok_seq, tok_pos, num_heads: int, num_kv_heads: int,
+    head_dim: int, window: int = 0, scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Attention of each token over its sequence's cached keys 0..pos; any head size up to 256, both dtypes.
+
+    q: [T, >= H*hd] rows (the q part of the fused projection may be passed as is)."""
+    _cuda(q, "attn_generic q", contiguous=False)
+    qs = _rows(q, "attn_generic q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * head_dim, "attn_generic: q rows too short")
+    _check_pages(k_pages, v_pages, q.dtype, num_kv_heads, head_dim, "attn_generic")
+    _cuda(block_table, "attn_generic block_table", torch.int32)
+    _cuda(tok_seq, "attn_generic tok_seq", torch.int32)
+    _cuda(tok_pos, "attn_generic tok_pos", torch.int32)
+    _need(tok_seq.numel() == T and tok_pos.numel() == T and block_table.dim() == 2, "attn_generic: metadata sizes")
+    if out is None:
+        out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _cuda(out, "attn_generic out", q.dtype)
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    lib = build.load("attention_generic")
+    rc = lib.rl_attn_generic(
+        _p(q), c_int(_dt(q, "attn_generic")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table),
+        c_int(block_table.shape[1]), _p(tok_seq), _p(tok_pos), _p(out), c_int(out.stride(0)), c_int(T),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _stream(),
+    )
+    _check(lib, rc, "attn_generic")
+    return out
+
+
+def attn_decode_scratch_floats(n_seqs: int, num_heads: int, head_dim: int, n_splits: int) -> int:
+    return n_seqs * num_heads * n_splits * (head_dim + 2)
+
+
+def attn_decode(
+    q: torch.Tensor, k_pages, v_pages, block_table, seq_len, num_heads: int, num_kv_heads: int, head_dim: int,
+    n_splits: int, scratch: torch.Tensor, window: int = 0, scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One query token per sequence over keys 0..seq_len-1, the key range cut into `n_splits`.
+
+    scratch: float32 tensor of at least attn_decode_scratch_floats(...) elements."""
+    _cuda(q, "attn_decode q", contiguous=False)
+    qs = _rows(q, "attn_decode q")
+    S = q.shape[0]
+    _need(q.shape[1] >= num_heads * head_dim, "attn_decode: q rows too short")
+    _check_pages(k_pages, v_pages, q.dtype, num_kv_heads, head_dim, "attn_decode")
+    _cuda(block_table, "attn_decode block_table", torch.int32)
+    _cuda(seq_len, "attn_decode seq_len", torch.int32)
+    _need(block_table.dim() == 2 and block_table.shape[0] >= S and seq_len.numel() == S, "attn_decode: metadata sizes")
+    _cuda(scratch, "attn_decode scratch", torch.float32)
+    need = attn_decode_scratch_floats(S, num_heads, head_dim, n_splits)
+    _need(scratch.numel() >= need, f"attn_decode: scratch holds {scratch.numel()} floats, {need} needed")
+    if out is None:
+        out = torch.empty((S, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _cuda(out, "attn_decode out", q.dtype)
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    n_o = S * num_heads * n_splits * head_dim
+    part_o = c_void_p(scratch.data_ptr())
+    part_ml = c_void_p(scratch.data_ptr() + 4 * n_o)
+    lib = build.load("attention_decode")
+    rc = lib.rl_attn_decode(
+        _p(q), c_int(_dt(q, "attn_decode")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table),
+        c_int(block_table.shape[1]), _p(seq_len), part_o, part_ml, _p(out), c_int(out.stride(0)), c_int(S),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
+        c_int(n_splits), _stream(),
+    )
+    _check(lib, rc, "attn_decode")
+    return out
+
+
+def flash_prefill(
+    q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int,
+    num_kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """bfloat16 causal attention of a ragged batch over the paged cache (tensor cores)."""
+    _cuda(q, "flash_prefill q", torch.bfloat16, contiguous=False)
+    qs = _rows(q, "flash_prefill q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * head_dim, "flash_prefill: q rows too short")
+    _need(q.data_ptr() % 16 == 0, "flash_prefill: q is not 16-byte aligned")
+    _check_pages(k_pages, v_pages, torch.bfloat16, num_kv_heads, head_dim, "flash_prefill")
+    _cuda(block_table, "flash_prefill block_table", torch.int32)
+    _cuda(seq_start, "flash_prefill seq_start", torch.int32)
+    _cuda(seq_pos0, "flash_prefill seq_pos0", torch.int32)
+    S = seq_pos0.numel()
+    _need(seq_start.numel() == S + 1 and block_table.dim() == 2 and block_table.shape[0] >= S, "flash_prefill: metadata sizes")
+    if out is None:
+        out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    _cuda(out, "flash_prefill out", torch.bfloat16)
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    lib = build.load("attention_prefill")
+    rc = lib.rl_flash_prefill(
+        _p(q), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(seq_start),
+        _p(seq_pos0), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _stream(),
+    )
+    _check(lib, rc, "flash_prefill")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+GEMV_MAX_ROWS = 64
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T in true 32-bit."""
+    _cuda(x, "gemm_f32 x", torch.float32, contiguous=False)
+    _cuda(w, "gemm_f32 w", torch.float32, contiguous=False)
+    ldx, ldw = _rows(x, "gemm_f32 x"), _rows(w, "gemm_f32 w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, f"gemm_f32: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _cuda(out, "gemm_f32 out", torch.float32, contiguous=False)
+    _need(tuple(out.shape) == (M, N), "gemm_f32: out has the wrong shape")
+    lib = build.load("gemm_f32")
+    rc = lib.rl_gemm_f32(_p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_rows(out, "gemm_f32 out")), c_int(M), c_int(N), c_int(K), _stream())
+    _check(lib, rc, "gemm_f32")
+    return out
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 rows, bfloat16 in, 32-bit accumulate."""
+    _cuda(x, "gemv_bf16 x", torch.bfloat16, contiguous=False)
+    _cuda(w, "gemv_bf16 w", torch.bfloat16, contiguous=False)
+    ldx, ldw = _rows(x, "gemv_bf16 x"), _rows(w, "gemv_bf16 w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, f"gemv_bf16: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
+    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemv_bf16: operands must be 16-byte aligned")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _cuda(out, "gemv_bf16 out", out_dtype, contiguous=False)
+    _need(tuple(out.shape) == (M, N), "gemv_bf16: out has the wrong shape")
+    lib = build.load("gemv_bf16")
+    rc = lib.rl_gemv_bf16(
+        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_bf16 out")), c_int(_rows(out, "gemv_bf16 out")),
+        c_int(M), c_int(N), c_int(K), _stream(),
+    )
+    _check(lib, rc, "gemv_bf16")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of the largest logit of each row, the last one among equals."""
+    _cuda(logits, "argmax logits", torch.float32, contiguous=False)
+    stride = _rows(logits, "argmax logits")
+    R, n = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _cuda(out, "argmax out", torch.int32)
+    lib = build.load("sampling")
+    rc = lib.rl_argmax(_p(logits), c_ll(stride), c_int(R), c_int(n), _p(out), _stream())
+    _check(lib, rc, "argmax")
+    return out
+
+
+def sample(
+    logits: torch.Tensor, temperature: float, top_p: float, rng_states: torch.Tensor, rng_index: torch.Tensor,
+    scratch: torch.Tensor, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One draw per row from softmax(logits / temperature), cut to the top-p nucleus when 0 < top_p < 1.
+
+    rng_states: int64 tensor of xorshift64* states; row r uses and advances rng_states[rng_index[r]].
+    scratch: float32, at least rows * vocabulary elements."""
+    _cuda(logits, "sample logits", torch.float32, contiguous=False)
+    stride = _rows(logits, "sample logits")
+    R, n = logits.shape
+    _cuda(rng_states, "sample rng_states", torch.int64)
+    _cuda(rng_index, "sample rng_index", torch.int32)
+    _need(rng_index.numel() == R, "sample: one random-state index per row")
+    _cuda(scratch, "sample scratch", torch.float32)
+    _need(scratch.numel() >= R * n, f"sample: scratch holds {scratch.numel()} floats, {R * n} needed")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _cuda(out, "sample out", torch.int32)
+    lib = build.load("sampling")
+    rc = lib.rl_sample(
+        _p(logits), c_ll(stride), c_int(R), c_int(n), c_float(temperature), c_float(top_p), _p(rng_states),
+        _p(rng_index), _p(scratch), _p(out), _stream(),
+    )
+    _check(lib, rc, "sample")
+    return out

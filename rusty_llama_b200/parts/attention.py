@@ -1,0 +1,110 @@
+"""Causal grouped-query attention over the paged cache."""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping
+
+import torch
+
+from ..errors import ConfigError
+from ..kernels import ops
+from ..kernels.linear import linear
+from ..spec import PartSpec
+from .base import MIXERS, POSITIONS, KVNeed, Mixer, ParamInfo
+
+# blocks the decode kernel should have in flight on the whole GPU before more
+# splits stop paying: a few per SM of a 148-SM part
+_DECODE_TARGET_BLOCKS = 592
+_DECODE_HEADS_PER_BLOCK = 4
+
+
+def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int) -> int:
+    """How many pieces to cut the key range into, from shapes only."""
+    group = num_heads // num_kv_heads
+    per_split = n_seqs * num_kv_heads * ((group + _DECODE_HEADS_PER_BLOCK - 1) // _DECODE_HEADS_PER_BLOCK)
+    tiles = max(1, (kv_len + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE)
+    want = (_DECODE_TARGET_BLOCKS + per_split - 1) // per_split
+    return max(1, min(want, tiles, 64))
+
+
+@MIXERS.register("attention")
+class Attention(Mixer):
+    """q = Wq xn, k = Wk xn, v = Wv xn; positions encoded into q and k; k, v stored in the
+    cache; each query attends to its sequence's keys up to its own position (all of
+    them, or the last `window`); the heads' results go through Wo
+    (src/model.rs:1253-1301, src/backend/cpu.rs:363-433).  Query head h reads kv head
+    h // (H / K); the score scale is 1/sqrt(head_dim).
+
+    params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = all keys),
+            position (a PartSpec of the position family).
+    tensors: <prefix>q_proj.weight [H hd, d], k_proj.weight [K hd, d], v_proj.weight [K hd, d],
+             o_proj.weight [d, H hd].  q, k, v are kept as one matrix so that one product
+             serves the three (src/backend/cuda.rs:423-442)."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.d = int(self._param("hidden_size"))
+        self.H = int(self._param("num_heads"))
+        self.K = int(self._param("num_kv_heads"))
+        self.hd = int(self._param("head_dim"))
+        self.window = int(self._param("window"))
+        if self.H % self.K:
+            raise ConfigError(f"attention: {self.H} heads are not a multiple of {self.K} kv heads")
+        if self.hd % 8 or self.hd > 256:
+            raise ConfigError(f"attention: head_dim {self.hd} must be a multiple of 8 and at most 256 for the kernels built here")
+        pos_spec = self._param("position")
+        if not isinstance(pos_spec, PartSpec):
+            raise ConfigError("attention: 'position' must be a PartSpec")
+        self.position = POSITIONS.build(pos_spec, runtime)
+        self.scale = 1.0 / math.sqrt(self.hd)
+        self.qd, self.kvd = self.H * self.hd, self.K * self.hd
+        self.w_qkv = None
+        self.w_o = None
+
+    def cache_need(self):
+        return KVNeed(self.K, self.hd, self.window)
+
+    def param_infos(self) -> Dict[str, ParamInfo]:
+        p = self.prefix
+        return {
+            p + "q_proj.weight": ParamInfo((self.qd, self.d)),
+            p + "k_proj.weight": ParamInfo((self.kvd, self.d)),
+            p + "v_proj.weight": ParamInfo((self.kvd, self.d)),
+            p + "o_proj.weight": ParamInfo((self.d, self.qd)),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.w_qkv = torch.cat(
+            [tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"], tensors[p + "v_proj.weight"]], dim=0
+        ).contiguous()
+        self.w_o = tensors[p + "o_proj.weight"].contiguous()
+
+    def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
+        if shared_cache:
+            # the keys and values are another run's: project the queries only
+            qkv = linear(xn, self.w_qkv[: self.qd])
+        else:
+            qkv = linear(xn, self.w_qkv)
+        self.position.write_qk(qkv, step, cache, self.H, self.K, self.hd, write_kv=not shared_cache)
+        if self.rt.dtype == torch.float32:
+            a = ops.attn_generic(
+                qkv, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos,
+                self.H, self.K, self.hd, window=self.window, scale=self.scale,
+            )
+        elif step.decode_only:
+            n_splits = decode_splits(step.n_seqs, self.H, self.K, step.plan_kv_len)
+            scratch = self.rt.workspace.get(
+                "attn_decode", ops.attn_decode_scratch_floats(step.n_seqs, self.H, self.hd, n_splits), torch.float32
+            )
+            a = ops.attn_decode(
+                qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_len, self.H, self.K, self.hd,
+                n_splits, scratch, window=self.window, scale=self.scale,
+            )
+        else:
+            a = ops.flash_prefill(
+                qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
+                step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,
+            )
+        return linear(a, self.w_o)

@@ -1,0 +1,156 @@
+"""The generation loop's decisions, with a scripted engine and sampler (no GPU)."""
+
+import pytest
+import torch
+
+from rusty_llama_b200.cache import Cache
+from rusty_llama_b200.engine import GenerationStats, generate, plan_batches
+from rusty_llama_b200.engine.generate import MAX_NEW_TOKENS, POSITION_LIMIT, STOP_TOKEN
+from rusty_llama_b200.errors import CacheError, StepError
+from rusty_llama_b200.parts import KVNeed
+from rusty_llama_b200.sampling import SamplingParams, sequence_seed
+
+
+class FakeSpec:
+    stop_token_ids = (0,)
+
+
+class FakeModel:
+    spec = FakeSpec()
+
+
+class FakeEngine:
+    """Keeps a real Cache (so slots and pages are really taken and given back) and answers a step with
+    'logits' that encode (slot, position of the row): the fake sampler turns them into scripted tokens."""
+
+    def __init__(self, max_tokens=64 * 8, max_seqs=4, max_positions=40):
+        self.cache = Cache([(0, KVNeed(1, 8, 0))], max_tokens, max_seqs, torch.float32, "cpu")
+        self.model = FakeModel()
+        self.max_positions = max_positions
+        self.steps = []  # per step: list of (slot, n tokens)
+        self.fed = {}  # slot -> tokens fed so far
+        self.peak_open = 0
+
+    def open_sequence(self):
+        s = self.cache.open_sequence()
+        self.fed[s] = []
+        self.peak_open = max(self.peak_open, self.cache.n_open)
+        return s
+
+    def close_sequence(self, slot):
+        self.cache.close_sequence(slot)
+
+    def step(self, entries):
+        slots = [e.slot for e in entries]
+        lens = [len(e.tokens) for e in entries]
+        self.cache.reserve(slots, lens)
+        self.cache.commit(slots, lens)
+        self.steps.append(list(zip(slots, lens)))
+        rows = []
+        for e in entries:
+            self.fed[e.slot].extend(e.tokens)
+            assert list(e.want) == [len(e.tokens) - 1]
+            rows.append([float(e.slot), float(self.cache.length(e.slot))])
+        return torch.tensor(rows)
+
+
+class ScriptedSampler:
+    """Token for the row of a sequence of length n that began with prompt token p: script[p][n]."""
+
+    def __init__(self, engine, script):
+        self.engine, self.script, self.seeded = engine, script, {}
+
+    def seed_slots(self, slots, seeds):
+        for s, sd in zip(slots, seeds):
+            self.seeded[s] = sd
+
+    def sample(self, logits, slots, params):
+        out = []
+        for row, slot in zip(logits.tolist(), slots):
+            assert int(row[0]) == slot
+            first = self.engine.fed[slot][0]
+            out.append(self.script(first, int(row[1])))
+        return torch.tensor(out, dtype=torch.int32)
+
+
+def test_plan_batches_respects_pages_and_batch_size():
+    assert plan_batches([10, 10, 10], [20, 20, 20], 1000, page_budget=2, max_batch=8) == [[0, 1], [2]]
+    assert plan_batches([10] * 5, [5] * 5, 1000, page_budget=100, max_batch=2) == [[0, 1], [2, 3], [4]]
+    assert plan_batches([100], [1000], 128, page_budget=2, max_batch=8) == [[0]]  # clamped by the position limit
+    with pytest.raises(StepError, match="pages"):
+        plan_batches([200], [10], 1000, page_budget=2, max_batch=8)
+
+
+def test_unequal_prompts_stop_tokens_and_early_leavers():
+    eng = FakeEngine()
+    # sequences are known by their first prompt token; token 0 stops
+    script = lambda first, n: {11: 0 if n == 6 else 50 + n, 12: 60 + n, 13: 0 if n == 3 else 70 + n}[first]
+    smp = ScriptedSampler(eng, script)
+    prompts = [[11, 1, 1, 1], [12, 2], [13, 3, 3]]
+    stats = GenerationStats()
+    res = generate(eng, smp, prompts, 5, SamplingParams(0.0, 0.9, 7), stats=stats)
+    assert [r.tokens for r in res] == [[54, 55], [62, 63, 64, 65, 66], []]
+    assert [r.finish_reason for r in res] == [STOP_TOKEN, MAX_NEW_TOKENS, STOP_TOKEN]
+    # first step: the three prompts together, with their own lengths; then shrinking decode batches
+    assert sorted(n for _, n in eng.steps[0]) == [2, 3, 4]
+    assert [len(s) for s in eng.steps[1:]] == [2, 2, 1, 1]
+    assert all(n == 1 for st in eng.steps[1:] for _, n in st)
+    # the last emitted token is not fed back; a stop token is never fed
+    for slot, fed in eng.fed.items():
+        assert 0 not in fed
+    assert eng.cache.n_open == 0 and eng.cache.pages_free() == eng.cache.n_pages
+    assert stats.prompt_tokens == 9 and stats.generated_tokens == 7 and stats.decode_steps == 4 and stats.batches == 1
+    assert smp.seeded and set(smp.seeded.values()) == {sequence_seed(7, i) for i in range(3)}
+
+
+def test_include_stop_and_callback_order():
+    eng = FakeEngine()
+    smp = ScriptedSampler(eng, lambda first, n: 0 if n == 4 else 9)
+    seen = []
+    res = generate(eng, smp, [[5, 5]], 10, SamplingParams(0.0), include_stop=True, on_token=lambda r, t: seen.append((r, t)))
+    assert res[0].tokens == [9, 9, 0] and res[0].finish_reason == STOP_TOKEN
+    assert seen == [(0, 9), (0, 9)]
+
+
+def test_more_requests_than_slots_run_batch_after_batch_in_the_same_slots():
+    eng = FakeEngine(max_seqs=2)
+    smp = ScriptedSampler(eng, lambda first, n: first)
+    prompts = [[20 + i] * (1 + i) for i in range(5)]
+    res = generate(eng, smp, prompts, 3, SamplingParams(0.0), stop_token_ids=[])
+    assert [r.tokens for r in res] == [[20 + i] * 3 for i in range(5)]
+    assert eng.peak_open == 2 and set(eng.fed) == {0, 1}  # only two slots ever existed
+    assert eng.cache.n_open == 0
+    eng.cache.check_consistent()
+
+
+def test_position_limit_and_budget_per_prompt():
+    eng = FakeEngine(max_positions=6)
+    smp = ScriptedSampler(eng, lambda first, n: 9)
+    res = generate(eng, smp, [[1, 1, 1, 1], [2]], [10, 2], SamplingParams(0.0), stop_token_ids=[])
+    # 4 prompt positions + 2 fed tokens fill the 6 positions; the third token is produced but cannot be fed
+    assert res[0].tokens == [9, 9, 9] and res[0].finish_reason == POSITION_LIMIT
+    assert res[1].tokens == [9, 9] and res[1].finish_reason == MAX_NEW_TOKENS
+    with pytest.raises(StepError, match="limit"):
+        generate(eng, smp, [[1] * 7], 1, SamplingParams(0.0))
+    with pytest.raises(StepError, match="empty"):
+        generate(eng, smp, [[]], 1, SamplingParams(0.0))
+    assert generate(eng, smp, [[1]], 0, SamplingParams(0.0))[0].tokens == []
+
+
+def test_slots_are_given_back_when_a_step_fails():
+    eng = FakeEngine()
+    smp = ScriptedSampler(eng, lambda first, n: 9)
+
+    def boom(entries):
+        raise CacheError("scripted failure")
+
+    eng.step = boom
+    with pytest.raises(CacheError, match="scripted"):
+        generate(eng, smp, [[1, 2], [3]], 4, SamplingParams(0.0))
+    assert eng.cache.n_open == 0
+
+
+def test_sequence_seeds():
+    assert sequence_seed(12345, 0) == 12345 and sequence_seed(0, 0) == 1
+    seeds = {sequence_seed(12345, i) for i in range(100)}
+    assert len(seeds) == 100 and 0 not in seeds
