@@ -35,6 +35,7 @@ NVCC_FLAGS = [
 ]
 
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
 
 
@@ -53,8 +54,19 @@ def source_names() -> List[str]:
     return sorted(f[:-3] for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
 
 
+_build_dir_cached: Optional[str] = None
+
+
 def _build_dir() -> str:
     """`csrc/_build` when it can be written, else a per-user folder under the temp dir."""
+    global _build_dir_cached
+    with _dir_lock:
+        if _build_dir_cached is None:
+            _build_dir_cached = _find_build_dir()
+        return _build_dir_cached
+
+
+def _find_build_dir() -> str:
     override = os.environ.get("RUSTY_LLAMA_BUILD_DIR")
     cands = [override] if override else []
     cands.append(os.path.join(CSRC_DIR, "_build"))
@@ -62,7 +74,7 @@ def _build_dir() -> str:
     for d in cands:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
+            probe = os.path.join(d, f".w{os.getpid()}_{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)

@@ -1,0 +1,424 @@
+"""Each kernel alone against a plain float32/float64 reference of the same formula, at sizes the
+engine's own models do not use (head sizes 24, 40, 128, 256; widths that are no power of two;
+groups of 1, 3, 4, 5; pages in scrambled order)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain_llama import PlainRng, plain_argmax, plain_attention, plain_rmsnorm, plain_rope, plain_sample, plain_silu
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+PAGE = 64
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from rusty_llama_b200.kernels import ops as o
+
+    return o
+
+
+def bf16_round(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def close_f32(got, ref, rel=2e-5):
+    got, ref = got.detach().cpu().double(), ref.detach().cpu().double()
+    tol = rel * float(ref.abs().max()) + 1e-7
+    err = float((got - ref).abs().max())
+    assert err <= tol, f"max error {err:.3e} exceeds {tol:.3e}"
+
+
+def close_bf16(got, ref):
+    """bfloat16 keeps 8 bits: an element may be off by 2^-8 of its own size from the final rounding,
+    plus what rounding the operands of an inner product adds, which scales with the result's range."""
+    got, ref = got.detach().cpu().double(), ref.detach().cpu().double()
+    scale = float(ref.abs().max()) + 1e-6
+    err = (got - ref).abs()
+    assert float(err.max()) <= 1.2e-2 * scale, f"max error {float(err.max()):.3e} vs range {scale:.3e}"
+    assert float(err.mean()) <= 2e-3 * scale, f"mean error {float(err.mean()):.3e} vs range {scale:.3e}"
+
+
+class PagedKV:
+    """Dense keys/values of several sequences laid out in scrambled pages."""
+
+    def __init__(self, lens, K, hd, dtype, seed=0, extra_pages=3):
+        g = torch.Generator().manual_seed(seed)
+        self.lens, self.K, self.hd = lens, K, hd
+        self.k = [torch.randn(n, K, hd, generator=g) for n in lens]
+        self.v = [torch.randn(n, K, hd, generator=g) for n in lens]
+        if dtype == torch.bfloat16:
+            self.k = [bf16_round(t) for t in self.k]
+            self.v = [bf16_round(t) for t in self.v]
+        n_pages = sum((n + PAGE - 1) // PAGE for n in lens) + extra_pages
+        order = torch.randperm(n_pages, generator=g).tolist()
+        width = max((n + PAGE - 1) // PAGE for n in lens)
+        self.table = torch.zeros(len(lens), width, dtype=torch.int32)
+        # unwritten pages hold large finite junk: reading them shows up in the result
+        self.k_pages = torch.full((n_pages, K, PAGE, hd), 77.0)
+        self.v_pages = torch.full((n_pages, K, PAGE, hd), -55.0)
+        for s, n in enumerate(lens):
+            for j in range((n + PAGE - 1) // PAGE):
+                page = order.pop()
+                self.table[s, j] = page
+                lo, hi = j * PAGE, min(n, (j + 1) * PAGE)
+                self.k_pages[page, :, : hi - lo] = self.k[s][lo:hi].transpose(0, 1)
+                self.v_pages[page, :, : hi - lo] = self.v[s][lo:hi].transpose(0, 1)
+        self.k_pages = self.k_pages.to(dtype).to(DEV)
+        self.v_pages = self.v_pages.to(dtype).to(DEV)
+        self.table = self.table.to(DEV)
+
+
+def ref_attention_rows(q_rows, kv: PagedKV, s, positions, window=0, scale=None):
+    """Attention of query rows at `positions` of sequence s over its keys 0..pos (float64)."""
+    H, hd = q_rows.shape[1], q_rows.shape[2]
+    K = kv.K
+    scale = scale or 1.0 / math.sqrt(hd)
+    out = torch.zeros(len(positions), H, hd, dtype=torch.float64)
+    for i, pos in enumerate(positions):
+        lo = max(0, pos + 1 - window) if window else 0
+        for h in range(H):
+            g = h // (H // K)
+            sc = (kv.k[s][lo : pos + 1, g].double() @ q_rows[i, h].double()) * scale
+            p = torch.softmax(sc, dim=0)
+            out[i, h] = p @ kv.v[s][lo : pos + 1, g].double()
+    return out
+
+
+# --------------------------------------------------------------------------- row kernels
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(ops, dtype):
+    table = torch.randn(300, 72).to(dtype)
+    toks = torch.tensor([0, 299, 17, 17, 5], dtype=torch.int32)
+    out = ops.embed_gather(toks.to(DEV), table.to(DEV))
+    assert out.dtype == torch.float32
+    assert torch.equal(out.cpu(), table[toks.long()].float())
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d, parts", [(200, 0), (72, 1), (4104, 3)])
+def test_add_rmsnorm(ops, act, wdt, d, parts):
+    T, eps = 5, 3e-6
+    x = torch.randn(T, d) * 3
+    w = (1 + 0.1 * torch.randn(d)).to(wdt)
+    delta = None if parts == 0 else torch.randn(parts, T, d).to(act)
+    ref_x = x.clone()
+    if delta is not None:
+        for p in range(parts):
+            ref_x = ref_x + delta[p].float()
+    ref = plain_rmsnorm(ref_x.double(), w.double(), eps)
+    xd = x.to(DEV)
+    dd = None if delta is None else (delta[0] if parts == 1 else delta).contiguous().to(DEV)
+    out = ops.add_rmsnorm(xd, dd, w.to(DEV), eps, act)
+    assert out.dtype == act
+    close_f32(xd, ref_x, 1e-6)  # the stream holds the 32-bit sum
+    (close_f32 if act == torch.float32 else close_bf16)(out, ref)
+    # a subset of rows, stream untouched
+    xd2 = x.to(DEV)
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    out2 = ops.add_rmsnorm(xd2, dd, w.to(DEV), eps, act, rows=rows, write_x=False)
+    assert torch.equal(xd2.cpu(), x)
+    assert torch.equal(out2.cpu(), out[[4, 1]].cpu())
+    # the sum alone
+    if delta is not None:
+        xd3 = x.to(DEV)
+        assert ops.add_rmsnorm(xd3, dd, None, 0.0, act) is None
+        close_f32(xd3, ref_x, 1e-6)
+
+
+def test_rmsnorm_of_ones_and_eps(ops):
+    # src/backend/cpu.rs:750-771
+    x = torch.ones(2, 64, device=DEV)
+    out = ops.add_rmsnorm(x, None, torch.ones(64, device=DEV), 1e-5, torch.float32)
+    assert abs(float(out[0, 0]) - 1 / math.sqrt(1 + 1e-5)) < 1e-7
+    out = ops.add_rmsnorm(torch.zeros(1, 64, device=DEV), None, torch.ones(64, device=DEV), 1e-5, torch.float32)
+    assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(ops, dtype):
+    gu = (torch.randn(3, 200) * 4).to(dtype)
+    ref = plain_silu(gu[:, :100].double()) * gu[:, 100:].double()
+    out = ops.swiglu(gu.to(DEV))
+    (close_f32 if dtype == torch.float32 else close_bf16)(out, ref)
+    one = torch.tensor([[1.0, 2.0]], device=DEV)
+    assert abs(float(ops.swiglu(one)[0, 0]) - 0.7310586 * 2) < 1e-6  # src/backend/cpu.rs:781-787
+
+
+# --------------------------------------------------------------------------- rotary + cache write
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("H, K, hd, rot", [(6, 3, 40, 40), (4, 4, 24, 16), (5, 1, 128, 128)])
+def test_rope_kv_write(ops, dtype, interleaved, H, K, hd, rot):
+    lens = [70, 3]  # the first sequence crosses a page
+    pos0 = [60, 130]  # and both start late in their sequences
+    T = sum(lens)
+    qkv = torch.randn(T, (H + 2 * K) * hd + 8).to(dtype)  # rows longer than needed: the stride is honoured
+    tok_seq = torch.tensor(sum(([s] * n for s, n in enumerate(lens)), []), dtype=torch.int32)
+    tok_pos = torch.tensor(sum((list(range(p, p + n)) for p, n in zip(pos0, lens)), []), dtype=torch.int32)
+    inv = torch.tensor([10000.0 ** (-2 * j / rot) for j in range(rot // 2)], dtype=torch.float32)
+    n_pages = 8
+    table = torch.tensor([[5, 2, 7], [1, 0, 3]], dtype=torch.int32)
+    kp = torch.zeros(n_pages, K, PAGE, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    qd = qkv.to(DEV)
+    ops.rope_kv_write(qd, tok_pos.to(DEV), tok_seq.to(DEV), table.to(DEV), kp, vp, inv.to(DEV), H, K, hd, rot, interleaved)
+    q = qkv[:, : H * hd].float().view(T, H, hd)
+    k = qkv[:, H * hd : (H + K) * hd].float().view(T, K, hd)
+    v = qkv[:, (H + K) * hd : (H + 2 * K) * hd].float().view(T, K, hd)
+
+    def rotated(x):
+        out = x.clone().double()
+        out[..., :rot] = plain_rope(x[..., :rot].double(), tok_pos, inv, interleaved)
+        return out
+
+    cmp = close_f32 if dtype == torch.float32 else close_bf16
+    cmp(qd[:, : H * hd].view(T, H, hd), rotated(q))
+    assert torch.equal(qd[:, H * hd :].cpu(), qkv[:, H * hd :])  # k, v and the padding of the row are not touched
+    kr = rotated(k)
+    got_k = torch.zeros(T, K, hd)
+    got_v = torch.zeros(T, K, hd)
+    for t in range(T):
+        s, p = int(tok_seq[t]), int(tok_pos[t])
+        page = int(table[s, p // PAGE])
+        got_k[t] = kp[page, :, p % PAGE].float().cpu()
+        got_v[t] = vp[page, :, p % PAGE].float().cpu()
+    cmp(got_k, kr)
+    assert torch.equal(got_v, v)
+    # nothing else was written
+    written = torch.zeros(n_pages, PAGE, dtype=torch.bool)
+    for t in range(T):
+        s, p = int(tok_seq[t]), int(tok_pos[t])
+        written[int(table[s, p // PAGE]), p % PAGE] = True
+    assert (kp.float().cpu().abs().sum(dim=(1, 3))[~written] == 0).all()
+
+
+# --------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, K, hd, window", [(4, 2, 40, 0), (3, 3, 24, 0), (6, 2, 256, 0), (4, 1, 16, 37)])
+def test_attn_generic(ops, dtype, H, K, hd, window):
+    lens = [150, 64, 1]
+    kv = PagedKV(lens, K, hd, dtype, seed=1)
+    # queries: every position of sequence 1, a few of the others
+    queries = [(0, [0, 63, 64, 149]), (1, list(range(64))), (2, [0])]
+    tok_seq = torch.tensor(sum(([s] * len(p) for s, p in queries), []), dtype=torch.int32)
+    tok_pos = torch.tensor(sum((p for _, p in queries), []), dtype=torch.int32)
+    T = len(tok_seq)
+    q = torch.randn(T, H * hd + 16)
+    if dtype == torch.bfloat16:
+        q = bf16_round(q)
+    out = ops.attn_generic(q.to(dtype).to(DEV), kv.k_pages, kv.v_pages, kv.table, tok_seq.to(DEV), tok_pos.to(DEV), H, K, hd, window=window)
+    ref = torch.cat([
+        ref_attention_rows(q[tok_seq == s][:, : H * hd].view(-1, H, hd), kv, s, p, window) for s, p in queries
+    ]).view(T, H * hd)
+    (close_f32 if dtype == torch.float32 else close_bf16)(out, ref)
+
+
+def test_attn_generic_bits_do_not_depend_on_the_batch(ops):
+    """32-bit attention of a token is the same bits alone or among others."""
+    H, K, hd = 4, 2, 48
+    kv = PagedKV([200, 90], K, hd, torch.float32, seed=2)
+    q = torch.randn(5, H * hd)
+    tok_seq = torch.tensor([0, 0, 1, 0, 1], dtype=torch.int32)
+    tok_pos = torch.tensor([10, 199, 89, 64, 0], dtype=torch.int32)
+    full = ops.attn_generic(q.to(DEV), kv.k_pages, kv.v_pages, kv.table, tok_seq.to(DEV), tok_pos.to(DEV), H, K, hd)
+    for i in range(5):
+        one = ops.attn_generic(q[i : i + 1].to(DEV), kv.k_pages, kv.v_pages, kv.table, tok_seq[i : i + 1].to(DEV), tok_pos[i : i + 1].to(DEV), H, K, hd)
+        assert torch.equal(one[0], full[i])
+
+
+@pytest.mark.parametrize("H, K, hd", [(8, 2, 128), (6, 2, 24), (5, 1, 64), (3, 3, 256), (16, 2, 40)])
+@pytest.mark.parametrize("n_splits, window", [(1, 0), (3, 0), (8, 0), (2, 100)])
+def test_attn_decode(ops, H, K, hd, n_splits, window):
+    lens = [1, 64, 65, 300, 128]
+    S = len(lens)
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=3)
+    q = bf16_round(torch.randn(S, (H + 2 * K) * hd))
+    scratch = torch.full((ops.attn_decode_scratch_floats(S, H, hd, n_splits) + 7,), float("nan"), device=DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = ops.attn_decode(q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window)
+    ref = torch.cat([
+        ref_attention_rows(q[s : s + 1, : H * hd].view(1, H, hd), kv, s, [lens[s] - 1], window) for s in range(S)
+    ]).view(S, H * hd)
+    close_bf16(out, ref)
+    assert torch.isnan(scratch[-7:]).all()  # the kernel stays inside the scratch it asked for
+
+
+def test_attn_decode_finds_a_far_key(ops):
+    """One key far back among hundreds carries almost all the weight: a kernel that skips a page,
+    a split or a tile edge returns something else entirely."""
+    H, K, hd = 4, 1, 64
+    for far in (0, 63, 64, 127, 450):
+        kv = PagedKV([513], K, hd, torch.bfloat16, seed=4)
+        q = bf16_round(torch.randn(1, H * hd))
+        # make key `far` point along each head's query
+        page, slot = int(kv.table[0, far // PAGE]), far % PAGE
+        boost = bf16_round(q.view(H, hd).mean(dim=0) * 4)
+        kv.k[0][far, 0] = boost
+        kv.k_pages[page, 0, slot] = boost.to(torch.bfloat16).to(DEV)
+        qq = bf16_round(boost.repeat(H) * 1.0)[None]
+        scratch = torch.empty(ops.attn_decode_scratch_floats(1, H, hd, 4), device=DEV)
+        out = ops.attn_decode(qq.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([513], dtype=torch.int32, device=DEV), H, K, hd, 4, scratch)
+        ref = ref_attention_rows(qq.view(1, H, hd), kv, 0, [512]).view(1, H * hd)
+        close_bf16(out, ref)
+        # and the weight really is on that key
+        assert float((ref.view(H, hd)[0] - kv.v[0][far, 0].double()).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("H, K, hd", [(4, 2, 128), (6, 6, 24), (5, 1, 64), (2, 1, 256), (8, 2, 40)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_flash_prefill(ops, H, K, hd, window):
+    # sequence 0: a whole prompt; 1: a chunk appended to 100 cached positions; 2: a single row deep in a sequence;
+    # 3: exactly one tile
+    pos0 = [0, 100, 199, 0]
+    q_lens = [150, 77, 1, 64]
+    lens = [p + n for p, n in zip(pos0, q_lens)]
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=5)
+    T = sum(q_lens)
+    q = bf16_round(torch.randn(T, H * hd + 24))
+    seq_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    out = ops.flash_prefill(
+        q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, seq_start,
+        torch.tensor(pos0, dtype=torch.int32, device=DEV), max(q_lens), H, K, hd, window=window,
+    )
+    refs, at = [], 0
+    for s, (p, n) in enumerate(zip(pos0, q_lens)):
+        refs.append(ref_attention_rows(q[at : at + n, : H * hd].view(n, H, hd), kv, s, list(range(p, p + n)), window))
+        at += n
+    close_bf16(out, torch.cat(refs).view(T, H * hd))
+
+
+def test_flash_prefill_finds_a_far_key_and_respects_the_causal_edge(ops):
+    H, K, hd = 2, 1, 64
+    n = 400
+    kv = PagedKV([n], K, hd, torch.bfloat16, seed=6)
+    direction = bf16_round(torch.randn(hd))
+    far = 130
+    kv.k[0][far, 0] = direction * 3
+    kv.k_pages[int(kv.table[0, far // PAGE]), 0, far % PAGE] = (direction * 3).to(torch.bfloat16).to(DEV)
+    q = bf16_round(direction.repeat(n, H) * 1.0)
+    out = ops.flash_prefill(
+        q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([0, n], dtype=torch.int32, device=DEV),
+        torch.tensor([0], dtype=torch.int32, device=DEV), n, H, K, hd,
+    )
+    ref = ref_attention_rows(q.view(n, H, hd), kv, 0, list(range(n))).view(n, H * hd)
+    close_bf16(out, ref)
+    # rows before the far key cannot see it, rows from it on are dominated by its value
+    v_far = kv.v[0][far, 0].double()
+    assert float((ref[far + 5].view(H, hd)[0] - v_far).abs().max()) < 0.05
+    assert float((ref[far - 1].view(H, hd)[0] - v_far).abs().max()) > 0.5
+    got = out.float().cpu().view(n, H, hd)
+    assert float((got[far, 0] - v_far.float()).abs().max()) < 0.08 and float((got[far - 1, 0] - v_far.float()).abs().max()) > 0.5
+
+
+# --------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("M, N, K", [(1, 130, 50), (70, 130, 50), (5, 64, 17), (129, 65, 257)])
+def test_gemm_f32(ops, M, N, K):
+    x, w = torch.randn(M, K), torch.randn(N, K)
+    out = ops.gemm_f32(x.to(DEV), w.to(DEV))
+    close_f32(out, x.double() @ w.double().T, 1e-6)
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch(ops):
+    x, w = torch.randn(100, 300).to(DEV), torch.randn(77, 300).to(DEV)
+    full = ops.gemm_f32(x, w)
+    for r in (0, 63, 64, 99):
+        assert torch.equal(ops.gemm_f32(x[r : r + 1], w)[0], full[r])
+    assert torch.equal(ops.gemm_f32(x[10:50], w), full[10:50])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N, K", [(100, 72), (48, 4096), (257, 1000)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemv_bf16(ops, M, N, K, out_dtype):
+    x = bf16_round(torch.randn(M, K))
+    w = bf16_round(torch.randn(N, K) * 0.05)
+    out = ops.gemv_bf16(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
+    ref = x.double() @ w.double().T
+    if out_dtype == torch.float32:
+        close_f32(out, ref, 5e-6)
+    else:
+        close_bf16(out, ref)
+
+
+def test_gemv_bf16_refuses_what_it_cannot_do(ops):
+    from rusty_llama_b200.errors import KernelError
+
+    x = torch.zeros(2, 20, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        ops.gemv_bf16(x, w)
+    with pytest.raises(KernelError, match="at most 64"):
+        ops.gemv_bf16(torch.zeros(65, 16, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 16, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(KernelError, match="CUDA only"):
+        ops.gemv_bf16(x.cpu(), w.cpu())
+
+
+# --------------------------------------------------------------------------- sampling
+def test_argmax_last_of_ties(ops):
+    logits = torch.randn(6, 1000)
+    logits[0, [5, 700, 999]] = 9.0
+    logits[1, :] = 1.0
+    logits[2, 0] = 50.0
+    out = ops.argmax(logits.to(DEV)).cpu().tolist()
+    assert out == [plain_argmax(row.tolist()) for row in logits]
+    assert out[0] == 999 and out[1] == 999 and out[2] == 0
+
+
+@pytest.mark.parametrize("n, temperature, top_p", [(300, 1.0, 0.9), (300, 0.7, 0.0), (5000, 1.3, 0.5), (5000, 0.8, 0.95), (8, 1.0, 0.9)])
+def test_sample_follows_the_plain_sampler(ops, n, temperature, top_p):
+    rows = 6
+    g = torch.Generator().manual_seed(n)
+    logits = torch.randn(rows, n, generator=g) * 2.0
+    logits[1] = torch.round(logits[1] * 2) / 2  # many equal probabilities
+    logits[2, 3] = 30.0  # one dominant token
+    if n == 8:
+        logits[0] = torch.tensor([2.0, 1.8, 1.6, 1.4, 1.2, 1.0, 0.8, 0.6])
+    seeds = [12345, 1, 2, 3, 99, 2**63 + 5]
+    states = torch.from_numpy(np.array(seeds, dtype=np.uint64).view(np.int64).copy()).to(DEV)
+    index = torch.arange(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * n, device=DEV)
+    rngs = [PlainRng(s) for s in seeds]
+    ld = logits.to(DEV)
+    draws, total, same = 12, 0, 0
+    for d in range(draws):
+        got = ops.sample(ld, temperature, top_p, states, index, scratch).cpu().tolist()
+        want = [plain_sample(logits[r].tolist(), temperature, top_p, rngs[r]) for r in range(rows)]
+        total += rows
+        same += sum(int(a == b) for a, b in zip(got, want))
+        if n == 8 and top_p == 0.9 and d < 8:
+            assert got[0] == [2, 4, 0, 4, 0, 0, 6, 2][d]  # the reference's golden stream (src/sampler.rs:1009-1014)
+    # tokens of equal probability are ordered by the reference's unstable sort, here by index; rows without
+    # ties must agree draw for draw
+    assert same >= total - draws, f"{total - same} of {total} draws differ"
+    # the generator states advanced exactly as the plain ones
+    want_states = np.array([r.state for r in rngs], dtype=np.uint64)
+    assert np.array_equal(states.cpu().numpy().view(np.uint64), want_states)
+
+
+def test_sample_rows_without_ties_agree_exactly(ops):
+    n, rows = 2000, 8
+    logits = torch.randn(rows, n, generator=torch.Generator().manual_seed(5)) * 3
+    seeds = list(range(1, rows + 1))
+    states = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    index = torch.arange(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * n, device=DEV)
+    rngs = [PlainRng(s) for s in seeds]
+    for _ in range(10):
+        got = ops.sample(logits.to(DEV), 1.0, 0.9, states, index, scratch).cpu().tolist()
+        want = [plain_sample(logits[r].tolist(), 1.0, 0.9, rngs[r]) for r in range(rows)]
+        assert got == want
+
+
+def test_sample_empty_nucleus_collapses_to_argmax(ops):
+    # src/sampler.rs:1035-1043: uniform distribution and a tiny top-p
+    logits = torch.ones(1, 4, device=DEV)
+    states = torch.tensor([7], dtype=torch.int64, device=DEV)
+    out = ops.sample(logits, 1.0, 0.1, states, torch.zeros(1, dtype=torch.int32, device=DEV), torch.empty(4, device=DEV))
+    assert out.item() == 3 and states.item() != 7  # the coin is still drawn

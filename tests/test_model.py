@@ -1,0 +1,219 @@
+"""The engine in-process against the plain implementation: whole sequences, cuts, batches, long decoding,
+slot reuse, generation through the entry point."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import TINY, rounded_weights
+from helpers import check_logits, plain_all_logits
+from plain_llama import plain_generate, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def llms(tiny_dirs):
+    import rusty_llama_b200 as rl
+
+    made = {}
+
+    def get(name, dtype, **kw):
+        key = (name, dtype, tuple(sorted(kw.items())))
+        if key not in made:
+            made[key] = rl.load(tiny_dirs[name], dtype=dtype, max_tokens=kw.pop("max_tokens", 64 * 16), **kw)
+        return made[key]
+
+    return get
+
+
+def step_all(llm, slot, tokens):
+    from rusty_llama_b200 import StepEntry
+
+    return llm.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu().numpy()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_sequence_logits(name, dtype, llms, tiny_weights):
+    cfg = TINY[name][0]
+    llm = llms(name, dtype)
+    rng = np.random.default_rng(3)
+    for n in (1, 7, 64, 65, cfg["max_position_embeddings"]):
+        toks = rng.integers(0, cfg["vocab_size"], n).tolist()
+        ref = plain_all_logits(cfg, tiny_weights[name], dtype, {"r": toks})["r"]
+        slot = llm.open_sequence()
+        got = step_all(llm, slot, toks)
+        llm.close_sequence(slot)
+        check_logits(got, ref, dtype, f"tiny {name}, {n} tokens")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_float32_bits_do_not_depend_on_cut_or_batch(name, llms):
+    """In 32-bit every kernel adds in an order that depends on the token alone, so the logits at a
+    position are the same bits whole, one by one, chunked, or next to other sequences."""
+    from rusty_llama_b200 import StepEntry
+
+    cfg = TINY[name][0]
+    llm = llms(name, "float32")
+    rng = np.random.default_rng(5)
+    a = rng.integers(0, cfg["vocab_size"], 90).tolist()
+    b = rng.integers(0, cfg["vocab_size"], 37).tolist()
+    s = llm.open_sequence()
+    whole = torch.from_numpy(step_all(llm, s, a))
+    llm.close_sequence(s)
+    s = llm.open_sequence()
+    parts = [torch.from_numpy(step_all(llm, s, a[:50]))]
+    parts.append(torch.from_numpy(step_all(llm, s, a[50:58])))
+    for t in a[58:]:
+        parts.append(torch.from_numpy(step_all(llm, s, [t])))
+    llm.close_sequence(s)
+    assert torch.equal(torch.cat(parts), whole)
+    s1, s2 = llm.open_sequence(), llm.open_sequence()
+    out = llm.step([StepEntry(s2, b, [len(b) - 1]), StepEntry(s1, a, list(range(90)))]).cpu()
+    llm.close_sequence(s1)
+    llm.close_sequence(s2)
+    assert torch.equal(out[1:], whole)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_with_and_without_graphs(dtype, llms, tiny_weights):
+    """A prompt of 3 tokens, then one token per step up to the position limit: the decode kernels and
+    the captured graph see every length, page boundaries included."""
+    from rusty_llama_b200 import StepEntry
+
+    name = "B"
+    cfg = TINY[name][0]
+    n = cfg["max_position_embeddings"]
+    toks = np.random.default_rng(9).integers(0, cfg["vocab_size"], n).tolist()
+    ref = plain_all_logits(cfg, tiny_weights[name], dtype, {"r": toks})["r"]
+    for graphs in (True, False):
+        llm = llms(name, dtype, use_graphs=graphs)
+        s = llm.open_sequence()
+        rows = [step_all(llm, s, toks[:3])]
+        for t in toks[3:]:
+            rows.append(llm.step([StepEntry(s, [t], [0])]).cpu().numpy())
+        llm.close_sequence(s)
+        check_logits(np.concatenate(rows), ref, dtype, f"decoding to {n}, graphs={graphs}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batched_decoding_with_leavers_and_slot_reuse(dtype, llms, tiny_weights):
+    """Batches of unequal prompts decode together; the short ones end; their slots and pages go to the
+    next batch, whose logits must not see what the slots held before."""
+    from rusty_llama_b200 import StepEntry
+
+    name = "A"
+    cfg = TINY[name][0]
+    llm = llms(name, dtype, max_tokens=64 * 4, max_seqs=3)
+    rng = np.random.default_rng(21)
+    for round_ in range(3):
+        lens = [(5, 12), (9, 30), (13, 66)] if round_ % 2 == 0 else [(70, 75), (1, 20), (64, 65)]
+        seqs = {i: rng.integers(0, cfg["vocab_size"], total).tolist() for i, (_, total) in enumerate(lens)}
+        ref = plain_all_logits(cfg, tiny_weights[name], dtype, seqs)
+        slots = {i: llm.open_sequence() for i in seqs}
+        assert set(slots.values()) == {0, 1, 2}
+        got = {i: [] for i in seqs}
+        out = llm.step([StepEntry(slots[i], seqs[i][: lens[i][0]], [lens[i][0] - 1]) for i in seqs]).cpu().numpy()
+        pos = {}
+        for j, i in enumerate(seqs):
+            got[i].append(out[j : j + 1])
+            pos[i] = lens[i][0]
+        while True:
+            live = [i for i in seqs if pos[i] < lens[i][1]]
+            if not live:
+                break
+            out = llm.step([StepEntry(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu().numpy()
+            for j, i in enumerate(live):
+                got[i].append(out[j : j + 1])
+                pos[i] += 1
+                if pos[i] == lens[i][1]:
+                    llm.close_sequence(slots[i])
+        for i in seqs:
+            check_logits(np.concatenate(got[i]), ref[i][lens[i][0] - 1 :], dtype, f"round {round_}, sequence {i}")
+        llm.engine.cache.check_consistent()
+        assert llm.engine.cache.n_open == 0
+
+
+def test_step_errors_come_before_any_launch(llms):
+    from rusty_llama_b200 import CacheError, StepEntry, StepError
+
+    llm = llms("A", "float32", max_tokens=64 * 2, max_seqs=2)
+    s = llm.open_sequence()
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        llm.step([StepEntry(s, [1, 256], [0])])
+    with pytest.raises(StepError, match="no token"):
+        llm.step([StepEntry(s, [], [])])
+    with pytest.raises(StepError, match="limit"):
+        llm.step([StepEntry(s, [1] * 129, [])])
+    with pytest.raises(StepError, match="index 3"):
+        llm.step([StepEntry(s, [1, 2, 3], [3])])
+    with pytest.raises(StepError, match="twice"):
+        llm.step([StepEntry(s, [1], []), StepEntry(s, [2], [])])
+    with pytest.raises(StepError, match="at least one"):
+        llm.step([])
+    with pytest.raises(CacheError, match="not open"):
+        llm.step([StepEntry(1, [1], [])])
+    assert llm.engine.cache.length(s) == 0
+    s2 = llm.open_sequence()
+    llm.step([StepEntry(s, [1] * 100, [])])
+    with pytest.raises(CacheError, match="out of cache pages"):
+        llm.step([StepEntry(s2, [1] * 10, [])])
+    assert llm.engine.cache.length(s2) == 0 and llm.engine.cache.length(s) == 100
+    llm.close_sequence(s)
+    llm.close_sequence(s2)
+
+
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32")])
+def test_greedy_generation_through_the_entry_point(name, dtype, llms, tiny_weights):
+    """Tiny A's workload: prompts of 5, 9 and 13 tokens, 8 greedy tokens each, one batch."""
+    cfg = TINY[name][0]
+    llm = llms(name, dtype)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (5, 9, 13)]
+    outs = llm.generate(prompts, max_new_tokens=8, temperature=0.0, stop_token_ids=[])
+    w = rounded_weights(tiny_weights[name], dtype)
+    for p, got in zip(prompts, outs):
+        want = plain_generate(cfg, w, p, 8, temperature=0.0)
+        if dtype == "float32":
+            assert got == want
+        else:
+            # bfloat16 may pick the other of two nearly equal logits; up to there the streams agree, and
+            # the token it picked is within rounding of the best one
+            k = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), None)
+            if k is not None:
+                l = plain_logits(cfg, w, p + want[:k])[-1]
+                assert float(l[want[k]] - l[got[k]]) <= 3e-2 * float(l.abs().max())
+    assert llm.last_stats.prompt_tokens == 27 and llm.last_stats.generated_tokens == 24
+    assert llm.engine.cache.n_open == 0
+    # the reference's `steps` counts positions, prompt included (src/model.rs:1668-1690)
+    assert len(llm.generate(prompts[0], steps=9, temperature=0.0, stop_token_ids=[])) == 4
+    # one prompt, one list back; stop tokens end a sequence and are not returned
+    first = llm.generate(prompts[1], max_new_tokens=8, temperature=0.0, stop_token_ids=[])
+    res = llm.generate(prompts[1], max_new_tokens=8, temperature=0.0, stop_token_ids=[first[3]], return_results=True)
+    assert res.tokens == first[:3] and res.finish_reason == "stop_token"
+
+
+def test_sampled_generation_follows_the_plain_sampler(llms, tiny_weights):
+    """Tiny B's workload: prompts of 1, 4, 17, 33 and 60 tokens, 16 tokens each at temperature 0.8, top-p 0.9.
+    In 32-bit the engine's logits equal the plain ones to rounding, so the same seeds give the same draws
+    unless a draw lands within rounding of a boundary; then the streams part and are compared up to there."""
+    from rusty_llama_b200.sampling import sequence_seed
+
+    name = "B"
+    cfg = TINY[name][0]
+    llm = llms(name, "float32")
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (1, 4, 17, 33, 60)]
+    outs = llm.generate(prompts, max_new_tokens=16, temperature=0.8, top_p=0.9, seed=4242, stop_token_ids=[])
+    again = llm.generate(prompts, max_new_tokens=16, temperature=0.8, top_p=0.9, seed=4242, stop_token_ids=[])
+    assert outs == again
+    alone = llm.generate(prompts[2], max_new_tokens=16, temperature=0.8, top_p=0.9, seed=sequence_seed(4242, 2), stop_token_ids=[])
+    w = rounded_weights(tiny_weights[name], "float32")
+    agree = 0
+    for i, (p, got) in enumerate(zip(prompts, outs)):
+        want = plain_generate(cfg, w, p, 16, temperature=0.8, top_p=0.9, seed=sequence_seed(4242, i))
+        agree += int(got == want)
+        assert len(got) == 16
+    assert agree >= 4
+    assert alone == outs[2]  # a sequence's draws do not depend on its neighbours
