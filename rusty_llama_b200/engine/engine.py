@@ -28,6 +28,7 @@ import torch
 
 from ..cache import PAGE_SIZE, Cache
 from ..errors import StepError
+from ..kernels import ops
 from ..models.model import Model
 
 
@@ -123,6 +124,7 @@ class _DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.warm = 0
+        self.launches = 0  # kernels of this library inside the captured graph
 
 
 class Engine:
@@ -143,7 +145,6 @@ class Engine:
         self.use_graphs = use_graphs and self.rt.device.type == "cuda"
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self._meta = _MetaBuffers(self.rt.device)
-        self.kernel_launches = 0
 
     # ------------------------------------------------------------------ sequences
     def open_sequence(self) -> int:
@@ -277,13 +278,16 @@ class Engine:
             else:
                 torch.cuda.synchronize(self.rt.device)
                 graph = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
                 with torch.cuda.graph(graph):
                     g.logits = self.model.forward(step, self.cache, tables)
+                g.launches = ops.launch_count() - before
                 g.graph = graph
                 graph.replay()
                 logits = g.logits
         else:
             g.graph.replay()
+            ops.add_launches(g.launches)
             logits = g.logits
         if rows == all_rows:
             return logits

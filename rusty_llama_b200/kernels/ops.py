@@ -62,7 +62,22 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(lib, rc: int, name: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far in this process (replayed graph nodes included)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(lib, rc: int, name: str, kernels: int = 1) -> None:
+    global _launches
+    _launches += kernels
     if rc != 0:
         text = lib.rl_error_text().decode("utf-8", "replace")
         kind = "refused its arguments" if rc < 0 else f"failed to launch (CUDA error {rc})"
@@ -285,7 +300,7 @@ def attn_decode(
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
         c_int(n_splits), _stream(),
     )
-    _check(lib, rc, "attn_decode")
+    _check(lib, rc, "attn_decode", kernels=2)
     return out
 
 
