@@ -134,7 +134,8 @@ def run_ours(args) -> dict:
     dev = torch.device("cuda:0")
     t_load = time.time()
     max_tokens = max(64 * ctx, batch * ctx) + 64 * 64
-    llm = rl.load_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_tokens, max_seqs=64)
+    llm = rl.load_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_tokens, max_seqs=64,
+                         use_graphs=not args.no_graphs)
     torch.cuda.synchronize()
     print(f"[bench] model of {L} layers ready in {time.time() - t_load:.1f} s", file=sys.stderr, flush=True)
     gen = torch.Generator().manual_seed(0)
@@ -174,13 +175,21 @@ def run_ours(args) -> dict:
             llm.close_sequence(s)
         return B * 1000.0 / ms, ms, bytes_step, clocks, launches
 
-    # ---- headline: batch `batch`
-    value, ms_step, bytes_step, clocks, launches = decode_run(batch, K, W, True)
+    if args.only == "prefill":
+        value, ms_step, bytes_step, clocks, launches = 0.0, 1.0, 0.0, None, 0
+    else:
+        # ---- headline: batch `batch`
+        value, ms_step, bytes_step, clocks, launches = decode_run(batch, K, W, True)
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "batch": batch, "ms_per_step": ms_step, "tokens_per_s": value, "GBps": achieved, "layers": L}))
+        return None
 
     # ---- other batch sizes
     points = {}
     for B in (1, 64):
+        if args.only == "prefill":
+            break
         v, _, _, _, _ = decode_run(B, max(8, K // 2), W, False)
         points[f"decode_b{B}"] = round(v, 1)
 
@@ -203,6 +212,9 @@ def run_ours(args) -> dict:
     H, hd = cfg["num_attention_heads"], cfg["head_dim"]
     flops = 2.0 * T * per_layer * L + 4.0 * T * T * hd * H / 2 * L + 2.0 * V * cfg["hidden_size"]
     pre_frac = flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "tokens": T, "ms": pre_ms, "tokens_per_s": T * 1000.0 / pre_ms, "frac": pre_frac, "layers": L}))
+        return None
 
     # ---- end to end through the Python entry point: host token lists in, host token lists out
     prompts = [torch.randint(0, V, (ctx - (K + 1),), generator=gen).tolist() for _ in range(batch)]
@@ -274,6 +286,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in the output)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="profiling aid: run one phase only")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({
@@ -286,7 +300,9 @@ def main() -> int:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for --gpus {args.gpus})")
         return 2
     args.warmup = max(args.warmup, 3)
-    print(json.dumps(run_ours(args)))
+    out = run_ours(args)
+    if out is not None:
+        print(json.dumps(out))
     return 0
 
 

@@ -105,7 +105,7 @@ def test_batched_decoding_with_leavers_and_slot_reuse(dtype, llms, tiny_weights)
 
     name = "A"
     cfg = TINY[name][0]
-    llm = llms(name, dtype, max_tokens=64 * 4, max_seqs=3)
+    llm = llms(name, dtype, max_tokens=64 * 5, max_seqs=3)
     rng = np.random.default_rng(21)
     for round_ in range(3):
         lens = [(5, 12), (9, 30), (13, 66)] if round_ % 2 == 0 else [(70, 75), (1, 20), (64, 65)]

@@ -120,14 +120,18 @@ def test_attention_part_prefill_then_decode(dtype, H, K, hd, window, interleaved
     xs = [torch.randn(n + 3, d, generator=g).to(dtype) for n in lens]
     inv = att.position.inv_freq.cpu()
 
+    # the engine keeps q, k, v, the rotated q and k, and the heads' output in the run's type: the
+    # reference rounds at the same places, so that what is compared is the arithmetic in between
+    rnd = (lambda t: t.to(torch.bfloat16).double()) if dtype == torch.bfloat16 else (lambda t: t)
+
     def ref_for(x):
         T = x.shape[0]
         xd = x.double()
-        q = (xd @ w["a.q_proj.weight"].double().T).view(T, H, hd)
-        k = (xd @ w["a.k_proj.weight"].double().T).view(T, K, hd)
-        v = (xd @ w["a.v_proj.weight"].double().T).view(T, K, hd)
-        q, k = plain_rope(q, torch.arange(T), inv, interleaved), plain_rope(k, torch.arange(T), inv, interleaved)
-        return plain_attention(q, k, v, window).reshape(T, H * hd) @ w["a.o_proj.weight"].double().T
+        q = rnd(xd @ w["a.q_proj.weight"].double().T).view(T, H, hd)
+        k = rnd(xd @ w["a.k_proj.weight"].double().T).view(T, K, hd)
+        v = rnd(xd @ w["a.v_proj.weight"].double().T).view(T, K, hd)
+        q, k = rnd(plain_rope(q, torch.arange(T), inv, interleaved)), rnd(plain_rope(k, torch.arange(T), inv, interleaved))
+        return rnd(plain_attention(q, k, v, window).reshape(T, H * hd)) @ w["a.o_proj.weight"].double().T
 
     refs = [ref_for(x) for x in xs]
     slots = [cache.open_sequence(), cache.open_sequence()]

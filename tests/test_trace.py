@@ -26,9 +26,10 @@ def test_replay_whole_one_by_one_and_in_batches(name, dtype, tiny_dirs, tiny_wei
     V = cfg["vocab_size"]
     requests = make_requests(name)
     ref = plain_all_logits(cfg, tiny_weights[name], dtype, requests)
-    # room for the two longest requests at once, each rounded up to 64: batches below are planned to fit
-    longest = sorted(LENGTHS[name])[-2:]
-    max_tokens = sum((n + 63) // 64 * 64 for n in longest)
+    # room for the second and third longest requests at once, each rounded up to 64 (the longest fits
+    # alone): the batches below are planned to fit, and the cache has to be used again and again
+    some = sorted(LENGTHS[name])[-3:-1]
+    max_tokens = sum((n + 63) // 64 * 64 for n in some)
     run = TraceRun(tiny_dirs[name], dtype, str(tmp_path / "out"), max_tokens, V)
     try:
         # 1. each request alone and whole, logits at every position
