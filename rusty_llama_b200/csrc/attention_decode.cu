@@ -1,24 +1,25 @@
-// Decode attention over the paged cache: one new token per sequence, keys and
-// values streamed from HBM once per (sequence, kv head) for all query heads of
-// the group, the key range cut into splits so that a small batch still fills
-// the GPU (flash-decoding).  The reference runs its one prefill kernel with a
-// single row here (src/backend/cuda.rs:1189-1192), one block per query head,
-// which reads every key `group size` times.
+// Decode attention over the paged cache in bfloat16: one new token per sequence, keys and
+// values streamed from HBM once per (sequence, kv head) for all query heads of the group, the
+// key range cut into splits so that a small batch still fills the GPU (flash-decoding).  The
+// reference runs its one scalar kernel with a single row here (src/backend/cuda.rs:1189-1192),
+// one block per query head, which reads every key `group size` times.
 //
-// Kernel 1 (grid: splits x (kv heads * head groups of GT) x sequences): for its
-// pages, tile = one page of 64 keys, K and V tiles copied to shared memory with
-// cp.async (two stages), scores and the online softmax in 32-bit, partial
-// (max, sum, unnormalised output) written to scratch.
-// Kernel 2 (grid: query heads x sequences): merges the splits in split order.
+// Kernel 1 (grid: splits x (kv heads * groups of 16 query heads) x sequences, one warp each):
+// the query heads of the group are the rows of a 16-row tile (unused rows are zero), so that
+// Q K^T and P V run on the tensor cores (mma.sync m16n8k16, 32-bit accumulate) exactly as in the
+// prompt kernel; a key tile is one cache page of 64 positions, copied to shared memory with
+// cp.async while the previous one is in use; max, sum and rescaling of the online softmax stay
+// in 32-bit registers.  Each warp writes its partial (max, sum, unnormalised output) to scratch.
+// Kernel 2 (grid: query heads x sequences) merges the splits in split order.
 //
 // Scratch layout: part_o[seq][head][split][hd] floats, part_ml[seq][head][split][2].
+// Head sizes are padded with zeros to HD in shared memory: any multiple of 8 up to 256.
 #include "common.cuh"
 
 RL_DEFINE_ERROR_TEXT()
 
-#define GT 4          // query heads per block
-#define TILE 64       // keys per tile = page size
-#define THREADS 128
+#define ROWS 16   // query heads per warp tile
+#define BN 64     // keys per tile = page size
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -28,190 +29,229 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <typename T>
-struct Vec16 {
-  static constexpr int N = 16 / sizeof(T);  // elements per 16 bytes
-};
-
-template <typename T>
-__device__ __forceinline__ void load_vec_f32(const T* p, float* f);
-template <>
-__device__ __forceinline__ void load_vec_f32<bf16>(const bf16* p, float* f) {
-  bf16x8_to_f32(*reinterpret_cast<const uint4*>(p), f);
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
 }
-template <>
-__device__ __forceinline__ void load_vec_f32<float>(const float* p, float* f) {
-  const float4 v = *reinterpret_cast<const float4*>(p);
-  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copy one page tile [TILE][hd] (contiguous in global memory) into rows of
-// `stride` elements in shared memory.
-template <typename T>
-__device__ __forceinline__ void load_tile(T* dst, const T* src, int hd, int stride) {
-  constexpr int VN = Vec16<T>::N;
-  const int chunks_per_row = hd / VN;
-  const int total = TILE * chunks_per_row;
-  for (int c = threadIdx.x; c < total; c += THREADS) {
+// Copy a page tile [BN][hd] (contiguous) into rows of `stride` elements, by one warp.
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* src, int hd, int stride, int lane) {
+  const int chunks_per_row = hd >> 3;
+  const int total = BN * chunks_per_row;
+  for (int c = lane; c < total; c += 32) {
     const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
-    cp_async_16(dst + (size_t)r * stride + cc * VN, src + (size_t)r * hd + cc * VN);
+    cp_async_16(dst + (size_t)r * stride + cc * 8, src + (size_t)r * hd + cc * 8);
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(THREADS)
-attn_decode_split_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_pages,
-                         const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+template <int HD>
+__global__ void __launch_bounds__(32)
+attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_pages,
+                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_len, float* __restrict__ part_o,
-                         float* __restrict__ part_ml, int H, int K, int hd, int window, float scale,
+                         float* __restrict__ part_ml, int H, int K, int hd, int window, float scale_log2,
                          int n_splits) {
-  constexpr int VN = Vec16<T>::N;
+  constexpr int STRIDE = HD + 8;
+  constexpr int KSTEPS = HD / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int stride = hd + VN;  // padded row: consecutive keys fall into different banks
-  T* k_s[2];
-  T* v_s[2];
-  k_s[0] = reinterpret_cast<T*>(smem_raw);
-  v_s[0] = k_s[0] + (size_t)TILE * stride;
-  k_s[1] = v_s[0] + (size_t)TILE * stride;
-  v_s[1] = k_s[1] + (size_t)TILE * stride;
-  float* q_s = reinterpret_cast<float*>(v_s[1] + (size_t)TILE * stride);  // [GT][hd]
-  float* sc = q_s + GT * hd;                                               // [GT][TILE]
-  __shared__ float alpha_s[GT];
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [ROWS][STRIDE]
+  bf16* k_s0 = q_s + ROWS * STRIDE;               // two stages of K and V, [BN][STRIDE] each
+  bf16* v_s0 = k_s0 + BN * STRIDE;
+  bf16* k_s1 = v_s0 + BN * STRIDE;
+  bf16* v_s1 = k_s1 + BN * STRIDE;
 
   const int G = H / K;
-  const int groups_per_kv = (G + GT - 1) / GT;
+  const int groups_per_kv = (G + ROWS - 1) / ROWS;
   const int split = blockIdx.x;
   const int kh = blockIdx.y / groups_per_kv;
-  const int g0 = (blockIdx.y - kh * groups_per_kv) * GT;  // first head of this block within the group
-  const int n_heads = min(GT, G - g0);
+  const int g0 = (blockIdx.y - kh * groups_per_kv) * ROWS;
+  const int n_heads = min(ROWS, G - g0);
   const int h0 = kh * G + g0;
   const int s = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane = threadIdx.x;
+  const int g = lane >> 2, t4 = lane & 3;
 
   const int kv_len = seq_len[s];
   const int pos = kv_len - 1;
   const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
-  const int tile_lo = first / TILE, tile_hi = pos / TILE;  // inclusive
+  const int tile_lo = first / BN, tile_hi = pos / BN;  // inclusive
   const int n_tiles = tile_hi - tile_lo + 1;
   const int per_split = (n_tiles + n_splits - 1) / n_splits;
   const int my_lo = tile_lo + split * per_split;
   const int my_hi = min(my_lo + per_split - 1, tile_hi);
 
-  float m_run = -INFINITY, l_run = 0.f;  // meaningful in warp g (< n_heads), all lanes equal
-  float acc[GT][2];
+  float o_acc[HD / 8][4];
 #pragma unroll
-  for (int g = 0; g < GT; ++g) acc[g][0] = acc[g][1] = 0.f;
+  for (int i = 0; i < HD / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
 
   if (my_lo <= my_hi) {
-    const int* table = block_table + (size_t)s * table_width;
-    for (int i = tid; i < GT * hd; i += THREADS) {
-      const int g = i / hd, d = i - g * hd;
-      q_s[i] = (g < n_heads) ? to_f32(q[(size_t)s * q_stride + (size_t)(h0 + g) * hd + d]) : 0.f;
-    }
+    // zero the padding (columns past hd, rows past the group's heads), then fetch Q and the first tile
     {
-      const size_t base = ((size_t)table[my_lo] * K + kh) * TILE * hd;
-      load_tile(k_s[0], k_pages + base, hd, stride);
-      load_tile(v_s[0], v_pages + base, hd, stride);
-      cp_async_commit();
+      uint4 z = make_uint4(0, 0, 0, 0);
+      uint4* p = reinterpret_cast<uint4*>(smem_raw);
+      const int n16 = ((ROWS + 4 * BN) * STRIDE * (int)sizeof(bf16)) / 16;
+      for (int i = lane; i < n16; i += 32) p[i] = z;
     }
+    __syncwarp();
+    {
+      const int chunks_per_row = hd >> 3;
+      for (int c = lane; c < n_heads * chunks_per_row; c += 32) {
+        const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
+        cp_async_16(q_s + (size_t)r * STRIDE + cc * 8, q + (size_t)s * q_stride + (size_t)(h0 + r) * hd + cc * 8);
+      }
+    }
+    const int* table = block_table + (size_t)s * table_width;
+    {
+      const size_t base = ((size_t)table[my_lo] * K + kh) * BN * hd;
+      load_kv_tile(k_s0, k_pages + base, hd, STRIDE, lane);
+      load_kv_tile(v_s0, v_pages + base, hd, STRIDE, lane);
+    }
+    cp_async_commit();
+
     for (int tile = my_lo; tile <= my_hi; ++tile) {
       const int buf = (tile - my_lo) & 1;
+      bf16* k_s = buf ? k_s1 : k_s0;
+      bf16* v_s = buf ? v_s1 : v_s0;
       if (tile + 1 <= my_hi) {
-        const size_t base = ((size_t)table[tile + 1] * K + kh) * TILE * hd;
-        load_tile(k_s[buf ^ 1], k_pages + base, hd, stride);
-        load_tile(v_s[buf ^ 1], v_pages + base, hd, stride);
+        const size_t base = ((size_t)table[tile + 1] * K + kh) * BN * hd;
+        load_kv_tile(buf ? k_s0 : k_s1, k_pages + base, hd, STRIDE, lane);
+        load_kv_tile(buf ? v_s0 : v_s1, v_pages + base, hd, STRIDE, lane);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
       }
-      __syncthreads();  // tile `buf` (and q_s) visible to all
+      __syncwarp();
 
-      // ---- scores: thread = (key, pair of heads)
-      {
-        const int key = tid & (TILE - 1);
-        const int hp = tid >> 6;  // 0: heads 0,1   1: heads 2,3
-        const T* kr = k_s[buf] + (size_t)key * stride;
-        const float* qa = q_s + (2 * hp) * hd;
-        const float* qb = qa + hd;
-        float sa = 0.f, sb = 0.f;
-        for (int c = 0; c < hd; c += VN) {
-          float kf[VN];
-          load_vec_f32<T>(kr + c, kf);
+      // ---- S = Q K^T: 16 rows (heads) x 64 keys
+      float s_acc[BN / 8][4];
 #pragma unroll
-          for (int e = 0; e < VN; ++e) {
-            sa += qa[c + e] * kf[e];
-            sb += qb[c + e] * kf[e];
-          }
-        }
-        const int kpos = tile * TILE + key;
-        const bool seen = kpos >= first && kpos <= pos;
-        sc[(2 * hp) * TILE + key] = seen ? sa * scale : -INFINITY;
-        sc[(2 * hp + 1) * TILE + key] = seen ? sb * scale : -INFINITY;
-      }
-      __syncthreads();
-
-      // ---- online softmax: warp g owns head g
-      if (warp < n_heads) {
-        float* row = sc + warp * TILE;
-        const float s0 = row[lane], s1 = row[lane + 32];
-        const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));  // finite: every tile holds a seen key
-        const float alpha = expf(m_run - m_new);
-        const float p0 = expf(s0 - m_new), p1 = expf(s1 - m_new);  // exp(-inf) = 0 for unseen keys
-        row[lane] = p0;
-        row[lane + 32] = p1;
-        l_run = l_run * alpha + warp_sum(p0 + p1);
-        m_run = m_new;
-        if (lane == 0) alpha_s[warp] = alpha;
-      }
-      __syncthreads();
-
-      // ---- values: thread = output dimension(s) tid, tid + 128
-      {
-        const int n_valid = min(TILE, pos - tile * TILE + 1);  // rows past the last position are not read
+      for (int i = 0; i < BN / 8; ++i) s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f;
 #pragma unroll
-        for (int dd = 0; dd < 2; ++dd) {
-          const int d = tid + dd * THREADS;
-          if (d < hd) {
-            float a[GT];
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_s + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
 #pragma unroll
-            for (int g = 0; g < GT; ++g) a[g] = acc[g][dd] * ((g < n_heads) ? alpha_s[g] : 0.f);
-            const T* vc = v_s[buf] + d;
-            for (int key = 0; key < n_valid; ++key) {
-              const float v = to_f32(vc[(size_t)key * stride]);
-#pragma unroll
-              for (int g = 0; g < GT; ++g) a[g] += sc[g * TILE + key] * v;
-            }
-#pragma unroll
-            for (int g = 0; g < GT; ++g) acc[g][dd] = a[g];
-          }
+        for (int np = 0; np < BN / 16; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4(b, k_s + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + kk * 16 + 8 * ((lane >> 3) & 1));
+          mma_bf16(s_acc[2 * np], a, b[0], b[1]);
+          mma_bf16(s_acc[2 * np + 1], a, b[2], b[3]);
         }
       }
-      __syncthreads();  // before the next iteration overwrites sc and the other buffer
+
+      // ---- mask by position, scale to base-2 exponents, online softmax
+      const int key0 = tile * BN;
+      const bool need_mask = key0 < first || key0 + BN - 1 > pos;
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s_acc[n][e] * scale_log2;
+          if (need_mask) {
+            const int key = key0 + n * 8 + 2 * t4 + (e & 1);
+            if (key < first || key > pos) v = -INFINITY;
+          }
+          s_acc[n][e] = v;
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = tile_max[r];
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[r], mx);  // finite: every tile of the range holds a seen key
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[r] = exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= alpha[r];
+      }
+#pragma unroll
+      for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p = exp2f(s_acc[n][e] - m_use[e >> 1]);
+          s_acc[n][e] = p;
+          l_run[e >> 1] += p;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o_acc[i][0] *= alpha[0];
+        o_acc[i][1] *= alpha[0];
+        o_acc[i][2] *= alpha[1];
+        o_acc[i][3] *= alpha[1];
+      }
+
+      // ---- O += P V
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+        a[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+        a[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+        a[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, v_s + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
+          mma_bf16(o_acc[2 * dp], a, b[0], b[1]);
+          mma_bf16(o_acc[2 * dp + 1], a, b[2], b[3]);
+        }
+      }
+      __syncwarp();  // the stage is free for the load after next
     }
   }
 
-  // ---- partial results
-  if (warp < n_heads && lane == 0) {
-    float* ml = part_ml + (((size_t)s * H + h0 + warp) * n_splits + split) * 2;
-    ml[0] = m_run;
-    ml[1] = l_run;
-  }
+  // ---- partial results: max (base-2 exponent), sum, unnormalised output
 #pragma unroll
-  for (int dd = 0; dd < 2; ++dd) {
-    const int d = tid + dd * THREADS;
-    if (d < hd) {
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = g + 8 * r;
+    if (row < n_heads) {
+      const size_t slot = ((size_t)s * H + h0 + row) * n_splits + split;
+      if (t4 == 0) {
+        part_ml[slot * 2] = m_run[r];
+        part_ml[slot * 2 + 1] = l;
+      }
+      float* po = part_o + slot * hd;
 #pragma unroll
-      for (int g = 0; g < GT; ++g)
-        if (g < n_heads) part_o[(((size_t)s * H + h0 + g) * n_splits + split) * hd + d] = acc[g][dd];
+      for (int n = 0; n < HD / 8; ++n) {
+        const int d = n * 8 + 2 * t4;
+        if (d < hd) *reinterpret_cast<float2*>(po + d) = make_float2(o_acc[n][2 * r], o_acc[n][2 * r + 1]);
+      }
     }
   }
 }
 
-// out[s, h, :] = sum_split exp(m_split - M) o_split / sum_split exp(m_split - M) l_split
-template <typename T>
+// out[s, h, :] = sum_split 2^(m_split - M) o_split / sum_split 2^(m_split - M) l_split
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         T* __restrict__ out, int out_stride, int H, int hd, int n_splits) {
+                                         bf16* __restrict__ out, int out_stride, int H, int hd, int n_splits) {
   const int h = blockIdx.x, s = blockIdx.y;
   const float* ml = part_ml + ((size_t)s * H + h) * n_splits * 2;
   const float* po = part_o + ((size_t)s * H + h) * n_splits * hd;
@@ -220,72 +260,69 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
   float L = 0.f;
   for (int i = 0; i < n_splits; ++i) {
     const float m = ml[2 * i];
-    if (m != -INFINITY) L += expf(m - M) * ml[2 * i + 1];
+    if (m != -INFINITY) L += exp2f(m - M) * ml[2 * i + 1];
   }
   const float inv = 1.0f / L;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
     for (int i = 0; i < n_splits; ++i) {
       const float m = ml[2 * i];
-      if (m != -INFINITY) o += expf(m - M) * po[(size_t)i * hd + d];
+      if (m != -INFINITY) o += exp2f(m - M) * po[(size_t)i * hd + d];
     }
-    out[(size_t)s * out_stride + (size_t)h * hd + d] = from_f32<T>(o * inv);
+    out[(size_t)s * out_stride + (size_t)h * hd + d] = __float2bfloat16_rn(o * inv);
   }
 }
 
-template <typename T>
-static size_t split_smem_bytes(int hd) {
-  const int stride = hd + Vec16<T>::N;
-  return (size_t)4 * TILE * stride * sizeof(T) + (size_t)GT * hd * sizeof(float) + (size_t)GT * TILE * sizeof(float);
-}
-
-template <typename T>
-static int launch_decode(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+template <int HD>
+static int launch_decode(const bf16* q, int q_stride, const bf16* k_pages, const bf16* v_pages,
                          const int* block_table, int table_width, const int* seq_len, float* part_o,
-                         float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
+                         float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
                          float scale, int n_splits, cudaStream_t stream) {
-  const size_t smem = split_smem_bytes<T>(hd);
-  auto kern = attn_decode_split_kernel<T>;
-  if (smem > 220 * 1024) RL_REFUSE(7, "attn_decode: head size %d needs %zu bytes of shared memory", hd, smem);
+  const size_t smem = (size_t)(ROWS + 4 * BN) * (HD + 8) * sizeof(bf16);
+  auto kern = attn_decode_split_kernel<HD>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(8, "attn_decode: cannot get %zu bytes of shared memory", smem);
   }
   const int G = H / K;
-  dim3 grid(n_splits, K * ((G + GT - 1) / GT), n_seqs);
-  kern<<<grid, THREADS, smem, stream>>>((const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
-                                        table_width, seq_len, part_o, part_ml, H, K, hd, window, scale, n_splits);
+  dim3 grid(n_splits, K * ((G + ROWS - 1) / ROWS), n_seqs);
+  kern<<<grid, 32, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
+                                   H, K, hd, window, scale * 1.4426950408889634f, n_splits);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(e));
     return (int)e;
   }
   dim3 grid2(H, n_seqs);
-  attn_decode_merge_kernel<T><<<grid2, 128, 0, stream>>>(part_o, part_ml, (T*)out, out_stride, H, hd, n_splits);
+  attn_decode_merge_kernel<<<grid2, 128, 0, stream>>>(part_o, part_ml, out, out_stride, H, hd, n_splits);
   RL_LAUNCH_RESULT();
 }
 
-// Scratch needed, in floats: n_seqs * H * n_splits * (hd + 2); the caller passes
-// part_o of n_seqs*H*n_splits*hd floats and part_ml of n_seqs*H*n_splits*2.
+// Scratch needed, in floats: n_seqs * H * n_splits * (hd + 2); the caller passes part_o of
+// n_seqs*H*n_splits*hd floats and part_ml of n_seqs*H*n_splits*2.
 RL_API int rl_attn_decode(const void* q, int dtype, int q_stride, const void* k_pages, const void* v_pages,
                           const int* block_table, int table_width, const int* seq_len, float* part_o,
                           float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int hd,
                           int page_size, int window, float scale, int n_splits, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || hd <= 0) RL_REFUSE(1, "attn_decode: S=%d H=%d K=%d hd=%d", n_seqs, H, K, hd);
   if (H % K) RL_REFUSE(2, "attn_decode: %d query heads are not a multiple of %d kv heads", H, K);
-  if (page_size != TILE) RL_REFUSE(3, "attn_decode: page size %d, this kernel is built for %d", page_size, TILE);
-  if (hd > 2 * THREADS) RL_REFUSE(4, "attn_decode: head size %d exceeds %d", hd, 2 * THREADS);
+  if (page_size != BN) RL_REFUSE(3, "attn_decode: page size %d, this kernel is built for %d", page_size, BN);
+  if (dtype != RL_BF16) RL_REFUSE(4, "attn_decode: bfloat16 only (32-bit runs use attn_generic), got dtype %d", dtype);
+  if (hd % 8) RL_REFUSE(9, "attn_decode: head size %d is not a multiple of 8", hd);
+  if (q_stride % 8) RL_REFUSE(9, "attn_decode: query row stride %d breaks 16-byte alignment", q_stride);
   if (n_splits <= 0 || n_splits > 65535 || n_seqs > 65535) RL_REFUSE(5, "attn_decode: splits=%d seqs=%d", n_splits, n_seqs);
   if (window < 0) RL_REFUSE(6, "attn_decode: negative window");
-  if (dtype == RL_BF16) {
-    if (hd % 8) RL_REFUSE(9, "attn_decode: head size %d is not a multiple of 8", hd);
-    return launch_decode<bf16>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml, out,
-                               out_stride, n_seqs, H, K, hd, window, scale, n_splits, stream);
-  }
-  if (dtype == RL_F32) {
-    if (hd % 4) RL_REFUSE(9, "attn_decode: head size %d is not a multiple of 4", hd);
-    return launch_decode<float>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
-                                out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, stream);
-  }
-  RL_REFUSE(10, "attn_decode: unknown dtype %d", dtype);
+  const bf16* qq = (const bf16*)q;
+  const bf16* kp = (const bf16*)k_pages;
+  const bf16* vp = (const bf16*)v_pages;
+  bf16* oo = (bf16*)out;
+#define RL_DECODE(HDV)                                                                                              \
+  return launch_decode<HDV>(qq, q_stride, kp, vp, block_table, table_width, seq_len, part_o, part_ml, oo, out_stride, \
+                            n_seqs, H, K, hd, window, scale, n_splits, stream)
+  if (hd <= 32) RL_DECODE(32);
+  if (hd <= 64) RL_DECODE(64);
+  if (hd <= 128) RL_DECODE(128);
+  if (hd <= 256) RL_DECODE(256);
+#undef RL_DECODE
+  RL_REFUSE(10, "attn_decode: head size %d exceeds 256", hd);
 }

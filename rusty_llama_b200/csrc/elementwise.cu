@@ -13,22 +13,40 @@ RL_DEFINE_ERROR_TEXT()
 
 // ---------------------------------------------------------------- embedding
 // out[t, :] = table[tokens[t], :] widened to 32-bit, no scale (src/model.rs:1237-1242).
-template <typename TW>
+template <typename TW, bool VEC>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                     float* __restrict__ out, int d) {
   const int t = blockIdx.x;
   const TW* row = table + (size_t)tokens[t] * d;
   float* o = out + (size_t)t * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]);
+  if (VEC) {  // d is a multiple of 4: every thread moves four values per round, all loads in flight at once
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4];
+      load4<TW>(row + i, v);
+      store4<float>(o + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]);
+  }
+}
+
+static int row_threads(int d) {
+  int t = ((d / 4 + 31) / 32) * 32;
+  return t < 32 ? 32 : (t > 1024 ? 1024 : t);
 }
 
 RL_API int rl_embed_gather(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens,
                            int d, cudaStream_t stream) {
   if (n_tokens <= 0 || d <= 0) RL_REFUSE(1, "embed_gather: n_tokens=%d d=%d", n_tokens, d);
-  if (table_dtype == RL_BF16)
-    embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>(tokens, (const bf16*)table, out, d);
+  const int th = row_threads(d);
+  if (table_dtype == RL_BF16 && d % 4 == 0)
+    embed_gather_kernel<bf16, true><<<n_tokens, th, 0, stream>>>(tokens, (const bf16*)table, out, d);
+  else if (table_dtype == RL_BF16)
+    embed_gather_kernel<bf16, false><<<n_tokens, 256, 0, stream>>>(tokens, (const bf16*)table, out, d);
+  else if (table_dtype == RL_F32 && d % 4 == 0)
+    embed_gather_kernel<float, true><<<n_tokens, th, 0, stream>>>(tokens, (const float*)table, out, d);
   else if (table_dtype == RL_F32)
-    embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, out, d);
+    embed_gather_kernel<float, false><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, out, d);
   else
     RL_REFUSE(2, "embed_gather: unknown table dtype %d", table_dtype);
   RL_LAUNCH_RESULT();
@@ -40,28 +58,59 @@ RL_API int rl_embed_gather(const int* tokens, const void* table, int table_dtype
 //   if write_x: x[t] = v
 //   if w: out[r] = v * (1 / sqrt(sum(v^2)/d + eps)) * w   (src/backend/cpu.rs:96-105)
 // The row is held in shared memory between the two passes.
-template <typename TA, typename TW>
+// With VEC (d a multiple of 4) a thread handles four neighbouring values per round and the block
+// is sized so that a row of up to 4096 values takes one round: all loads are in flight together,
+// which is what the few rows of a decode step need.
+template <typename TA, typename TW, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, int n_parts,
                                    long long part_stride, const TW* __restrict__ w, TA* __restrict__ out,
                                    const int* __restrict__ rows, int d, float eps, int write_x) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * d;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float v = xr[i];
-    for (int p = 0; p < n_parts; ++p) v += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
-    row[i] = v;
-    if (write_x) xr[i] = v;
-    ss += v * v;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4];
+      load4<float>(xr + i, v);
+      for (int p = 0; p < n_parts; ++p) {
+        float dv[4];
+        load4<TA>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] += dv[e];
+      }
+      store4<float>(row + i, v);
+      if (write_x) store4<float>(xr + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float v = xr[i];
+      for (int p = 0; p < n_parts; ++p) v += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
+      row[i] = v;
+      if (write_x) xr[i] = v;
+      ss += v * v;
+    }
   }
   if (w == nullptr) return;
   const float total = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(total / (float)d + eps);
   TA* o = out + (size_t)r * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>(row[i] * inv * to_f32(w[i]));
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4], wv[4];
+      load4<float>(row + i, v);
+      load4<TW>(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * wv[e];
+      store4<TA>(o + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>(row[i] * inv * to_f32(w[i]));
+  }
 }
 
 template <typename TA, typename TW>
@@ -69,14 +118,15 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_parts, long lon
                               void* out, const int* rows, int n_rows, int d, float eps, int write_x,
                               cudaStream_t stream) {
   const size_t smem = (size_t)d * sizeof(float);
-  auto kern = add_rmsnorm_kernel<TA, TW>;
+  const bool vec = d % 4 == 0;
+  auto kern = vec ? add_rmsnorm_kernel<TA, TW, true> : add_rmsnorm_kernel<TA, TW, false>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) RL_REFUSE(3, "add_rmsnorm: a row of %d values does not fit shared memory", d);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(4, "add_rmsnorm: cannot get %zu bytes of shared memory", smem);
   }
-  kern<<<n_rows, 256, smem, stream>>>(x, (const TA*)delta, n_parts, part_stride, (const TW*)w, (TA*)out, rows, d,
-                                      eps, write_x);
+  kern<<<n_rows, vec ? row_threads(d) : 256, smem, stream>>>(x, (const TA*)delta, n_parts, part_stride,
+                                                             (const TW*)w, (TA*)out, rows, d, eps, write_x);
   RL_LAUNCH_RESULT();
 }
 

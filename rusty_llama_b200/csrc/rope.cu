@@ -78,6 +78,90 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
   }
 }
 
+// The same work four values at a time: a thread takes one group of four neighbouring values of a
+// query head, a key head (with its cache write) or a value head, so a token's row is done in one
+// or two rounds with every load in flight at once; a decode step has few tokens and would
+// otherwise wait for one load after the other.  Needs head size, rotary size / 2 (or rotary size
+// when interleaved) and the row stride to be multiples of 4.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ tok_pos,
+                                         const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                         int table_width, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                         const float* __restrict__ inv_freq, int H, int K, int hd, int rot,
+                                         int interleaved, int page_size, int write_kv) {
+  extern __shared__ float trig[];
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = rot >> 1;
+  float* cs = trig;
+  float* sn = trig + half;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const float a = (float)pos * inv_freq[j];
+    float s, c;
+    sincosf(a, &s, &c);
+    cs[j] = c;
+    sn[j] = s;
+  }
+  __syncthreads();
+
+  T* row = qkv + (size_t)t * row_stride;
+  size_t page_base = 0;
+  if (write_kv) {
+    const int page = block_table[(size_t)tok_seq[t] * table_width + pos / page_size];
+    page_base = ((size_t)page * K * page_size + pos % page_size) * hd;  // + h * page_size * hd per head
+  }
+  // groups per head: rotated part (pairs) and unrotated tail
+  const int rot_groups = interleaved ? rot / 4 : half / 4;  // each covers 2 (interleaved) or 4 pairs
+  const int tail_groups = (hd - rot) / 4;
+  const int per_head = rot_groups + tail_groups;
+  const int n_q = H * rot_groups;  // the tail of q stays as it is
+  const int n_k = write_kv ? K * per_head : 0;
+  const int n_v = write_kv ? K * (hd / 4) : 0;
+  for (int item = threadIdx.x; item < n_q + n_k + n_v; item += blockDim.x) {
+    if (item < n_q + n_k) {
+      const bool is_q = item < n_q;
+      const int idx = is_q ? item : item - n_q;
+      const int groups = is_q ? rot_groups : per_head;
+      const int h = idx / groups, gq = idx - h * groups;
+      T* head = row + (size_t)(is_q ? h : H + h) * hd;
+      T* dst = is_q ? head : k_pages + page_base + (size_t)h * page_size * hd;
+      if (gq >= rot_groups) {  // unrotated tail of a key head
+        const int i = rot + 4 * (gq - rot_groups);
+        float v[4];
+        load4<T>(head + i, v);
+        store4<T>(dst + i, v);
+      } else if (interleaved) {
+        const int i = 4 * gq, j = 2 * gq;
+        float v[4], o[4];
+        load4<T>(head + i, v);
+        o[0] = v[0] * cs[j] - v[1] * sn[j];
+        o[1] = v[0] * sn[j] + v[1] * cs[j];
+        o[2] = v[2] * cs[j + 1] - v[3] * sn[j + 1];
+        o[3] = v[2] * sn[j + 1] + v[3] * cs[j + 1];
+        store4<T>(dst + i, o);
+      } else {
+        const int j = 4 * gq;
+        float a[4], b[4], oa[4], ob[4];
+        load4<T>(head + j, a);
+        load4<T>(head + j + half, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          oa[e] = a[e] * cs[j + e] - b[e] * sn[j + e];
+          ob[e] = a[e] * sn[j + e] + b[e] * cs[j + e];
+        }
+        store4<T>(dst + j, oa);
+        store4<T>(dst + j + half, ob);
+      }
+    } else {
+      const int idx = item - n_q - n_k;
+      const int h = idx / (hd / 4), i = 4 * (idx - h * (hd / 4));
+      float v[4];
+      load4<T>(row + (size_t)(H + K + h) * hd + i, v);
+      store4<T>(v_pages + page_base + (size_t)h * page_size * hd + i, v);
+    }
+  }
+}
+
 RL_API int rl_rope_kv_write(void* qkv, int dtype, int row_stride, const int* tok_pos, const int* tok_seq,
                             const int* block_table, int table_width, void* k_pages, void* v_pages,
                             const float* inv_freq, int n_tokens, int H, int K, int hd, int rot, int interleaved,
@@ -90,6 +174,23 @@ RL_API int rl_rope_kv_write(void* qkv, int dtype, int row_stride, const int* tok
   if (rot > 0 && inv_freq == nullptr) RL_REFUSE(5, "rope_kv_write: no frequency table");
   const size_t smem = (size_t)rot * sizeof(float);
   if (smem > 48 * 1024) RL_REFUSE(6, "rope_kv_write: rotary size %d too large", rot);
+  const bool vec = hd % 4 == 0 && row_stride % 4 == 0 && (interleaved ? rot % 4 == 0 : rot % 8 == 0);
+  if (vec) {
+    const int items = H * (rot / 8 + 1) + (write_kv ? K * (hd / 4) * 2 : 0);
+    int threads = ((items + 31) / 32) * 32;
+    threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+    if (dtype == RL_BF16)
+      rope_kv_write_vec_kernel<bf16><<<n_tokens, threads, smem, stream>>>(
+          (bf16*)qkv, row_stride, tok_pos, tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq, H,
+          K, hd, rot, interleaved, page_size, write_kv);
+    else if (dtype == RL_F32)
+      rope_kv_write_vec_kernel<float><<<n_tokens, threads, smem, stream>>>(
+          (float*)qkv, row_stride, tok_pos, tok_seq, block_table, table_width, (float*)k_pages, (float*)v_pages, inv_freq,
+          H, K, hd, rot, interleaved, page_size, write_kv);
+    else
+      RL_REFUSE(7, "rope_kv_write: unknown dtype %d", dtype);
+    RL_LAUNCH_RESULT();
+  }
   if (dtype == RL_BF16)
     rope_kv_write_kernel<bf16><<<n_tokens, 128, smem, stream>>>((bf16*)qkv, row_stride, tok_pos, tok_seq, block_table,
                                                                table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq,

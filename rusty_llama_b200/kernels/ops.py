@@ -95,6 +95,7 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.
         out = torch.empty((T, d), dtype=torch.float32, device=table.device)
     _cuda(out, "embed_gather out", torch.float32)
     _need(tuple(out.shape) == (T, d), "embed_gather: out has the wrong shape")
+    _need(table.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0, "embed_gather: tensors must be 16-byte aligned")
     lib = build.load("elementwise")
     rc = lib.rl_embed_gather(_p(tokens), _p(table), c_int(_dt(table, "embed_gather table")), _p(out), c_int(T), c_int(d), _stream())
     _check(lib, rc, "embed_gather")
@@ -146,6 +147,8 @@ def add_rmsnorm(
         out = None
     if n_rows == 0:
         return out
+    for name, t in (("x", x), ("delta", delta), ("weight", weight), ("out", out)):
+        _need(t is None or t.data_ptr() % 16 == 0, f"add_rmsnorm: {name} is not 16-byte aligned")
     lib = build.load("elementwise")
     rc = lib.rl_add_rmsnorm(
         _p(x), _p(delta), c_int(n_parts), c_ll(part_stride), _p(weight), c_int(w_dt), _p(out),
@@ -209,6 +212,7 @@ def rope_kv_write(
                 f"rope_kv_write: {name} {tuple(pages.shape)} is not [pages, {num_kv_heads}, {PAGE_SIZE}, {head_dim}]",
             )
         _need(qkv.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim, "rope_kv_write: qkv rows too short")
+    _need(qkv.data_ptr() % 16 == 0, "rope_kv_write: qkv is not 16-byte aligned")
     if rotary_dim:
         _cuda(inv_freq, "rope_kv_write inv_freq", torch.float32)
         _need(inv_freq.numel() == rotary_dim // 2, "rope_kv_write: inv_freq must hold rotary_dim/2 values")
@@ -278,6 +282,7 @@ def attn_decode(
     qs = _rows(q, "attn_decode q")
     S = q.shape[0]
     _need(q.shape[1] >= num_heads * head_dim, "attn_decode: q rows too short")
+    _need(q.data_ptr() % 16 == 0, "attn_decode: q is not 16-byte aligned")
     _check_pages(k_pages, v_pages, q.dtype, num_kv_heads, head_dim, "attn_decode")
     _cuda(block_table, "attn_decode block_table", torch.int32)
     _cuda(seq_len, "attn_decode seq_len", torch.int32)

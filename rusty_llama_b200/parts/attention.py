@@ -13,10 +13,10 @@ from ..kernels.linear import linear
 from ..spec import PartSpec
 from .base import MIXERS, POSITIONS, KVNeed, Mixer, ParamInfo
 
-# blocks the decode kernel should have in flight on the whole GPU before more
-# splits stop paying: a few per SM of a 148-SM part
-_DECODE_TARGET_BLOCKS = 592
-_DECODE_HEADS_PER_BLOCK = 4
+# one-warp blocks the decode kernel should have on the whole GPU before more splits stop
+# paying: twice what a 148-SM part holds at three blocks per SM (its shared memory's limit)
+_DECODE_TARGET_BLOCKS = 888
+_DECODE_HEADS_PER_BLOCK = 16
 
 
 def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int) -> int:

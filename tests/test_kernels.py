@@ -92,8 +92,9 @@ def ref_attention_rows(q_rows, kv: PagedKV, s, positions, window=0, scale=None):
 
 # --------------------------------------------------------------------------- row kernels
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_embed_gather(ops, dtype):
-    table = torch.randn(300, 72).to(dtype)
+@pytest.mark.parametrize("d", [72, 70, 4096])
+def test_embed_gather(ops, dtype, d):
+    table = torch.randn(300, d).to(dtype)
     toks = torch.tensor([0, 299, 17, 17, 5], dtype=torch.int32)
     out = ops.embed_gather(toks.to(DEV), table.to(DEV))
     assert out.dtype == torch.float32
@@ -102,7 +103,7 @@ def test_embed_gather(ops, dtype):
 
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d, parts", [(200, 0), (72, 1), (4104, 3)])
+@pytest.mark.parametrize("d, parts", [(200, 0), (72, 1), (4104, 3), (201, 2)])
 def test_add_rmsnorm(ops, act, wdt, d, parts):
     T, eps = 5, 3e-6
     x = torch.randn(T, d) * 3
@@ -154,7 +155,7 @@ def test_swiglu(ops, dtype):
 # --------------------------------------------------------------------------- rotary + cache write
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("interleaved", [False, True])
-@pytest.mark.parametrize("H, K, hd, rot", [(6, 3, 40, 40), (4, 4, 24, 16), (5, 1, 128, 128)])
+@pytest.mark.parametrize("H, K, hd, rot", [(6, 3, 40, 40), (4, 4, 24, 16), (5, 1, 128, 128), (3, 1, 18, 10)])
 def test_rope_kv_write(ops, dtype, interleaved, H, K, hd, rot):
     lens = [70, 3]  # the first sequence crosses a page
     pos0 = [60, 130]  # and both start late in their sequences
@@ -233,7 +234,7 @@ def test_attn_generic_bits_do_not_depend_on_the_batch(ops):
         assert torch.equal(one[0], full[i])
 
 
-@pytest.mark.parametrize("H, K, hd", [(8, 2, 128), (6, 2, 24), (5, 1, 64), (3, 3, 256), (16, 2, 40)])
+@pytest.mark.parametrize("H, K, hd", [(8, 2, 128), (6, 2, 24), (5, 1, 64), (3, 3, 256), (16, 2, 40), (40, 2, 64)])
 @pytest.mark.parametrize("n_splits, window", [(1, 0), (3, 0), (8, 0), (2, 100)])
 def test_attn_decode(ops, H, K, hd, n_splits, window):
     lens = [1, 64, 65, 300, 128]

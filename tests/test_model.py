@@ -190,8 +190,9 @@ def test_greedy_generation_through_the_entry_point(name, dtype, llms, tiny_weigh
     assert len(llm.generate(prompts[0], steps=9, temperature=0.0, stop_token_ids=[])) == 4
     # one prompt, one list back; stop tokens end a sequence and are not returned
     first = llm.generate(prompts[1], max_new_tokens=8, temperature=0.0, stop_token_ids=[])
-    res = llm.generate(prompts[1], max_new_tokens=8, temperature=0.0, stop_token_ids=[first[3]], return_results=True)
-    assert res.tokens == first[:3] and res.finish_reason == "stop_token"
+    k = max(i for i in range(8) if first[i] not in first[:i])  # the last token that did not occur before
+    res = llm.generate(prompts[1], max_new_tokens=8, temperature=0.0, stop_token_ids=[first[k]], return_results=True)
+    assert res.tokens == first[:k] and res.finish_reason == "stop_token"
 
 
 def test_sampled_generation_follows_the_plain_sampler(llms, tiny_weights):
