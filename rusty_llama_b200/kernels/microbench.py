@@ -1,0 +1,139 @@
+"""Time one kernel of the library at a given shape, with CUDA events.
+
+    python -m rusty_llama_b200.kernels.microbench gemv --rows 8 --n 28672 --k 4096
+    python -m rusty_llama_b200.kernels.microbench attn_decode --seqs 8 --ctx 4096
+    python -m rusty_llama_b200.kernels.microbench flash_prefill --tokens 2048
+    python -m rusty_llama_b200.kernels.microbench gemm --rows 2048 --n 6144 --k 4096
+
+Each timed call works on its own copy of the large operand (weights, cache pages), and the copies
+together exceed the 126 MB L2, so the figures are HBM figures.  Prints one JSON line: microseconds
+per call, and GB/s or TFLOP/s of the bytes or flops the call has to move or do.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+from . import ops
+from .linear import linear
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _time(fn, n_variants: int, iters: int, warmup: int) -> float:
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i % n_variants)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / iters
+
+
+def _copies(nbytes: int) -> int:
+    return max(2, math.ceil(2 * L2_BYTES / max(nbytes, 1)))
+
+
+def bench_gemv(a) -> dict:
+    dev = "cuda:0"
+    wbytes = a.n * a.k * 2
+    nv = min(_copies(wbytes), 64)
+    ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
+    x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
+    us = _time(lambda i: ops.gemv_bf16(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
+    return {"kernel": "gemv_bf16", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "GBps": round(wbytes / us / 1e3, 1), "weight_copies": nv}
+
+
+def bench_gemm(a) -> dict:
+    dev = "cuda:0"
+    nv = min(_copies(a.n * a.k * 2), 16)
+    ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
+    x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
+    us = _time(lambda i: linear(x, ws[i]), nv, a.iters, a.warmup)
+    flops = 2.0 * a.rows * a.n * a.k
+    return {"kernel": "linear(bf16)", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+
+
+def _paged(seqs: int, ctx: int, K: int, hd: int, copies: int):
+    dev = "cuda:0"
+    pages_per_seq = (ctx + 63) // 64
+    n_pages = seqs * pages_per_seq
+    ks = [torch.randn(n_pages, K, 64, hd, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+    vs = [torch.randn(n_pages, K, 64, hd, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+    table = torch.randperm(n_pages, device=dev).to(torch.int32).view(seqs, pages_per_seq).contiguous()
+    return ks, vs, table
+
+
+def bench_attn_decode(a) -> dict:
+    from ..parts.attention import decode_splits
+
+    dev = "cuda:0"
+    H, K, hd = a.heads, a.kv_heads, a.head_dim
+    kv_bytes = a.seqs * a.ctx * K * hd * 2 * 2
+    nv = min(_copies(kv_bytes), 16)
+    ks, vs, table = _paged(a.seqs, a.ctx, K, hd, nv)
+    q = torch.randn(a.seqs, (H + 2 * K) * hd, device=dev, dtype=torch.bfloat16)
+    seq_len = torch.full((a.seqs,), a.ctx, dtype=torch.int32, device=dev)
+    n_splits = a.splits or decode_splits(a.seqs, H, K, a.ctx)
+    scratch = torch.empty(ops.attn_decode_scratch_floats(a.seqs, H, hd, n_splits), device=dev)
+    out = torch.empty(a.seqs, H * hd, device=dev, dtype=torch.bfloat16)
+    us = _time(lambda i: ops.attn_decode(q, ks[i], vs[i], table, seq_len, H, K, hd, n_splits, scratch, out=out), nv, a.iters, a.warmup)
+    return {"kernel": "attn_decode", "seqs": a.seqs, "ctx": a.ctx, "H": H, "K": K, "hd": hd, "splits": n_splits, "us": round(us, 2),
+            "GBps": round(kv_bytes / us / 1e3, 1)}
+
+
+def bench_flash_prefill(a) -> dict:
+    dev = "cuda:0"
+    H, K, hd, T = a.heads, a.kv_heads, a.head_dim, a.tokens
+    ks, vs, table = _paged(1, T, K, hd, 1)
+    q = torch.randn(T, (H + 2 * K) * hd, device=dev, dtype=torch.bfloat16)
+    seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    pos0 = torch.zeros(1, dtype=torch.int32, device=dev)
+    us = _time(lambda i: ops.flash_prefill(q, ks[0], vs[0], table, seq_start, pos0, T, H, K, hd), 1, a.iters, a.warmup)
+    flops = 4.0 * T * T * hd * H / 2
+    return {"kernel": "flash_prefill", "tokens": T, "H": H, "K": K, "hd": hd, "us": round(us, 2), "causal_TFLOPs": round(flops / us / 1e6, 1)}
+
+
+def bench_rows(a) -> dict:
+    dev = "cuda:0"
+    d = a.k
+    x = torch.randn(a.rows, d, device=dev)
+    delta = torch.randn(a.rows, d, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+    us = _time(lambda i: ops.add_rmsnorm(x, delta, w, 1e-5, torch.bfloat16), 1, a.iters, a.warmup)
+    return {"kernel": "add_rmsnorm", "rows": a.rows, "d": d, "us": round(us, 2)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=["gemv", "gemm", "attn_decode", "flash_prefill", "add_rmsnorm"])
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--seqs", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    a = ap.parse_args(argv)
+    fn = {"gemv": bench_gemv, "gemm": bench_gemm, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
+          "add_rmsnorm": bench_rows}[a.kernel]
+    print(json.dumps(fn(a)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
