@@ -1,0 +1,352 @@
+// bfloat16 matrix product for prompts on the 5th-generation tensor cores:
+//   out[M, N] = x[M, K] . w[N, K]^T,  32-bit accumulation in tensor memory.
+// The reference hands these products to cuBLASLt (src/backend/cuda.rs:717-758); this is the
+// library's own kernel for the same shapes (M tokens of a prompt step, N output features).
+//
+// One block computes a 128 x 256 tile.  Warp 0 (one lane) is the producer: it asks the TMA unit
+// for 64-wide k slices of the x tile (128 rows) and the w tile (256 rows), 128-byte swizzled,
+// into a ring of 4 shared-memory stages, and arms each stage's `full` mbarrier with the byte
+// count.  Warp 1 (one lane) issues tcgen05.mma (M 128, N 256, K 16, four per slice) on shared-
+// memory descriptors of the stage, accumulating in 256 columns of tensor memory, and commits each
+// slice to the stage's `empty` mbarrier, which hands the stage back to the producer when the
+// tensor core has read it.  After the last slice a commit arms `done`; warps 2..5 then read the
+// accumulator with tcgen05.ld (each warp owns 32 of the 128 lanes = rows), round to the output
+// type and store 64-byte row pieces.  Rows and columns past M, N and K are zero-filled by TMA on
+// the way in and masked on the way out, so any M and N work; K and the row strides must be
+// multiples of 8 (16-byte alignment of TMA rows).
+//
+// Every wait on an mbarrier is bounded (about one second of polling): on expiry the waiter
+// records a code in `status[0]`, the block drains, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define BM 128
+#define BN 256
+#define BK 64
+#define STAGES 4
+#define UMMA_K 16
+#define TMEM_COLS 256
+#define NUM_THREADS 192
+#define STAGE_A_BYTES (BM * BK * 2)
+#define STAGE_B_BYTES (BN * BK * 2)
+#define STAGE_BYTES (STAGE_A_BYTES + STAGE_B_BYTES)
+#define WAIT_LIMIT_NS 1000000000ull
+
+// ------------------------------------------------------------------ small PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the barrier did not flip within WAIT_LIMIT_NS.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The barrier receives one arrival when every tcgen05.mma issued before by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) and 128-byte
+// swizzled, as TMA writes it: start address, stride between 8-row groups = 1024 bytes, descriptor
+// version 1, layout type 2 (128-byte swizzle).  The leading-dimension field is not used by this layout.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor of kind::f16: D 32-bit, A and B bfloat16, both K-major, N and M of the tile.
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename TO>
+__device__ __forceinline__ void store_row32(TO* dst, const uint32_t (&r)[32], int n_valid);
+template <>
+__device__ __forceinline__ void store_row32<bf16>(bf16* dst, const uint32_t (&r)[32], int n_valid) {
+  if (n_valid >= 32) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 v;
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+      __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+      __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+      v.x = *reinterpret_cast<uint32_t*>(&p0);
+      v.y = *reinterpret_cast<uint32_t*>(&p1);
+      v.z = *reinterpret_cast<uint32_t*>(&p2);
+      v.w = *reinterpret_cast<uint32_t*>(&p3);
+      d4[i] = v;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < n_valid) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&r)[32], int n_valid) {
+  if (n_valid >= 32) {
+    float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      d4[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                          __uint_as_float(r[4 * i + 3]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < n_valid) dst[i] = __uint_as_float(r[i]);
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <typename TO>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               TO* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ status) {
+  extern __shared__ unsigned char smem_dyn[];
+  // the swizzled stages must start on a 1024-byte boundary
+  unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t done_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int n_slices = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&done_bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < n_slices; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+          atomicExch(status, 1);
+          abort_flag = 1;
+          break;
+        }
+        if (*(volatile int*)&abort_flag) break;
+        unsigned char* a_dst = stages + (size_t)s * STAGE_BYTES;
+        unsigned char* b_dst = a_dst + STAGE_A_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
+        tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
+        issued = kb + 1;
+      }
+      // nothing may still be writing shared memory when the block ends: if the consumer gave up,
+      // wait (bounded) for the copies that were started
+      if (*(volatile int*)&abort_flag) {
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- tensor-core issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < n_slices && ok; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) {
+          atomicExch(status, 2);
+          abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(stages + (size_t)s * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + STAGE_A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t a_desc = make_smem_desc(a_addr + k * UMMA_K * 2);
+          const uint64_t b_desc = make_smem_desc(b_addr + k * UMMA_K * 2);
+          umma_bf16(tmem_base, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(&done_bar);  // arrives when everything issued above has completed (also after an abort)
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, each on its quarter of the 128 lanes
+    const int quarter = warp & 3;
+    const bool ok = mbar_wait(&done_bar, 0);
+    if (!ok && lane == 0) {
+      atomicExch(status, 3);
+      abort_flag = 1;
+    }
+    tc_fence_after();
+    const bool aborted = *(volatile int*)&abort_flag != 0;
+    if (ok && !aborted) {
+      const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < M && col < N) store_row32<TO>(out + (size_t)row * ldo + col, r, N - col);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+// rows x K bfloat16 matrix with row stride ld (elements); boxes of `box_rows` rows x 64 columns, 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return 1;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+// status: one int in device memory, 0 before the call; non-zero afterwards means a bounded wait expired
+// (1 producer, 2 tensor-core issuer, 3 epilogue) and the output is not valid.
+RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                      int K, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
+  if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
+  if (ldx < K || ldw < K || ldo < N) RL_REFUSE(3, "gemm_tc: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) RL_REFUSE(4, "gemm_tc: operands must be 16-byte aligned");
+  if (out_dtype == RL_BF16 ? (ldo % 8) : (ldo % 4)) RL_REFUSE(5, "gemm_tc: output row stride %d breaks 16-byte alignment", ldo);
+  if (out_dtype != RL_BF16 && out_dtype != RL_F32) RL_REFUSE(6, "gemm_tc: unknown output dtype %d", out_dtype);
+  if (status == nullptr) RL_REFUSE(7, "gemm_tc: no status word");
+  const int gy = (N + BN - 1) / BN;
+  if (gy > 65535) RL_REFUSE(8, "gemm_tc: N=%d too large", N);
+  CUtensorMap map_x, map_w;
+  int e1 = make_map(&map_x, x, M, K, ldx, BM), e2 = make_map(&map_w, w, N, K, ldw, BN);
+  if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  dim3 grid((M + BM - 1) / BM, gy);
+  cudaError_t e;
+  if (out_dtype == RL_BF16) {
+    auto kern = gemm_tc_kernel<bf16>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (bf16*)out, ldo, M, N, K, status);
+  } else {
+    auto kern = gemm_tc_kernel<float>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (float*)out, ldo, M, N, K, status);
+  }
+  RL_LAUNCH_RESULT();
+}

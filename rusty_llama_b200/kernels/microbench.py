@@ -58,9 +58,14 @@ def bench_gemm(a) -> dict:
     nv = min(_copies(a.n * a.k * 2), 16)
     ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
     x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
-    us = _time(lambda i: linear(x, ws[i]), nv, a.iters, a.warmup)
+    if a.impl == "tc":
+        out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
+        us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
+        ops.tc_status_check()
+    else:
+        us = _time(lambda i: linear(x, ws[i]), nv, a.iters, a.warmup)
     flops = 2.0 * a.rows * a.n * a.k
-    return {"kernel": "linear(bf16)", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+    return {"kernel": "gemm_tc" if a.impl == "tc" else "linear(bf16)", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def _paged(seqs: int, ctx: int, K: int, hd: int, copies: int):
@@ -126,6 +131,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--impl", default="linear", choices=["linear", "tc"], help="gemm: the dispatching linear() or the tcgen05 kernel")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     a = ap.parse_args(argv)

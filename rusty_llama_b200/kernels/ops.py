@@ -385,6 +385,48 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     return out
 
 
+_tc_status = {}
+
+
+def _tc_status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index)
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
+def tc_status_check() -> None:
+    """Raise if a bounded wait inside a tensor-core kernel expired since the last check (synchronises)."""
+    names = {1: "the TMA producer", 2: "the tensor-core issuer", 3: "the epilogue"}
+    for word in _tc_status.values():
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise KernelError(f"gemm_tc: {names.get(code, 'a role')} gave up waiting on a barrier (code {code}); results of that step are not valid")
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory)."""
+    _cuda(x, "gemm_tc x", torch.bfloat16, contiguous=False)
+    _cuda(w, "gemm_tc w", torch.bfloat16, contiguous=False)
+    ldx, ldw = _rows(x, "gemm_tc x"), _rows(w, "gemm_tc w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, f"gemm_tc: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _cuda(out, "gemm_tc out", out_dtype, contiguous=False)
+    _need(tuple(out.shape) == (M, N), "gemm_tc: out has the wrong shape")
+    status = _tc_status_word(x.device)
+    lib = build.load("gemm_tc")
+    rc = lib.rl_gemm_tc(
+        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(_rows(out, "gemm_tc out")),
+        c_int(M), c_int(N), c_int(K), _p(status), _stream(),
+    )
+    _check(lib, rc, "gemm_tc")
+    return out
+
+
 # ------------------------------------------------------------------ sampling
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Index of the largest logit of each row, the last one among equals."""

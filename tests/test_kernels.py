@@ -348,6 +348,37 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
         close_bf16(out, ref)
 
 
+@pytest.mark.parametrize("M, N, K", [(128, 256, 64), (128, 256, 256), (200, 300, 72), (2048, 512, 4096), (65, 1000, 1000), (129, 257, 4104)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tc(ops, M, N, K, out_dtype):
+    """The tcgen05 kernel at full tiles, at ragged edges in M, N and K, and with a long K."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = bf16_round(torch.randn(M, K, generator=g))
+    w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
+    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    ref = x.double() @ w.double().T
+    if out_dtype == torch.float32:
+        close_f32(out, ref, 5e-6)
+    else:
+        close_bf16(out, ref)
+
+
+def test_gemm_tc_each_output_sees_its_own_row_and_column(ops):
+    """x = one-hot rows, w = distinct rows: out[m, n] must be w[n, pick(m)], which exposes any mix-up of
+    rows, columns, k slices or the swizzle."""
+    M, N, K = 256, 512, 320
+    pick = torch.arange(M) * 7 % K
+    x = torch.zeros(M, K)
+    x[torch.arange(M), pick] = 1.0
+    w = bf16_round(torch.randn(N, K, generator=torch.Generator().manual_seed(1)))
+    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert torch.equal(out.cpu(), w[:, pick].T.contiguous())
+
+
 def test_gemv_bf16_refuses_what_it_cannot_do(ops):
     from rusty_llama_b200.errors import KernelError
 
