@@ -163,8 +163,35 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ h, int
   }
 }
 
+// The same, four values per thread and one row per blockIdx.y (ff a multiple of 4): a prompt step
+// moves hundreds of megabytes through this kernel, so loads are wide and there is no division.
+template <typename TA>
+__global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ h, int ff) {
+  const TA* row = gu + (size_t)blockIdx.y * 2 * ff;
+  TA* out = h + (size_t)blockIdx.y * ff;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4; i < ff; i += gridDim.x * blockDim.x * 4) {
+    float g[4], u[4], o[4];
+    load4<TA>(row + i, g);
+    load4<TA>(row + ff + i, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = g[e] * (1.0f / (1.0f + expf(-g[e]))) * u[e];
+    store4<TA>(out + i, o);
+  }
+}
+
 RL_API int rl_swiglu(const void* gate_up, void* h, int act_dtype, int n_tokens, int ff, cudaStream_t stream) {
   if (n_tokens <= 0 || ff <= 0) RL_REFUSE(1, "swiglu: n_tokens=%d ff=%d", n_tokens, ff);
+  if (ff % 4 == 0 && n_tokens <= 65535) {
+    const int bx = (ff / 4 + 255) / 256;
+    dim3 grid(bx > 16 ? 16 : bx, n_tokens);
+    if (act_dtype == RL_BF16)
+      swiglu_vec_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)h, ff);
+    else if (act_dtype == RL_F32)
+      swiglu_vec_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)h, ff);
+    else
+      RL_REFUSE(2, "swiglu: unknown dtype %d", act_dtype);
+    RL_LAUNCH_RESULT();
+  }
   const long long total = (long long)n_tokens * ff;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;

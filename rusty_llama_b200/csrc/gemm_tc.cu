@@ -3,17 +3,20 @@
 // The reference hands these products to cuBLASLt (src/backend/cuda.rs:717-758); this is the
 // library's own kernel for the same shapes (M tokens of a prompt step, N output features).
 //
-// One block computes a 128 x 256 tile.  Warp 0 (one lane) is the producer: it asks the TMA unit
-// for 64-wide k slices of the x tile (128 rows) and the w tile (256 rows), 128-byte swizzled,
-// into a ring of 4 shared-memory stages, and arms each stage's `full` mbarrier with the byte
-// count.  Warp 1 (one lane) issues tcgen05.mma (M 128, N 256, K 16, four per slice) on shared-
-// memory descriptors of the stage, accumulating in 256 columns of tensor memory, and commits each
-// slice to the stage's `empty` mbarrier, which hands the stage back to the producer when the
-// tensor core has read it.  After the last slice a commit arms `done`; warps 2..5 then read the
-// accumulator with tcgen05.ld (each warp owns 32 of the 128 lanes = rows), round to the output
-// type and store 64-byte row pieces.  Rows and columns past M, N and K are zero-filled by TMA on
-// the way in and masked on the way out, so any M and N work; K and the row strides must be
-// multiples of 8 (16-byte alignment of TMA rows).
+// The kernel is persistent: one block per SM walks over 128 x 256 output tiles (tiles that share
+// a w tile are neighbours in the walk, so they run at the same time and w is fetched from HBM
+// once).  Warp 0 (one lane) is the producer: it asks the TMA unit for 64-wide k slices of the x
+// tile (128 rows) and the w tile (256 rows), 128-byte swizzled, into a ring of 4 shared-memory
+// stages, and arms each stage's `full` mbarrier with the byte count; it runs ahead across tile
+// borders.  Warp 1 (one lane) issues tcgen05.mma (M 128, N 256, K 16, four per slice) on shared-
+// memory descriptors of the stage, accumulating in one of two 256-column halves of tensor memory,
+// and commits each slice to the stage's `empty` mbarrier, which hands the stage back to the
+// producer when the tensor core has read it.  After a tile's last slice a commit arms the half's
+// `acc_full`; warps 2..5 then read that half with tcgen05.ld (each warp owns 32 of the 128 lanes
+// = rows), round to the output type, store 64-byte row pieces and release the half through
+// `acc_empty`, while the tensor core already fills the other half with the next tile.  Rows and
+// columns past M, N and K are zero-filled by TMA on the way in and masked on the way out, so any
+// M and N work; K and the row strides of x and w must be multiples of 8 (16-byte TMA rows).
 //
 // Every wait on an mbarrier is bounded (about one second of polling): on expiry the waiter
 // records a code in `status[0]`, the block drains, frees its tensor memory and returns.
@@ -28,7 +31,7 @@ RL_DEFINE_ERROR_TEXT()
 #define BK 64
 #define STAGES 4
 #define UMMA_K 16
-#define TMEM_COLS 256
+#define TMEM_COLS 512  // two accumulators of BN columns
 #define NUM_THREADS 192
 #define STAGE_A_BYTES (BM * BK * 2)
 #define STAGE_B_BYTES (BN * BK * 2)
@@ -137,10 +140,10 @@ __device__ __forceinline__ uint32_t make_idesc(int m, int n) {
 }
 
 template <typename TO>
-__device__ __forceinline__ void store_row32(TO* dst, const uint32_t (&r)[32], int n_valid);
+__device__ __forceinline__ void store_row32(TO* dst, const uint32_t (&r)[32], int n_valid, bool vec);
 template <>
-__device__ __forceinline__ void store_row32<bf16>(bf16* dst, const uint32_t (&r)[32], int n_valid) {
-  if (n_valid >= 32) {
+__device__ __forceinline__ void store_row32<bf16>(bf16* dst, const uint32_t (&r)[32], int n_valid, bool vec) {
+  if (vec && n_valid >= 32) {
     uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -162,8 +165,8 @@ __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const uint32_t (&r)
   }
 }
 template <>
-__device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&r)[32], int n_valid) {
-  if (n_valid >= 32) {
+__device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&r)[32], int n_valid, bool vec) {
+  if (vec && n_valid >= 32) {
     float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -177,21 +180,27 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
 }
 
 // ------------------------------------------------------------------ the kernel
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               TO* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ status) {
+               TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int* __restrict__ status) {
   extern __shared__ unsigned char smem_dyn[];
   // the swizzled stages must start on a 1024-byte boundary
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
-  __shared__ __align__(8) uint64_t done_bar;
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
   const int n_slices = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -199,7 +208,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&done_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -212,75 +224,107 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   if (warp == 0) {
     // ---------------- producer
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < n_slices; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = kb / STAGES;
-        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-          atomicExch(status, 1);
-          abort_flag = 1;
-          break;
+      uint32_t it = 0;  // slices requested so far, over all tiles of this block
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < n_slices; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = it / STAGES;
+          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+            atomicExch(status, 1);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          if (*(volatile int*)&abort_flag) {
+            ok = false;
+            break;
+          }
+          unsigned char* a_dst = stages + (size_t)s * STAGE_BYTES;
+          unsigned char* b_dst = a_dst + STAGE_A_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
+          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
         }
-        if (*(volatile int*)&abort_flag) break;
-        unsigned char* a_dst = stages + (size_t)s * STAGE_BYTES;
-        unsigned char* b_dst = a_dst + STAGE_A_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
-        tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
-        issued = kb + 1;
       }
-      // nothing may still be writing shared memory when the block ends: if the consumer gave up,
-      // wait (bounded) for the copies that were started
-      if (*(volatile int*)&abort_flag) {
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1);
+      // nothing may still be writing shared memory when the block ends: if someone gave up, wait
+      // (bounded) for the copies that were started and not consumed
+      if (!ok) {
+        const uint32_t first = it > STAGES ? it - STAGES : 0;
+        for (uint32_t j = first; j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
       }
     }
   } else if (warp == 1) {
     // ---------------- tensor-core issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, BN);
+      uint32_t it = 0;
       bool ok = true;
-      for (int kb = 0; kb < n_slices && ok; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) {
-          atomicExch(status, 2);
+      int local = 0;  // tiles done by this block
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t use = local >> 1;  // how often this half was used before
+        if (use > 0 && !mbar_wait(&acc_empty[acc], (use - 1) & 1)) {
+          atomicExch(status, 4);
           abort_flag = 1;
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(stages + (size_t)s * STAGE_BYTES);
-        const uint32_t b_addr = a_addr + STAGE_A_BYTES;
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < n_slices; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+            atomicExch(status, 2);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(stages + (size_t)s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + STAGE_A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t a_desc = make_smem_desc(a_addr + k * UMMA_K * 2);
-          const uint64_t b_desc = make_smem_desc(b_addr + k * UMMA_K * 2);
-          umma_bf16(tmem_base, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = make_smem_desc(a_addr + k * UMMA_K * 2);
+            const uint64_t b_desc = make_smem_desc(b_addr + k * UMMA_K * 2);
+            umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
         }
-        umma_commit(&empty_bar[s]);
+        if (ok) umma_commit(&acc_full[acc]);  // arrives when the whole tile has been accumulated
       }
-      umma_commit(&done_bar);  // arrives when everything issued above has completed (also after an abort)
     }
   } else {
     // ---------------- epilogue: warps 2..5, each on its quarter of the 128 lanes
     const int quarter = warp & 3;
-    const bool ok = mbar_wait(&done_bar, 0);
-    if (!ok && lane == 0) {
-      atomicExch(status, 3);
-      abort_flag = 1;
-    }
-    tc_fence_after();
-    const bool aborted = *(volatile int*)&abort_flag != 0;
-    if (ok && !aborted) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const bool ok = mbar_wait(&acc_full[acc], (local >> 1) & 1);
+      if (!ok) {
+        if (lane == 0) {
+          atomicExch(status, 3);
+          abort_flag = 1;
+        }
+        break;
+      }
+      if (*(volatile int*)&abort_flag) break;
+      tc_fence_after();
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
-        if (row < M && col < N) store_row32<TO>(out + (size_t)row * ldo + col, r, N - col);
+        if (row < M && col < N) store_row32<TO>(out + (size_t)row * ldo + col, r, N - col, vec_store != 0);
       }
+      // this half may be overwritten once all four warps have read it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
   }
   tc_fence_before();
@@ -319,34 +363,40 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 }
 
 // status: one int in device memory, 0 before the call; non-zero afterwards means a bounded wait expired
-// (1 producer, 2 tensor-core issuer, 3 epilogue) and the output is not valid.
+// (1 producer, 2 tensor-core issuer waiting for data, 3 epilogue, 4 tensor-core issuer waiting for the
+// epilogue) and the output is not valid.
 RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
                       int K, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
   if (ldx < K || ldw < K || ldo < N) RL_REFUSE(3, "gemm_tc: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) RL_REFUSE(4, "gemm_tc: operands must be 16-byte aligned");
-  if (out_dtype == RL_BF16 ? (ldo % 8) : (ldo % 4)) RL_REFUSE(5, "gemm_tc: output row stride %d breaks 16-byte alignment", ldo);
+  const int vec_store = (out_dtype == RL_BF16 ? (ldo % 8) : (ldo % 4)) == 0;  // else the epilogue stores element by element
   if (out_dtype != RL_BF16 && out_dtype != RL_F32) RL_REFUSE(6, "gemm_tc: unknown output dtype %d", out_dtype);
   if (status == nullptr) RL_REFUSE(7, "gemm_tc: no status word");
-  const int gy = (N + BN - 1) / BN;
-  if (gy > 65535) RL_REFUSE(8, "gemm_tc: N=%d too large", N);
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
+  }
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   CUtensorMap map_x, map_w;
   int e1 = make_map(&map_x, x, M, K, ldx, BM), e2 = make_map(&map_w, w, N, K, ldw, BN);
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-  dim3 grid((M + BM - 1) / BM, gy);
+  dim3 grid((unsigned)(tiles < n_sms ? tiles : n_sms));
   cudaError_t e;
   if (out_dtype == RL_BF16) {
     auto kern = gemm_tc_kernel<bf16>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (bf16*)out, ldo, M, N, K, status);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (bf16*)out, ldo, M, N, K, vec_store, status);
   } else {
     auto kern = gemm_tc_kernel<float>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (float*)out, ldo, M, N, K, status);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (float*)out, ldo, M, N, K, vec_store, status);
   }
   RL_LAUNCH_RESULT();
 }

@@ -397,7 +397,7 @@ def _tc_status_word(device: torch.device) -> torch.Tensor:
 
 def tc_status_check() -> None:
     """Raise if a bounded wait inside a tensor-core kernel expired since the last check (synchronises)."""
-    names = {1: "the TMA producer", 2: "the tensor-core issuer", 3: "the epilogue"}
+    names = {1: "the TMA producer", 2: "the tensor-core issuer", 3: "the epilogue", 4: "the tensor-core issuer (for a free accumulator)"}
     for word in _tc_status.values():
         code = int(word.item())
         if code:

@@ -143,9 +143,10 @@ def test_rmsnorm_of_ones_and_eps(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu(ops, dtype):
-    gu = (torch.randn(3, 200) * 4).to(dtype)
-    ref = plain_silu(gu[:, :100].double()) * gu[:, 100:].double()
+@pytest.mark.parametrize("ff", [100, 101, 14336])
+def test_swiglu(ops, dtype, ff):
+    gu = (torch.randn(3, 2 * ff) * 4).to(dtype)
+    ref = plain_silu(gu[:, :ff].double()) * gu[:, ff:].double()
     out = ops.swiglu(gu.to(DEV))
     (close_f32 if dtype == torch.float32 else close_bf16)(out, ref)
     one = torch.tensor([[1.0, 2.0]], device=DEV)
@@ -348,7 +349,11 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
         close_bf16(out, ref)
 
 
-@pytest.mark.parametrize("M, N, K", [(128, 256, 64), (128, 256, 256), (200, 300, 72), (2048, 512, 4096), (65, 1000, 1000), (129, 257, 4104)])
+@pytest.mark.parametrize(
+    "M, N, K",
+    [(128, 256, 64), (128, 256, 256), (200, 300, 72), (2048, 512, 4096), (65, 1000, 1000), (129, 257, 4104),
+     (640, 17920, 128), (1280, 25600, 64)],  # the last two give every block several tiles: both accumulators, many rounds
+)
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tc(ops, M, N, K, out_dtype):
     """The tcgen05 kernel at full tiles, at ragged edges in M, N and K, and with a long K."""
