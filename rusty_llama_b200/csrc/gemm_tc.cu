@@ -179,12 +179,33 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
   }
 }
 
+// 32 accumulator columns that alternate gate and up -> 16 values silu(gate) * up
+template <typename TO>
+__device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32], int n_valid, bool vec) {
+  float h[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
+    h[i] = g * (1.0f / (1.0f + expf(-g))) * u;
+  }
+  if (vec && n_valid >= 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) store4<TO>(dst + 4 * i, h + 4 * i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n_valid) dst[i] = from_f32<TO>(h[i]);
+  }
+}
+
 // ------------------------------------------------------------------ the kernel
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <typename TO>
+// SWIGLU: w's rows alternate gate and up (row 2i gate i, row 2i+1 up i); the epilogue writes
+// h[m, i] = silu(gate) * up from the 32-bit accumulators, N / 2 columns per row.
+template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int* __restrict__ status) {
@@ -319,7 +340,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
-        if (row < M && col < N) store_row32<TO>(out + (size_t)row * ldo + col, r, N - col, vec_store != 0);
+        if (row < M && col < N) {
+          if (SWIGLU)
+            store_swiglu16<TO>(out + (size_t)row * ldo + (col >> 1), r, (N - col) >> 1, vec_store != 0);
+          else
+            store_row32<TO>(out + (size_t)row * ldo + col, r, N - col, vec_store != 0);
+        }
       }
       // this half may be overwritten once all four warps have read it
       tc_fence_before();
@@ -365,11 +391,13 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 // status: one int in device memory, 0 before the call; non-zero afterwards means a bounded wait expired
 // (1 producer, 2 tensor-core issuer waiting for data, 3 epilogue, 4 tensor-core issuer waiting for the
 // epilogue) and the output is not valid.
+// swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel).
 RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                      int K, int* status, cudaStream_t stream) {
+                      int K, int swiglu, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
-  if (ldx < K || ldw < K || ldo < N) RL_REFUSE(3, "gemm_tc: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
+  if (swiglu && (N & 1)) RL_REFUSE(11, "gemm_tc: %d gate/up rows are not pairs", N);
+  if (ldx < K || ldw < K || ldo < (swiglu ? N / 2 : N)) RL_REFUSE(3, "gemm_tc: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) RL_REFUSE(4, "gemm_tc: operands must be 16-byte aligned");
   const int vec_store = (out_dtype == RL_BF16 ? (ldo % 8) : (ldo % 4)) == 0;  // else the epilogue stores element by element
   if (out_dtype != RL_BF16 && out_dtype != RL_F32) RL_REFUSE(6, "gemm_tc: unknown output dtype %d", out_dtype);
@@ -386,17 +414,17 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
   dim3 grid((unsigned)(tiles < n_sms ? tiles : n_sms));
-  cudaError_t e;
-  if (out_dtype == RL_BF16) {
-    auto kern = gemm_tc_kernel<bf16>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (bf16*)out, ldo, M, N, K, vec_store, status);
-  } else {
-    auto kern = gemm_tc_kernel<float>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);
-    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (float*)out, ldo, M, N, K, vec_store, status);
-  }
+#define RL_TC_LAUNCH(TOUT, SW)                                                                                      \
+  do {                                                                                                            \
+    auto kern = gemm_tc_kernel<TOUT, SW>;                                                                         \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
+      RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
+    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store, status);         \
+  } while (0)
+  if (out_dtype == RL_BF16 && swiglu) RL_TC_LAUNCH(bf16, true);
+  else if (out_dtype == RL_BF16) RL_TC_LAUNCH(bf16, false);
+  else if (swiglu) RL_TC_LAUNCH(float, true);
+  else RL_TC_LAUNCH(float, false);
+#undef RL_TC_LAUNCH
   RL_LAUNCH_RESULT();
 }

@@ -42,7 +42,9 @@ __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <int NT, typename TO>
+// SWIGLU: the weight rows alternate gate and up (row 2i is gate i, row 2i+1 is up i) and the
+// kernel writes h[m, i] = silu(gate) * up, N / 2 values per row, from the 32-bit sums.
+template <int NT, typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, int ldw, TO* __restrict__ out,
                  int ldo, int M, int N, int K) {
@@ -60,9 +62,10 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
   const int n_blocks = (K + 31) / 32;
-  // U k blocks of weights are requested before the first is used, so that each
-  // lane keeps 2 * U 16-byte loads in flight.
-  constexpr int U = 4;
+  // U k blocks of weights are requested before the first is used, so that each lane keeps
+  // 2 * U 16-byte loads in flight: with few rows the kernel waits on memory latency, and what
+  // is in flight per SM is what sets its bandwidth.
+  constexpr int U = NT <= 2 ? 8 : 4;
   for (int kb = warp; kb < n_blocks; kb += WARPS * U) {
     uint4 a0[U], a1[U];
 #pragma unroll
@@ -95,41 +98,66 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
 #pragma unroll
     for (int c = 0; c < 4; ++c) red[warp][nt * 128 + lane * 4 + c] = acc[nt][c];
   __syncthreads();
-  for (int e = tid; e < NT * 128; e += WARPS * 32) {
-    float sum = 0.f;
+  if (SWIGLU) {
+    // 8 (gate, up) pairs of features x NT * 8 batch rows
+    for (int e = tid; e < NT * 64; e += WARPS * 32) {
+      const int pr = e & 7, m = e >> 3;
+      const int nt = m >> 3, t = (m & 7) >> 1, c_lo = m & 1;
+      const int ng = 2 * pr, nu = 2 * pr + 1;  // feature index inside the block's 16
+      const int ig = nt * 128 + ((ng & 7) * 4 + t) * 4 + (ng >> 3) * 2 + c_lo;
+      const int iu = nt * 128 + ((nu & 7) * 4 + t) * 4 + (nu >> 3) * 2 + c_lo;
+      float gsum = 0.f, usum = 0.f;
 #pragma unroll
-    for (int wq = 0; wq < WARPS; ++wq) sum += red[wq][e];
-    const int nt = e >> 7, l = (e & 127) >> 2, c = e & 3;
-    const int n = n0 + (l >> 2) + 8 * (c >> 1);
-    const int m = nt * 8 + 2 * (l & 3) + (c & 1);
-    if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, sum);
+      for (int wq = 0; wq < WARPS; ++wq) {
+        gsum += red[wq][ig];
+        usum += red[wq][iu];
+      }
+      const int col = (n0 >> 1) + pr;
+      if (col < (N >> 1) && m < M) store_out<TO>(out + (size_t)m * ldo + col, gsum * (1.0f / (1.0f + expf(-gsum))) * usum);
+    }
+  } else {
+    for (int e = tid; e < NT * 128; e += WARPS * 32) {
+      float sum = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; ++wq) sum += red[wq][e];
+      const int nt = e >> 7, l = (e & 127) >> 2, c = e & 3;
+      const int n = n0 + (l >> 2) + 8 * (c >> 1);
+      const int m = nt * 8 + 2 * (l & 3) + (c & 1);
+      if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, sum);
+    }
   }
 }
 
 template <int NT>
 static int launch_gemv(const bf16* x, int ldx, const bf16* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                       int N, int K, cudaStream_t stream) {
+                       int N, int K, int swiglu, cudaStream_t stream) {
   const int blocks = (N + 15) / 16;
-  if (out_dtype == RL_F32)
-    gemv_bf16_kernel<NT, float><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (float*)out, ldo, M, N, K);
+  if (swiglu && out_dtype == RL_F32)
+    gemv_bf16_kernel<NT, float, true><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (float*)out, ldo, M, N, K);
+  else if (swiglu)
+    gemv_bf16_kernel<NT, bf16, true><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (bf16*)out, ldo, M, N, K);
+  else if (out_dtype == RL_F32)
+    gemv_bf16_kernel<NT, float, false><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (float*)out, ldo, M, N, K);
   else
-    gemv_bf16_kernel<NT, bf16><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (bf16*)out, ldo, M, N, K);
+    gemv_bf16_kernel<NT, bf16, false><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (bf16*)out, ldo, M, N, K);
   RL_LAUNCH_RESULT();
 }
 
 RL_API int rl_gemv_bf16_max_rows() { return 64; }
 
+// swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel).
 RL_API int rl_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                        int N, int K, cudaStream_t stream) {
+                        int N, int K, int swiglu, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_bf16: M=%d N=%d K=%d", M, N, K);
   if (M > 64) RL_REFUSE(2, "gemv_bf16: %d rows, this kernel takes at most 64", M);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_bf16: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte loads)", K, ldx, ldw);
-  if (ldx < K || ldw < K || ldo < N) RL_REFUSE(4, "gemv_bf16: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
+  if (swiglu && (N & 1)) RL_REFUSE(6, "gemv_bf16: %d gate/up rows are not pairs", N);
+  if (ldx < K || ldw < K || ldo < (swiglu ? N / 2 : N)) RL_REFUSE(4, "gemv_bf16: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) RL_REFUSE(5, "gemv_bf16: unknown output dtype %d", out_dtype);
   const bf16* xx = (const bf16*)x;
   const bf16* ww = (const bf16*)w;
-  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
-  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
-  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
-  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, stream);
+  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
+  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
+  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
+  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
 }

@@ -153,6 +153,10 @@ class Engine:
     def close_sequence(self, slot: int) -> None:
         self.cache.close_sequence(slot)
 
+    def check_device_status(self) -> None:
+        """Raise if a kernel with bounded waits gave up since the last check.  Synchronises the device."""
+        ops.tc_status_check()
+
     # ------------------------------------------------------------------ the step
     def _validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:

@@ -141,6 +141,9 @@ def generate(
             while running:
                 tokens = sampler.sample(logits, [s.slot for s in running], params).tolist()
                 if first:
+                    check = getattr(engine, "check_device_status", None)
+                    if check is not None:
+                        check()  # the prompt step's kernels have finished: did any of them give up?
                     stats.prefill_seconds += time.perf_counter() - t0
                     t0 = time.perf_counter()
                     first = False

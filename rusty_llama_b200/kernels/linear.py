@@ -1,10 +1,10 @@
 """y = x . W^T for the model's projections, chosen by precision and row count.
 
-float32 runs use the library's own 32-bit kernel for every shape.  bfloat16
-runs use the library's weight-streaming kernel for up to 64 rows (a decode
-step) and, above that, the vendor GEMM through torch.matmul: the reference does
-the same split, its own GEMV kernels for decode and cuBLASLt for prompts
-(src/backend/cuda.rs:717-758, :354-442).
+float32 runs use the library's own 32-bit FMA kernel for every shape.  bfloat16 runs use the
+weight-streaming kernel for up to 64 rows (a decode step) and the TMA + tcgen05 kernel above that
+(a prompt step).  The reference makes the same split, its own GEMV kernels for decode and a
+cuBLASLt call for prompts (src/backend/cuda.rs:354-442, :717-758); `use_library_gemm(True)` puts the
+vendor GEMM (torch.matmul) in the place of the tcgen05 kernel, for comparisons only.
 """
 
 from __future__ import annotations
@@ -15,6 +15,14 @@ import torch
 
 from ..errors import KernelError
 from . import ops
+
+_library_gemm = False
+
+
+def use_library_gemm(on: bool) -> None:
+    """Route bfloat16 products of more than 64 rows through torch.matmul instead of `gemm_tc`."""
+    global _library_gemm
+    _library_gemm = bool(on)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -30,14 +38,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     M = x.shape[0]
     if M <= ops.GEMV_MAX_ROWS:
         return ops.gemv_bf16(x, w, out_dtype)
-    if out_dtype == torch.bfloat16:
-        if not x.is_cuda:
-            raise KernelError("linear: tensors must be on a CUDA device")
+    if _library_gemm and out_dtype == torch.bfloat16 and x.is_cuda:
         return torch.matmul(x, w.t())
-    # float32 results of many rows (logits of every position of a prompt): keep the
-    # 32-bit accumulator's value by going through the streaming kernel in groups of rows
-    out = torch.empty((M, w.shape[0]), dtype=out_dtype, device=x.device)
-    for r0 in range(0, M, ops.GEMV_MAX_ROWS):
-        r1 = min(M, r0 + ops.GEMV_MAX_ROWS)
-        ops.gemv_bf16(x[r0:r1], w, out_dtype, out=out[r0:r1])
-    return out
+    return ops.gemm_tc(x, w, out_dtype)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """h[M, ff] = silu(x . Wg^T) * (x . Wu^T) in one kernel, for bfloat16.
+
+    w_gate_up[2 ff, K] holds the rows of Wg and Wu alternately (row 2i is gate i, row 2i + 1 is up i);
+    the product's 32-bit sums go through the activation before anything is rounded or stored."""
+    if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
+        raise KernelError(f"linear_swiglu: bfloat16 only, got {x.dtype} x {w_gate_up.dtype}")
+    if x.shape[0] <= ops.GEMV_MAX_ROWS:
+        return ops.gemv_bf16(x, w_gate_up, torch.bfloat16, swiglu=True)
+    return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True)

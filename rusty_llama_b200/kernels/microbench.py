@@ -25,15 +25,31 @@ from .linear import linear
 L2_BYTES = 126 * 1024 * 1024
 
 
+USE_GRAPH = True
+
+
 def _time(fn, n_variants: int, iters: int, warmup: int) -> float:
+    """Microseconds per call.  The timed calls are captured into one CUDA graph and replayed, so that
+    short kernels are not measured by how fast Python can launch them."""
     for i in range(warmup):
         fn(i % n_variants)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        fn(i % n_variants)
-    e1.record()
+    if USE_GRAPH:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(i % n_variants)
+        graph.replay()  # once untimed
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            fn(i % n_variants)
+        e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1000.0 / iters
 
@@ -134,7 +150,10 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="linear", choices=["linear", "tc"], help="gemm: the dispatching linear() or the tcgen05 kernel")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed calls one by one instead of as one graph")
     a = ap.parse_args(argv)
+    global USE_GRAPH
+    USE_GRAPH = not a.no_graph
     fn = {"gemv": bench_gemv, "gemm": bench_gemm, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
           "add_rmsnorm": bench_rows}[a.kernel]
     print(json.dumps(fn(a)))

@@ -363,8 +363,13 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
     return out
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 rows, bfloat16 in, 32-bit accumulate."""
+def gemv_bf16(
+    x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
+    swiglu: bool = False,
+) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 rows, bfloat16 in, 32-bit accumulate.
+
+    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums."""
     _cuda(x, "gemv_bf16 x", torch.bfloat16, contiguous=False)
     _cuda(w, "gemv_bf16 w", torch.bfloat16, contiguous=False)
     ldx, ldw = _rows(x, "gemv_bf16 x"), _rows(w, "gemv_bf16 w")
@@ -372,14 +377,15 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     N = w.shape[0]
     _need(w.shape[1] == K, f"gemv_bf16: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
     _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemv_bf16: operands must be 16-byte aligned")
+    n_out = N // 2 if swiglu else N
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _cuda(out, "gemv_bf16 out", out_dtype, contiguous=False)
-    _need(tuple(out.shape) == (M, N), "gemv_bf16: out has the wrong shape")
+    _need(tuple(out.shape) == (M, n_out), "gemv_bf16: out has the wrong shape")
     lib = build.load("gemv_bf16")
     rc = lib.rl_gemv_bf16(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_bf16 out")), c_int(_rows(out, "gemv_bf16 out")),
-        c_int(M), c_int(N), c_int(K), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream(),
     )
     _check(lib, rc, "gemv_bf16")
     return out
@@ -405,23 +411,29 @@ def tc_status_check() -> None:
             raise KernelError(f"gemm_tc: {names.get(code, 'a role')} gave up waiting on a barrier (code {code}); results of that step are not valid")
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory)."""
+def gemm_tc(
+    x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
+    swiglu: bool = False,
+) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+
+    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit accumulators."""
     _cuda(x, "gemm_tc x", torch.bfloat16, contiguous=False)
     _cuda(w, "gemm_tc w", torch.bfloat16, contiguous=False)
     ldx, ldw = _rows(x, "gemm_tc x"), _rows(w, "gemm_tc w")
     M, K = x.shape
     N = w.shape[0]
     _need(w.shape[1] == K, f"gemm_tc: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
+    n_out = N // 2 if swiglu else N
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     _cuda(out, "gemm_tc out", out_dtype, contiguous=False)
-    _need(tuple(out.shape) == (M, N), "gemm_tc: out has the wrong shape")
+    _need(tuple(out.shape) == (M, n_out), "gemm_tc: out has the wrong shape")
     status = _tc_status_word(x.device)
     lib = build.load("gemm_tc")
     rc = lib.rl_gemm_tc(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(_rows(out, "gemm_tc out")),
-        c_int(M), c_int(N), c_int(K), _p(status), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _p(status), _stream(),
     )
     _check(lib, rc, "gemm_tc")
     return out

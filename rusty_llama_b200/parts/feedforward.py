@@ -8,7 +8,7 @@ import torch
 
 from ..errors import ConfigError
 from ..kernels import ops
-from ..kernels.linear import linear
+from ..kernels.linear import linear, linear_swiglu
 from .base import FEED_FORWARDS, FeedForward, ParamInfo
 
 
@@ -19,8 +19,11 @@ class GatedMLP(FeedForward):
 
     params: hidden_size, intermediate_size, activation ("silu").
     tensors: <prefix>gate_proj.weight [ff, d], up_proj.weight [ff, d], down_proj.weight [d, ff].
-    gate and up are kept as one [2 ff, d] matrix so that one product serves both,
-    the counterpart of the reference's `matmul_shared` (src/backend/mod.rs:44-56)."""
+    gate and up are kept as one [2 ff, d] matrix so that one product serves both, the
+    counterpart of the reference's `matmul_shared` (src/backend/mod.rs:44-56).  In bfloat16 their
+    rows alternate (gate i, up i, gate i+1, ...), which lets the product's kernel apply the
+    activation to its 32-bit sums and write h directly; in 32-bit the halves follow each other
+    and a separate kernel applies the activation."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -41,10 +44,17 @@ class GatedMLP(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], dim=0).contiguous()
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        self.fused = self.rt.dtype == torch.bfloat16
+        if self.fused:
+            self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * self.ff, self.d).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"].contiguous()
 
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
-        gate_up = linear(xn, self.w_gate_up)
-        h = ops.swiglu(gate_up)
+        if self.fused:
+            h = linear_swiglu(xn, self.w_gate_up)
+        else:
+            h = ops.swiglu(linear(xn, self.w_gate_up))
         return linear(h, self.w_down)

@@ -57,6 +57,7 @@ def main(argv=None) -> int:
             logits = llm.step(entries)
             if logits.shape[0] > 0:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+                llm.engine.check_device_status()
                 tmp = os.path.join(args.out, f"{step_id}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(args.out, f"{step_id}.f32"))

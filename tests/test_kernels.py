@@ -34,6 +34,19 @@ def close_f32(got, ref, rel=2e-5):
     assert err <= tol, f"max error {err:.3e} exceeds {tol:.3e}"
 
 
+def close_dot_f32(got, x, w):
+    """32-bit results of K-term inner products accumulated in 32-bit: the rounding of a running sum
+    grows like sqrt(K) units in the last place of the sum of the terms' magnitudes (a random walk of
+    K roundings), whatever order the hardware adds in."""
+    ref = x.double() @ w.double().T
+    mags = x.abs().double() @ w.abs().double().T
+    K = x.shape[1]
+    tol = math.sqrt(K) * 2.0 ** -24 * mags + 1e-7
+    err = (got.detach().cpu().double() - ref).abs()
+    worst = float((err / tol).max())
+    assert worst <= 1.0, f"error reaches {worst:.2f} of sqrt(K) ulp of the summed magnitudes (K={K})"
+
+
 def close_bf16(got, ref):
     """bfloat16 keeps 8 bits: an element may be off by 2^-8 of its own size from the final rounding,
     plus what rounding the operands of an inner product adds, which scales with the result's range."""
@@ -342,11 +355,10 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
     x = bf16_round(torch.randn(M, K))
     w = bf16_round(torch.randn(N, K) * 0.05)
     out = ops.gemv_bf16(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
-    ref = x.double() @ w.double().T
     if out_dtype == torch.float32:
-        close_f32(out, ref, 5e-6)
+        close_dot_f32(out, x, w)
     else:
-        close_bf16(out, ref)
+        close_bf16(out, x.double() @ w.double().T)
 
 
 @pytest.mark.parametrize(
@@ -363,11 +375,10 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
     out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
     torch.cuda.synchronize()
     ops.tc_status_check()
-    ref = x.double() @ w.double().T
     if out_dtype == torch.float32:
-        close_f32(out, ref, 5e-6)
+        close_dot_f32(out, x, w)
     else:
-        close_bf16(out, ref)
+        close_bf16(out, x.double() @ w.double().T)
 
 
 def test_gemm_tc_each_output_sees_its_own_row_and_column(ops):
@@ -382,6 +393,26 @@ def test_gemm_tc_each_output_sees_its_own_row_and_column(ops):
     torch.cuda.synchronize()
     ops.tc_status_check()
     assert torch.equal(out.cpu(), w[:, pick].T.contiguous())
+
+
+@pytest.mark.parametrize("M", [1, 8, 40, 64, 65, 300])
+@pytest.mark.parametrize("ff, K", [(100, 72), (1432, 512)])
+def test_fused_gate_up_swiglu(ops, M, ff, K):
+    """silu(x Wg^T) * (x Wu^T) from one kernel over row-interleaved weights, for decode-sized and
+    prompt-sized M (the streaming kernel and the tcgen05 kernel)."""
+    from rusty_llama_b200.kernels.linear import linear_swiglu
+
+    g = torch.Generator().manual_seed(M + ff)
+    x = bf16_round(torch.randn(M, K, generator=g))
+    wg = bf16_round(torch.randn(ff, K, generator=g) * 0.1)
+    wu = bf16_round(torch.randn(ff, K, generator=g) * 0.1)
+    w = torch.stack([wg, wu], dim=1).reshape(2 * ff, K)
+    out = linear_swiglu(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV))
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert out.shape == (M, ff)
+    ref = plain_silu(x.double() @ wg.double().T) * (x.double() @ wu.double().T)
+    close_bf16(out, ref)
 
 
 def test_gemv_bf16_refuses_what_it_cannot_do(ops):

@@ -99,6 +99,10 @@ def test_run_types_of_loaded_tensors(tiny_weights):
     m = _cpu_model(TINY_B, "bfloat16")
     load_tensors(m, tiny_weights["B"])  # stored bfloat16
     assert m.final_norm.weight.dtype == torch.bfloat16 and m.blocks[2].feed_forward.w_gate_up.shape == (768, 144)
+    # bfloat16 runs keep gate and up rows alternating for the fused kernel
+    gu = m.blocks[2].feed_forward.w_gate_up
+    assert torch.equal(gu[0::2], tiny_weights["B"]["model.layers.2.mlp.gate_proj.weight"])
+    assert torch.equal(gu[1::2], tiny_weights["B"]["model.layers.2.mlp.up_proj.weight"])
     # a 32-bit run widens everything exactly
     m = _cpu_model(TINY_B, "float32")
     load_tensors(m, tiny_weights["B"])
