@@ -326,3 +326,43 @@ RL_API int rl_attn_decode(const void* q, int dtype, int q_stride, const void* k_
 #undef RL_DECODE
   RL_REFUSE(10, "attn_decode: head size %d exceeds 256", hd);
 }
+
+// ------------------------------------------------------------------ the same, with built-in scratch
+// See attention_decode_static.h for what this is for and what its limits are.
+#include "attention_decode_static.h"
+
+// The split partials of rl_attn_decode_static live here.  In host code this name is only a handle
+// for the runtime: the address a kernel can use is asked for with cudaGetSymbolAddress below.
+static __device__ __align__(256) float rl_static_scratch[RL_ATTN_DECODE_STATIC_FLOATS];
+
+#define RL_STATIC_MAX_DEVICES 64
+static float* rl_static_scratch_addr[RL_STATIC_MAX_DEVICES] = {nullptr};
+
+RL_API int rl_attn_decode_static(const void* q, int dtype, int q_stride, const void* k_pages, const void* v_pages,
+                                 const int* block_table, int table_width, const int* seq_len, void* out,
+                                 int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
+                                 float scale, int n_splits, cudaStream_t stream) {
+  if (n_seqs <= 0 || H <= 0 || hd <= 0 || n_splits <= 0)
+    RL_REFUSE(1, "attn_decode_static: S=%d H=%d hd=%d splits=%d", n_seqs, H, hd, n_splits);
+  const unsigned long long need = (unsigned long long)n_seqs * H * n_splits * (hd + 2);
+  if (need > RL_ATTN_DECODE_STATIC_FLOATS)
+    RL_REFUSE(11, "attn_decode_static: %d sequences x %d heads x %d splits x (%d + 2) = %llu floats of scratch, "
+              "the built-in array holds %u; use fewer splits or rl_attn_decode with scratch of your own",
+              n_seqs, H, n_splits, hd, need, (unsigned)RL_ATTN_DECODE_STATIC_FLOATS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= RL_STATIC_MAX_DEVICES)
+    RL_REFUSE(12, "attn_decode_static: cannot tell the current device (%s)", cudaGetErrorString(e));
+  if (rl_static_scratch_addr[dev] == nullptr) {
+    // once per device, with that device current: the array's address on this GPU
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, rl_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      RL_REFUSE(13, "attn_decode_static: cudaGetSymbolAddress failed on device %d (%s)", dev, cudaGetErrorString(e));
+    rl_static_scratch_addr[dev] = p;
+  }
+  float* part_o = rl_static_scratch_addr[dev];
+  float* part_ml = part_o + (size_t)n_seqs * H * n_splits * hd;
+  return rl_attn_decode(q, dtype, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml, out,
+                        out_stride, n_seqs, H, K, hd, page_size, window, scale, n_splits, stream);
+}
