@@ -4,12 +4,15 @@
 // reference runs its one scalar kernel with a single row here (src/backend/cuda.rs:1189-1192),
 // one block per query head, which reads every key `group size` times.
 //
-// Kernel 1 (grid: splits x (kv heads * groups of 16 query heads) x sequences, one warp each):
-// the query heads of the group are the rows of a 16-row tile (unused rows are zero), so that
-// Q K^T and P V run on the tensor cores (mma.sync m16n8k16, 32-bit accumulate) exactly as in the
-// prompt kernel; a key tile is one cache page of 64 positions, copied to shared memory with
-// cp.async while the previous one is in use; max, sum and rescaling of the online softmax stay
-// in 32-bit registers.  Each warp writes its partial (max, sum, unnormalised output) to scratch.
+// Kernel 1 (grid: splits x (kv heads * groups of 8 query heads) x sequences, one warp each).
+// A decode step has few queries and many keys, so the keys are the rows of the tensor-core
+// tiles: S^T[32 keys x 8 heads] = K_tile . Q^T and O^T[head size x 8 heads] += V_tile^T . P^T
+// (mma.sync m16n8k16, bfloat16 in, 32-bit accumulate).  The probabilities leave the first product
+// as accumulator fragments indexed (key, head) and enter the second as B fragments indexed
+// (head, key); `movmatrix` transposes them inside the warp.  A tile is half a cache page (32
+// positions), copied to shared memory with cp.async three tiles deep; max, sum and rescaling of
+// the online softmax are per head (per column) in 32-bit registers.  Each warp writes its partial
+// (max as a base-2 exponent, sum, unnormalised output) to scratch.
 // Kernel 2 (grid: query heads x sequences) merges the splits in split order.
 //
 // Scratch layout: part_o[seq][head][split][hd] floats, part_ml[seq][head][split][2].
@@ -18,8 +21,10 @@
 
 RL_DEFINE_ERROR_TEXT()
 
-#define ROWS 16   // query heads per warp tile
-#define BN 64     // keys per tile = page size
+#define HEADS 8    // query heads per warp (the N of the MMA)
+#define PAGE 64    // positions per cache page
+#define BK 32      // keys per tile
+#define STAGES 3   // tiles in shared memory
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -41,6 +46,12 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(a));
 }
+// 8x8 matrix of 16-bit values held one 32-bit register per lane (row lane/4, columns 2*(lane%4), +1): its transpose
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+  return r;
+}
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -52,13 +63,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copy a page tile [BN][hd] (contiguous) into rows of `stride` elements, by one warp.
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* src, int hd, int stride, int lane) {
-  const int chunks_per_row = hd >> 3;
-  const int total = BN * chunks_per_row;
+// Copy BK rows of hd values (contiguous in global memory) into rows of `stride` elements, by one warp.
+__device__ __forceinline__ void load_rows(bf16* dst, const bf16* src, int hd, int stride, int lane) {
+  const int cpr = hd >> 3;  // 16-byte pieces per row
+  const int total = BK * cpr;
+  int r = lane / cpr, cc = lane - r * cpr;
+  const int dr = 32 / cpr, dc = 32 - dr * cpr;
   for (int c = lane; c < total; c += 32) {
-    const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
     cp_async_16(dst + (size_t)r * stride + cc * 8, src + (size_t)r * hd + cc * 8);
+    r += dr;
+    cc += dc;
+    if (cc >= cpr) {
+      cc -= cpr;
+      ++r;
+    }
   }
 }
 
@@ -69,21 +87,20 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          const int* __restrict__ seq_len, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int H, int K, int hd, int window, float scale_log2,
                          int n_splits) {
-  constexpr int STRIDE = HD + 8;
+  constexpr int STRIDE = HD + 8;  // 16 bytes of padding per row keep ldmatrix free of bank conflicts
   constexpr int KSTEPS = HD / 16;
+  constexpr int DTILES = HD / 16;
+  constexpr int TILE_ELEMS = BK * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [ROWS][STRIDE]
-  bf16* k_s0 = q_s + ROWS * STRIDE;               // two stages of K and V, [BN][STRIDE] each
-  bf16* v_s0 = k_s0 + BN * STRIDE;
-  bf16* k_s1 = v_s0 + BN * STRIDE;
-  bf16* v_s1 = k_s1 + BN * STRIDE;
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [HEADS][STRIDE]
+  bf16* kv_s = q_s + HEADS * STRIDE;              // STAGES x (K tile, V tile), [BK][STRIDE] each
 
   const int G = H / K;
-  const int groups_per_kv = (G + ROWS - 1) / ROWS;
+  const int groups_per_kv = (G + HEADS - 1) / HEADS;
   const int split = blockIdx.x;
   const int kh = blockIdx.y / groups_per_kv;
-  const int g0 = (blockIdx.y - kh * groups_per_kv) * ROWS;
-  const int n_heads = min(ROWS, G - g0);
+  const int g0 = (blockIdx.y - kh * groups_per_kv) * HEADS;
+  const int n_heads = min(HEADS, G - g0);
   const int h0 = kh * G + g0;
   const int s = blockIdx.z;
   const int lane = threadIdx.x;
@@ -92,158 +109,166 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   const int kv_len = seq_len[s];
   const int pos = kv_len - 1;
   const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
-  const int tile_lo = first / BN, tile_hi = pos / BN;  // inclusive
+  const int tile_lo = first / BK, tile_hi = pos / BK;  // inclusive, in tiles of BK keys
   const int n_tiles = tile_hi - tile_lo + 1;
   const int per_split = (n_tiles + n_splits - 1) / n_splits;
   const int my_lo = tile_lo + split * per_split;
   const int my_hi = min(my_lo + per_split - 1, tile_hi);
 
-  float o_acc[HD / 8][4];
+  float o_acc[DTILES][4];  // (dim dt*16 + g [+8], head 2*t4 [+1])
 #pragma unroll
-  for (int i = 0; i < HD / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.f, 0.f};
+  for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // heads 2*t4, 2*t4+1
+  float l_run[2] = {0.f, 0.f};              // per-thread partial sums over this thread's keys
 
   if (my_lo <= my_hi) {
-    // zero the padding (columns past hd, rows past the group's heads), then fetch Q and the first tile
+    // zero the padding (columns past hd, rows past the group's heads) once
     {
       uint4 z = make_uint4(0, 0, 0, 0);
       uint4* p = reinterpret_cast<uint4*>(smem_raw);
-      const int n16 = ((ROWS + 4 * BN) * STRIDE * (int)sizeof(bf16)) / 16;
+      const int n16 = ((HEADS + 2 * STAGES * BK) * STRIDE * (int)sizeof(bf16)) / 16;
       for (int i = lane; i < n16; i += 32) p[i] = z;
     }
     __syncwarp();
     {
-      const int chunks_per_row = hd >> 3;
-      for (int c = lane; c < n_heads * chunks_per_row; c += 32) {
-        const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
+      const int cpr = hd >> 3;
+      for (int c = lane; c < n_heads * cpr; c += 32) {
+        const int r = c / cpr, cc = c - r * cpr;
         cp_async_16(q_s + (size_t)r * STRIDE + cc * 8, q + (size_t)s * q_stride + (size_t)(h0 + r) * hd + cc * 8);
       }
     }
-    const int* table = block_table + (size_t)s * table_width;
-    {
-      const size_t base = ((size_t)table[my_lo] * K + kh) * BN * hd;
-      load_kv_tile(k_s0, k_pages + base, hd, STRIDE, lane);
-      load_kv_tile(v_s0, v_pages + base, hd, STRIDE, lane);
-    }
     cp_async_commit();
+    const int* table = block_table + (size_t)s * table_width;
+    auto fetch = [&](int tile) {
+      if (tile <= my_hi) {
+        const int stage = (tile - my_lo) % STAGES;
+        const size_t base = (((size_t)table[tile >> 1] * K + kh) * PAGE + (tile & 1) * BK) * hd;
+        load_rows(kv_s + (size_t)(2 * stage) * TILE_ELEMS, k_pages + base, hd, STRIDE, lane);
+        load_rows(kv_s + (size_t)(2 * stage + 1) * TILE_ELEMS, v_pages + base, hd, STRIDE, lane);
+      }
+      cp_async_commit();  // also when there was nothing to fetch: the group count stays uniform
+    };
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) fetch(my_lo + i);
+    cp_async_wait<STAGES - 1>();  // the queries have arrived
+    __syncwarp();
+    uint32_t qf[KSTEPS][2];  // Q^T as B fragments: (dims kk*16 + 2*t4 [+8], head g)
+#pragma unroll
+    for (int k2 = 0; k2 < KSTEPS / 2; ++k2) {
+      uint32_t r[4];
+      ldmatrix_x4(r, q_s + (size_t)(lane & 7) * STRIDE + k2 * 32 + 8 * (lane >> 3));
+      qf[2 * k2][0] = r[0];
+      qf[2 * k2][1] = r[1];
+      qf[2 * k2 + 1][0] = r[2];
+      qf[2 * k2 + 1][1] = r[3];
+    }
 
     for (int tile = my_lo; tile <= my_hi; ++tile) {
-      const int buf = (tile - my_lo) & 1;
-      bf16* k_s = buf ? k_s1 : k_s0;
-      bf16* v_s = buf ? v_s1 : v_s0;
-      if (tile + 1 <= my_hi) {
-        const size_t base = ((size_t)table[tile + 1] * K + kh) * BN * hd;
-        load_kv_tile(buf ? k_s0 : k_s1, k_pages + base, hd, STRIDE, lane);
-        load_kv_tile(buf ? v_s0 : v_s1, v_pages + base, hd, STRIDE, lane);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
+      fetch(tile + STAGES - 1);
+      cp_async_wait<STAGES - 1>();  // tile `tile` has arrived
       __syncwarp();
+      const int stage = (tile - my_lo) % STAGES;
+      const bf16* k_s = kv_s + (size_t)(2 * stage) * TILE_ELEMS;
+      const bf16* v_s = k_s + TILE_ELEMS;
 
-      // ---- S = Q K^T: 16 rows (heads) x 64 keys
-      float s_acc[BN / 8][4];
+      // ---- S^T = K Q^T: 32 keys (two 16-row tiles) x 8 heads
+      float s_acc[2][4];  // (key mt*16 + g [+8], head 2*t4 [+1])
 #pragma unroll
-      for (int i = 0; i < BN / 8; ++i) s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f;
+      for (int mt = 0; mt < 2; ++mt) s_acc[mt][0] = s_acc[mt][1] = s_acc[mt][2] = s_acc[mt][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
-        uint32_t a[4];
-        ldmatrix_x4(a, q_s + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
 #pragma unroll
-        for (int np = 0; np < BN / 16; ++np) {
-          uint32_t b[4];
-          ldmatrix_x4(b, k_s + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + kk * 16 + 8 * ((lane >> 3) & 1));
-          mma_bf16(s_acc[2 * np], a, b[0], b[1]);
-          mma_bf16(s_acc[2 * np + 1], a, b[2], b[3]);
+        for (int mt = 0; mt < 2; ++mt) {
+          uint32_t a[4];
+          ldmatrix_x4(a, k_s + (size_t)(mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
+          mma_bf16(s_acc[mt], a, qf[kk][0], qf[kk][1]);
         }
       }
 
-      // ---- mask by position, scale to base-2 exponents, online softmax
-      const int key0 = tile * BN;
-      const bool need_mask = key0 < first || key0 + BN - 1 > pos;
-      float tile_max[2] = {-INFINITY, -INFINITY};
+      // ---- mask by position, scale to base-2 exponents, online softmax per head (column)
+      const int key0 = tile * BK;
+      const bool need_mask = key0 < first || key0 + BK - 1 > pos;
+      float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int n = 0; n < BN / 8; ++n) {
+      for (int mt = 0; mt < 2; ++mt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = s_acc[n][e] * scale_log2;
+          float v = s_acc[mt][e] * scale_log2;
           if (need_mask) {
-            const int key = key0 + n * 8 + 2 * t4 + (e & 1);
+            const int key = key0 + mt * 16 + g + 8 * (e >> 1);
             if (key < first || key > pos) v = -INFINITY;
           }
-          s_acc[n][e] = v;
-          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+          s_acc[mt][e] = v;
+          tmax[e & 1] = fmaxf(tmax[e & 1], v);
         }
       }
       float alpha[2], m_use[2];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        float mx = tile_max[r];
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run[r], mx);  // finite: every tile of the range holds a seen key
-        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[r] = exp2f(m_run[r] - m_use[r]);
-        m_run[r] = m_new;
-        l_run[r] *= alpha[r];
+      for (int j = 0; j < 2; ++j) {
+        float mx = tmax[j];
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run[j], mx);  // finite: every tile of the range holds a seen key
+        m_use[j] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[j] = exp2f(m_run[j] - m_use[j]);
+        m_run[j] = m_new;
+        l_run[j] *= alpha[j];
       }
+      uint32_t pb[2][2];  // P^T as B fragments of the two 16-key steps
 #pragma unroll
-      for (int n = 0; n < BN / 8; ++n) {
+      for (int mt = 0; mt < 2; ++mt) {
+        float p[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p = exp2f(s_acc[n][e] - m_use[e >> 1]);
-          s_acc[n][e] = p;
-          l_run[e >> 1] += p;
+          p[e] = exp2f(s_acc[mt][e] - m_use[e & 1]);
+          l_run[e & 1] += p[e];
         }
+        pb[mt][0] = movmatrix_trans(pack_bf16(p[0], p[1]));  // keys mt*16 + 0..7
+        pb[mt][1] = movmatrix_trans(pack_bf16(p[2], p[3]));  // keys mt*16 + 8..15
       }
 #pragma unroll
-      for (int i = 0; i < HD / 8; ++i) {
+      for (int i = 0; i < DTILES; ++i) {
         o_acc[i][0] *= alpha[0];
-        o_acc[i][1] *= alpha[0];
-        o_acc[i][2] *= alpha[1];
+        o_acc[i][1] *= alpha[1];
+        o_acc[i][2] *= alpha[0];
         o_acc[i][3] *= alpha[1];
       }
 
-      // ---- O += P V
+      // ---- O^T += V^T P^T: head size (16-row tiles) x 8 heads over the tile's 32 keys
 #pragma unroll
-      for (int kk = 0; kk < BN / 16; ++kk) {
-        uint32_t a[4];
-        a[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
-        a[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
-        a[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
-        a[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+      for (int mt = 0; mt < 2; ++mt) {
 #pragma unroll
-        for (int dp = 0; dp < HD / 16; ++dp) {
-          uint32_t b[4];
-          ldmatrix_x4_trans(b, v_s + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
-          mma_bf16(o_acc[2 * dp], a, b[0], b[1]);
-          mma_bf16(o_acc[2 * dp + 1], a, b[2], b[3]);
+        for (int dt = 0; dt < DTILES; ++dt) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, v_s + (size_t)(mt * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + dt * 16 + 8 * ((lane >> 3) & 1));
+          mma_bf16(o_acc[dt], a, pb[mt][0], pb[mt][1]);
         }
       }
-      __syncwarp();  // the stage is free for the load after next
+      __syncwarp();  // the stage may be refilled by the next fetch
     }
   }
 
   // ---- partial results: max (base-2 exponent), sum, unnormalised output
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    float l = l_run[r];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const int row = g + 8 * r;
-    if (row < n_heads) {
-      const size_t slot = ((size_t)s * H + h0 + row) * n_splits + split;
-      if (t4 == 0) {
-        part_ml[slot * 2] = m_run[r];
+  for (int j = 0; j < 2; ++j) {
+    float l = l_run[j];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    const int head = 2 * t4 + j;
+    if (head < n_heads) {
+      const size_t slot = ((size_t)s * H + h0 + head) * n_splits + split;
+      if (g == 0) {
+        part_ml[slot * 2] = m_run[j];
         part_ml[slot * 2 + 1] = l;
       }
       float* po = part_o + slot * hd;
 #pragma unroll
-      for (int n = 0; n < HD / 8; ++n) {
-        const int d = n * 8 + 2 * t4;
-        if (d < hd) *reinterpret_cast<float2*>(po + d) = make_float2(o_acc[n][2 * r], o_acc[n][2 * r + 1]);
+      for (int dt = 0; dt < DTILES; ++dt) {
+        const int d = dt * 16 + g;
+        if (d < hd) po[d] = o_acc[dt][j];
+        if (d + 8 < hd) po[d + 8] = o_acc[dt][2 + j];
       }
     }
   }
@@ -278,14 +303,14 @@ static int launch_decode(const bf16* q, int q_stride, const bf16* k_pages, const
                          const int* block_table, int table_width, const int* seq_len, float* part_o,
                          float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
                          float scale, int n_splits, cudaStream_t stream) {
-  const size_t smem = (size_t)(ROWS + 4 * BN) * (HD + 8) * sizeof(bf16);
+  const size_t smem = (size_t)(HEADS + 2 * STAGES * BK) * (HD + 8) * sizeof(bf16);
   auto kern = attn_decode_split_kernel<HD>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(8, "attn_decode: cannot get %zu bytes of shared memory", smem);
   }
   const int G = H / K;
-  dim3 grid(n_splits, K * ((G + ROWS - 1) / ROWS), n_seqs);
+  dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
   kern<<<grid, 32, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
                                    H, K, hd, window, scale * 1.4426950408889634f, n_splits);
   cudaError_t e = cudaGetLastError();
@@ -306,7 +331,7 @@ RL_API int rl_attn_decode(const void* q, int dtype, int q_stride, const void* k_
                           int page_size, int window, float scale, int n_splits, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || hd <= 0) RL_REFUSE(1, "attn_decode: S=%d H=%d K=%d hd=%d", n_seqs, H, K, hd);
   if (H % K) RL_REFUSE(2, "attn_decode: %d query heads are not a multiple of %d kv heads", H, K);
-  if (page_size != BN) RL_REFUSE(3, "attn_decode: page size %d, this kernel is built for %d", page_size, BN);
+  if (page_size != PAGE) RL_REFUSE(3, "attn_decode: page size %d, this kernel is built for %d", page_size, PAGE);
   if (dtype != RL_BF16) RL_REFUSE(4, "attn_decode: bfloat16 only (32-bit runs use attn_generic), got dtype %d", dtype);
   if (hd % 8) RL_REFUSE(9, "attn_decode: head size %d is not a multiple of 8", hd);
   if (q_stride % 8) RL_REFUSE(9, "attn_decode: query row stride %d breaks 16-byte alignment", q_stride);

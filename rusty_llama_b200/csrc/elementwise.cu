@@ -61,8 +61,10 @@ RL_API int rl_embed_gather(const int* tokens, const void* table, int table_dtype
 // With VEC (d a multiple of 4) a thread handles four neighbouring values per round and the block
 // is sized so that a row of up to 4096 values takes one round: all loads are in flight together,
 // which is what the few rows of a decode step need.
-template <typename TA, typename TW, bool VEC>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, int n_parts,
+// TD is the type of the parts that are added: the activation type, or float32 for the partial sums
+// of a product that was split over k.
+template <typename TA, typename TW, typename TD, bool VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts,
                                    long long part_stride, const TW* __restrict__ w, TA* __restrict__ out,
                                    const int* __restrict__ rows, int d, float eps, int write_x) {
   extern __shared__ __align__(16) float row[];
@@ -77,7 +79,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
       load4<float>(xr + i, v);
       for (int p = 0; p < n_parts; ++p) {
         float dv[4];
-        load4<TA>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv);
+        load4<TD>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv);
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[e] += dv[e];
       }
@@ -113,37 +115,40 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
   }
 }
 
-template <typename TA, typename TW>
+template <typename TA, typename TW, typename TD>
 static int launch_add_rmsnorm(float* x, const void* delta, int n_parts, long long part_stride, const void* w,
                               void* out, const int* rows, int n_rows, int d, float eps, int write_x,
                               cudaStream_t stream) {
   const size_t smem = (size_t)d * sizeof(float);
   const bool vec = d % 4 == 0;
-  auto kern = vec ? add_rmsnorm_kernel<TA, TW, true> : add_rmsnorm_kernel<TA, TW, false>;
+  auto kern = vec ? add_rmsnorm_kernel<TA, TW, TD, true> : add_rmsnorm_kernel<TA, TW, TD, false>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) RL_REFUSE(3, "add_rmsnorm: a row of %d values does not fit shared memory", d);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(4, "add_rmsnorm: cannot get %zu bytes of shared memory", smem);
   }
-  kern<<<n_rows, vec ? row_threads(d) : 256, smem, stream>>>(x, (const TA*)delta, n_parts, part_stride,
+  kern<<<n_rows, vec ? row_threads(d) : 256, smem, stream>>>(x, (const TD*)delta, n_parts, part_stride,
                                                              (const TW*)w, (TA*)out, rows, d, eps, write_x);
   RL_LAUNCH_RESULT();
 }
 
-RL_API int rl_add_rmsnorm(float* x, const void* delta, int n_parts, long long part_stride, const void* w,
-                          int w_dtype, void* out, int act_dtype, const int* rows, int n_rows, int d, float eps,
-                          int write_x, cudaStream_t stream) {
+RL_API int rl_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride,
+                          const void* w, int w_dtype, void* out, int act_dtype, const int* rows, int n_rows, int d,
+                          float eps, int write_x, cudaStream_t stream) {
   if (n_rows <= 0 || d <= 0 || n_parts < 0) RL_REFUSE(1, "add_rmsnorm: n_rows=%d d=%d n_parts=%d", n_rows, d, n_parts);
   if (n_parts > 0 && delta == nullptr) RL_REFUSE(2, "add_rmsnorm: %d parts but no delta", n_parts);
   if (w != nullptr && out == nullptr) RL_REFUSE(2, "add_rmsnorm: a weight but no output");
-  if (act_dtype == RL_BF16 && w_dtype == RL_BF16)
-    return launch_add_rmsnorm<bf16, bf16>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
-  if (act_dtype == RL_BF16 && w_dtype == RL_F32)
-    return launch_add_rmsnorm<bf16, float>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
-  if (act_dtype == RL_F32 && w_dtype == RL_F32)
-    return launch_add_rmsnorm<float, float>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
-  if (act_dtype == RL_F32 && w_dtype == RL_BF16)
-    return launch_add_rmsnorm<float, bf16>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream);
+  if (n_parts == 0) delta_dtype = act_dtype;
+  if (delta_dtype != act_dtype && delta_dtype != RL_F32) RL_REFUSE(6, "add_rmsnorm: parts of dtype %d in a run of dtype %d", delta_dtype, act_dtype);
+#define RL_NORM(TA, TW, TD) \
+  return launch_add_rmsnorm<TA, TW, TD>(x, delta, n_parts, part_stride, w, out, rows, n_rows, d, eps, write_x, stream)
+  if (act_dtype == RL_BF16 && w_dtype == RL_BF16 && delta_dtype == RL_BF16) RL_NORM(bf16, bf16, bf16);
+  if (act_dtype == RL_BF16 && w_dtype == RL_BF16 && delta_dtype == RL_F32) RL_NORM(bf16, bf16, float);
+  if (act_dtype == RL_BF16 && w_dtype == RL_F32 && delta_dtype == RL_BF16) RL_NORM(bf16, float, bf16);
+  if (act_dtype == RL_BF16 && w_dtype == RL_F32 && delta_dtype == RL_F32) RL_NORM(bf16, float, float);
+  if (act_dtype == RL_F32 && w_dtype == RL_F32) RL_NORM(float, float, float);
+  if (act_dtype == RL_F32 && w_dtype == RL_BF16) RL_NORM(float, bf16, float);
+#undef RL_NORM
   RL_REFUSE(5, "add_rmsnorm: unknown dtypes act=%d w=%d", act_dtype, w_dtype);
 }
 

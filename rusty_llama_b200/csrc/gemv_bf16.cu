@@ -52,6 +52,13 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int n0 = blockIdx.x * 16;
+  // blockIdx.y: which slice of k this block sums (k_splits > 1: out receives one partial result
+  // per slice, [slice][M][ldo], that the consumer adds up)
+  const int k_blocks_total = (K + 31) / 32;
+  const int per_split = (k_blocks_total + gridDim.y - 1) / gridDim.y;
+  const int kb_begin = blockIdx.y * per_split;
+  const int kb_end = min(k_blocks_total, kb_begin + per_split);
+  out += (size_t)blockIdx.y * M * ldo;
   const bool row0_ok = n0 + g < N, row1_ok = n0 + g + 8 < N;
   const bf16* w0 = w + (size_t)(row0_ok ? n0 + g : 0) * ldw;
   const bf16* w1 = w + (size_t)(row1_ok ? n0 + g + 8 : 0) * ldw;
@@ -61,24 +68,23 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  const int n_blocks = (K + 31) / 32;
   // U k blocks of weights are requested before the first is used, so that each lane keeps
-  // 2 * U 16-byte loads in flight: with few rows the kernel waits on memory latency, and what
-  // is in flight per SM is what sets its bandwidth.
-  constexpr int U = NT <= 2 ? 8 : 4;
-  for (int kb = warp; kb < n_blocks; kb += WARPS * U) {
+  // 2 * U 16-byte loads in flight (measured: 8 is slower than 4, the registers cost more
+  // resident warps than the deeper queue gains).
+  constexpr int U = 4;
+  for (int kb = kb_begin + warp; kb < kb_end; kb += WARPS * U) {
     uint4 a0[U], a1[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (kb + u * WARPS) * 32 + 8 * t4;
-      const bool k_ok = k + 8 <= K;
+      const bool k_ok = k + 8 <= K && kb + u * WARPS < kb_end;
       a0[u] = (k_ok && row0_ok) ? ld_stream(w0 + k) : zero;
       a1[u] = (k_ok && row1_ok) ? ld_stream(w1 + k) : zero;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (kb + u * WARPS) * 32 + 8 * t4;
-      const bool k_ok = k + 8 <= K;
+      const bool k_ok = k + 8 <= K && kb + u * WARPS < kb_end;
       uint4 b[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -130,8 +136,8 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
 
 template <int NT>
 static int launch_gemv(const bf16* x, int ldx, const bf16* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                       int N, int K, int swiglu, cudaStream_t stream) {
-  const int blocks = (N + 15) / 16;
+                       int N, int K, int swiglu, int k_splits, cudaStream_t stream) {
+  const dim3 blocks((N + 15) / 16, k_splits);
   if (swiglu && out_dtype == RL_F32)
     gemv_bf16_kernel<NT, float, true><<<blocks, WARPS * 32, 0, stream>>>(x, ldx, w, ldw, (float*)out, ldo, M, N, K);
   else if (swiglu)
@@ -146,18 +152,22 @@ static int launch_gemv(const bf16* x, int ldx, const bf16* w, int ldw, void* out
 RL_API int rl_gemv_bf16_max_rows() { return 64; }
 
 // swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel).
+// k_splits > 1: the k range is cut into that many slices, each summed by blocks of its own; out is then
+// [k_splits][M][ldo] float32 partial results (more blocks in flight for matrices with few rows).
 RL_API int rl_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                        int N, int K, int swiglu, cudaStream_t stream) {
+                        int N, int K, int swiglu, int k_splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_bf16: M=%d N=%d K=%d", M, N, K);
   if (M > 64) RL_REFUSE(2, "gemv_bf16: %d rows, this kernel takes at most 64", M);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_bf16: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte loads)", K, ldx, ldw);
   if (swiglu && (N & 1)) RL_REFUSE(6, "gemv_bf16: %d gate/up rows are not pairs", N);
+  if (k_splits < 1 || k_splits > 64) RL_REFUSE(7, "gemv_bf16: %d k slices", k_splits);
+  if (k_splits > 1 && (swiglu || out_dtype != RL_F32)) RL_REFUSE(8, "gemv_bf16: partial sums over k slices are float32 and cannot go through the activation");
   if (ldx < K || ldw < K || ldo < (swiglu ? N / 2 : N)) RL_REFUSE(4, "gemv_bf16: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) RL_REFUSE(5, "gemv_bf16: unknown output dtype %d", out_dtype);
   const bf16* xx = (const bf16*)x;
   const bf16* ww = (const bf16*)w;
-  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
-  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
-  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
-  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, stream);
+  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
+  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
+  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
+  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
 }

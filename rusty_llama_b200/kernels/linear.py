@@ -53,3 +53,22 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     if x.shape[0] <= ops.GEMV_MAX_ROWS:
         return ops.gemv_bf16(x, w_gate_up, torch.bfloat16, swiglu=True)
     return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
+
+
+# blocks of the streaming kernel that fill a 148-SM part (six resident blocks per SM)
+_STREAM_TARGET_BLOCKS = 888
+
+
+def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """A projection whose result is added to the residual stream (attention output, feed-forward
+    down projection).  For a decode step in bfloat16 with few output features the k range is split
+    and the float32 partial sums [parts, M, N] are returned, which the next norm's kernel adds up
+    in 32-bit; otherwise the same as `linear`."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype == torch.bfloat16 and M <= ops.GEMV_MAX_ROWS:
+        blocks = (N + 15) // 16
+        splits = min((_STREAM_TARGET_BLOCKS + blocks - 1) // blocks, 8, max(1, K // 1024))
+        if splits > 1:
+            return ops.gemv_bf16(x, w, torch.float32, k_splits=splits)
+    return linear(x, w)

@@ -114,15 +114,19 @@ def add_rmsnorm(
 ) -> Optional[torch.Tensor]:
     """x (float32 [T, d]) += sum of delta parts; returns rmsnorm(x) * weight in `act_dtype`.
 
-    delta: None, [T, d] or [parts, T, d] in `act_dtype`.  weight None: only the sum.
+    delta: None, [T, d] or [parts, T, d], in `act_dtype` or in float32 (partial sums of a product
+    split over k).  weight None: only the sum.
     rows: int32 indices of the rows to produce (all rows if None).
     """
     _cuda(x, "add_rmsnorm x", torch.float32)
     _need(x.dim() == 2, "add_rmsnorm: x must be [T, d]")
     T, d = x.shape
     n_parts, part_stride = 0, 0
+    delta_dt = _DT[act_dtype]
     if delta is not None:
-        _cuda(delta, "add_rmsnorm delta", act_dtype)
+        _cuda(delta, "add_rmsnorm delta")
+        _need(delta.dtype in (act_dtype, torch.float32), f"add_rmsnorm: delta is {delta.dtype} in a run of {act_dtype}")
+        delta_dt = _DT[delta.dtype]
         if delta.dim() == 2:
             _need(tuple(delta.shape) == (T, d), f"add_rmsnorm: delta {tuple(delta.shape)} does not match x {(T, d)}")
             n_parts = 1
@@ -151,7 +155,7 @@ def add_rmsnorm(
         _need(t is None or t.data_ptr() % 16 == 0, f"add_rmsnorm: {name} is not 16-byte aligned")
     lib = build.load("elementwise")
     rc = lib.rl_add_rmsnorm(
-        _p(x), _p(delta), c_int(n_parts), c_ll(part_stride), _p(weight), c_int(w_dt), _p(out),
+        _p(x), _p(delta), c_int(delta_dt), c_int(n_parts), c_ll(part_stride), _p(weight), c_int(w_dt), _p(out),
         c_int(_DT[act_dtype]), _p(rows), c_int(n_rows), c_int(d), c_float(eps), c_int(1 if write_x else 0), _stream(),
     )
     _check(lib, rc, "add_rmsnorm")
@@ -365,11 +369,13 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
 
 def gemv_bf16(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False,
+    swiglu: bool = False, k_splits: int = 1,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 rows, bfloat16 in, 32-bit accumulate.
 
-    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums."""
+    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums.
+    k_splits > 1: returns float32 [k_splits, M, N], one partial sum per slice of k, for a consumer
+    that adds them (`add_rmsnorm`): more blocks in flight when N is small."""
     _cuda(x, "gemv_bf16 x", torch.bfloat16, contiguous=False)
     _cuda(w, "gemv_bf16 w", torch.bfloat16, contiguous=False)
     ldx, ldw = _rows(x, "gemv_bf16 x"), _rows(w, "gemv_bf16 w")
@@ -378,14 +384,23 @@ def gemv_bf16(
     _need(w.shape[1] == K, f"gemv_bf16: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
     _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemv_bf16: operands must be 16-byte aligned")
     n_out = N // 2 if swiglu else N
-    if out is None:
-        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    _cuda(out, "gemv_bf16 out", out_dtype, contiguous=False)
-    _need(tuple(out.shape) == (M, n_out), "gemv_bf16: out has the wrong shape")
+    if k_splits > 1:
+        _need(out_dtype == torch.float32 and not swiglu, "gemv_bf16: partial sums over k slices are float32, without activation")
+        if out is None:
+            out = torch.empty((k_splits, M, n_out), dtype=torch.float32, device=x.device)
+        _cuda(out, "gemv_bf16 out", torch.float32)
+        _need(tuple(out.shape) == (k_splits, M, n_out), "gemv_bf16: out has the wrong shape")
+        ldo = n_out
+    else:
+        if out is None:
+            out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        _cuda(out, "gemv_bf16 out", out_dtype, contiguous=False)
+        _need(tuple(out.shape) == (M, n_out), "gemv_bf16: out has the wrong shape")
+        ldo = _rows(out, "gemv_bf16 out")
     lib = build.load("gemv_bf16")
     rc = lib.rl_gemv_bf16(
-        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_bf16 out")), c_int(_rows(out, "gemv_bf16 out")),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream(),
+        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_bf16 out")), c_int(ldo),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), _stream(),
     )
     _check(lib, rc, "gemv_bf16")
     return out

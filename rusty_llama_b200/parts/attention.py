@@ -9,14 +9,14 @@ import torch
 
 from ..errors import ConfigError
 from ..kernels import ops
-from ..kernels.linear import linear
+from ..kernels.linear import linear, linear_to_stream
 from ..spec import PartSpec
 from .base import MIXERS, POSITIONS, KVNeed, Mixer, ParamInfo
 
 # one-warp blocks the decode kernel should have on the whole GPU before more splits stop
-# paying: twice what a 148-SM part holds at three blocks per SM (its shared memory's limit)
+# paying: a bit more than what a 148-SM part holds at four blocks per SM (its shared memory's limit)
 _DECODE_TARGET_BLOCKS = 888
-_DECODE_HEADS_PER_BLOCK = 16
+_DECODE_HEADS_PER_BLOCK = 8
 
 
 def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int) -> int:
@@ -107,4 +107,4 @@ class Attention(Mixer):
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
                 step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,
             )
-        return linear(a, self.w_o)
+        return linear_to_stream(a, self.w_o)

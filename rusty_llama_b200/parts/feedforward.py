@@ -8,7 +8,7 @@ import torch
 
 from ..errors import ConfigError
 from ..kernels import ops
-from ..kernels.linear import linear, linear_swiglu
+from ..kernels.linear import linear, linear_swiglu, linear_to_stream
 from .base import FEED_FORWARDS, FeedForward, ParamInfo
 
 
@@ -57,4 +57,4 @@ class GatedMLP(FeedForward):
             h = linear_swiglu(xn, self.w_gate_up)
         else:
             h = ops.swiglu(linear(xn, self.w_gate_up))
-        return linear(h, self.w_down)
+        return linear_to_stream(h, self.w_down)

@@ -415,6 +415,35 @@ def test_fused_gate_up_swiglu(ops, M, ff, K):
     close_bf16(out, ref)
 
 
+@pytest.mark.parametrize("M, N, K, splits", [(8, 100, 4096, 4), (1, 48, 1000, 3), (64, 257, 2048, 8), (3, 16, 72, 2)])
+def test_gemv_bf16_partial_sums_over_k_slices(ops, M, N, K, splits):
+    x = bf16_round(torch.randn(M, K))
+    w = bf16_round(torch.randn(N, K) * 0.05)
+    parts = ops.gemv_bf16(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits)
+    assert parts.shape == (splits, M, N) and parts.dtype == torch.float32
+    close_dot_f32(parts.sum(dim=0), x, w)
+    # each slice really is its own range of k
+    per = ((K + 31) // 32 + splits - 1) // splits * 32
+    for i in range(splits):
+        lo, hi = i * per, min(K, (i + 1) * per)
+        if lo < hi:
+            close_dot_f32(parts[i], x[:, lo:hi], w[:, lo:hi])
+        else:
+            assert float(parts[i].abs().max()) == 0.0
+
+
+def test_add_rmsnorm_takes_float32_partial_sums_in_a_bfloat16_run(ops):
+    T, d = 6, 520
+    x = torch.randn(T, d)
+    parts = torch.randn(3, T, d)
+    w = (1 + 0.1 * torch.randn(d)).to(torch.bfloat16)
+    xd = x.to(DEV)
+    out = ops.add_rmsnorm(xd, parts.to(DEV), w.to(DEV), 1e-5, torch.bfloat16)
+    total = x + parts[0] + parts[1] + parts[2]
+    close_f32(xd, total, 1e-6)
+    close_bf16(out, plain_rmsnorm(total.double(), w.double(), 1e-5))
+
+
 def test_gemv_bf16_refuses_what_it_cannot_do(ops):
     from rusty_llama_b200.errors import KernelError
 
