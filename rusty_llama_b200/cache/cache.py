@@ -83,7 +83,7 @@ class StateView:
 
 
 class KVGroup:
-    def __init__(self, need: KVNeed, runs: List[int], n_pages: int, dtype: torch.dtype, device: torch.device):
+    def __init__(self, need: KVNeed, runs: List[int], n_pages: int, dtype: torch.dtype, device: torch.device, max_seqs: int = 1):
         self.need = need
         self.runs = list(runs)
         self.pool = PagePool(n_pages)
@@ -94,6 +94,16 @@ class KVGroup:
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         self.pages: Dict[int, List[int]] = {}  # slot -> page id per page index (-1: given back)
         self.first_held: Dict[int, int] = {}  # slot -> lowest page index still held
+        # the same page lists as one matrix [slot, page index] (0 where nothing is held), kept in
+        # step with `pages` so that a step's block table is one indexing operation
+        self.table = np.zeros((max_seqs, 8), dtype=np.int32)
+
+    def _set(self, slot: int, index: int, page: int) -> None:
+        if index >= self.table.shape[1]:
+            grown = np.zeros((self.table.shape[0], max(2 * self.table.shape[1], index + 1)), dtype=np.int32)
+            grown[:, : self.table.shape[1]] = self.table
+            self.table = grown
+        self.table[slot, index] = max(page, 0)
 
     def bytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
@@ -145,7 +155,7 @@ class Cache:
         self._where: Dict[int, Tuple[str, int, int]] = {}  # run -> (family, group index, index in group)
         for need, runs in by_need.items():
             if isinstance(need, KVNeed):
-                self.kv_groups.append(KVGroup(need, runs, self.n_pages, dtype, self.device))
+                self.kv_groups.append(KVGroup(need, runs, self.n_pages, dtype, self.device, max_seqs))
                 gi = len(self.kv_groups) - 1
                 for j, run in enumerate(runs):
                     self._where[run] = ("kv", gi, j)
@@ -177,6 +187,7 @@ class Cache:
         for g in self.kv_groups:
             g.pages[slot] = []
             g.first_held[slot] = 0
+            g.table[slot, :] = 0
         for g in self.state_groups:
             g.state[:, slot].zero_()
         return slot
@@ -221,9 +232,11 @@ class Cache:
                     while len(have) < need_pages:
                         page = g.pool.take()
                         have.append(page)
+                        g._set(slot, len(have) - 1, page)
                         taken.append((g, slot))
         except CacheError:
             for g, slot in reversed(taken):
+                g._set(slot, len(g.pages[slot]) - 1, 0)
                 g.pool.give_back(g.pages[slot].pop())
             raise
 
@@ -241,21 +254,43 @@ class Cache:
                     if have[idx] >= 0:
                         g.pool.give_back(have[idx])
                         have[idx] = -1
+                        g._set(slot, idx, 0)
                 g.first_held[slot] = max(g.first_held[slot], min(keep_from, len(have)))
 
     def table_width(self, slots: Sequence[int]) -> int:
         return max((len(g.pages[s]) for g in self.kv_groups for s in slots), default=1) or 1
 
+    def lengths(self, slots: np.ndarray) -> np.ndarray:
+        """Positions held by each of `slots` (an integer array); raises if one is not open."""
+        if slots.size and (slots.min() < 0 or slots.max() >= self.max_seqs or not self._open[slots].all()):
+            bad = [int(s) for s in slots if not (0 <= s < self.max_seqs) or not self._open[s]]
+            raise CacheError(f"slots {bad} are not open (never opened, or closed already)")
+        return self._length[slots]
+
+    def has_window_groups(self) -> bool:
+        return any(g.need.window for g in self.kv_groups)
+
+    def reserve_one_each(self, slots: Sequence[int], lengths: np.ndarray) -> None:
+        """`reserve(slots, [1] * len(slots))` for the common decode step: a page is taken only by the
+        sequences that stand at a page boundary."""
+        at_boundary = [int(s) for s, n in zip(slots, lengths) if n % PAGE_SIZE == 0]
+        if at_boundary:
+            self.reserve(at_boundary, [1] * len(at_boundary))
+
+    def commit_one_each(self, slots: np.ndarray) -> None:
+        if self.has_window_groups():
+            self.commit([int(s) for s in slots], [1] * len(slots))
+        else:
+            self._length[slots] += 1
+
     def block_table(self, group_index: int, slots: Sequence[int], width: int) -> np.ndarray:
         """int32 [len(slots), width]: page id of page index j of each sequence; unheld entries are 0."""
         g = self.kv_groups[group_index]
+        have = g.table.shape[1]
+        if width <= have:
+            return g.table[np.asarray(slots, dtype=np.intp), :width]
         table = np.zeros((len(slots), width), dtype=np.int32)
-        for i, slot in enumerate(slots):
-            pages = g.pages[slot]
-            n = min(len(pages), width)
-            if n:
-                row = np.asarray(pages[:n], dtype=np.int32)
-                table[i, :n] = np.where(row >= 0, row, 0)
+        table[:, :have] = g.table[np.asarray(slots, dtype=np.intp)]
         return table
 
     # ------------------------------------------------------------------ views

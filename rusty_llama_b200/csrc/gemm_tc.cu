@@ -208,7 +208,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int* __restrict__ status) {
+               TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int k_splits,
+               int* __restrict__ status) {
   extern __shared__ unsigned char smem_dyn[];
   // the swizzled stages must start on a 1024-byte boundary
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -222,7 +223,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
-  const int n_slices = (K + BK - 1) / BK;
+  // a unit of work is one output tile and one slice of the k range (k_splits > 1: each slice
+  // writes its own partial result, out[slice][M][ldo], and the consumer adds them)
+  const int n_units = n_tiles * k_splits;
+  const int slices_total = (K + BK - 1) / BK;
+  const int slices_per_split = (slices_total + k_splits - 1) / k_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -247,9 +252,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;  // slices requested so far, over all tiles of this block
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+        const int tile = unit % n_tiles, ks = unit / n_tiles;
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < n_slices; ++kb, ++it) {
+        const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t round = it / STAGES;
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
@@ -283,7 +290,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       int local = 0;  // tiles done by this block
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+      for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++local) {
+        const int ks = unit / n_tiles;
+        const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
         const int acc = local & 1;
         const uint32_t use = local >> 1;  // how often this half was used before
         if (use > 0 && !mbar_wait(&acc_empty[acc], (use - 1) & 1)) {
@@ -294,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < n_slices; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
             atomicExch(status, 2);
@@ -309,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t a_desc = make_smem_desc(a_addr + k * UMMA_K * 2);
             const uint64_t b_desc = make_smem_desc(b_addr + k * UMMA_K * 2);
-            umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);
         }
@@ -320,7 +329,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---------------- epilogue: warps 2..5, each on its quarter of the 128 lanes
     const int quarter = warp & 3;
     int local = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+    for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++local) {
+      const int tile = unit % n_tiles, ks = unit / n_tiles;
+      TO* out_k = out + (size_t)ks * M * ldo;
       const int acc = local & 1;
       const bool ok = mbar_wait(&acc_full[acc], (local >> 1) & 1);
       if (!ok) {
@@ -342,9 +353,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int col = n0 + c * 32;
         if (row < M && col < N) {
           if (SWIGLU)
-            store_swiglu16<TO>(out + (size_t)row * ldo + (col >> 1), r, (N - col) >> 1, vec_store != 0);
+            store_swiglu16<TO>(out_k + (size_t)row * ldo + (col >> 1), r, (N - col) >> 1, vec_store != 0);
           else
-            store_row32<TO>(out + (size_t)row * ldo + col, r, N - col, vec_store != 0);
+            store_row32<TO>(out_k + (size_t)row * ldo + col, r, N - col, vec_store != 0);
         }
       }
       // this half may be overwritten once all four warps have read it
@@ -392,8 +403,10 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 // (1 producer, 2 tensor-core issuer waiting for data, 3 epilogue, 4 tensor-core issuer waiting for the
 // epilogue) and the output is not valid.
 // swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel).
+// k_splits > 1: the k range is cut into that many slices (rounded so that none is empty; the number
+// used is returned through *k_splits_used), out is [slices][M][ldo] float32 partial results.
 RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                      int K, int swiglu, int* status, cudaStream_t stream) {
+                      int K, int swiglu, int k_splits, int* k_splits_used, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
   if (swiglu && (N & 1)) RL_REFUSE(11, "gemm_tc: %d gate/up rows are not pairs", N);
@@ -402,13 +415,22 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   const int vec_store = (out_dtype == RL_BF16 ? (ldo % 8) : (ldo % 4)) == 0;  // else the epilogue stores element by element
   if (out_dtype != RL_BF16 && out_dtype != RL_F32) RL_REFUSE(6, "gemm_tc: unknown output dtype %d", out_dtype);
   if (status == nullptr) RL_REFUSE(7, "gemm_tc: no status word");
+  if (k_splits < 1) RL_REFUSE(12, "gemm_tc: %d k slices", k_splits);
+  if (k_splits > 1 && (swiglu || out_dtype != RL_F32)) RL_REFUSE(13, "gemm_tc: partial sums over k slices are float32 and cannot go through the activation");
+  {
+    const int slices = (K + BK - 1) / BK;
+    if (k_splits > slices) k_splits = slices;
+    const int per = (slices + k_splits - 1) / k_splits;
+    k_splits = (slices + per - 1) / per;  // no empty slice
+    if (k_splits_used) *k_splits_used = k_splits;
+  }
   static int n_sms = 0;
   if (n_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
   }
-  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   CUtensorMap map_x, map_w;
   int e1 = make_map(&map_x, x, M, K, ldx, BM), e2 = make_map(&map_w, w, N, K, ldw, BN);
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
@@ -419,7 +441,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     auto kern = gemm_tc_kernel<TOUT, SW>;                                                                         \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
       RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
-    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store, status);         \
+    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store, k_splits, status);         \
   } while (0)
   if (out_dtype == RL_BF16 && swiglu) RL_TC_LAUNCH(bf16, true);
   else if (out_dtype == RL_BF16) RL_TC_LAUNCH(bf16, false);

@@ -95,14 +95,18 @@ class _MetaBuffers:
             self.offsets.append(total)
             total += _pad4(max(n, 1))
         self.total = total
-        if self._copied is not None:
-            self._copied.synchronize()
+        self.wait_for_copy()
         if total > self.capacity:
             self.capacity = max(total, 2 * self.capacity)
             pin = self.device.type == "cuda"
             self.host = torch.zeros(self.capacity, dtype=torch.int32, pin_memory=pin)
             self.host_np = self.host.numpy()
             self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=self.device)
+
+    def wait_for_copy(self) -> None:
+        """The host side may be rewritten once the last copy out of it has finished."""
+        if self._copied is not None:
+            self._copied.synchronize()
 
     def host_part(self, i: int) -> np.ndarray:
         return self.host_np[self.offsets[i] : self.offsets[i] + self.sizes[i]]
@@ -230,6 +234,8 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens; returns float32 logits [wanted, vocab] on the device,
         in the order of the entries and of each entry's `want`."""
+        if self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
+            return self._decode_graph_step(entries)
         self._validate(entries)
         slots = [e.slot for e in entries]
         q_lens = [len(e.tokens) for e in entries]
@@ -240,26 +246,40 @@ class Engine:
         for e in entries:
             rows.extend(at + int(w) for w in e.want)
             at += len(e.tokens)
-        decode_only = all(q == 1 for q in q_lens)
-        if decode_only and self.use_graphs:
-            logits = self._decode_graph_step(entries, pos0, rows)
-        else:
-            T, S = sum(q_lens), len(entries)
-            widths = tuple(self.cache.table_width(slots) for _ in self.cache.kv_groups)
-            meta = self._meta
-            meta.layout(T, S, len(rows), widths)
-            self._fill_meta(meta, entries, pos0, rows)
-            meta.upload()
-            step, tables = self._context(meta, entries, pos0, len(rows), max(p + q for p, q in zip(pos0, q_lens)))
-            logits = self.model.forward(step, self.cache, tables)
+        T, S = sum(q_lens), len(entries)
+        widths = tuple(self.cache.table_width(slots) for _ in self.cache.kv_groups)
+        meta = self._meta
+        meta.layout(T, S, len(rows), widths)
+        self._fill_meta(meta, entries, pos0, rows)
+        meta.upload()
+        step, tables = self._context(meta, entries, pos0, len(rows), max(p + q for p, q in zip(pos0, q_lens)))
+        logits = self.model.forward(step, self.cache, tables)
         self.cache.commit(slots, q_lens)
         return logits
 
     # ------------------------------------------------------------------ decode through a graph
-    def _decode_graph_step(self, entries, pos0, rows: List[int]) -> torch.Tensor:
+    def _decode_graph_step(self, entries) -> torch.Tensor:
+        """A step whose entries all bring one token: checks, cache bookkeeping and the step's integers
+        are done with array operations, the kernels are one graph replay."""
         S = len(entries)
-        slots = [e.slot for e in entries]
-        need_width = self.cache.table_width(slots)
+        slots = np.fromiter((e.slot for e in entries), dtype=np.intp, count=S)
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+        if len(set(slots.tolist())) != S:
+            raise StepError(f"a slot appears twice in one step: {slots.tolist()}")
+        pos0 = self.cache.lengths(slots)  # raises CacheError for a slot that is not open
+        if ((toks < 0) | (toks >= self.vocab_size)).any():
+            bad = toks[(toks < 0) | (toks >= self.vocab_size)][0]
+            raise StepError(f"token id {int(bad)} is outside the vocabulary of {self.vocab_size}")
+        if (pos0 + 1 > self.max_positions).any():
+            raise StepError(f"a sequence would pass the model's limit of {self.max_positions} positions")
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            if len(e.want):
+                if len(e.want) != 1 or int(e.want[0]) != 0:
+                    raise StepError(f"slot {e.slot} wants logits at {list(e.want)} of 1 token")
+                rows.append(i)
+        self.cache.reserve_one_each(slots, pos0)
+        need_width = (int(pos0.max()) + PAGE_SIZE) // PAGE_SIZE
         width = 4
         while width < need_width:
             width *= 2
@@ -268,13 +288,27 @@ class Engine:
         if g is None:
             g = _DecodeGraph()
             g.meta = _MetaBuffers(self.rt.device)
+            g.meta.layout(S, S, S, tuple(width for _ in self.cache.kv_groups))
+            ar = np.arange(S + 1, dtype=np.int32)
+            g.meta.host_part(1)[:] = ar[:S]  # each token is its own sequence
+            g.meta.host_part(3)[:] = ar
+            g.meta.host_part(7)[:] = ar[:S]
+            g.host = [g.meta.host_part(i) for i in range(8 + len(self.cache.kv_groups))]
             self._graphs[key] = g
-        g.meta.layout(S, S, S, tuple(width for _ in self.cache.kv_groups))
-        all_rows = list(range(S))
-        self._fill_meta(g.meta, entries, pos0, all_rows)
+        else:
+            g.meta.wait_for_copy()
+        h = g.host
+        h[0][:] = toks
+        h[2][:] = pos0
+        h[4][:] = pos0
+        h[5][:] = pos0 + 1
+        h[6][:] = slots
+        for gi in range(len(self.cache.kv_groups)):
+            h[8 + gi][:] = self.cache.block_table(gi, slots, width).reshape(-1)
         g.meta.upload()
-        step, tables = self._context(g.meta, entries, pos0, S, width * PAGE_SIZE)
         if g.graph is None:
+            pos_list = pos0.tolist()
+            step, tables = self._context(g.meta, entries, pos_list, S, width * PAGE_SIZE)
             if g.warm < 1:
                 # first use of this shape: run it plainly, which also sizes the workspaces
                 g.warm += 1
@@ -293,7 +327,8 @@ class Engine:
             g.graph.replay()
             ops.add_launches(g.launches)
             logits = g.logits
-        if rows == all_rows:
+        self.cache.commit_one_each(slots)
+        if len(rows) == S:
             return logits
         if not rows:
             return logits[:0]

@@ -18,6 +18,12 @@ from . import ops
 
 _library_gemm = False
 
+# Rows up to which the weight-streaming kernel is used.  Above it every warp of that kernel re-reads
+# the activations for its 16 features and the L1/L2 traffic, not HBM, sets the pace; the tcgen05
+# kernel stages the activations in shared memory once per tile and streams weights at HBM rate.
+STREAM_MAX_ROWS = 8
+_SMS = 148
+
 
 def use_library_gemm(on: bool) -> None:
     """Route bfloat16 products of more than 64 rows through torch.matmul instead of `gemm_tc`."""
@@ -36,7 +42,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
     M = x.shape[0]
-    if M <= ops.GEMV_MAX_ROWS:
+    if M <= STREAM_MAX_ROWS:
+        return ops.gemv_bf16(x, w, out_dtype)
+    if M <= 32 and ((M + 127) // 128) * ((w.shape[0] + 255) // 256) < _SMS // 2:
+        # too few output tiles to keep the SMs busy, and nothing downstream that could add up
+        # partial sums: the streaming kernel's many small blocks still win here (measured)
         return ops.gemv_bf16(x, w, out_dtype)
     if _library_gemm and out_dtype == torch.bfloat16 and x.is_cuda:
         return torch.matmul(x, w.t())
@@ -50,7 +60,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     the product's 32-bit sums go through the activation before anything is rounded or stored."""
     if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
         raise KernelError(f"linear_swiglu: bfloat16 only, got {x.dtype} x {w_gate_up.dtype}")
-    if x.shape[0] <= ops.GEMV_MAX_ROWS:
+    if x.shape[0] <= STREAM_MAX_ROWS:
         return ops.gemv_bf16(x, w_gate_up, torch.bfloat16, swiglu=True)
     return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
 
@@ -61,14 +71,23 @@ _STREAM_TARGET_BLOCKS = 888
 
 def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """A projection whose result is added to the residual stream (attention output, feed-forward
-    down projection).  For a decode step in bfloat16 with few output features the k range is split
-    and the float32 partial sums [parts, M, N] are returned, which the next norm's kernel adds up
-    in 32-bit; otherwise the same as `linear`."""
+    down projection).  In bfloat16, when the output alone gives the GPU too few blocks (a decode
+    step, a short prompt), the k range is split and the float32 partial sums [parts, M, N] are
+    returned, which the next norm's kernel adds up in 32-bit; otherwise the same as `linear`."""
     M, K = x.shape
     N = w.shape[0]
-    if x.dtype == torch.bfloat16 and M <= ops.GEMV_MAX_ROWS:
+    if x.dtype != torch.bfloat16:
+        return linear(x, w)
+    if M <= STREAM_MAX_ROWS:
         blocks = (N + 15) // 16
         splits = min((_STREAM_TARGET_BLOCKS + blocks - 1) // blocks, 8, max(1, K // 1024))
         if splits > 1:
             return ops.gemv_bf16(x, w, torch.float32, k_splits=splits)
-    return linear(x, w)
+        return ops.gemv_bf16(x, w)
+    if _library_gemm:
+        return linear(x, w)
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    splits = min(_SMS // tiles, 8, max(1, K // 512)) if tiles <= _SMS // 2 else 1
+    if splits > 1:
+        return ops.gemm_tc(x, w, torch.float32, k_splits=splits)
+    return ops.gemm_tc(x, w)

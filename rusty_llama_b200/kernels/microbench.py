@@ -65,7 +65,10 @@ def bench_gemv(a) -> dict:
     ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
     x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
     out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
-    us = _time(lambda i: ops.gemv_bf16(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
+    if a.splits > 1:
+        us = _time(lambda i: ops.gemv_bf16(x, ws[i], torch.float32, k_splits=a.splits), nv, a.iters, a.warmup)
+    else:
+        us = _time(lambda i: ops.gemv_bf16(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
     return {"kernel": "gemv_bf16", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "GBps": round(wbytes / us / 1e3, 1), "weight_copies": nv}
 
 
@@ -76,7 +79,10 @@ def bench_gemm(a) -> dict:
     x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
     if a.impl == "tc":
         out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
-        us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
+        if a.splits > 1:
+            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.float32, k_splits=a.splits), nv, a.iters, a.warmup)
+        else:
+            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
         ops.tc_status_check()
     else:
         us = _time(lambda i: linear(x, ws[i]), nv, a.iters, a.warmup)
@@ -146,7 +152,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
-    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
     ap.add_argument("--impl", default="linear", choices=["linear", "tc"], help="gemm: the dispatching linear() or the tcgen05 kernel")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

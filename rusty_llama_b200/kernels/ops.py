@@ -428,11 +428,13 @@ def tc_status_check() -> None:
 
 def gemm_tc(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False,
+    swiglu: bool = False, k_splits: int = 1,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
 
-    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit accumulators."""
+    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit accumulators.
+    k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (at most k_splits of
+    them), for a consumer that adds them up: more blocks at work when the output has few tiles."""
     _cuda(x, "gemm_tc x", torch.bfloat16, contiguous=False)
     _cuda(w, "gemm_tc w", torch.bfloat16, contiguous=False)
     ldx, ldw = _rows(x, "gemm_tc x"), _rows(w, "gemm_tc w")
@@ -440,17 +442,29 @@ def gemm_tc(
     N = w.shape[0]
     _need(w.shape[1] == K, f"gemm_tc: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
     n_out = N // 2 if swiglu else N
-    if out is None:
-        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    _cuda(out, "gemm_tc out", out_dtype, contiguous=False)
-    _need(tuple(out.shape) == (M, n_out), "gemm_tc: out has the wrong shape")
+    used = c_int(1)
+    if k_splits > 1:
+        _need(out is None and out_dtype == torch.float32 and not swiglu, "gemm_tc: partial sums over k slices are float32, without activation")
+        slices = (K + 63) // 64
+        per = (slices + min(k_splits, slices) - 1) // min(k_splits, slices)
+        k_splits = (slices + per - 1) // per
+        out = torch.empty((k_splits, M, n_out), dtype=torch.float32, device=x.device)
+        ldo = n_out
+    else:
+        if out is None:
+            out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        _cuda(out, "gemm_tc out", out_dtype, contiguous=False)
+        _need(tuple(out.shape) == (M, n_out), "gemm_tc: out has the wrong shape")
+        ldo = _rows(out, "gemm_tc out")
     status = _tc_status_word(x.device)
     lib = build.load("gemm_tc")
     rc = lib.rl_gemm_tc(
-        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(_rows(out, "gemm_tc out")),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _p(status), _stream(),
+        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(ldo),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), _stream(),
     )
     _check(lib, rc, "gemm_tc")
+    if k_splits > 1:
+        _need(used.value == k_splits, f"gemm_tc: kernel used {used.value} slices, the wrapper planned {k_splits}")
     return out
 
 

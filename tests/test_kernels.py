@@ -381,6 +381,21 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
         close_bf16(out, x.double() @ w.double().T)
 
 
+@pytest.mark.parametrize("M, N, K, splits", [(64, 512, 4096, 8), (20, 300, 1000, 3), (200, 256, 640, 64), (64, 4096, 14336, 8)])
+def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits):
+    g = torch.Generator().manual_seed(M + N)
+    x = bf16_round(torch.randn(M, K, generator=g))
+    w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
+    parts = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert parts.dim() == 3 and parts.shape[1:] == (M, N) and 1 < parts.shape[0] <= splits
+    close_dot_f32(parts.sum(dim=0), x, w)
+    per = ((K + 63) // 64 + parts.shape[0] - 1) // parts.shape[0] * 64
+    for i in range(parts.shape[0]):
+        close_dot_f32(parts[i], x[:, i * per : (i + 1) * per], w[:, i * per : (i + 1) * per])
+
+
 def test_gemm_tc_each_output_sees_its_own_row_and_column(ops):
     """x = one-hot rows, w = distinct rows: out[m, n] must be w[n, pick(m)], which exposes any mix-up of
     rows, columns, k slices or the swizzle."""

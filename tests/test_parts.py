@@ -139,6 +139,8 @@ def test_attention_part_prefill_then_decode(dtype, H, K, hd, window, interleaved
     slots = [cache.open_sequence(), cache.open_sequence()]
     step, tables = ctx_for(cache, slots, [0, 0], lens)
     out = att.forward(torch.cat([x[:n] for x, n in zip(xs, lens)]).to(DEV), step, cache.view(0, tables))
+    if out.dim() == 3:  # partial sums of a split product: what the next norm would add up
+        out = out.float().sum(dim=0)
     cache.commit(slots, lens)
     check(out[: lens[0]], refs[0][: lens[0]], dtype)
     check(out[lens[0] :], refs[1][: lens[1]], dtype)
