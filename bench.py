@@ -265,6 +265,8 @@ def run_ours(args) -> dict:
             "h2d_bytes_per_step": meta_ints,
             "d2h_bytes_per_step": 4 * batch,
             "what": "LLM.generate decode phase, greedy, host lists in and out, host clock",
+            "host_ms_per_step_in_step_call": round(1000.0 * st.decode_step_call_seconds / max(st.decode_steps, 1), 4),
+            "host_ms_per_step_in_sample_call": round(1000.0 * st.decode_sample_call_seconds / max(st.decode_steps, 1), 4),
         },
         "gpu_launches": launches,
         "prefill": {"value": round(T * 1000.0 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3), "frac": round(pre_frac, 4),

@@ -10,13 +10,15 @@
 // (mma.sync m16n8k16, bfloat16 in, 32-bit accumulate).  The probabilities leave the first product
 // as accumulator fragments indexed (key, head) and enter the second as B fragments indexed
 // (head, key); `movmatrix` transposes them inside the warp.  A tile is half a cache page (32
-// positions), copied to shared memory with cp.async three tiles deep; max, sum and rescaling of
+// positions), copied to shared memory with cp.async while the previous tile is in use; max, sum and rescaling of
 // the online softmax are per head (per column) in 32-bit registers.  Each warp writes its partial
 // (max as a base-2 exponent, sum, unnormalised output) to scratch.
 // Kernel 2 (grid: query heads x sequences) merges the splits in split order.
 //
 // Scratch layout: part_o[seq][head][split][hd] floats, part_ml[seq][head][split][2].
 // Head sizes are padded with zeros to HD in shared memory: any multiple of 8 up to 256.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 RL_DEFINE_ERROR_TEXT()
@@ -24,7 +26,6 @@ RL_DEFINE_ERROR_TEXT()
 #define HEADS 8    // query heads per warp (the N of the MMA)
 #define PAGE 64    // positions per cache page
 #define BK 32      // keys per tile
-#define STAGES 3   // tiles in shared memory
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -80,7 +81,9 @@ __device__ __forceinline__ void load_rows(bf16* dst, const bf16* src, int hd, in
   }
 }
 
-template <int HD>
+// STAGES: tiles in shared memory per warp (2 or 3): 3 keeps more bytes in flight per warp, 2 lets six
+// instead of four warps share an SM.
+template <int HD, int STAGES>
 __global__ void __launch_bounds__(32)
 attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_pages,
                          const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
@@ -106,6 +109,23 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   const int lane = threadIdx.x;
   const int g = lane >> 2, t4 = lane & 3;
 
+  float o_acc[DTILES][4];  // (dim dt*16 + g [+8], head 2*t4 [+1])
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // heads 2*t4, 2*t4+1
+  float l_run[2] = {0.f, 0.f};              // per-thread partial sums over this thread's keys
+
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  // zero the padding (columns past hd, rows past the group's heads) once; this needs nothing from
+  // the kernel before, so it runs while that kernel finishes
+  {
+    uint4 z = make_uint4(0, 0, 0, 0);
+    uint4* p = reinterpret_cast<uint4*>(smem_raw);
+    const int n16 = ((HEADS + 2 * STAGES * BK) * STRIDE * (int)sizeof(bf16)) / 16;
+    for (int i = lane; i < n16; i += 32) p[i] = z;
+  }
+  __syncwarp();
+  pdl_wait();
   const int kv_len = seq_len[s];
   const int pos = kv_len - 1;
   const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
@@ -115,21 +135,9 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   const int my_lo = tile_lo + split * per_split;
   const int my_hi = min(my_lo + per_split - 1, tile_hi);
 
-  float o_acc[DTILES][4];  // (dim dt*16 + g [+8], head 2*t4 [+1])
-#pragma unroll
-  for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};  // heads 2*t4, 2*t4+1
-  float l_run[2] = {0.f, 0.f};              // per-thread partial sums over this thread's keys
 
   if (my_lo <= my_hi) {
-    // zero the padding (columns past hd, rows past the group's heads) once
-    {
-      uint4 z = make_uint4(0, 0, 0, 0);
-      uint4* p = reinterpret_cast<uint4*>(smem_raw);
-      const int n16 = ((HEADS + 2 * STAGES * BK) * STRIDE * (int)sizeof(bf16)) / 16;
-      for (int i = lane; i < n16; i += 32) p[i] = z;
-    }
-    __syncwarp();
+
     {
       const int cpr = hd >> 3;
       for (int c = lane; c < n_heads * cpr; c += 32) {
@@ -277,25 +285,48 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 // out[s, h, :] = sum_split 2^(m_split - M) o_split / sum_split 2^(m_split - M) l_split
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int out_stride, int H, int hd, int n_splits) {
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_wait();
   const int h = blockIdx.x, s = blockIdx.y;
   const float* ml = part_ml + ((size_t)s * H + h) * n_splits * 2;
   const float* po = part_o + ((size_t)s * H + h) * n_splits * hd;
   float M = -INFINITY;
-  for (int i = 0; i < n_splits; ++i) M = fmaxf(M, ml[2 * i]);
+  for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(ml + 2 * i));
   float L = 0.f;
   for (int i = 0; i < n_splits; ++i) {
-    const float m = ml[2 * i];
-    if (m != -INFINITY) L += exp2f(m - M) * ml[2 * i + 1];
+    const float m = __ldcg(ml + 2 * i);
+    if (m != -INFINITY) L += exp2f(m - M) * __ldcg(ml + 2 * i + 1);
   }
   const float inv = 1.0f / L;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
     for (int i = 0; i < n_splits; ++i) {
-      const float m = ml[2 * i];
-      if (m != -INFINITY) o += exp2f(m - M) * po[(size_t)i * hd + d];
+      const float m = __ldcg(ml + 2 * i);
+      if (m != -INFINITY) o += exp2f(m - M) * __ldcg(po + (size_t)i * hd + d);
     }
     out[(size_t)s * out_stride + (size_t)h * hd + d] = __float2bfloat16_rn(o * inv);
   }
+}
+
+template <int HD, int STAGES>
+static int launch_decode_stages(const bf16* q, int q_stride, const bf16* k_pages, const bf16* v_pages,
+                         const int* block_table, int table_width, const int* seq_len, float* part_o,
+                         float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
+                         float scale, int n_splits, cudaStream_t stream) {
+  const size_t smem = (size_t)(HEADS + 2 * STAGES * BK) * (HD + 8) * sizeof(bf16);
+  auto kern = attn_decode_split_kernel<HD, STAGES>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) RL_REFUSE(8, "attn_decode: cannot get %zu bytes of shared memory", smem);
+  }
+  const int G = H / K;
+  dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
+  RL_LAUNCH_CHECK(rl_launch(kern, grid, 32, smem, stream, q, q_stride, k_pages, v_pages, block_table, table_width, seq_len,
+                            part_o, part_ml, H, K, hd, window, scale * 1.4426950408889634f, n_splits));
+  dim3 grid2(H, n_seqs);
+  RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
+                            out, out_stride, H, hd, n_splits));
+  return 0;
 }
 
 template <int HD>
@@ -303,24 +334,19 @@ static int launch_decode(const bf16* q, int q_stride, const bf16* k_pages, const
                          const int* block_table, int table_width, const int* seq_len, float* part_o,
                          float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
                          float scale, int n_splits, cudaStream_t stream) {
-  const size_t smem = (size_t)(HEADS + 2 * STAGES * BK) * (HD + 8) * sizeof(bf16);
-  auto kern = attn_decode_split_kernel<HD>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) RL_REFUSE(8, "attn_decode: cannot get %zu bytes of shared memory", smem);
+  // Three stages (measured best at batch 8 and 64 once the splits are chosen to fill the GPU once);
+  // RL_ATTN_STAGES=2 in the environment selects two, for measurements.
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("RL_ATTN_STAGES");
+    forced = e ? atoi(e) : 0;
   }
-  const int G = H / K;
-  dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
-  kern<<<grid, 32, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
-                                   H, K, hd, window, scale * 1.4426950408889634f, n_splits);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) {
-    snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(e));
-    return (int)e;
-  }
-  dim3 grid2(H, n_seqs);
-  attn_decode_merge_kernel<<<grid2, 128, 0, stream>>>(part_o, part_ml, out, out_stride, H, hd, n_splits);
-  RL_LAUNCH_RESULT();
+  const int stages = forced == 2 ? 2 : 3;
+  if (stages == 2)
+    return launch_decode_stages<HD, 2>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
+                                       out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, stream);
+  return launch_decode_stages<HD, 3>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
+                                     out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, stream);
 }
 
 // Scratch needed, in floats: n_seqs * H * n_splits * (hd + 2); the caller passes part_o of

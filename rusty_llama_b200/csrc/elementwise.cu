@@ -16,13 +16,15 @@ RL_DEFINE_ERROR_TEXT()
 template <typename TW, bool VEC>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                     float* __restrict__ out, int d) {
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_wait();
   const int t = blockIdx.x;
   const TW* row = table + (size_t)tokens[t] * d;
   float* o = out + (size_t)t * d;
   if (VEC) {  // d is a multiple of 4: every thread moves four values per round, all loads in flight at once
     for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
       float v[4];
-      load4<TW>(row + i, v);
+      load4_g<TW>(row + i, v);
       store4<float>(o + i, v);
     }
   } else {
@@ -40,16 +42,16 @@ RL_API int rl_embed_gather(const int* tokens, const void* table, int table_dtype
   if (n_tokens <= 0 || d <= 0) RL_REFUSE(1, "embed_gather: n_tokens=%d d=%d", n_tokens, d);
   const int th = row_threads(d);
   if (table_dtype == RL_BF16 && d % 4 == 0)
-    embed_gather_kernel<bf16, true><<<n_tokens, th, 0, stream>>>(tokens, (const bf16*)table, out, d);
+    RL_LAUNCH_CHECK(rl_launch(embed_gather_kernel<bf16, true>, n_tokens, th, 0, stream, tokens, (const bf16*)table, out, d));
   else if (table_dtype == RL_BF16)
-    embed_gather_kernel<bf16, false><<<n_tokens, 256, 0, stream>>>(tokens, (const bf16*)table, out, d);
+    RL_LAUNCH_CHECK(rl_launch<false>(embed_gather_kernel<bf16, false>, n_tokens, 256, 0, stream, tokens, (const bf16*)table, out, d));
   else if (table_dtype == RL_F32 && d % 4 == 0)
-    embed_gather_kernel<float, true><<<n_tokens, th, 0, stream>>>(tokens, (const float*)table, out, d);
+    RL_LAUNCH_CHECK(rl_launch(embed_gather_kernel<float, true>, n_tokens, th, 0, stream, tokens, (const float*)table, out, d));
   else if (table_dtype == RL_F32)
-    embed_gather_kernel<float, false><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, out, d);
+    RL_LAUNCH_CHECK(rl_launch<false>(embed_gather_kernel<float, false>, n_tokens, 256, 0, stream, tokens, (const float*)table, out, d));
   else
     RL_REFUSE(2, "embed_gather: unknown table dtype %d", table_dtype);
-  RL_LAUNCH_RESULT();
+  return 0;
 }
 
 // ---------------------------------------------------------------- residual sum + RMSNorm
@@ -69,6 +71,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const int* __restrict__ rows, int d, float eps, int write_x) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_wait();
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * d;
@@ -76,10 +80,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   if (VEC) {
     for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
       float v[4];
-      load4<float>(xr + i, v);
+      load4_g<float>(xr + i, v);
       for (int p = 0; p < n_parts; ++p) {
         float dv[4];
-        load4<TD>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv);
+        load4_g<TD>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv);
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[e] += dv[e];
       }
@@ -105,7 +109,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
       float v[4], wv[4];
       load4<float>(row + i, v);
-      load4<TW>(w + i, wv);
+      load4_g<TW>(w + i, wv);
 #pragma unroll
       for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * wv[e];
       store4<TA>(o + i, v);
@@ -127,9 +131,13 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_parts, long lon
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(4, "add_rmsnorm: cannot get %zu bytes of shared memory", smem);
   }
-  kern<<<n_rows, vec ? row_threads(d) : 256, smem, stream>>>(x, (const TD*)delta, n_parts, part_stride,
-                                                             (const TW*)w, (TA*)out, rows, d, eps, write_x);
-  RL_LAUNCH_RESULT();
+  if (vec)
+    RL_LAUNCH_CHECK(rl_launch(kern, n_rows, row_threads(d), smem, stream, x, (const TD*)delta, n_parts, part_stride,
+                              (const TW*)w, (TA*)out, rows, d, eps, write_x));
+  else  // the element-by-element variant uses ordinary loads: plain stream order for it
+    RL_LAUNCH_CHECK(rl_launch<false>(kern, n_rows, 256, smem, stream, x, (const TD*)delta, n_parts, part_stride,
+                                     (const TW*)w, (TA*)out, rows, d, eps, write_x));
+  return 0;
 }
 
 RL_API int rl_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride,

@@ -246,6 +246,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  // barriers and tensor memory are set up: from here on the kernel reads what its predecessor wrote
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------- producer
@@ -441,12 +444,13 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     auto kern = gemm_tc_kernel<TOUT, SW>;                                                                         \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
       RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
-    kern<<<grid, NUM_THREADS, smem, stream>>>(map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store, k_splits, status);         \
+    RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store,  \
+                              k_splits, status));                                                                 \
   } while (0)
   if (out_dtype == RL_BF16 && swiglu) RL_TC_LAUNCH(bf16, true);
   else if (out_dtype == RL_BF16) RL_TC_LAUNCH(bf16, false);
   else if (swiglu) RL_TC_LAUNCH(float, true);
   else RL_TC_LAUNCH(float, false);
 #undef RL_TC_LAUNCH
-  RL_LAUNCH_RESULT();
+  return 0;
 }

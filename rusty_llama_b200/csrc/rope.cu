@@ -22,6 +22,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const float* __restrict__ inv_freq, int H, int K, int hd, int rot,
                                      int interleaved, int page_size, int write_kv) {
   extern __shared__ float trig[];  // cos[rot/2], sin[rot/2]
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int half = rot >> 1;
@@ -90,6 +92,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride, co
                                          const float* __restrict__ inv_freq, int H, int K, int hd, int rot,
                                          int interleaved, int page_size, int write_kv) {
   extern __shared__ float trig[];
+  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int half = rot >> 1;
@@ -128,12 +132,12 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride, co
       if (gq >= rot_groups) {  // unrotated tail of a key head
         const int i = rot + 4 * (gq - rot_groups);
         float v[4];
-        load4<T>(head + i, v);
+        load4_g<T>(head + i, v);
         store4<T>(dst + i, v);
       } else if (interleaved) {
         const int i = 4 * gq, j = 2 * gq;
         float v[4], o[4];
-        load4<T>(head + i, v);
+        load4_g<T>(head + i, v);
         o[0] = v[0] * cs[j] - v[1] * sn[j];
         o[1] = v[0] * sn[j] + v[1] * cs[j];
         o[2] = v[2] * cs[j + 1] - v[3] * sn[j + 1];
@@ -142,8 +146,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride, co
       } else {
         const int j = 4 * gq;
         float a[4], b[4], oa[4], ob[4];
-        load4<T>(head + j, a);
-        load4<T>(head + j + half, b);
+        load4_g<T>(head + j, a);
+        load4_g<T>(head + j + half, b);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           oa[e] = a[e] * cs[j + e] - b[e] * sn[j + e];
@@ -156,7 +160,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride, co
       const int idx = item - n_q - n_k;
       const int h = idx / (hd / 4), i = 4 * (idx - h * (hd / 4));
       float v[4];
-      load4<T>(row + (size_t)(H + K + h) * hd + i, v);
+      load4_g<T>(row + (size_t)(H + K + h) * hd + i, v);
       store4<T>(v_pages + page_base + (size_t)h * page_size * hd + i, v);
     }
   }
@@ -175,32 +179,22 @@ RL_API int rl_rope_kv_write(void* qkv, int dtype, int row_stride, const int* tok
   const size_t smem = (size_t)rot * sizeof(float);
   if (smem > 48 * 1024) RL_REFUSE(6, "rope_kv_write: rotary size %d too large", rot);
   const bool vec = hd % 4 == 0 && row_stride % 4 == 0 && (interleaved ? rot % 4 == 0 : rot % 8 == 0);
+  int threads = 128;
   if (vec) {
     const int items = H * (rot / 8 + 1) + (write_kv ? K * (hd / 4) * 2 : 0);
-    int threads = ((items + 31) / 32) * 32;
+    threads = ((items + 31) / 32) * 32;
     threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
-    if (dtype == RL_BF16)
-      rope_kv_write_vec_kernel<bf16><<<n_tokens, threads, smem, stream>>>(
-          (bf16*)qkv, row_stride, tok_pos, tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq, H,
-          K, hd, rot, interleaved, page_size, write_kv);
-    else if (dtype == RL_F32)
-      rope_kv_write_vec_kernel<float><<<n_tokens, threads, smem, stream>>>(
-          (float*)qkv, row_stride, tok_pos, tok_seq, block_table, table_width, (float*)k_pages, (float*)v_pages, inv_freq,
-          H, K, hd, rot, interleaved, page_size, write_kv);
-    else
-      RL_REFUSE(7, "rope_kv_write: unknown dtype %d", dtype);
-    RL_LAUNCH_RESULT();
   }
-  if (dtype == RL_BF16)
-    rope_kv_write_kernel<bf16><<<n_tokens, 128, smem, stream>>>((bf16*)qkv, row_stride, tok_pos, tok_seq, block_table,
-                                                               table_width, (bf16*)k_pages, (bf16*)v_pages, inv_freq,
-                                                               H, K, hd, rot, interleaved, page_size, write_kv);
-  else if (dtype == RL_F32)
-    rope_kv_write_kernel<float><<<n_tokens, 128, smem, stream>>>((float*)qkv, row_stride, tok_pos, tok_seq,
-                                                                 block_table, table_width, (float*)k_pages,
-                                                                 (float*)v_pages, inv_freq, H, K, hd, rot,
-                                                                 interleaved, page_size, write_kv);
-  else
-    RL_REFUSE(7, "rope_kv_write: unknown dtype %d", dtype);
-  RL_LAUNCH_RESULT();
+  // only the four-at-a-time kernel (L2 loads) may start before its predecessor has finished
+#define RL_ROPE(KERNEL, T, EARLY)                                                                                      \
+  RL_LAUNCH_CHECK(rl_launch<EARLY>(KERNEL<T>, n_tokens, threads, smem, stream, (T*)qkv, row_stride, tok_pos, tok_seq,   \
+                                   block_table, table_width, (T*)k_pages, (T*)v_pages, inv_freq, H, K, hd, rot,       \
+                                   interleaved, page_size, write_kv))
+  if (dtype == RL_BF16 && vec) RL_ROPE(rope_kv_write_vec_kernel, bf16, true);
+  else if (dtype == RL_BF16) RL_ROPE(rope_kv_write_kernel, bf16, false);
+  else if (dtype == RL_F32 && vec) RL_ROPE(rope_kv_write_vec_kernel, float, true);
+  else if (dtype == RL_F32) RL_ROPE(rope_kv_write_kernel, float, false);
+  else RL_REFUSE(7, "rope_kv_write: unknown dtype %d", dtype);
+#undef RL_ROPE
+  return 0;
 }

@@ -31,7 +31,36 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
 
 __device__ int block_argmax(const float* row, int n, float t, ArgMax* sh) {
   ArgMax best = {-INFINITY, -1};
-  for (int i = threadIdx.x; i < n; i += blockDim.x) best = better(best, ArgMax{row[i] / t, i});
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // four values per load, four loads in flight: a row of 128k logits is scanned by one block,
+    // which would otherwise wait for one load after the other
+    const int n4 = n >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    int i = threadIdx.x;
+    for (; i + 3 * (int)blockDim.x < n4; i += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = r4[i + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int base = 4 * (i + u * blockDim.x);
+        best = better(best, ArgMax{v[u].x / t, base});
+        best = better(best, ArgMax{v[u].y / t, base + 1});
+        best = better(best, ArgMax{v[u].z / t, base + 2});
+        best = better(best, ArgMax{v[u].w / t, base + 3});
+      }
+    }
+    for (; i < n4; i += blockDim.x) {
+      const float4 v = r4[i];
+      best = better(best, ArgMax{v.x / t, 4 * i});
+      best = better(best, ArgMax{v.y / t, 4 * i + 1});
+      best = better(best, ArgMax{v.z / t, 4 * i + 2});
+      best = better(best, ArgMax{v.w / t, 4 * i + 3});
+    }
+    for (int j = 4 * n4 + threadIdx.x; j < n; j += blockDim.x) best = better(best, ArgMax{row[j] / t, j});
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) best = better(best, ArgMax{row[i] / t, i});
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     ArgMax other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};

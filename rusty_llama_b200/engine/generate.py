@@ -43,6 +43,10 @@ class GenerationStats:
     decode_steps: int = 0
     prefill_seconds: float = 0.0
     decode_seconds: float = 0.0
+    # host time inside the calls of the decode phase (part of decode_seconds): building and
+    # launching steps, which the GPU waits for, and sampling, which mostly waits for the GPU
+    decode_step_call_seconds: float = 0.0
+    decode_sample_call_seconds: float = 0.0
 
 
 @dataclass
@@ -139,7 +143,10 @@ def generate(
                 stats.prompt_tokens += s.length
             first = True
             while running:
+                t_call = time.perf_counter()
                 tokens = sampler.sample(logits, [s.slot for s in running], params).tolist()
+                if not first:
+                    stats.decode_sample_call_seconds += time.perf_counter() - t_call
                 if first:
                     check = getattr(engine, "check_device_status", None)
                     if check is not None:
@@ -173,7 +180,9 @@ def generate(
                 running = still
                 if not running:
                     break
+                t_call = time.perf_counter()
                 logits = engine.step([StepEntry(s.slot, [s.next_token], [0]) for s in running])
+                stats.decode_step_call_seconds += time.perf_counter() - t_call
                 stats.decode_steps += 1
                 for s in running:
                     s.length += 1

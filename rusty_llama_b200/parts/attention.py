@@ -13,9 +13,9 @@ from ..kernels.linear import linear, linear_to_stream
 from ..spec import PartSpec
 from .base import MIXERS, POSITIONS, KVNeed, Mixer, ParamInfo
 
-# one-warp blocks the decode kernel should have on the whole GPU before more splits stop
-# paying: a bit more than what a 148-SM part holds at four blocks per SM (its shared memory's limit)
-_DECODE_TARGET_BLOCKS = 888
+# one-warp blocks of the decode kernel that a 148-SM part holds at once (four per SM at head size
+# 128, its shared memory's limit): measured best when the splits fill that and no more
+_DECODE_TARGET_BLOCKS = 592
 _DECODE_HEADS_PER_BLOCK = 8
 
 
@@ -24,7 +24,7 @@ def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int) -
     group = num_heads // num_kv_heads
     per_split = n_seqs * num_kv_heads * ((group + _DECODE_HEADS_PER_BLOCK - 1) // _DECODE_HEADS_PER_BLOCK)
     tiles = max(1, (kv_len + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE)
-    want = (_DECODE_TARGET_BLOCKS + per_split - 1) // per_split
+    want = _DECODE_TARGET_BLOCKS // per_split
     return max(1, min(want, tiles, 64))
 
 
