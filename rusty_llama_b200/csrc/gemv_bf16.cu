@@ -82,11 +82,7 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
       a1[u] = (k_ok && row1_ok) ? ld_stream(w1 + k) : zero;
     }
   };
-  // the first weights are requested before the wait for the previous kernel: weights are never
-  // written by a kernel, the activations may still be on their way
   request(kb_begin + warp);
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
-  pdl_wait();
   for (int kb = kb_begin + warp; kb < kb_end; kb += WARPS * U) {
     if (kb != kb_begin + warp) request(kb);
 #pragma unroll
@@ -97,7 +93,7 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const int m = nt * 8 + g;
-        b[nt] = (k_ok && m < M) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k)) : zero;
+        b[nt] = (k_ok && m < M) ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k)) : zero;
       }
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -147,13 +143,13 @@ static int launch_gemv(const bf16* x, int ldx, const bf16* w, int ldw, void* out
                        int N, int K, int swiglu, int k_splits, cudaStream_t stream) {
   const dim3 blocks((N + 15) / 16, k_splits);
   if (swiglu && out_dtype == RL_F32)
-    RL_LAUNCH_CHECK(rl_launch(gemv_bf16_kernel<NT, float, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, float, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K));
   else if (swiglu)
-    RL_LAUNCH_CHECK(rl_launch(gemv_bf16_kernel<NT, bf16, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, bf16, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K));
   else if (out_dtype == RL_F32)
-    RL_LAUNCH_CHECK(rl_launch(gemv_bf16_kernel<NT, float, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, float, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K));
   else
-    RL_LAUNCH_CHECK(rl_launch(gemv_bf16_kernel<NT, bf16, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, bf16, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K));
   return 0;
 }
 

@@ -78,7 +78,9 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     N = w.shape[0]
     if x.dtype != torch.bfloat16:
         return linear(x, w)
-    if M <= STREAM_MAX_ROWS:
+    if M <= STREAM_MAX_ROWS and K <= 8192:
+        # (for a long k the tcgen05 kernel below is faster even at one row: 25 us against 32 us
+        # for the 8B down projection)
         blocks = (N + 15) // 16
         splits = min((_STREAM_TARGET_BLOCKS + blocks - 1) // blocks, 8, max(1, K // 1024))
         if splits > 1:
