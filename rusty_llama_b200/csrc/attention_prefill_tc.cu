@@ -1,0 +1,458 @@
+// Causal flash attention for prompts on the 5th-generation tensor cores, head size 128, bfloat16,
+// reading keys and values from the paged cache.  Same contract as `flash_prefill` (ragged batch,
+// positions from seq_pos0, optional window); the reference's counterpart is its scalar
+// `attention_kernel` (src/backend/cuda.rs:157-232).
+//
+// A block owns 128 query rows of one head of one sequence and walks over key tiles of 128
+// positions (two cache pages):
+//   warp 8 (one lane)  TMA: the Q tile once, then K and V tiles (four 64 x 64 boxes each, straight
+//                      from their pages, 128-byte swizzled) into two-stage rings;
+//   warp 9 (one lane)  tcgen05.mma: S = Q K^T (128 x 128, k = head size) into one of two S buffers
+//                      in tensor memory, always one tile ahead; then O += P V (k = 128 keys) into
+//                      the output accumulator, which stays in tensor memory for the whole block,
+//                      with V read as the M/N-contiguous operand it is;
+//   warps 0-7          two threads per query row (warps w and w + 4 share the tensor-memory lanes of
+//                      rows 32w.., each takes 64 of the 128 keys: one softmax warp per scheduler
+//                      cannot hide its own latencies, two can): read the half row of S with
+//                      tcgen05.ld (one round trip), its maximum without any shuffle, exchange the
+//                      two halves' maxima through shared memory, P = 2^(s - m) rounded to bfloat16
+//                      and written to one of two shared-memory buffers in the swizzled k-major
+//                      layout the tensor core expects.  The running maximum m is only raised when the new one
+//                      exceeds it by more than 8 (P then stays below 2^8, harmless in bfloat16 and
+//                      32-bit sums); raising it means rescaling the accumulator in tensor memory
+//                      (tcgen05.ld, multiply, tcgen05.st), which after the first tiles is rare.  At
+//                      the end the row's output is read once and divided by the row sum.
+// Softmax statistics, the accumulator and the final division are 32-bit.
+//
+// Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
+#include "tc_common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define HD 128
+#define BMQ 128          // query rows per block
+#define BNK 128          // keys per tile
+#define PAGE 64
+#define KV_STAGES 2
+#define SUB_BYTES (128 * 64 * 2)        // one [128 rows][64 columns] swizzled sub-tile: 16 KB
+#define TILE_BYTES (2 * SUB_BYTES)      // a 128 x 128 bf16 tile: 32 KB
+#define SOFTMAX_WARPS 8
+#define NUM_THREADS ((SOFTMAX_WARPS + 2) * 32)
+#define HALF_COLS (BNK / 2)
+#define TMEM_COLS 512                   // S0 at 0, S1 at 128, O at 256
+#define RESCALE_THRESHOLD 8.0f          // in base-2 exponents
+
+struct SmallItems {
+  uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2], p_ready, pv_done[2];
+  uint64_t pair_bar[4];            // the two warps of a lane quarter meet here
+  float pair_val[2][2][BMQ];       // [tile parity][column half][row]
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+#define SMEM_BYTES ((3 + 2 * KV_STAGES) * TILE_BYTES + 3072)
+static_assert(sizeof(SmallItems) <= 3072, "the small items must fit behind the tiles");
+static_assert(SMEM_BYTES <= 227 * 1024, "more shared memory than a block can have");
+
+// 2^x for x <= 8 or so; -inf gives 0
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
+                        const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
+                        int out_stride, int H, int K, int window, float scale_log2, int* __restrict__ status) {
+  // All shared memory is dynamic, so that the seven 32 KB tiles start at the block's first byte
+  // (1024-byte aligned, as the 128-byte swizzle needs) and the small items fit behind them.
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  unsigned char* q_s = smem_dyn;                           // 32 KB
+  unsigned char* k_s = q_s + TILE_BYTES;                   // KV_STAGES x 32 KB
+  unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;       // KV_STAGES x 32 KB
+  unsigned char* p_s = v_s + KV_STAGES * TILE_BYTES;       // 2 x 32 KB
+  SmallItems& sm = *reinterpret_cast<SmallItems*>(p_s + 2 * TILE_BYTES);
+  uint64_t& q_full = sm.q_full;
+  uint64_t(&k_full)[KV_STAGES] = sm.k_full;
+  uint64_t(&k_empty)[KV_STAGES] = sm.k_empty;
+  uint64_t(&v_full)[KV_STAGES] = sm.v_full;
+  uint64_t(&v_empty)[KV_STAGES] = sm.v_empty;
+  uint64_t(&s_full)[2] = sm.s_full;
+  uint64_t& p_ready = sm.p_ready;
+  uint64_t(&pv_done)[2] = sm.pv_done;
+  uint64_t(&pair_bar)[4] = sm.pair_bar;
+  float(&pair_val)[2][2][BMQ] = sm.pair_val;
+  uint32_t& tmem_slot = sm.tmem_slot;
+  int& abort_flag = sm.abort_flag;
+  if (smem_u32(smem_dyn) & 1023u) {  // uniform over the block; nothing has been set up yet
+    if (threadIdx.x == 0) atomicExch(status, 23);
+    return;
+  }
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s = blockIdx.z, h = blockIdx.y;
+  const int tok0 = seq_start[s];
+  const int q_len = seq_start[s + 1] - tok0;
+  // late row tiles have the most keys to visit: they are handed out first
+  const int row0 = (int)(gridDim.x - 1 - blockIdx.x) * BMQ;
+  if (row0 >= q_len) return;  // before any barrier or tensor-memory use: the whole block leaves
+  const int pos0 = seq_pos0[s];
+  const int kh = h / (H / K);
+  const int rows_here = min(BMQ, q_len - row0);
+  const int first_pos = pos0 + row0, last_pos = first_pos + rows_here - 1;
+  const int lowest_key = (window != 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+  const int tile_lo = lowest_key / BNK, tile_hi = last_pos / BNK;
+  const int n_tiles = tile_hi - tile_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(&p_ready, SOFTMAX_WARPS);  // one arrival per softmax warp
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == SOFTMAX_WARPS + 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == SOFTMAX_WARPS) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, TILE_BYTES);
+      tma_load_2d(q_s, &map_q, &q_full, h * HD, tok0 + row0);
+      tma_load_2d(q_s + SUB_BYTES, &map_q, &q_full, h * HD + 64, tok0 + row0);
+      const int* table = block_table + (size_t)s * table_width;
+      bool ok = true;
+      int issued_k = 0, issued_v = 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t round = j / KV_STAGES;
+        const int tile = tile_lo + j;
+        int pages[2];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int idx = 2 * tile + p;
+          pages[p] = idx < table_width ? table[idx] : 0;  // a page past the sequence's end is never attended to
+        }
+        // K
+        if (round > 0 && !mbar_wait(&k_empty[st], (round - 1) & 1)) {
+          atomicExch(status, 11);
+          abort_flag = 1;
+          break;
+        }
+        if (*(volatile int*)&abort_flag) break;
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+            tma_load_4d(k_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_k, &k_full[st], 64 * b, 0, kh, pages[p]);
+        issued_k = j + 1;
+        // V
+        if (round > 0 && !mbar_wait(&v_empty[st], (round - 1) & 1)) {
+          atomicExch(status, 12);
+          abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+            tma_load_4d(v_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_v, &v_full[st], 64 * b, 0, kh, pages[p]);
+        issued_v = j + 1;
+      }
+      // nothing may still be writing shared memory when the block ends: if someone gave up, wait
+      // (bounded) for the copies that were started
+      if (*(volatile int*)&abort_flag) {
+        mbar_wait(&q_full, 0);
+        for (int j = max(0, issued_k - KV_STAGES); j < issued_k; ++j) mbar_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+        for (int j = max(0, issued_v - KV_STAGES); j < issued_v; ++j) mbar_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+      }
+    }
+  } else if (warp == SOFTMAX_WARPS + 1) {
+    // ---------------- tensor-core issuer
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc_bf16(BMQ, BNK, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(BMQ, HD, 0, 1);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      bool ok = mbar_wait(&q_full, 0);
+      if (!ok) {
+        atomicExch(status, 13);
+        abort_flag = 1;
+      }
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j % KV_STAGES;
+        if (!mbar_wait(&k_full[st], (j / KV_STAGES) & 1)) {
+          atomicExch(status, 14);
+          abort_flag = 1;
+          return false;
+        }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(k_s + (size_t)st * TILE_BYTES);
+        const uint32_t tmem_s = tmem_base + (uint32_t)((j & 1) * BNK);
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_s, make_smem_desc(q_addr + b * SUB_BYTES + kk * 32), make_smem_desc(k_addr + b * SUB_BYTES + kk * 32),
+                      idesc_qk, (b > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);  // S of the next tile is computed while this tile's softmax runs
+        if (!ok) break;
+        if (!mbar_wait(&p_ready, j & 1)) {
+          atomicExch(status, 15);
+          abort_flag = 1;
+          break;
+        }
+        const int st = j % KV_STAGES;
+        if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1)) {
+          atomicExch(status, 16);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(v_s + (size_t)st * TILE_BYTES);
+        const uint32_t tmem_o = tmem_base + 2 * BNK;
+        const uint32_t pj_addr = p_addr + (uint32_t)((j & 1) * TILE_BYTES);
+        // O[128 rows x 128 dims] += P[128 x 128 keys] . V[128 keys x 128 dims]; a k step is 16 keys
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_o, make_smem_desc(pj_addr + (kk >> 2) * SUB_BYTES + (kk & 3) * 32),
+                    make_smem_desc_mn(v_addr + kk * 2048, SUB_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&v_empty[st]);
+        umma_commit(&pv_done[j & 1]);
+      }
+    }
+  } else {
+    // ---------------- softmax and output: warps w and w + 4 own tensor-memory lanes 32(w % 4)..+31,
+    // thread = (query row, half of the columns)
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;
+    const int qpos = first_pos + r;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t o_addr = lane_addr + 2 * BNK + half * (HD / 2);
+    float m_run = -INFINITY, l_run = 0.f;   // m_run in units of raw scores times scale_log2
+    uint32_t pair_phase = 0;
+    bool ok = true;
+    auto give_up = [&](int code) {
+      if (lane == 0) {
+        atomicExch(status, code);
+        abort_flag = 1;
+      }
+      ok = false;
+    };
+    // both halves of a row learn the other's value: write, arrive, wait (bounded), read
+    auto exchange = [&](float mine, int parity_slot, float& other) -> bool {
+      pair_val[parity_slot][half][r] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[quarter]);
+      if (!mbar_wait(&pair_bar[quarter], pair_phase)) return false;
+      pair_phase ^= 1;
+      other = pair_val[parity_slot][half ^ 1][r];
+      return true;
+    };
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) {
+        give_up(17);
+        break;
+      }
+      if (*(volatile int*)&abort_flag) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int key0 = (tile_lo + j) * BNK + half * HALF_COLS;
+      const bool need_mask = (tile_lo + j) * BNK + BNK - 1 > first_pos || window != 0;
+      const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * BNK + half * HALF_COLS);
+      // this thread's half of the row of S in one round trip
+      uint32_t v[HALF_COLS];
+#pragma unroll
+      for (int c = 0; c < HALF_COLS / 32; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      tmem_ld_wait();
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < HALF_COLS; ++i) {
+          const int key = key0 + i;
+          if (key > qpos || (window != 0 && qpos - key >= window)) v[i] = __float_as_uint(-INFINITY);
+          mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < HALF_COLS; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+      }
+      float mx_other;
+      if (!exchange(mx, j & 1, mx_other)) {
+        give_up(21);
+        break;
+      }
+      mx = fmaxf(mx, mx_other) * scale_log2;   // the scale is positive: the maximum commutes with it
+      // raise the running maximum only when it pays (see the header); the first tile sets it
+      const bool raise = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx != -INFINITY);
+      const float m_next = raise ? mx : m_run;
+      if (j > 0 && __any_sync(0xffffffffu, raise && m_run != -INFINITY)) {
+        // the accumulator holds sums scaled by 2^-m_run: bring this warp's rows and columns to 2^-m_next
+        if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) {
+          give_up(18);
+          break;
+        }
+        tc_fence_after();
+        const float a = (raise && m_run != -INFINITY) ? exp2f(m_run - m_next) : 1.0f;
+#pragma unroll 1
+        for (int c = 0; c < HD / 64; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(o_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * a);
+          tmem_st_32x32b_x32(o_addr + c * 32, o);
+        }
+        tmem_st_wait();
+        l_run *= a;
+      }
+      m_run = m_next;
+      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;  // a row past the sequence's end may see nothing
+      // the P buffer of this tile was last read by the product of tile j - 2
+      if (j >= 2 && !mbar_wait(&pv_done[j & 1], ((j - 2) >> 1) & 1)) {
+        give_up(19);
+        break;
+      }
+      float row_sum = 0.f;
+      unsigned char* p_sub = p_s + (size_t)(j & 1) * TILE_BYTES + half * SUB_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < HALF_COLS / 8; ++c8) {  // eight keys = one 16-byte piece of the row
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = exp2_fast(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2, neg_m));
+          const float p1 = exp2_fast(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2, neg_m));
+          row_sum += p0 + p1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          pk[e] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        // piece c8 of the row's 128 bytes in this half's sub-tile, swizzled
+        *reinterpret_cast<uint4*>(p_sub + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l_run += row_sum;
+      // P is complete (and the accumulator rescaled if it had to be): hand both to the tensor core
+      tc_fence_before();
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready);
+    }
+    if (ok && !mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) give_up(20);
+    float l_other = 0.f;
+    if (ok && !exchange(l_run, n_tiles & 1, l_other)) give_up(22);
+    if (ok) {
+      tc_fence_after();
+      const float l_all = l_run + l_other;
+      const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+      bf16* o = out + (size_t)(tok0 + row0 + r) * out_stride + (size_t)h * HD + half * (HD / 2);
+#pragma unroll 1
+      for (int c = 0; c < HD / 64; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(o_addr + c * 32, v);
+        tmem_ld_wait();
+        if (r < rows_here) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(o + c * 32 + i) = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                                                   *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+RL_API int rl_flash_prefill_tc_head_dim() { return HD; }
+
+// status: one int in device memory, 0 before the call; afterwards non-zero means that a bounded wait
+// expired (11-22: which one; 23: shared memory not aligned) and the output is not valid.
+RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
+                               int n_pages, const int* block_table, int table_width, const int* seq_start,
+                               const int* seq_pos0, void* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
+                               int hd, int page_size, int window, float scale, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || n_tokens <= 0 || n_pages <= 0)
+    RL_REFUSE(1, "flash_prefill_tc: S=%d max_q=%d H=%d K=%d T=%d pages=%d", n_seqs, max_q_len, H, K, n_tokens, n_pages);
+  if (hd != HD) RL_REFUSE(2, "flash_prefill_tc: head size %d, this kernel is built for %d", hd, HD);
+  if (H % K) RL_REFUSE(3, "flash_prefill_tc: %d query heads are not a multiple of %d kv heads", H, K);
+  if (page_size != PAGE) RL_REFUSE(4, "flash_prefill_tc: page size %d, this kernel is built for %d", page_size, PAGE);
+  if (q_stride % 8 || out_stride % 8) RL_REFUSE(5, "flash_prefill_tc: strides %d/%d break 16-byte alignment", q_stride, out_stride);
+  if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) RL_REFUSE(6, "flash_prefill_tc: operands must be 16-byte aligned");
+  if (H > 65535 || n_seqs > 65535) RL_REFUSE(7, "flash_prefill_tc: H=%d or S=%d exceeds 65535", H, n_seqs);
+  if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "flash_prefill_tc: bad window or scale, or no status word");
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) RL_REFUSE(9, "flash_prefill_tc: cuTensorMapEncodeTiled is not available");
+  CUtensorMap map_q, map_k, map_v;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)q_stride, (cuuint64_t)n_tokens};
+    cuuint64_t strides[1] = {(cuuint64_t)q_stride * 2};
+    cuuint32_t box[2] = {64, BMQ};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
+  }
+  for (int which = 0; which < 2; ++which) {
+    cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)PAGE, (cuuint64_t)K, (cuuint64_t)n_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)PAGE * HD * 2, (cuuint64_t)K * PAGE * HD * 2};
+    cuuint32_t box[4] = {64, PAGE, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_pages : k_pages), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      RL_REFUSE(11, "flash_prefill_tc: cannot describe the cache pages to TMA");
+  }
+  const size_t smem = SMEM_BYTES;
+  auto kern = flash_prefill_tc_kernel;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    RL_REFUSE(12, "flash_prefill_tc: cannot get %zu bytes of shared memory", smem);
+  dim3 grid((max_q_len + BMQ - 1) / BMQ, H, n_seqs);
+  kern<<<grid, NUM_THREADS, smem, stream>>>(map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0, (bf16*)out, out_stride,
+                                            H, K, window, scale * 1.4426950408889634f, status);
+  RL_LAUNCH_RESULT();
+}

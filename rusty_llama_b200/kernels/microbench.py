@@ -125,9 +125,12 @@ def bench_flash_prefill(a) -> dict:
     q = torch.randn(T, (H + 2 * K) * hd, device=dev, dtype=torch.bfloat16)
     seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
     pos0 = torch.zeros(1, dtype=torch.int32, device=dev)
-    us = _time(lambda i: ops.flash_prefill(q, ks[0], vs[0], table, seq_start, pos0, T, H, K, hd), 1, a.iters, a.warmup)
+    fn = ops.flash_prefill_tc if a.impl == "tc" else ops.flash_prefill
+    us = _time(lambda i: fn(q, ks[0], vs[0], table, seq_start, pos0, T, H, K, hd), 1, a.iters, a.warmup)
+    if a.impl == "tc":
+        ops.tc_status_check()
     flops = 4.0 * T * T * hd * H / 2
-    return {"kernel": "flash_prefill", "tokens": T, "H": H, "K": K, "hd": hd, "us": round(us, 2), "causal_TFLOPs": round(flops / us / 1e6, 1)}
+    return {"kernel": "flash_prefill_tc" if a.impl == "tc" else "flash_prefill", "tokens": T, "H": H, "K": K, "hd": hd, "us": round(us, 2), "causal_TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def bench_rows(a) -> dict:
@@ -153,7 +156,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
-    ap.add_argument("--impl", default="linear", choices=["linear", "tc"], help="gemm: the dispatching linear() or the tcgen05 kernel")
+    ap.add_argument("--impl", default="linear", choices=["linear", "tc"], help="gemm: the dispatching linear() or the tcgen05 kernel; flash_prefill: tc = the tcgen05 kernel")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch the timed calls one by one instead of as one graph")

@@ -345,6 +345,43 @@ def flash_prefill(
     return out
 
 
+FLASH_TC_HEAD_DIM = 128
+
+
+def flash_prefill_tc(
+    q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int,
+    num_kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """`flash_prefill` on the tcgen05 tensor cores (TMA-fed, S and P V in tensor memory); head size 128 only."""
+    _need(head_dim == FLASH_TC_HEAD_DIM, f"flash_prefill_tc: head size {head_dim}, this kernel is built for {FLASH_TC_HEAD_DIM}")
+    _cuda(q, "flash_prefill_tc q", torch.bfloat16, contiguous=False)
+    qs = _rows(q, "flash_prefill_tc q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * head_dim, "flash_prefill_tc: q rows too short")
+    _check_pages(k_pages, v_pages, torch.bfloat16, num_kv_heads, head_dim, "flash_prefill_tc")
+    _need(k_pages.shape[0] == v_pages.shape[0], "flash_prefill_tc: k and v have different page counts")
+    _cuda(block_table, "flash_prefill_tc block_table", torch.int32)
+    _cuda(seq_start, "flash_prefill_tc seq_start", torch.int32)
+    _cuda(seq_pos0, "flash_prefill_tc seq_pos0", torch.int32)
+    S = seq_pos0.numel()
+    _need(seq_start.numel() == S + 1 and block_table.dim() == 2 and block_table.shape[0] >= S, "flash_prefill_tc: metadata sizes")
+    if out is None:
+        out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    _cuda(out, "flash_prefill_tc out", torch.bfloat16)
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    status = _tc_status_word(q.device)
+    lib = build.load("attention_prefill_tc")
+    rc = lib.rl_flash_prefill_tc(
+        _p(q), c_int(qs), c_int(T), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
+        c_int(block_table.shape[1]), _p(seq_start), _p(seq_pos0), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), _stream(),
+    )
+    _check(lib, rc, "flash_prefill_tc")
+    return out
+
+
 # ------------------------------------------------------------------ matrix products
 GEMV_MAX_ROWS = 64
 
@@ -418,12 +455,14 @@ def _tc_status_word(device: torch.device) -> torch.Tensor:
 
 def tc_status_check() -> None:
     """Raise if a bounded wait inside a tensor-core kernel expired since the last check (synchronises)."""
-    names = {1: "the TMA producer", 2: "the tensor-core issuer", 3: "the epilogue", 4: "the tensor-core issuer (for a free accumulator)"}
+    names = {1: "gemm_tc: the TMA producer", 2: "gemm_tc: the tensor-core issuer", 3: "gemm_tc: the epilogue",
+             4: "gemm_tc: the tensor-core issuer (for a free accumulator)"}
     for word in _tc_status.values():
         code = int(word.item())
         if code:
             word.zero_()
-            raise KernelError(f"gemm_tc: {names.get(code, 'a role')} gave up waiting on a barrier (code {code}); results of that step are not valid")
+            who = names.get(code, f"flash_prefill_tc: a role (wait {code})" if 11 <= code <= 20 else "a role")
+            raise KernelError(f"{who} gave up waiting on a barrier (code {code}); results of that step are not valid")
 
 
 def gemm_tc(

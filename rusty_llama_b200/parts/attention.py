@@ -102,6 +102,11 @@ class Attention(Mixer):
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_len, self.H, self.K, self.hd,
                 n_splits, scratch, window=self.window, scale=self.scale,
             )
+        elif self.hd == ops.FLASH_TC_HEAD_DIM:
+            a = ops.flash_prefill_tc(
+                qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
+                step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,
+            )
         else:
             a = ops.flash_prefill(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,

@@ -309,6 +309,64 @@ def test_flash_prefill(ops, H, K, hd, window):
     close_bf16(out, torch.cat(refs).view(T, H * hd))
 
 
+@pytest.mark.parametrize("H, K", [(4, 2), (3, 3), (8, 1)])
+@pytest.mark.parametrize("window", [0, 200])
+def test_flash_prefill_tc(ops, H, K, window):
+    """The tcgen05 prompt-attention kernel (head size 128): whole prompts, a chunk behind cached positions,
+    single rows, tile-sized and ragged lengths, several key tiles per row tile."""
+    hd = 128
+    pos0 = [0, 100, 199, 0, 300]
+    q_lens = [150, 77, 1, 128, 257]
+    lens = [p + n for p, n in zip(pos0, q_lens)]
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=15)
+    T = sum(q_lens)
+    q = bf16_round(torch.randn(T, (H + 2 * K) * hd))
+    seq_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    out = ops.flash_prefill_tc(
+        q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, seq_start,
+        torch.tensor(pos0, dtype=torch.int32, device=DEV), max(q_lens), H, K, hd, window=window,
+    )
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    refs, at = [], 0
+    for s, (p, n) in enumerate(zip(pos0, q_lens)):
+        refs.append(ref_attention_rows(q[at : at + n, : H * hd].view(n, H, hd), kv, s, list(range(p, p + n)), window))
+        at += n
+    close_bf16(out, torch.cat(refs).view(T, H * hd))
+
+
+def test_flash_prefill_tc_each_key_and_dimension_lands_where_it_should(ops):
+    """Values that name their own key and dimension, queries that each pick one key: any mix-up of pages,
+    swizzled pieces, k steps or the transposed V operand shows as a wrong number, not as noise."""
+    H, K, hd, n = 1, 1, 128, 320
+    kv = PagedKV([n], K, hd, torch.bfloat16, seed=16)
+    # keys: orthogonal-ish directions; query t points at key pick(t) <= t
+    keys = bf16_round(torch.randn(n, hd, generator=torch.Generator().manual_seed(3)))
+    vals = torch.zeros(n, hd)
+    vals[torch.arange(n), torch.arange(n) % hd] = 1.0  # value row t is a one-hot at dimension t % 128
+    vals += (torch.arange(n)[:, None] // hd) * 0.25    # plus a step that tells the three 128-key tiles apart
+    vals = bf16_round(vals)
+    pick = (torch.arange(n) * 5) % (torch.arange(n) + 1)
+    q = bf16_round(keys[pick] * 2.0)
+    for t in range(n):
+        page, slot = int(kv.table[0, t // PAGE]), t % PAGE
+        kv.k_pages[page, 0, slot] = keys[t].to(torch.bfloat16).to(DEV)
+        kv.v_pages[page, 0, slot] = vals[t].to(torch.bfloat16).to(DEV)
+    kv.k[0][:, 0] = keys
+    kv.v[0][:, 0] = vals
+    out = ops.flash_prefill_tc(
+        q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([0, n], dtype=torch.int32, device=DEV),
+        torch.tensor([0], dtype=torch.int32, device=DEV), n, H, K, hd,
+    )
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    ref = ref_attention_rows(q.view(n, H, hd), kv, 0, list(range(n))).view(n, hd)
+    close_bf16(out, ref)
+    # the picked key dominates: the output is close to that key's value row
+    got = out.float().cpu()
+    assert float((got - vals[pick]).abs().max()) < 0.1
+
+
 def test_flash_prefill_finds_a_far_key_and_respects_the_causal_edge(ops):
     H, K, hd = 2, 1, 64
     n = 400
