@@ -1,0 +1,388 @@
+// Matrix products of the decode step in bfloat16, out[M, N] = x[M, K] . w[N, K]^T for M <= 16,
+// as a persistent kernel that keeps the copy engine busy: every weight is read from HBM once, and
+// what limits the step is how many bytes are in flight, so the weights never pass through registers
+// on their way in.  Counterpart of the reference's warp-per-row GEMV family
+// (src/backend/cuda.rs:354-442).
+//
+// Work: the matrix is cut into items of 8 weight rows x one slice of k (at most 4096; the whole of
+// k unless the caller asks for partial sums); the items, slice by slice, are dealt out to one block
+// per SM in contiguous, equally long ranges.  In a block
+//   warp 16 (one lane)  copies stage after stage of weights, 8 rows x 1024 k = 16 KB each, into a
+//                       ring of shared memory (13 stages, about 200 KB in flight per SM), each stage
+//                       with an mbarrier that counts its bytes.  A stage is ONE tensor copy: the
+//                       weight matrix is described to TMA as [row][k / 64][64 k], so that a box of
+//                       8 x 16 x 64 is eight rows of 1024 k (copies of a row's 2 KB at a time were
+//                       measured at 2.7 TB/s over the GPU: the copy engine wants large requests).
+//                       The weights depend on no other kernel, so the copies start before the
+//                       programmatic-dependency wait.
+//   warps 0-15          hold the activations of the slice in registers for the whole range of items:
+//                       warp w owns the 32-wide k blocks w and w + 16 of every stage.  The
+//                       activations are the A operand of mma.sync.m16n8k16 (16 batch rows x 16 k),
+//                       the weights the B operand (16 k x 8 features), 32-bit accumulators.  A lane
+//                       reads 16 contiguous bytes of a row and uses them as its k elements of two
+//                       consecutive MMAs; both operands follow the same rule, so the sum over k is
+//                       unchanged.  Per stage a warp issues two 16-byte shared-memory loads and
+//                       four MMAs into four independent accumulators.
+//   warps 17-20         At the end of an item the sixteen warps leave their partial sums in one of two
+//                       buffers of shared memory and go on with the next item at once; these four
+//                       warps add them in warp order (no atomics, the same bits every run) and
+//                       store the 16 x 8 results: as they are, or through SwiGLU when the rows
+//                       alternate gate and up, or as one of k_slices partial results.  (With the
+//                       sum done by the product warps themselves, every item cost them about half
+//                       a microsecond of waiting for one another.)
+// Every wait is bounded: on expiry a code goes to status[0] and the block drains.
+#include "tc_common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define CONSUMER_WARPS 16
+#define STORE_WARPS 4
+#define NUM_THREADS ((CONSUMER_WARPS + 1 + STORE_WARPS) * 32)
+#define UNIT_ROWS 8
+#define KC 1024                           // k per stage
+#define STAGE_BYTES (UNIT_ROWS * KC * 2)  // [8 rows][16 blocks of 64 k][128 bytes, swizzled]
+#define MAX_SLICE 4096                    // k per slice: what a warp keeps of the activations is MAX_SLICE / 512 fragments
+#define SLICE_STAGES (MAX_SLICE / KC)
+#define KB_PER_WARP (KC / 32 / CONSUMER_WARPS)   // 2
+#define STAGES 13
+#define MAX_M 16
+#define RED_BYTES (2 * CONSUMER_WARPS * 32 * 16)
+#define SMALL_BYTES 1024
+#define SMEM_BYTES (STAGES * STAGE_BYTES + RED_BYTES + SMALL_BYTES)
+static_assert(SMEM_BYTES <= 227 * 1024, "more shared memory than a block can have");
+
+struct StreamBarriers {
+  uint64_t full[STAGES], empty[STAGES];
+  uint64_t red_full[2], red_free[2];
+  int abort_flag;
+};
+static_assert(sizeof(StreamBarriers) <= SMALL_BYTES, "barriers must fit their area");
+
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <typename TO>
+__device__ __forceinline__ void store_out(TO* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// slice_len: k per slice, a multiple of KC and at most MAX_SLICE (the last slice may be shorter);
+// units = ceil(N / 8); items = units * slices, numbered slice by slice.  HI: more than 8 batch rows.
+template <typename TO, bool SWIGLU, bool HI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ CUtensorMap map_w, TO* __restrict__ out, int ldo,
+                   int M, int N, int K, int slice_len, int units, int items, int* __restrict__ status) {
+  // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
+  // aligned, as the 128-byte swizzle needs)
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* ring = smem;                                                       // [STAGES][8][16][128 bytes]
+  float4* red = reinterpret_cast<float4*>(ring + (size_t)STAGES * STAGE_BYTES);     // [2][warps][32]
+  StreamBarriers& bars = *reinterpret_cast<StreamBarriers*>(reinterpret_cast<unsigned char*>(red) + RED_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (smem_u32(smem) & 1023u) {  // uniform over the block; nothing has been set up yet
+    if (threadIdx.x == 0) atomicExch(status, 36);
+    return;
+  }
+
+  const int first_item = (int)((long long)blockIdx.x * items / gridDim.x);
+  const int end_item = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&bars.full[i], 1);
+      mbar_init(&bars.empty[i], CONSUMER_WARPS);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.red_full[i], CONSUMER_WARPS);
+      mbar_init(&bars.red_free[i], STORE_WARPS);
+    }
+    bars.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == CONSUMER_WARPS) {
+    // ---------------- copies
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first();
+      const uint32_t ring_addr = smem_u32(ring);
+      int it = 0;
+      bool ok = true;
+      for (int item = first_item; item < end_item && ok; ++item) {
+        const int slice = item / units, unit = item - slice * units;
+        const int kbeg = slice * slice_len, klen = min(slice_len, K - kbeg);
+        for (int k0 = 0; k0 < klen; k0 += KC, ++it) {
+          const int st = it % STAGES, round = it / STAGES;
+          if (round > 0 && !mbar_wait(&bars.empty[st], (round - 1) & 1)) {
+            atomicExch(status, 32);
+            bars.abort_flag = 1;
+            ok = false;
+            break;
+          }
+          if (*(volatile int*)&bars.abort_flag) {
+            ok = false;
+            break;
+          }
+          // rows past N and k past K arrive as zeros and count like the rest
+          mbar_expect_tx(&bars.full[st], STAGE_BYTES);
+          tma_load_3d(ring_addr + st * STAGE_BYTES, &map_w, &bars.full[st], 0, (kbeg + k0) / 64, unit * UNIT_ROWS, pol_w);
+        }
+      }
+      // nothing may still be writing shared memory when the block ends: if someone gave up, wait
+      // (bounded) for the copies that were started
+      if (*(volatile int*)&bars.abort_flag)
+        for (int j = max(0, it - STAGES); j < it; ++j) mbar_wait(&bars.full[j % STAGES], (j / STAGES) & 1);
+    }
+  } else if (warp > CONSUMER_WARPS) {
+    // ---------------- sums and stores
+    const int e = threadIdx.x - (CONSUMER_WARPS + 1) * 32;  // 0..127
+    pdl_wait();  // the kernel before this one may still read the output buffer
+    int done_items = 0;
+    for (int item = first_item; item < end_item; ++item, ++done_items) {
+      const int slice = item / units, unit = item - slice * units;
+      const int buf = done_items & 1;
+      if (!mbar_wait(&bars.red_full[buf], (done_items >> 1) & 1)) {
+        if (lane == 0) {
+          atomicExch(status, 35);
+          bars.abort_flag = 1;
+        }
+        break;
+      }
+      if (*(volatile int*)&bars.abort_flag) break;
+      const float* red_f = reinterpret_cast<const float*>(red + buf * (CONSUMER_WARPS * 32));
+      TO* out_slice = out + (size_t)slice * M * ldo;
+      if (SWIGLU) {
+        if (e < 64) {
+          const int l = e >> 1, hi = e & 1;
+          float gate = 0.f, up = 0.f;
+#pragma unroll
+          for (int wq = 0; wq < CONSUMER_WARPS; ++wq) {
+            gate += red_f[(wq * 32 + l) * 4 + 2 * hi];
+            up += red_f[(wq * 32 + l) * 4 + 2 * hi + 1];
+          }
+          const int m = (l >> 2) + 8 * hi, col = unit * (UNIT_ROWS / 2) + (l & 3);
+          if (m < M && col < (N >> 1)) store_out<TO>(out_slice + (size_t)m * ldo + col, gate * (1.0f / (1.0f + expf(-gate))) * up);
+        }
+      } else {
+        const int l = e >> 2, c = e & 3;
+        float sum = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < CONSUMER_WARPS; ++wq) sum += red_f[(wq * 32 + l) * 4 + c];
+        const int m = (l >> 2) + 8 * (c >> 1), n = unit * UNIT_ROWS + 2 * (l & 3) + (c & 1);
+        if (m < M && n < N) store_out<TO>(out_slice + (size_t)m * ldo + n, sum);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.red_free[buf]);
+    }
+  } else {
+    // ---------------- products
+    const int g = lane >> 2, t4 = lane & 3;
+    // row g of a stage; k block kb = warp + 16 j lies in 64-k block kb / 2 as 16-byte pieces
+    // (kb & 1) * 4 + t4, swizzled by the 64-k block's number
+    uint32_t w_off[KB_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < KB_PER_WARP; ++j) {
+      const int kb = warp + CONSUMER_WARPS * j;
+      w_off[j] = smem_u32(ring) + g * (KC * 2) + (kb >> 1) * 128 + (((((kb & 1) << 2) | t4) ^ ((kb >> 1) & 7)) << 4);
+    }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint4 xa[SLICE_STAGES][KB_PER_WARP], xb[HI ? SLICE_STAGES : 1][KB_PER_WARP];
+    int loaded_slice = -1, it = 0, done_items = 0;
+    bool ok = true;
+    auto give_up = [&](int code) {
+      if (lane == 0) {
+        atomicExch(status, code);
+        bars.abort_flag = 1;
+      }
+      ok = false;
+    };
+    pdl_wait();  // the activations are the previous kernel's output, and it may still read ours
+    for (int item = first_item; item < end_item && ok; ++item, ++done_items) {
+      const int slice = item / units, unit = item - slice * units;
+      const int kbeg = slice * slice_len, klen = min(slice_len, K - kbeg);
+      if (slice != loaded_slice) {
+        // this lane's pieces of the activations of the slice, zero where there is no row or no k
+#pragma unroll
+        for (int s = 0; s < SLICE_STAGES; ++s)
+#pragma unroll
+          for (int j = 0; j < KB_PER_WARP; ++j) {
+            const int k = s * KC + (warp + CONSUMER_WARPS * j) * 32 + t4 * 8;
+            const bool k_ok = k + 8 <= klen;
+            xa[s][j] = (k_ok && g < M) ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)g * ldx + kbeg + k)) : zero;
+            if (HI) xb[s][j] = (k_ok && g + 8 < M) ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)(g + 8) * ldx + kbeg + k)) : zero;
+          }
+        loaded_slice = slice;
+      }
+      float acc[2 * KB_PER_WARP][4];
+#pragma unroll
+      for (int i = 0; i < 2 * KB_PER_WARP; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+      for (int s = 0; s < SLICE_STAGES; ++s) {
+        if (s * KC < klen && ok) {
+          const int st = it % STAGES;
+          if (!mbar_wait(&bars.full[st], (it / STAGES) & 1)) {
+            give_up(34);
+          } else if (*(volatile int*)&bars.abort_flag) {
+            ok = false;
+          } else {
+            uint4 b[KB_PER_WARP];
+#pragma unroll
+            for (int j = 0; j < KB_PER_WARP; ++j) b[j] = lds128(w_off[j] + st * STAGE_BYTES);
+#pragma unroll
+            for (int j = 0; j < KB_PER_WARP; ++j) {
+              const uint4 lo = xa[s][j], hi = HI ? xb[s][j] : zero;
+              mma_bf16_16x8x16(acc[2 * j], lo.x, hi.x, lo.y, hi.y, b[j].x, b[j].y);
+              mma_bf16_16x8x16(acc[2 * j + 1], lo.z, hi.z, lo.w, hi.w, b[j].z, b[j].w);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.empty[st]);
+            ++it;
+          }
+        }
+      }
+      if (!ok) break;
+      // leave the partial sums to the storing warps; the buffer was last read two items ago
+      const int buf = done_items & 1;
+      if (done_items >= 2 && !mbar_wait(&bars.red_free[buf], ((done_items >> 1) - 1) & 1)) {
+        give_up(37);
+        break;
+      }
+      float4 sum4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 2 * KB_PER_WARP; ++i) {
+        sum4.x += acc[i][0];
+        sum4.y += acc[i][1];
+        sum4.z += acc[i][2];
+        sum4.w += acc[i][3];
+      }
+      red[buf * (CONSUMER_WARPS * 32) + warp * 32 + lane] = sum4;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.red_full[buf]);
+    }
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+// How the kernel cuts k: k per slice (a multiple of KC, at most MAX_SLICE) and the slices that
+// result from at least k_slices of them.
+static void plan(int K, int k_slices, int* slice_len, int* slices) {
+  const int chunks = (K + KC - 1) / KC;
+  const int want = k_slices < chunks ? k_slices : chunks;
+  int per = (chunks + want - 1) / want;
+  if (per > SLICE_STAGES) per = SLICE_STAGES;
+  *slice_len = per * KC;
+  *slices = (chunks + per - 1) / per;
+}
+
+RL_API int rl_gemv_stream_max_rows() { return MAX_M; }
+
+// The slices of k that a call with these arguments produces (1: a finished result; more: partial
+// sums), or 0 when the kernel does not take the shape.  A block keeps a slice of the activations in
+// registers, so a slice is at most 4096 long and longer k always comes in slices.
+RL_API int rl_gemv_stream_slices(int M, int K, int k_slices) {
+  if (M <= 0 || M > MAX_M || K <= 0 || K % 64 || k_slices < 1 || k_slices > 64) return 0;
+  int slice_len, slices;
+  plan(K, k_slices, &slice_len, &slices);
+  return slices;
+}
+
+// swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns.
+// k_slices > 1: out is [slices_used][M][ldo] float32 partial results that the consumer adds up.
+// status: one int in device memory, 0 before the call; non-zero afterwards means that a bounded
+// wait expired (32, 34, 35, 37: which one; 36: shared memory not aligned) and the output is not valid.
+RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                          int K, int swiglu, int k_slices, int* slices_used, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_stream: M=%d N=%d K=%d", M, N, K);
+  if (M > MAX_M) RL_REFUSE(2, "gemv_stream: %d rows, this kernel takes at most %d", M, MAX_M);
+  if (K % 64 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_stream: K=%d must be a multiple of 64, ldx=%d and ldw=%d of 8", K, ldx, ldw);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) RL_REFUSE(9, "gemv_stream: operands must be 16-byte aligned");
+  if (swiglu && (N & 1)) RL_REFUSE(6, "gemv_stream: %d gate/up rows are not pairs", N);
+  if (k_slices < 1 || k_slices > 64) RL_REFUSE(7, "gemv_stream: %d k slices", k_slices);
+  if (ldx < K || ldw < K || ldo < (swiglu ? N / 2 : N)) RL_REFUSE(4, "gemv_stream: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
+  if (out_dtype != RL_F32 && out_dtype != RL_BF16) RL_REFUSE(5, "gemv_stream: unknown output dtype %d", out_dtype);
+  if (status == nullptr) RL_REFUSE(10, "gemv_stream: no status word");
+  int slice_len, slices;
+  plan(K, k_slices, &slice_len, &slices);
+  if (slices > 1 && (swiglu || out_dtype != RL_F32))
+    RL_REFUSE(8, "gemv_stream: k = %d comes in %d slices of at most %d, whose partial sums are float32 and cannot go through the activation", K, slices, MAX_SLICE);
+  if (slices_used) *slices_used = slices;
+  const int units = (N + UNIT_ROWS - 1) / UNIT_ROWS;
+  const long long items_ll = (long long)units * slices;
+  if (items_ll > 0x7fffffffLL) RL_REFUSE(12, "gemv_stream: too many work items");
+  const int items = (int)items_ll;
+  static int sm_count[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) RL_REFUSE(13, "gemv_stream: cannot tell the device");
+  if (!sm_count[dev] && cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    RL_REFUSE(13, "gemv_stream: cannot count the SMs");
+  const int blocks = items < sm_count[dev] ? items : sm_count[dev];
+  // the weights as [row][k / 64][64 k]: a box of 8 x 16 x 64 is eight rows of 1024 k
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) RL_REFUSE(15, "gemv_stream: cuTensorMapEncodeTiled is not available");
+  CUtensorMap map_w;
+  {
+    cuuint64_t dims[3] = {64, (cuuint64_t)(K / 64), (cuuint64_t)N};
+    cuuint64_t strides[2] = {128, (cuuint64_t)ldw * 2};
+    cuuint32_t box[3] = {64, KC / 64, UNIT_ROWS};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      RL_REFUSE(16, "gemv_stream: cannot describe the weights to TMA");
+  }
+#define LAUNCH(TO, SW, HI)                                                                                                  \
+  do {                                                                                                                      \
+    auto kern = gemv_stream_kernel<TO, SW, HI>;                                                                             \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)                 \
+      RL_REFUSE(14, "gemv_stream: cannot get %d bytes of shared memory", SMEM_BYTES);                                       \
+    RL_LAUNCH_CHECK(rl_launch<true>(kern, dim3(blocks), NUM_THREADS, SMEM_BYTES, stream, (const bf16*)x, ldx, map_w,       \
+                                    (TO*)out, ldo, M, N, K, slice_len, units, items, status));                            \
+  } while (0)
+#define LAUNCH_ROWS(TO, SW)      \
+  do {                           \
+    if (M > 8) LAUNCH(TO, SW, true); \
+    else LAUNCH(TO, SW, false);  \
+  } while (0)
+  if (swiglu && out_dtype == RL_F32) LAUNCH_ROWS(float, true);
+  else if (swiglu) LAUNCH_ROWS(bf16, true);
+  else if (out_dtype == RL_F32) LAUNCH_ROWS(float, false);
+  else LAUNCH_ROWS(bf16, false);
+#undef LAUNCH_ROWS
+#undef LAUNCH
+  return 0;
+}

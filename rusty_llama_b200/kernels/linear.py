@@ -1,10 +1,11 @@
 """y = x . W^T for the model's projections, chosen by precision and row count.
 
 float32 runs use the library's own 32-bit FMA kernel for every shape.  bfloat16 runs use the
-weight-streaming kernel for up to 64 rows (a decode step) and the TMA + tcgen05 kernel above that
-(a prompt step).  The reference makes the same split, its own GEMV kernels for decode and a
-cuBLASLt call for prompts (src/backend/cuda.rs:354-442, :717-758); `use_library_gemm(True)` puts the
-vendor GEMM (torch.matmul) in the place of the tcgen05 kernel, for comparisons only.
+persistent TMA-fed streaming kernel for up to 8 rows (a decode step; the older register-streaming
+kernel where k is no multiple of 64) and the TMA + tcgen05 kernel above that (a prompt step).  The
+reference makes the same split, its own GEMV kernels for decode and a cuBLASLt call for prompts
+(src/backend/cuda.rs:354-442, :717-758); `use_library_gemm(True)` puts the vendor GEMM
+(torch.matmul) in the place of the tcgen05 kernel, for comparisons only.
 """
 
 from __future__ import annotations
@@ -25,6 +26,13 @@ STREAM_MAX_ROWS = 8
 _SMS = 148
 
 
+def _streams(M: int, K: int, whole: bool) -> bool:
+    """Whether the persistent streaming kernel takes the product; whole: only with all of k in one
+    slice (the result goes on as it is, not as partial sums)."""
+    slices = ops.gemv_stream_slices(M, K, 1)
+    return slices == 1 or (slices > 1 and not whole)
+
+
 def use_library_gemm(on: bool) -> None:
     """Route bfloat16 products of more than 64 rows through torch.matmul instead of `gemm_tc`."""
     global _library_gemm
@@ -41,8 +49,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return ops.gemm_f32(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
-    M = x.shape[0]
+    M, K = x.shape
     if M <= STREAM_MAX_ROWS:
+        if _streams(M, K, whole=True):
+            return ops.gemv_stream(x, w, out_dtype)
         return ops.gemv_bf16(x, w, out_dtype)
     if M <= 32 and ((M + 127) // 128) * ((w.shape[0] + 255) // 256) < _SMS // 2:
         # too few output tiles to keep the SMs busy, and nothing downstream that could add up
@@ -61,6 +71,8 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
         raise KernelError(f"linear_swiglu: bfloat16 only, got {x.dtype} x {w_gate_up.dtype}")
     if x.shape[0] <= STREAM_MAX_ROWS:
+        if _streams(x.shape[0], x.shape[1], whole=True):
+            return ops.gemv_stream(x, w_gate_up, torch.bfloat16, swiglu=True)
         return ops.gemv_bf16(x, w_gate_up, torch.bfloat16, swiglu=True)
     return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
 
@@ -78,6 +90,11 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     N = w.shape[0]
     if x.dtype != torch.bfloat16:
         return linear(x, w)
+    if M <= STREAM_MAX_ROWS and _streams(M, K, whole=False):
+        # as few slices of k as the kernel allows (each costs a partial result to write and to add)
+        if ops.gemv_stream_slices(M, K, 1) > 1:
+            return ops.gemv_stream(x, w, torch.float32, k_splits=2)
+        return ops.gemv_stream(x, w)
     if M <= STREAM_MAX_ROWS and K <= 8192:
         # (for a long k the tcgen05 kernel below is faster even at one row: 25 us against 32 us
         # for the 8B down projection)

@@ -65,11 +65,13 @@ def bench_gemv(a) -> dict:
     ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
     x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
     out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
+    fn = ops.gemv_stream if a.impl == "stream" else ops.gemv_bf16
     if a.splits > 1:
-        us = _time(lambda i: ops.gemv_bf16(x, ws[i], torch.float32, k_splits=a.splits), nv, a.iters, a.warmup)
+        us = _time(lambda i: fn(x, ws[i], torch.float32, k_splits=a.splits), nv, a.iters, a.warmup)
     else:
-        us = _time(lambda i: ops.gemv_bf16(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
-    return {"kernel": "gemv_bf16", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "GBps": round(wbytes / us / 1e3, 1), "weight_copies": nv}
+        us = _time(lambda i: fn(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
+    ops.tc_status_check()
+    return {"kernel": "gemv_stream" if a.impl == "stream" else "gemv_bf16", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "GBps": round(wbytes / us / 1e3, 1), "weight_copies": nv}
 
 
 def bench_gemm(a) -> dict:
@@ -156,7 +158,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
-    ap.add_argument("--impl", default="linear", choices=["linear", "tc"], help="gemm: the dispatching linear() or the tcgen05 kernel; flash_prefill: tc = the tcgen05 kernel")
+    ap.add_argument("--impl", default="linear", choices=["linear", "tc", "stream"], help="gemm: the dispatching linear() or the tcgen05 kernel; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent bulk-copy kernel")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch the timed calls one by one instead of as one graph")

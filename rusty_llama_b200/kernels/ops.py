@@ -443,6 +443,54 @@ def gemv_bf16(
     return out
 
 
+def gemv_stream_slices(M: int, K: int, k_splits: int = 1) -> int:
+    """How many slices of k `gemv_stream` produces for these arguments: 1 is a finished result, more
+    are float32 partial sums, 0 means that the kernel does not take the shape (more than 16 rows, k
+    no multiple of 64).  A slice is at most 4096 long, so longer k always comes in slices."""
+    lib = build.load("gemv_stream")
+    return int(lib.rl_gemv_stream_slices(c_int(M), c_int(K), c_int(k_splits)))
+
+
+def gemv_stream(
+    x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
+    swiglu: bool = False, k_splits: int = 1,
+) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 16 rows: the persistent weight-streaming kernel of
+    decode steps (bulk copies into a ring of shared memory, one block per SM).
+
+    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums.
+    k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (`gemv_stream_slices`
+    says how many: each is a multiple of 1024 and at most 4096 long), for a consumer that adds them up."""
+    _cuda(x, "gemv_stream x", torch.bfloat16, contiguous=False)
+    _cuda(w, "gemv_stream w", torch.bfloat16, contiguous=False)
+    ldx, ldw = _rows(x, "gemv_stream x"), _rows(w, "gemv_stream w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, f"gemv_stream: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
+    n_out = N // 2 if swiglu else N
+    used = c_int(1)
+    slices = gemv_stream_slices(M, K, k_splits) if k_splits > 1 else 1
+    if k_splits > 1 and slices > 1:
+        _need(out is None and out_dtype == torch.float32 and not swiglu, "gemv_stream: partial sums over k slices are float32, without activation")
+        out = torch.empty((slices, M, n_out), dtype=torch.float32, device=x.device)
+        ldo = n_out
+    else:
+        if out is None:
+            out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        _cuda(out, "gemv_stream out", out_dtype, contiguous=False)
+        _need(tuple(out.shape) == (M, n_out), "gemv_stream: out has the wrong shape")
+        ldo = _rows(out, "gemv_stream out")
+    status = _tc_status_word(x.device)
+    lib = build.load("gemv_stream")
+    rc = lib.rl_gemv_stream(
+        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_stream out")), c_int(ldo),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), _stream(),
+    )
+    _check(lib, rc, "gemv_stream")
+    _need(used.value == slices, f"gemv_stream: kernel used {used.value} slices, the wrapper planned {slices}")
+    return out
+
+
 _tc_status = {}
 
 
@@ -461,7 +509,8 @@ def tc_status_check() -> None:
         code = int(word.item())
         if code:
             word.zero_()
-            who = names.get(code, f"flash_prefill_tc: a role (wait {code})" if 11 <= code <= 20 else "a role")
+            who = names.get(code, f"flash_prefill_tc: a role (wait {code})" if 11 <= code <= 23 else
+                            f"gemv_stream: a role (wait {code})" if 31 <= code <= 37 else "a role")
             raise KernelError(f"{who} gave up waiting on a barrier (code {code}); results of that step are not valid")
 
 

@@ -505,6 +505,87 @@ def test_gemv_bf16_partial_sums_over_k_slices(ops, M, N, K, splits):
             assert float(parts[i].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N, K", [(100, 64), (48, 4096), (257, 960), (4099, 2112), (20000, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemv_stream(ops, M, N, K, out_dtype):
+    """The persistent TMA-fed kernel: row counts on both sides of 8, feature counts that are no
+    multiple of 8 (a last unit with fewer rows), k that ends inside a stage, fewer items than SMs
+    and many items per block."""
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = bf16_round(torch.randn(M, K, generator=g))
+    w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
+    out = ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    if out_dtype == torch.float32:
+        close_dot_f32(out, x, w)
+    else:
+        close_bf16(out, x.double() @ w.double().T)
+
+
+@pytest.mark.parametrize("M, N, K, splits", [(8, 100, 4096, 4), (1, 48, 960, 3), (16, 257, 3136, 2), (3, 4096, 14336, 7), (8, 24, 2048, 2), (9, 40, 14336, 2)])
+def test_gemv_stream_partial_sums_over_k_slices(ops, M, N, K, splits):
+    x = bf16_round(torch.randn(M, K))
+    w = bf16_round(torch.randn(N, K) * 0.05)
+    parts = ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    chunks = (K + 1023) // 1024
+    per = min(4, (chunks + min(splits, chunks) - 1) // min(splits, chunks))
+    used = (chunks + per - 1) // per
+    assert used == ops.gemv_stream_slices(M, K, splits)
+    if used == 1:
+        assert parts.shape == (M, N)
+        close_dot_f32(parts, x, w)
+        return
+    assert parts.shape == (used, M, N) and parts.dtype == torch.float32
+    close_dot_f32(parts.sum(dim=0), x, w)
+    for i in range(used):  # each slice really is its own range of k
+        lo, hi = i * per * 1024, min(K, (i + 1) * per * 1024)
+        close_dot_f32(parts[i], x[:, lo:hi], w[:, lo:hi])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("ff, K", [(100, 64), (1432, 512), (7168, 1024)])
+def test_gemv_stream_fused_swiglu(ops, M, ff, K):
+    g = torch.Generator().manual_seed(M + ff)
+    x = bf16_round(torch.randn(M, K, generator=g))
+    wg = bf16_round(torch.randn(ff, K, generator=g) * 0.1)
+    wu = bf16_round(torch.randn(ff, K, generator=g) * 0.1)
+    w = torch.stack([wg, wu], dim=1).reshape(2 * ff, K)
+    out = ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), swiglu=True)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert out.shape == (M, ff)
+    close_bf16(out, plain_silu(x.double() @ wg.double().T) * (x.double() @ wu.double().T))
+
+
+def test_gemv_stream_strided_operands_and_repeat(ops):
+    """Operands that are column slices of wider tensors, and the same bits on every run."""
+    big_x = bf16_round(torch.randn(5, 3000))
+    big_w = bf16_round(torch.randn(300, 2600) * 0.05)
+    xd, wd = big_x.to(torch.bfloat16).to(DEV), big_w.to(torch.bfloat16).to(DEV)
+    x, w = xd[:, 8 : 8 + 2048], wd[:, 16 : 16 + 2048]
+    out = ops.gemv_stream(x, w, torch.float32)
+    close_dot_f32(out, big_x[:, 8 : 8 + 2048], big_w[:, 16 : 16 + 2048])
+    assert torch.equal(out, ops.gemv_stream(x, w, torch.float32))
+
+
+def test_gemv_stream_refuses_what_it_cannot_do(ops):
+    from rusty_llama_b200.errors import KernelError
+
+    with pytest.raises(KernelError, match="multiple of 64"):
+        ops.gemv_stream(torch.zeros(2, 72, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 72, dtype=torch.bfloat16, device=DEV))
+    assert ops.gemv_stream_slices(2, 72) == 0
+    with pytest.raises(KernelError, match="at most 16"):
+        ops.gemv_stream(torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV))
+    assert ops.gemv_stream_slices(16, 14336) == 4   # a block keeps at most 4096 activations per row
+    assert ops.gemv_stream_slices(16, 14336, 7) == 7
+    with pytest.raises(KernelError, match="comes in 4 slices"):
+        ops.gemv_stream(torch.zeros(16, 14336, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 14336, dtype=torch.bfloat16, device=DEV))
+
+
 def test_add_rmsnorm_takes_float32_partial_sums_in_a_bfloat16_run(ops):
     T, d = 6, 520
     x = torch.randn(T, d)
