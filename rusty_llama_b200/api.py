@@ -56,6 +56,7 @@ class LLM:
         max_batch: Optional[int] = None,
         on_token: Optional[Callable[[int, int], None]] = None,
         return_results: bool = False,
+        launch_ahead: bool = True,
     ):
         """Token ids generated after each prompt.
 
@@ -64,7 +65,8 @@ class LLM:
         instead: positions in total, prompt included, clamped to the model's limit
         (src/model.rs:1668); give one of the two (neither: steps = 256).
         temperature 0 is greedy; top_p outside (0, 1) turns the nucleus off; seed None
-        takes the wall clock."""
+        takes the wall clock.  launch_ahead=False makes the loop read every token before it
+        starts the next step (same tokens, more idle GPU time)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         batch: List[Sequence[int]] = [prompts] if single else list(prompts)  # type: ignore[list-item]
         if max_new_tokens is not None and steps is not None:
@@ -77,7 +79,8 @@ class LLM:
         else:
             budget = max_new_tokens
         results = generate(
-            self.engine, self.sampler, batch, budget, params, stop_token_ids, include_stop, max_batch, on_token, stats
+            self.engine, self.sampler, batch, budget, params, stop_token_ids, include_stop, max_batch, on_token, stats,
+            launch_ahead,
         )
         self.last_stats = stats
         if return_results:

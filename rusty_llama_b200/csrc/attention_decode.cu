@@ -125,6 +125,7 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     for (int i = lane; i < n16; i += 32) p[i] = z;
   }
   __syncwarp();
+  pdl_trigger();
   pdl_wait();
   const int kv_len = seq_len[s];
   const int pos = kv_len - 1;
@@ -289,7 +290,7 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int out_stride, int H, int hd, int n_splits) {
   __shared__ float w_s[64];
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, s = blockIdx.y;
   const float* ml = part_ml + ((size_t)s * H + h) * n_splits * 2;

@@ -16,7 +16,7 @@ RL_DEFINE_ERROR_TEXT()
 template <typename TW, bool VEC>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                     float* __restrict__ out, int d) {
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   const TW* row = table + (size_t)tokens[t] * d;
@@ -71,7 +71,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const int* __restrict__ rows, int d, float eps, int write_x) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;

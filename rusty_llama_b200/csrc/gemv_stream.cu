@@ -106,6 +106,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     return;
   }
 
+  pdl_trigger();
   const int first_item = (int)((long long)blockIdx.x * items / gridDim.x);
   const int end_item = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
 

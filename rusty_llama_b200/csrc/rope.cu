@@ -22,7 +22,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const float* __restrict__ inv_freq, int H, int K, int hd, int rot,
                                      int interleaved, int page_size, int write_kv) {
   extern __shared__ float trig[];  // cos[rot/2], sin[rot/2]
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
@@ -92,7 +92,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride, co
                                          const float* __restrict__ inv_freq, int H, int K, int hd, int rot,
                                          int interleaved, int page_size, int write_kv) {
   extern __shared__ float trig[];
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   const int pos = tok_pos[t];

@@ -258,9 +258,24 @@ class Engine:
         return logits
 
     # ------------------------------------------------------------------ decode through a graph
-    def _decode_graph_step(self, entries) -> torch.Tensor:
+    def step_device_tokens(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One token for each of `slots`, taken from `tokens` (int32 [len(slots)] on the device, for
+        instance what the sampler just wrote) without the host ever seeing them; logits for every
+        slot.  The generation loop uses it to launch a step before it has read the previous step's
+        tokens, so that launching overlaps the GPU's work."""
+        if tokens.dtype != torch.int32 or tokens.device != self.rt.device or tuple(tokens.shape) != (len(slots),):
+            raise StepError(f"step_device_tokens wants int32 [{len(slots)}] on {self.rt.device}, got {tokens.dtype} {tuple(tokens.shape)} on {tokens.device}")
+        entries = [StepEntry(int(s), [0], [0]) for s in slots]
+        if not self.use_graphs:
+            for e, t in zip(entries, tokens.tolist()):
+                e.tokens[0] = int(t)
+            return self.step(entries)
+        return self._decode_graph_step(entries, tokens)
+
+    def _decode_graph_step(self, entries, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """A step whose entries all bring one token: checks, cache bookkeeping and the step's integers
-        are done with array operations, the kernels are one graph replay."""
+        are done with array operations, the kernels are one graph replay.  device_tokens: the token
+        ids are copied from this device tensor into the step's buffer after the host's upload."""
         S = len(entries)
         slots = np.fromiter((e.slot for e in entries), dtype=np.intp, count=S)
         toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
@@ -306,6 +321,8 @@ class Engine:
         for gi in range(len(self.cache.kv_groups)):
             h[8 + gi][:] = self.cache.block_table(gi, slots, width).reshape(-1)
         g.meta.upload()
+        if device_tokens is not None:
+            g.meta.dev_part(0).copy_(device_tokens, non_blocking=True)
         if g.graph is None:
             pos_list = pos0.tolist()
             step, tables = self._context(g.meta, entries, pos_list, S, width * PAGE_SIZE)

@@ -9,6 +9,14 @@ one starts in the freed slots.  The reference's single-sequence loop is
 `generate_prefilled` (src/model.rs:1714-1763); its server runs the batched form with
 one slot per request (src/server.rs:400-453).
 
+Launching ahead: where the engine offers `step_device_tokens`, and every running sequence
+will go on unless it has just drawn a stop token, the next step is launched on the tokens
+as they lie on the device, before the host has read them.  The host then reads the tokens of
+step n while the GPU runs step n + 1, so that launching a step (a graph of a few hundred
+kernels) and the loop's own work cost no GPU time.  A sequence that did draw a stop token
+has then been stepped once too often: its row of the new logits is dropped and its slot
+closed, nothing else changes, and the tokens are the same as without launching ahead.
+
 The loop only needs the four methods of `Engine` and the one of `Sampler` it calls,
 so its decisions can be tested with stand-ins that need no GPU.
 """
@@ -93,13 +101,15 @@ def generate(
     max_batch: Optional[int] = None,
     on_token: Optional[Callable[[int, int], None]] = None,
     stats: Optional[GenerationStats] = None,
+    launch_ahead: bool = True,
 ) -> List[GenerationResult]:
     """Generate up to `max_new_tokens` tokens (one number, or one per prompt) after each prompt;
     results in the prompts' order.
 
     stop_token_ids: None = the model's own (config.json's eos_token_id).  A stop token ends
     its sequence and is not part of the result (src/model.rs:1749) unless `include_stop`.
-    on_token(request index, token) is called for every token as it is produced."""
+    on_token(request index, token) is called for every token as it is produced.
+    launch_ahead: see the module's text; False reads every token before the next step starts."""
     params = params or SamplingParams()
     params.validate()
     budgets = [int(max_new_tokens)] * len(prompts) if isinstance(max_new_tokens, int) else [int(b) for b in max_new_tokens]
@@ -127,6 +137,7 @@ def generate(
         )
     ]
     stats = stats if stats is not None else GenerationStats()
+    step_ahead = getattr(engine, "step_device_tokens", None) if launch_ahead else None
 
     for batch in batches:
         stats.batches += 1
@@ -144,7 +155,20 @@ def generate(
             first = True
             while running:
                 t_call = time.perf_counter()
-                tokens = sampler.sample(logits, [s.slot for s in running], params).tolist()
+                sampled = sampler.sample(logits, [s.slot for s in running], params)
+                begin_fetch = getattr(sampler, "begin_fetch", None)
+                pending = begin_fetch(sampled) if begin_fetch is not None else sampled  # the copy goes first
+                ahead = None
+                if step_ahead is not None and not first and all(
+                    len(s.out) + 1 < budgets[s.request] and s.length + 1 <= max_positions for s in running
+                ):
+                    # nobody ends on this token unless it is a stop token: launch the next step now
+                    # (not after the prompt step, whose end is awaited below to time it and to check it)
+                    t_step = time.perf_counter()
+                    ahead = step_ahead([s.slot for s in running], sampled)
+                    stats.decode_step_call_seconds += time.perf_counter() - t_step
+                    stats.decode_steps += 1
+                tokens = pending.tolist()
                 if not first:
                     stats.decode_sample_call_seconds += time.perf_counter() - t_call
                 if first:
@@ -155,7 +179,8 @@ def generate(
                     t0 = time.perf_counter()
                     first = False
                 still: List[_Running] = []
-                for s, tok in zip(running, tokens):
+                kept_rows: List[int] = []
+                for row, (s, tok) in enumerate(zip(running, tokens)):
                     reason = None
                     if tok in stops:
                         reason = STOP_TOKEN
@@ -173,17 +198,22 @@ def generate(
                     if reason is None:
                         s.next_token = tok
                         still.append(s)
+                        kept_rows.append(row)
                     else:
                         results[s.request] = GenerationResult(s.out, reason)
                         engine.close_sequence(s.slot)
                         s.slot = -1
+                n_before = len(running)
                 running = still
                 if not running:
                     break
-                t_call = time.perf_counter()
-                logits = engine.step([StepEntry(s.slot, [s.next_token], [0]) for s in running])
-                stats.decode_step_call_seconds += time.perf_counter() - t_call
-                stats.decode_steps += 1
+                if ahead is not None:
+                    logits = ahead if len(kept_rows) == n_before else ahead[kept_rows]
+                else:
+                    t_call = time.perf_counter()
+                    logits = engine.step([StepEntry(s.slot, [s.next_token], [0]) for s in running])
+                    stats.decode_step_call_seconds += time.perf_counter() - t_call
+                    stats.decode_steps += 1
                 for s in running:
                     s.length += 1
             stats.decode_seconds += time.perf_counter() - t0

@@ -59,6 +59,18 @@ class SamplingParams:
             raise ConfigError("top_p is NaN")
 
 
+class PendingTokens:
+    """Tokens on their way to the host (see Sampler.begin_fetch)."""
+
+    def __init__(self, host: torch.Tensor, event):
+        self._host, self._event = host, event
+
+    def tolist(self) -> List[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
     """Device-side sampling for the sequences of one cache (one random state per slot)."""
 
@@ -68,11 +80,29 @@ class Sampler:
         self.rng_states = torch.ones(max_seqs, dtype=torch.int64, device=self.device)
         self._workspace = workspace
         self._scratch: Optional[torch.Tensor] = None
+        self._pinned = None
+        self._events = None
+        self._turn = 0
 
     def seed_slots(self, slots: Sequence[int], seeds: Sequence[int]) -> None:
         vals = np.array([s or 1 for s in seeds], dtype=np.uint64).view(np.int64)
         idx = torch.tensor(list(slots), dtype=torch.long, device=self.device)
         self.rng_states[idx] = torch.from_numpy(vals).to(self.device)
+
+    def begin_fetch(self, tokens: torch.Tensor) -> "PendingTokens":
+        """Start copying sampled tokens to the host, now, in stream order: work that is launched
+        afterwards (the next step) does not delay the copy.  `.tolist()` of the result waits for it."""
+        n = tokens.numel()
+        if self.device.type != "cuda":
+            return PendingTokens(tokens.reshape(-1).clone(), None)
+        if self._pinned is None or self._pinned[0].numel() < n:
+            self._pinned = [torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._events = [torch.cuda.Event() for _ in range(2)]
+        self._turn ^= 1
+        host, event = self._pinned[self._turn][:n], self._events[self._turn]
+        host.copy_(tokens.reshape(-1), non_blocking=True)
+        event.record()
+        return PendingTokens(host, event)
 
     def sample(self, logits: torch.Tensor, slots: Sequence[int], params: SamplingParams) -> torch.Tensor:
         """int32 [rows] on the device: one token per row of logits[rows, vocab]; row i belongs to slots[i]."""

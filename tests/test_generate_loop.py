@@ -137,6 +137,69 @@ def test_position_limit_and_budget_per_prompt():
     assert generate(eng, smp, [[1]], 0, SamplingParams(0.0))[0].tokens == []
 
 
+class AheadEngine(FakeEngine):
+    """A FakeEngine that also steps on tokens it is handed as a tensor, as the real engine does for
+    tokens that are still on the device; it records which steps were launched that way."""
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.ahead_steps = []
+
+    def step_device_tokens(self, slots, tokens):
+        from rusty_llama_b200.engine import StepEntry
+
+        assert tokens.dtype == torch.int32 and tuple(tokens.shape) == (len(slots),)
+        self.ahead_steps.append(len(self.steps))
+        return self.step([StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens.tolist())])
+
+
+@pytest.mark.parametrize("case", ["stops", "budgets", "limit"])
+def test_launching_ahead_gives_the_same_tokens_and_frees_everything(case):
+    """Steps launched before the host has read the tokens: same results, reasons and callbacks as
+    the plain loop; a sequence that drew a stop token has been stepped once more (its stop token
+    was fed) and nothing of it is kept; no step is launched ahead when a budget or the position
+    limit may end a sequence."""
+    if case == "stops":
+        script = lambda first, n: {11: 0 if n == 6 else 50 + n, 12: 60 + n, 13: 0 if n == 5 else 70 + n}[first]
+        prompts, budget, kw = [[11, 1, 1, 1], [12, 2], [13, 3, 3]], 6, {}
+    elif case == "budgets":
+        script = lambda first, n: 30 + n
+        prompts, budget, kw = [[11, 1], [12, 2, 2], [13]], [2, 5, 3], {"stop_token_ids": []}
+    else:
+        script = lambda first, n: 9
+        prompts, budget, kw = [[1, 1, 1, 1], [2]], [10, 4], {"stop_token_ids": []}
+    runs = []
+    for ahead in (False, True):
+        eng = AheadEngine(max_positions=8 if case == "limit" else 40)
+        smp = ScriptedSampler(eng, script)
+        seen = []
+        stats = GenerationStats()
+        res = generate(eng, smp, prompts, budget, SamplingParams(0.0, 0.9, 7), on_token=lambda r, t: seen.append((r, t)),
+                       stats=stats, launch_ahead=ahead, **kw)
+        assert eng.cache.n_open == 0 and eng.cache.pages_free() == eng.cache.n_pages
+        eng.cache.check_consistent()
+        runs.append(([(r.tokens, r.finish_reason) for r in res], seen, stats.generated_tokens))
+        if not ahead:
+            assert eng.ahead_steps == []
+        else:
+            assert eng.ahead_steps, "no step was launched ahead"
+            assert stats.decode_steps == len(eng.steps) - 1
+            if case == "stops":
+                # a stop token is fed only by a step that was launched ahead
+                assert any(0 in fed for fed in eng.fed.values())
+    assert runs[0] == runs[1]
+
+
+def test_launching_ahead_never_steps_past_a_budget_or_the_position_limit():
+    eng = AheadEngine(max_positions=7)
+    smp = ScriptedSampler(eng, lambda first, n: 9)
+    res = generate(eng, smp, [[1, 1, 1, 1], [2]], [10, 3], SamplingParams(0.0), stop_token_ids=[])
+    assert res[0].tokens == [9, 9, 9, 9] and res[0].finish_reason == POSITION_LIMIT
+    assert res[1].tokens == [9, 9, 9] and res[1].finish_reason == MAX_NEW_TOKENS
+    # positions fed: the long one 4 + 3, the short one 1 + 2; the cache never saw more
+    assert sorted(len(f) for f in eng.fed.values()) == [3, 7]
+
+
 def test_slots_are_given_back_when_a_step_fails():
     eng = FakeEngine()
     smp = ScriptedSampler(eng, lambda first, n: 9)

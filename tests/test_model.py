@@ -218,3 +218,30 @@ def test_sampled_generation_follows_the_plain_sampler(llms, tiny_weights):
         assert len(got) == 16
     assert agree >= 4
     assert alone == outs[2]  # a sequence's draws do not depend on its neighbours
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_launching_ahead_changes_no_token(dtype, temperature, llms):
+    """Steps launched on tokens that are still on the device, against the loop that reads every token
+    first: the same tokens and finish reasons, for sequences that end on stop tokens at different
+    times, on their budgets and together; slots and pages all come back."""
+    name = "B"
+    cfg = TINY[name][0]
+    llm = llms(name, dtype)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (3, 11, 20, 34)]
+    kw = dict(temperature=temperature, top_p=0.9, seed=99, return_results=True)
+    free = llm.engine.cache.pages_free()
+    plain = llm.generate(prompts, max_new_tokens=[12, 20, 7, 20], stop_token_ids=[], launch_ahead=False, **kw)
+    # stop tokens taken from what the sequences really produce, so that they end at different steps
+    stops = [plain[0].tokens[5], plain[1].tokens[9], plain[3].tokens[14]]
+    for stop_ids in ([], stops):
+        a = llm.generate(prompts, max_new_tokens=[12, 20, 7, 20], stop_token_ids=stop_ids, launch_ahead=False, **kw)
+        steps_plain = llm.last_stats.decode_steps
+        b = llm.generate(prompts, max_new_tokens=[12, 20, 7, 20], stop_token_ids=stop_ids, launch_ahead=True, **kw)
+        assert [(r.tokens, r.finish_reason) for r in a] == [(r.tokens, r.finish_reason) for r in b]
+        assert llm.last_stats.decode_steps >= steps_plain
+        assert llm.engine.cache.n_open == 0 and llm.engine.cache.pages_free() == free
+        llm.engine.cache.check_consistent()
+    assert any(r.finish_reason == "stop_token" for r in b)
