@@ -7,6 +7,8 @@
 // kernel, which then writes the normalised row in the activation type: one
 // pass over the row instead of the reference's separate `add_kernel` and
 // `rmsnorm_kernel` (src/backend/cuda.rs:90-116).
+#include <type_traits>
+
 #include "common.cuh"
 
 RL_DEFINE_ERROR_TEXT()
@@ -119,12 +121,81 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   }
 }
 
+// The same for the many rows of a prompt step (bfloat16 runs): a quarter of the threads per row,
+// each keeping up to CHUNKS pieces of four values in registers between the two passes, so that
+// eight blocks share an SM and no shared-memory row is needed.  The sum of squares is added in
+// another order than above, so 32-bit runs, whose bits must not depend on how many rows a step
+// has, never come here.
+template <typename TA, typename TW, typename TD, int CHUNKS>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts, long long part_stride,
+                        const TW* __restrict__ w, TA* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+                        int write_x) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float* xr = x + (size_t)t * d;
+  float v[CHUNKS][4];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (threadIdx.x + c * 256) * 4;
+    if (i < d) load4_g<float>(xr + i, v[c]);
+    else v[c][0] = v[c][1] = v[c][2] = v[c][3] = 0.f;
+  }
+  for (int p = 0; p < n_parts; ++p) {
+    float dv[CHUNKS][4];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int i = (threadIdx.x + c * 256) * 4;
+      if (i < d) load4_g<TD>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv[c]);
+      else dv[c][0] = dv[c][1] = dv[c][2] = dv[c][3] = 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[c][e] += dv[c][e];
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (threadIdx.x + c * 256) * 4;
+    if (write_x && i < d) store4<float>(xr + i, v[c]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss += v[c][e] * v[c][e];
+  }
+  if (w == nullptr) return;
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)d + eps);
+  TA* o = out + (size_t)r * d;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (threadIdx.x + c * 256) * 4;
+    if (i < d) {
+      float wv[4], y[4];
+      load4_g<TW>(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] = v[c][e] * inv * wv[e];
+      store4<TA>(o + i, y);
+    }
+  }
+}
+
+#define ROWS_KERNEL_MIN_ROWS 64
+#define ROWS_KERNEL_CHUNKS 4
+
 template <typename TA, typename TW, typename TD>
 static int launch_add_rmsnorm(float* x, const void* delta, int n_parts, long long part_stride, const void* w,
                               void* out, const int* rows, int n_rows, int d, float eps, int write_x,
                               cudaStream_t stream) {
-  const size_t smem = (size_t)d * sizeof(float);
   const bool vec = d % 4 == 0;
+  if (vec && !std::is_same<TA, float>::value && n_rows >= ROWS_KERNEL_MIN_ROWS && d <= 256 * 4 * ROWS_KERNEL_CHUNKS) {
+    RL_LAUNCH_CHECK(rl_launch(add_rmsnorm_rows_kernel<TA, TW, TD, ROWS_KERNEL_CHUNKS>, n_rows, 256, 0, stream, x,
+                              (const TD*)delta, n_parts, part_stride, (const TW*)w, (TA*)out, rows, d, eps, write_x));
+    return 0;
+  }
+  const size_t smem = (size_t)d * sizeof(float);
   auto kern = vec ? add_rmsnorm_kernel<TA, TW, TD, true> : add_rmsnorm_kernel<TA, TW, TD, false>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) RL_REFUSE(3, "add_rmsnorm: a row of %d values does not fit shared memory", d);

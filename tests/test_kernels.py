@@ -146,6 +146,30 @@ def test_add_rmsnorm(ops, act, wdt, d, parts):
         close_f32(xd3, ref_x, 1e-6)
 
 
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T, d, parts, part_dtype", [(70, 4096, 1, torch.bfloat16), (64, 520, 2, torch.float32), (300, 4100, 0, None), (65, 72, 3, torch.bfloat16)])
+def test_add_rmsnorm_many_rows_in_bfloat16(ops, wdt, T, d, parts, part_dtype):
+    """From 64 rows on a bfloat16 run takes the kernel that keeps a row in registers: widths that
+    fill all of a thread's pieces, some of them and (4100) more than it holds, which falls back."""
+    eps = 1e-5
+    x = torch.randn(T, d) * 2
+    w = (1 + 0.1 * torch.randn(d)).to(wdt)
+    delta = None if parts == 0 else torch.randn(parts, T, d).to(part_dtype)
+    ref_x = x.clone()
+    for p in range(parts):
+        ref_x = ref_x + delta[p].float()
+    xd = x.to(DEV)
+    dd = None if delta is None else (delta[0] if parts == 1 and part_dtype == torch.bfloat16 else delta).contiguous().to(DEV)
+    out = ops.add_rmsnorm(xd, dd, w.to(DEV), eps, torch.bfloat16)
+    close_f32(xd, ref_x, 1e-6)
+    close_bf16(out, plain_rmsnorm(ref_x.double(), w.double(), eps))
+    rows = torch.arange(T - 1, -1, -1, dtype=torch.int32, device=DEV)  # every row, backwards, stream untouched
+    xd2 = x.to(DEV)
+    out2 = ops.add_rmsnorm(xd2, dd, w.to(DEV), eps, torch.bfloat16, rows=rows, write_x=False)
+    assert torch.equal(xd2.cpu(), x)
+    assert torch.equal(out2.cpu(), out.flip(0).cpu())
+
+
 def test_rmsnorm_of_ones_and_eps(ops):
     # src/backend/cpu.rs:750-771
     x = torch.ones(2, 64, device=DEV)
