@@ -183,7 +183,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---------------- tensor-core issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, BN);
-      uint32_t it = 0;
+      // descriptors differ from stage to stage only in their address field (bytes / 16)
+      const uint64_t a_desc0 = make_smem_desc(smem_u32(stages)), b_desc0 = make_smem_desc(smem_u32(stages) + STAGE_A_BYTES);
+      uint32_t it = 0, s = 0, phase = 0;  // slices so far; the stage and the parity of its `full` barrier
       bool ok = true;
       int local = 0;  // tiles done by this block
       for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++local) {
@@ -197,26 +199,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           ok = false;
           break;
         }
+        if (*(volatile int*)&abort_flag) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+          if (!mbar_wait(&full_bar[s], phase)) {
             atomicExch(status, 2);
             abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(stages + (size_t)s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + STAGE_A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = make_smem_desc(a_addr + k * UMMA_K * 2);
-            const uint64_t b_desc = make_smem_desc(b_addr + k * UMMA_K * 2);
-            umma_bf16(tmem_d, a_desc, b_desc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
+          const uint64_t stage_off = (uint64_t)(s * (STAGE_BYTES >> 4));
+          umma_bf16_x4(tmem_d, a_desc0 + stage_off, b_desc0 + stage_off, idesc, kb > kb0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
         }
         if (ok) umma_commit(&acc_full[acc]);  // arrives when the whole tile has been accumulated
       }

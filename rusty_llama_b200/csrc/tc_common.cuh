@@ -79,6 +79,36 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
       "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The four MMAs of a 64-wide k slice in one go: operands are k-major with 128-byte rows, so a k step
+// of 16 bfloat16 moves both descriptors' address fields (bytes / 16) by 2.  Only the first one's
+// accumulate flag varies.  The thread that issues MMAs is alone in feeding the tensor core, and every
+// instruction it spends on descriptors or predicates shows up as idle tensor cycles.
+#define RL_UMMA_X4(GROUP)                                                                                     \
+  asm volatile(                                                                                               \
+      "{\n"                                                                                                   \
+      ".reg .pred p, t;\n"                                                                                    \
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"                                                                   \
+      "setp.ne.b32 p, %4, 0;\n"                                                                               \
+      "setp.eq.b32 t, 0, 0;\n"                                                                                \
+      "add.u64 a1, %1, 2;\n"                                                                                  \
+      "add.u64 b1, %2, 2;\n"                                                                                  \
+      "add.u64 a2, %1, 4;\n"                                                                                  \
+      "add.u64 b2, %2, 4;\n"                                                                                  \
+      "add.u64 a3, %1, 6;\n"                                                                                  \
+      "add.u64 b3, %2, 6;\n"                                                                                  \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], %1, %2, %3, p;\n"                                     \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], a1, b1, %3, t;\n"                                     \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], a2, b2, %3, t;\n"                                     \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], a3, b3, %3, t;\n"                                     \
+      "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first)                         \
+      : "memory")
+__device__ __forceinline__ void umma_bf16_x4(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate_first) {
+  RL_UMMA_X4("1");
+}
+__device__ __forceinline__ void umma_bf16_x4_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate_first) {
+  RL_UMMA_X4("2");
+}
+
 // The barrier receives one arrival when every tcgen05.mma issued before by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

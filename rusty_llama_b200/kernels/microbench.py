@@ -79,17 +79,18 @@ def bench_gemm(a) -> dict:
     nv = min(_copies(a.n * a.k * 2), 16)
     ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
     x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
-    if a.impl == "tc":
+    if a.impl in ("tc", "tc2"):
+        pair = a.impl == "tc2"
         out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
         if a.splits > 1:
-            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.float32, k_splits=a.splits), nv, a.iters, a.warmup)
+            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.float32, k_splits=a.splits, pair=pair), nv, a.iters, a.warmup)
         else:
-            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
+            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out, pair=pair), nv, a.iters, a.warmup)
         ops.tc_status_check()
     else:
         us = _time(lambda i: linear(x, ws[i]), nv, a.iters, a.warmup)
     flops = 2.0 * a.rows * a.n * a.k
-    return {"kernel": "gemm_tc" if a.impl == "tc" else "linear(bf16)", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+    return {"kernel": {"tc": "gemm_tc", "tc2": "gemm_tc2"}.get(a.impl, "linear(bf16)"), "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def _paged(seqs: int, ctx: int, K: int, hd: int, copies: int):
@@ -158,7 +159,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
-    ap.add_argument("--impl", default="linear", choices=["linear", "tc", "stream"], help="gemm: the dispatching linear() or the tcgen05 kernel; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent bulk-copy kernel")
+    ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent bulk-copy kernel")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch the timed calls one by one instead of as one graph")

@@ -504,7 +504,9 @@ def _tc_status_word(device: torch.device) -> torch.Tensor:
 def tc_status_check() -> None:
     """Raise if a bounded wait inside a tensor-core kernel expired since the last check (synchronises)."""
     names = {1: "gemm_tc: the TMA producer", 2: "gemm_tc: the tensor-core issuer", 3: "gemm_tc: the epilogue",
-             4: "gemm_tc: the tensor-core issuer (for a free accumulator)"}
+             4: "gemm_tc: the tensor-core issuer (for a free accumulator)",
+             41: "gemm_tc2: a TMA producer", 42: "gemm_tc2: the tensor-core issuer", 43: "gemm_tc2: an epilogue",
+             44: "gemm_tc2: the tensor-core issuer (for a free accumulator)"}
     for word in _tc_status.values():
         code = int(word.item())
         if code:
@@ -516,10 +518,12 @@ def tc_status_check() -> None:
 
 def gemm_tc(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1,
+    swiglu: bool = False, k_splits: int = 1, pair: bool = False,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
 
+    pair: the kernel in which two SMs share a 256 x 256 tile (tcgen05 cta_group::2) instead of one SM
+    per 128 x 256 tile; same results, less shared-memory traffic per flop.
     swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit accumulators.
     k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (at most k_splits of
     them), for a consumer that adds them up: more blocks at work when the output has few tiles."""
@@ -545,8 +549,8 @@ def gemm_tc(
         _need(tuple(out.shape) == (M, n_out), "gemm_tc: out has the wrong shape")
         ldo = _rows(out, "gemm_tc out")
     status = _tc_status_word(x.device)
-    lib = build.load("gemm_tc")
-    rc = lib.rl_gemm_tc(
+    lib = build.load("gemm_tc2" if pair else "gemm_tc")
+    rc = (lib.rl_gemm_tc2 if pair else lib.rl_gemm_tc)(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(ldo),
         c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), _stream(),
     )

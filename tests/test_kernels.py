@@ -449,12 +449,14 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
      (640, 17920, 128), (1280, 25600, 64)],  # the last two give every block several tiles: both accumulators, many rounds
 )
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_tc(ops, M, N, K, out_dtype):
-    """The tcgen05 kernel at full tiles, at ragged edges in M, N and K, and with a long K."""
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc(ops, M, N, K, out_dtype, pair):
+    """The tcgen05 kernels (one SM per tile, and pairs of SMs) at full tiles, at ragged edges in M, N
+    and K, and with a long K."""
     g = torch.Generator().manual_seed(M + N + K)
     x = bf16_round(torch.randn(M, K, generator=g))
     w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
-    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
+    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype, pair=pair)
     torch.cuda.synchronize()
     ops.tc_status_check()
     if out_dtype == torch.float32:
@@ -464,11 +466,12 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("M, N, K, splits", [(64, 512, 4096, 8), (20, 300, 1000, 3), (200, 256, 640, 64), (64, 4096, 14336, 8)])
-def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits):
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits, pair):
     g = torch.Generator().manual_seed(M + N)
     x = bf16_round(torch.randn(M, K, generator=g))
     w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
-    parts = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits)
+    parts = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits, pair=pair)
     torch.cuda.synchronize()
     ops.tc_status_check()
     assert parts.dim() == 3 and parts.shape[1:] == (M, N) and 1 < parts.shape[0] <= splits
@@ -478,15 +481,16 @@ def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits):
         close_dot_f32(parts[i], x[:, i * per : (i + 1) * per], w[:, i * per : (i + 1) * per])
 
 
-def test_gemm_tc_each_output_sees_its_own_row_and_column(ops):
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc_each_output_sees_its_own_row_and_column(ops, pair):
     """x = one-hot rows, w = distinct rows: out[m, n] must be w[n, pick(m)], which exposes any mix-up of
-    rows, columns, k slices or the swizzle."""
-    M, N, K = 256, 512, 320
+    rows, columns, k slices, the swizzle, or the two halves of a pair's tile."""
+    M, N, K = 512, 768, 320
     pick = torch.arange(M) * 7 % K
     x = torch.zeros(M, K)
     x[torch.arange(M), pick] = 1.0
     w = bf16_round(torch.randn(N, K, generator=torch.Generator().manual_seed(1)))
-    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32)
+    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, pair=pair)
     torch.cuda.synchronize()
     ops.tc_status_check()
     assert torch.equal(out.cpu(), w[:, pick].T.contiguous())
