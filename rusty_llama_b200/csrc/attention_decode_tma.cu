@@ -1,0 +1,426 @@
+// Decode attention over the paged cache in bfloat16 for head size 128, the form for small batches
+// whose key range is cut into splits: the same mathematics and the same scratch layout as
+// `attn_decode` (attention_decode.cu; the reference runs its scalar kernel with a single row here,
+// src/backend/cuda.rs:1189-1192), another way of feeding it.
+//
+// There a block is one warp that copies its own tiles with cp.async, four blocks to an SM, and the
+// warp's instruction stream (about a thousand instructions per 16 KB of keys and values) sets the
+// pace.  Here a block is four product warps and one copying lane on a ring of whole cache pages:
+//   warp 4 (one lane)  TMA: page after page of the split (64 keys: K and V, 32 KB, four tensor
+//                      copies straight from the page, 128-byte swizzled) into a three-stage ring;
+//   warps 0-3          warp w owns keys 16w .. 16w + 15 of every page: S^T[16 keys x 8 heads] =
+//                      K Q^T and O^T[128 x 8 heads] += V^T P^T with mma.sync.m16n8k16, operands by
+//                      ldmatrix from the swizzled tiles, online softmax per head in 32-bit
+//                      registers, P^T by movmatrix; its own running maximum, sum and output.
+// At the end the four warps' partial results are merged in shared memory (in warp order) and the
+// block writes one partial (max as a base-2 exponent, sum, unnormalised output) per head to
+// scratch; the merge kernel adds the splits in split order.
+// Two blocks share an SM (99 KB of shared memory each): 192 KB of keys and values in flight per SM,
+// eight product warps.
+//
+// Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
+#include "tc_common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define HD 128
+#define HEADS 8     // query heads per block (the N of the MMA)
+#define PAGE 64     // positions per cache page = keys per tile
+#define STAGES 3
+#define PRODUCT_WARPS 4
+#define NUM_THREADS ((PRODUCT_WARPS + 1) * 32)
+#define HALF_BYTES (PAGE * 64 * 2)            // one [64 keys][64 dims] swizzled box: 8 KB
+#define STAGE_BYTES (4 * HALF_BYTES)          // K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127
+#define Q_STRIDE (HD + 8)                     // bf16 elements per row of the query tile
+#define O_STRIDE (HD + 4)                     // floats per head in the merge buffer
+#define SMEM_BYTES (STAGES * STAGE_BYTES + HEADS * Q_STRIDE * 2 + 1024)
+
+struct DecodeBarriers {
+  uint64_t full[STAGES], empty[STAGES];
+  int abort_flag;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// 8x8 matrix of 16-bit values held one 32-bit register per lane (row lane/4, columns 2*(lane%4), +1): its transpose
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void product_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(PRODUCT_WARPS * 32) : "memory"); }
+
+// byte offset, inside a [64 keys][64 dims] box, of the 16-byte piece `piece` (0..7) of row `row`
+__device__ __forceinline__ uint32_t swz(int row, int piece) { return (uint32_t)(row * 128 + ((piece ^ (row & 7)) << 4)); }
+
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table, int table_width,
+                       const int* __restrict__ seq_len, float* __restrict__ part_o, float* __restrict__ part_ml, int H,
+                       int K, int window, float scale_log2, int n_splits, int* __restrict__ status) {
+  // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
+  // aligned, as the 128-byte swizzle needs)
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* ring = smem;
+  bf16* q_s = reinterpret_cast<bf16*>(ring + STAGES * STAGE_BYTES);  // [HEADS][Q_STRIDE]
+  DecodeBarriers& bars = *reinterpret_cast<DecodeBarriers*>(reinterpret_cast<unsigned char*>(q_s) + HEADS * Q_STRIDE * 2);
+  // after the last page the ring is free and holds the four warps' partial results
+  float* merge_o = reinterpret_cast<float*>(ring);                      // [warps][HEADS][O_STRIDE]
+  float* merge_ml = merge_o + PRODUCT_WARPS * HEADS * O_STRIDE;         // [warps][HEADS][2]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = H / K;
+  const int groups_per_kv = (G + HEADS - 1) / HEADS;
+  const int split = blockIdx.x;
+  const int kh = blockIdx.y / groups_per_kv;
+  const int g0 = (blockIdx.y - kh * groups_per_kv) * HEADS;
+  const int n_heads = min(HEADS, G - g0);
+  const int h0 = kh * G + g0;
+  const int s = blockIdx.z;
+  const bool aligned = (smem_u32(smem) & 1023u) == 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&bars.full[i], 1);
+      mbar_init(&bars.empty[i], PRODUCT_WARPS);
+    }
+    bars.abort_flag = aligned ? 0 : 1;
+    if (!aligned) atomicExch(status, 56);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // rows of the query tile past the group's heads are zero
+  for (int i = threadIdx.x; i < HEADS * Q_STRIDE / 2; i += NUM_THREADS) reinterpret_cast<uint32_t*>(q_s)[i] = 0u;
+  __syncthreads();
+  pdl_trigger();
+  pdl_wait();  // the newest key and value and the queries are the previous kernel's output
+
+  const int kv_len = seq_len[s];
+  const int pos = kv_len - 1;
+  const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  const int tile_lo = first / PAGE, tile_hi = pos / PAGE;  // inclusive, in pages
+  const int n_tiles = tile_hi - tile_lo + 1;
+  const int per_split = (n_tiles + n_splits - 1) / n_splits;
+  const int my_lo = tile_lo + split * per_split;
+  const int my_hi = min(my_lo + per_split - 1, tile_hi);
+  const int* table = block_table + (size_t)s * table_width;
+
+  if (warp == PRODUCT_WARPS) {
+    // ---------------- copies
+    if (lane == 0 && !*(volatile int*)&bars.abort_flag) {
+      const uint32_t ring_addr = smem_u32(ring);
+      int issued = 0;
+      for (int tile = my_lo; tile <= my_hi; ++tile, ++issued) {
+        const int st = issued % STAGES, round = issued / STAGES;
+        if (round > 0 && !mbar_wait(&bars.empty[st], (round - 1) & 1)) {
+          atomicExch(status, 51);
+          bars.abort_flag = 1;
+          break;
+        }
+        if (*(volatile int*)&bars.abort_flag) break;
+        const int page = table[tile];
+        unsigned char* dst = ring + (size_t)st * STAGE_BYTES;
+        (void)ring_addr;
+        mbar_expect_tx(&bars.full[st], STAGE_BYTES);
+        tma_load_4d(dst, &map_k, &bars.full[st], 0, 0, kh, page);
+        tma_load_4d(dst + HALF_BYTES, &map_k, &bars.full[st], 64, 0, kh, page);
+        tma_load_4d(dst + 2 * HALF_BYTES, &map_v, &bars.full[st], 0, 0, kh, page);
+        tma_load_4d(dst + 3 * HALF_BYTES, &map_v, &bars.full[st], 64, 0, kh, page);
+      }
+      // nothing may still be writing shared memory when the block ends (or when the ring is reused for
+      // the merge): if someone gave up, wait (bounded) for the copies that were started
+      if (*(volatile int*)&bars.abort_flag)
+        for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&bars.full[j % STAGES], (j / STAGES) & 1);
+    }
+    return;  // the product warps meet at a barrier of their own
+  }
+
+  // ---------------- products
+  const int g = lane >> 2, t4 = lane & 3;
+  {
+    // this block's queries: HEADS rows of 128 values, 16 bytes per thread
+    const int r = threadIdx.x >> 4, piece = threadIdx.x & 15;  // 128 threads = 8 rows x 16 pieces
+    if (r < n_heads)
+      *reinterpret_cast<uint4*>(q_s + (size_t)r * Q_STRIDE + piece * 8) =
+          __ldcg(reinterpret_cast<const uint4*>(q + (size_t)s * q_stride + (size_t)(h0 + r) * HD + piece * 8));
+  }
+  product_warps_sync();
+  uint32_t qf[HD / 16][2];  // Q^T as B fragments: (dims kk*16 + 2*t4 [+8], head g)
+#pragma unroll
+  for (int k2 = 0; k2 < HD / 32; ++k2) {
+    uint32_t r[4];
+    ldmatrix_x4(r, smem_u32(q_s + (size_t)(lane & 7) * Q_STRIDE + k2 * 32 + 8 * (lane >> 3)));
+    qf[2 * k2][0] = r[0];
+    qf[2 * k2][1] = r[1];
+    qf[2 * k2 + 1][0] = r[2];
+    qf[2 * k2 + 1][1] = r[3];
+  }
+
+  float o_acc[HD / 16][4];  // (dim dt*16 + g [+8], head 2*t4 [+1])
+#pragma unroll
+  for (int i = 0; i < HD / 16; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // heads 2*t4, 2*t4+1
+  float l_run[2] = {0.f, 0.f};              // per-thread partial sums over this thread's keys
+
+  // rows this lane addresses in the ldmatrix calls: K as A operand (16 keys x 16 dims), V transposed
+  const int k_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), k_piece = lane >> 4;      // + 2 * kk
+  const int v_row = warp * 16 + (lane & 7) + 8 * (lane >> 4), v_piece = (lane >> 3) & 1;      // + 2 * dt
+  bool ok = true;
+  int done = 0;
+  for (int tile = my_lo; tile <= my_hi && ok; ++tile, ++done) {
+    const int st = done % STAGES;
+    if (!mbar_wait(&bars.full[st], (done / STAGES) & 1)) {
+      if (lane == 0) {
+        atomicExch(status, 52);
+        bars.abort_flag = 1;
+      }
+      ok = false;
+      break;
+    }
+    if (*(volatile int*)&bars.abort_flag) {
+      ok = false;
+      break;
+    }
+    const uint32_t k_s = smem_u32(ring) + st * STAGE_BYTES, v_s = k_s + 2 * HALF_BYTES;
+
+    // ---- S^T = K Q^T: this warp's 16 keys x 8 heads
+    float s_acc[4] = {0.f, 0.f, 0.f, 0.f};  // (key g [+8], head 2*t4 [+1])
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, k_s + (kk >> 2) * HALF_BYTES + swz(k_row, ((kk & 3) << 1) | k_piece));
+      mma_bf16(s_acc, a, qf[kk][0], qf[kk][1]);
+    }
+
+    // ---- mask by position, scale to base-2 exponents, online softmax per head (column)
+    const int key0 = tile * PAGE + warp * 16;
+    const bool need_mask = key0 < first || key0 + 15 > pos;
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float v = s_acc[e] * scale_log2;
+      if (need_mask) {
+        const int key = key0 + g + 8 * (e >> 1);
+        if (key < first || key > pos) v = -INFINITY;
+      }
+      s_acc[e] = v;
+      tmax[e & 1] = fmaxf(tmax[e & 1], v);
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float mx = tmax[j];
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[j], mx);
+      m_use[j] = (m_new == -INFINITY) ? 0.f : m_new;  // a warp whose 16 keys are all masked so far
+      alpha[j] = exp2f(m_run[j] - m_use[j]);
+      m_run[j] = m_new;
+      l_run[j] *= alpha[j];
+    }
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      p[e] = exp2f(s_acc[e] - m_use[e & 1]);
+      l_run[e & 1] += p[e];
+    }
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(p[0], p[1]));  // keys 0..7 of the warp's 16
+    const uint32_t pb1 = movmatrix_trans(pack_bf16(p[2], p[3]));  // keys 8..15
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) {
+      o_acc[i][0] *= alpha[0];
+      o_acc[i][1] *= alpha[1];
+      o_acc[i][2] *= alpha[0];
+      o_acc[i][3] *= alpha[1];
+    }
+
+    // ---- O^T += V^T P^T: head size (16-row tiles) x 8 heads over the warp's 16 keys
+#pragma unroll
+    for (int dt = 0; dt < HD / 16; ++dt) {
+      uint32_t a[4];
+      ldmatrix_x4_trans(a, v_s + (dt >> 2) * HALF_BYTES + swz(v_row, ((dt & 3) << 1) | v_piece));
+      mma_bf16(o_acc[dt], a, pb0, pb1);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars.empty[st]);
+  }
+
+  // ---- the four warps' partial results meet in the ring's memory, which nobody reads any more once
+  // every product warp is here (a warp that gave up comes here too)
+  product_warps_sync();
+  if (*(volatile int*)&bars.abort_flag) return;  // the same answer for all four warps: nothing changes it after the barrier
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float l = l_run[j];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    const int head = 2 * t4 + j;
+    if (g == 0) {
+      merge_ml[(warp * HEADS + head) * 2] = m_run[j];
+      merge_ml[(warp * HEADS + head) * 2 + 1] = l;
+    }
+    float* mo = merge_o + (size_t)(warp * HEADS + head) * O_STRIDE;
+#pragma unroll
+    for (int dt = 0; dt < HD / 16; ++dt) {
+      mo[dt * 16 + g] = o_acc[dt][j];
+      mo[dt * 16 + g + 8] = o_acc[dt][2 + j];
+    }
+  }
+  product_warps_sync();
+  {
+    const int head = threadIdx.x >> 4, d0 = threadIdx.x & 15;  // 128 threads = 8 heads x 16 lanes of dims
+    if (head < n_heads) {
+      float mw[PRODUCT_WARPS], M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < PRODUCT_WARPS; ++w) {
+        mw[w] = merge_ml[(w * HEADS + head) * 2];
+        M = fmaxf(M, mw[w]);
+      }
+      float l = 0.f;
+#pragma unroll
+      for (int w = 0; w < PRODUCT_WARPS; ++w) {
+        mw[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - M);
+        l += mw[w] * merge_ml[(w * HEADS + head) * 2 + 1];
+      }
+      const size_t slot = ((size_t)s * H + h0 + head) * n_splits + split;
+      if (d0 == 0) {
+        part_ml[slot * 2] = M;  // -inf when the split held no key at all (an empty split)
+        part_ml[slot * 2 + 1] = l;
+      }
+      float* po = part_o + slot * HD;
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) {
+        const int d = d0 + 16 * j;
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < PRODUCT_WARPS; ++w) o += mw[w] * merge_o[(size_t)(w * HEADS + head) * O_STRIDE + d];
+        po[d] = o;
+      }
+    }
+  }
+}
+
+// out[s, h, :] = sum_split 2^(m_split - M) o_split / sum_split 2^(m_split - M) l_split, in split order.
+// One block per (sequence, head); at most 64 splits.
+__global__ void attn_decode_tma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                             bf16* __restrict__ out, int out_stride, int H, int n_splits) {
+  __shared__ float w_s[64];
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, s = blockIdx.y;
+  const float* ml = part_ml + ((size_t)s * H + h) * n_splits * 2;
+  const float* po = part_o + ((size_t)s * H + h) * n_splits * HD;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
+    if (lane < n_splits) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(ml + 2 * lane));
+      m0 = v.x;
+      l0 = v.y;
+    }
+    if (lane + 32 < n_splits) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(ml + 2 * (lane + 32)));
+      m1 = v.x;
+      l1 = v.y;
+    }
+    const float M = warp_max(fmaxf(m0, m1));
+    const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
+    const float w1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - M);
+    const float inv = 1.0f / warp_sum(w0 * l0 + w1 * l1);
+    w_s[lane] = w0 * inv;
+    w_s[lane + 32] = w1 * inv;
+  }
+  __syncthreads();
+  const int d = threadIdx.x;  // HD threads
+  float o = 0.f;
+  int i = 0;
+  for (; i + 4 <= n_splits; i += 4) {
+    const float v0 = __ldcg(po + (size_t)i * HD + d), v1 = __ldcg(po + (size_t)(i + 1) * HD + d);
+    const float v2 = __ldcg(po + (size_t)(i + 2) * HD + d), v3 = __ldcg(po + (size_t)(i + 3) * HD + d);
+    o += w_s[i] * v0;
+    o += w_s[i + 1] * v1;
+    o += w_s[i + 2] * v2;
+    o += w_s[i + 3] * v3;
+  }
+  for (; i < n_splits; ++i) o += w_s[i] * __ldcg(po + (size_t)i * HD + d);
+  out[(size_t)s * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(o);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+RL_API int rl_attn_decode_tma_head_dim() { return HD; }
+
+// Same arguments as rl_attn_decode (scratch: part_o of n_seqs*H*n_splits*hd floats, part_ml of
+// n_seqs*H*n_splits*2), plus the number of cache pages and a status word: one int in device memory,
+// 0 before the call; non-zero afterwards means that a bounded wait expired (51 the copying lane, 52 a
+// product warp; 56: shared memory not aligned) and the output is not valid.
+RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
+                              const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
+                              void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
+                              float scale, int n_splits, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
+  if (hd != HD) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for %d", hd, HD);
+  if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
+  if (page_size != PAGE) RL_REFUSE(4, "attn_decode_tma: page size %d, this kernel is built for %d", page_size, PAGE);
+  if (q_stride % 8) RL_REFUSE(5, "attn_decode_tma: query row stride %d breaks 16-byte alignment", q_stride);
+  if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
+  if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
+  if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) RL_REFUSE(9, "attn_decode_tma: cuTensorMapEncodeTiled is not available");
+  CUtensorMap map_k, map_v;
+  for (int which = 0; which < 2; ++which) {
+    cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)PAGE, (cuuint64_t)K, (cuuint64_t)n_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)PAGE * HD * 2, (cuuint64_t)K * PAGE * HD * 2};
+    cuuint32_t box[4] = {64, PAGE, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_pages : k_pages), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      RL_REFUSE(10, "attn_decode_tma: cannot describe the cache pages to TMA");
+  }
+  auto kern = attn_decode_tma_kernel;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    RL_REFUSE(11, "attn_decode_tma: cannot get %d bytes of shared memory", SMEM_BYTES);
+  const int G = H / K;
+  dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
+  RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, SMEM_BYTES, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
+                            table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status));
+  dim3 grid2(H, n_seqs);
+  RL_LAUNCH_CHECK(rl_launch(attn_decode_tma_merge_kernel, grid2, HD, 0, stream, (const float*)part_o, (const float*)part_ml,
+                            (bf16*)out, out_stride, H, n_splits));
+  return 0;
+}

@@ -113,11 +113,13 @@ def bench_attn_decode(a) -> dict:
     ks, vs, table = _paged(a.seqs, a.ctx, K, hd, nv)
     q = torch.randn(a.seqs, (H + 2 * K) * hd, device=dev, dtype=torch.bfloat16)
     seq_len = torch.full((a.seqs,), a.ctx, dtype=torch.int32, device=dev)
-    n_splits = a.splits or decode_splits(a.seqs, H, K, a.ctx)
+    n_splits = a.splits or decode_splits(a.seqs, H, K, a.ctx, 0 if a.impl == 'warp' else hd)
     scratch = torch.empty(ops.attn_decode_scratch_floats(a.seqs, H, hd, n_splits), device=dev)
     out = torch.empty(a.seqs, H * hd, device=dev, dtype=torch.bfloat16)
-    us = _time(lambda i: ops.attn_decode(q, ks[i], vs[i], table, seq_len, H, K, hd, n_splits, scratch, out=out), nv, a.iters, a.warmup)
-    return {"kernel": "attn_decode", "seqs": a.seqs, "ctx": a.ctx, "H": H, "K": K, "hd": hd, "splits": n_splits, "us": round(us, 2),
+    impl = {"tma": "tma", "warp": "warp"}.get(a.impl, "auto")
+    us = _time(lambda i: ops.attn_decode(q, ks[i], vs[i], table, seq_len, H, K, hd, n_splits, scratch, out=out, impl=impl), nv, a.iters, a.warmup)
+    ops.tc_status_check()
+    return {"kernel": "attn_decode", "impl": impl, "seqs": a.seqs, "ctx": a.ctx, "H": H, "K": K, "hd": hd, "splits": n_splits, "us": round(us, 2),
             "GBps": round(kv_bytes / us / 1e3, 1)}
 
 
@@ -159,7 +161,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
-    ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent bulk-copy kernel")
+    ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream", "tma", "warp"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent TMA-fed kernel; attn_decode: tma or warp = one of its two kernels")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch the timed calls one by one instead of as one graph")

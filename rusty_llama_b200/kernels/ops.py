@@ -270,6 +270,9 @@ def attn_generic(
     return out
 
 
+ATTN_DECODE_TMA_HEAD_DIM = 128
+
+
 def attn_decode_scratch_floats(n_seqs: int, num_heads: int, head_dim: int, n_splits: int) -> int:
     return n_seqs * num_heads * n_splits * (head_dim + 2)
 
@@ -277,11 +280,13 @@ def attn_decode_scratch_floats(n_seqs: int, num_heads: int, head_dim: int, n_spl
 def attn_decode(
     q: torch.Tensor, k_pages, v_pages, block_table, seq_len, num_heads: int, num_kv_heads: int, head_dim: int,
     n_splits: int, scratch: torch.Tensor, window: int = 0, scale: Optional[float] = None,
-    out: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None, impl: str = "auto",
 ) -> torch.Tensor:
     """One query token per sequence over keys 0..seq_len-1, the key range cut into `n_splits`.
 
-    scratch: float32 tensor of at least attn_decode_scratch_floats(...) elements."""
+    scratch: float32 tensor of at least attn_decode_scratch_floats(...) elements.
+    impl: "warp" = one-warp blocks that copy their own tiles, "tma" = four-warp blocks on a TMA-fed
+    ring of whole pages (head size 128 only), "auto" = "tma" where it applies, else "warp"."""
     _cuda(q, "attn_decode q", contiguous=False)
     qs = _rows(q, "attn_decode q")
     S = q.shape[0]
@@ -302,6 +307,21 @@ def attn_decode(
     n_o = S * num_heads * n_splits * head_dim
     part_o = c_void_p(scratch.data_ptr())
     part_ml = c_void_p(scratch.data_ptr() + 4 * n_o)
+    _need(impl in ("auto", "warp", "tma"), f"attn_decode: unknown impl {impl!r}")
+    if impl == "auto":
+        impl = "tma" if (head_dim == ATTN_DECODE_TMA_HEAD_DIM and q.dtype == torch.bfloat16) else "warp"
+    if impl == "tma":
+        _need(q.dtype == torch.bfloat16, "attn_decode: the TMA kernel is bfloat16 only")
+        status = _tc_status_word(q.device)
+        lib = build.load("attention_decode_tma")
+        rc = lib.rl_attn_decode_tma(
+            _p(q), c_int(qs), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
+            c_int(block_table.shape[1]), _p(seq_len), part_o, part_ml, _p(out), c_int(out.stride(0)), c_int(S),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
+            c_int(n_splits), _p(status), _stream(),
+        )
+        _check(lib, rc, "attn_decode_tma", kernels=2)
+        return out
     lib = build.load("attention_decode")
     rc = lib.rl_attn_decode(
         _p(q), c_int(_dt(q, "attn_decode")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table),
@@ -512,7 +532,8 @@ def tc_status_check() -> None:
         if code:
             word.zero_()
             who = names.get(code, f"flash_prefill_tc: a role (wait {code})" if 11 <= code <= 23 else
-                            f"gemv_stream: a role (wait {code})" if 31 <= code <= 37 else "a role")
+                            f"gemv_stream: a role (wait {code})" if 31 <= code <= 37 else
+                            f"attn_decode_tma: a role (wait {code})" if 51 <= code <= 56 else "a role")
             raise KernelError(f"{who} gave up waiting on a barrier (code {code}); results of that step are not valid")
 
 

@@ -289,6 +289,52 @@ def test_attn_decode(ops, H, K, hd, n_splits, window):
     assert torch.isnan(scratch[-7:]).all()  # the kernel stays inside the scratch it asked for
 
 
+@pytest.mark.parametrize("H, K", [(8, 2), (4, 4), (32, 8), (24, 1), (5, 1)])
+@pytest.mark.parametrize("n_splits, window", [(1, 0), (3, 0), (8, 0), (2, 100), (64, 0), (5, 333)])
+def test_attn_decode_tma(ops, H, K, n_splits, window):
+    """The four-warp kernel on a TMA-fed ring of pages (head size 128): lengths that end at a page's
+    first and last key and inside a warp's 16 keys, more splits than pages (empty splits), groups
+    of 1, 4, 5 and 24 query heads per kv head (fewer than 8, and more than one block per kv head)."""
+    hd = 128
+    lens = [1, 64, 65, 300, 128, 1000, 17]
+    S = len(lens)
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=3)
+    q = bf16_round(torch.randn(S, (H + 2 * K) * hd))
+    scratch = torch.full((ops.attn_decode_scratch_floats(S, H, hd, n_splits) + 7,), float("nan"), device=DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = ops.attn_decode(q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, seq_len, H, K, hd, n_splits, scratch,
+                          window=window, impl="tma")
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    ref = torch.cat([
+        ref_attention_rows(q[s : s + 1, : H * hd].view(1, H, hd), kv, s, [lens[s] - 1], window) for s in range(S)
+    ]).view(S, H * hd)
+    close_bf16(out, ref)
+    assert torch.isnan(scratch[-7:]).all()  # the kernel stays inside the scratch it asked for
+
+
+def test_attn_decode_tma_finds_a_far_key(ops):
+    """One key far back among hundreds carries almost all the weight: a kernel that skips a page, a
+    split, a warp's 16 keys or a swizzled piece returns something else entirely."""
+    H, K, hd = 4, 1, 128
+    for far in (0, 15, 16, 63, 64, 127, 450, 512):
+        kv = PagedKV([513], K, hd, torch.bfloat16, seed=4)
+        q = bf16_round(torch.randn(1, H * hd))
+        page, slot = int(kv.table[0, far // PAGE]), far % PAGE
+        boost = bf16_round(q.view(H, hd).mean(dim=0) * 4)
+        kv.k[0][far, 0] = boost
+        kv.k_pages[page, 0, slot] = boost.to(torch.bfloat16).to(DEV)
+        qq = bf16_round(boost.repeat(H) * 1.0)[None]
+        scratch = torch.empty(ops.attn_decode_scratch_floats(1, H, hd, 4), device=DEV)
+        out = ops.attn_decode(qq.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([513], dtype=torch.int32, device=DEV),
+                              H, K, hd, 4, scratch, impl="tma")
+        torch.cuda.synchronize()
+        ops.tc_status_check()
+        ref = ref_attention_rows(qq.view(1, H, hd), kv, 0, [512]).view(1, H * hd)
+        close_bf16(out, ref)
+        assert float((ref.view(H, hd)[0] - kv.v[0][far, 0].double()).abs().max()) < 0.05
+
+
 def test_attn_decode_finds_a_far_key(ops):
     """One key far back among hundreds carries almost all the weight: a kernel that skips a page,
     a split or a tile edge returns something else entirely."""
