@@ -128,6 +128,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  // barriers and tensor memory are set up: from here on the kernel reads what its predecessor wrote
+  pdl_trigger();
+  pdl_wait();
 
   if (warp == SOFTMAX_WARPS) {
     // ---------------- TMA producer
@@ -452,7 +455,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     RL_REFUSE(12, "flash_prefill_tc: cannot get %zu bytes of shared memory", smem);
   dim3 grid((max_q_len + BMQ - 1) / BMQ, H, n_seqs);
-  kern<<<grid, NUM_THREADS, smem, stream>>>(map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0, (bf16*)out, out_stride,
-                                            H, K, window, scale * 1.4426950408889634f, status);
-  RL_LAUNCH_RESULT();
+  RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
+                            (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status));
+  return 0;
 }

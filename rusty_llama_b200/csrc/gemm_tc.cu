@@ -140,7 +140,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   // barriers and tensor memory are set up: from here on the kernel reads what its predecessor wrote
-  // (no explicit trigger: the next kernel is released when this one's blocks have finished)
+  pdl_trigger();
   pdl_wait();
 
   if (warp == 0) {
