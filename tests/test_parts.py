@@ -358,3 +358,161 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path, graphs):
     # the window group gave pages back while sequence a grew
     outs = llm.generate([a[:10], b[:3]], max_new_tokens=5, temperature=0.0, stop_token_ids=[])
     assert [len(o) for o in outs] == [5, 5]
+
+
+# --------------------------------------------------------------------------- a second toy: routing and another position encoding
+def register_toy_routed():
+    """A feed-forward that routes every token to one of its experts, and a position encoding that is
+    not rotary (sinusoids added to queries and keys), both defined here and named layer by layer:
+    layer 0 routes over three experts, layer 1 over two of another size and keeps the library's rotary."""
+    import rusty_llama_b200 as rl
+    from rusty_llama_b200.config import RopeScaling
+    from rusty_llama_b200.kernels.linear import linear
+    from rusty_llama_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, ParamInfo, PositionEncoding
+    from rusty_llama_b200.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    @FEED_FORWARDS.register("toy_top1_experts", replace=True)
+    class Top1Experts(FeedForward):
+        """Router logits r = Wr xn in 32-bit, p = softmax(r); the token goes to expert e = argmax p
+        alone and gets p_e * W2_e relu(W1_e xn).  Every expert runs on every token and a mask picks,
+        so that shapes never depend on data (a replayed graph stays valid)."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.d, self.n, self.E = spec.params["hidden_size"], spec.params["intermediate_size"], spec.params["experts"]
+
+        def param_infos(self):
+            infos = {self.prefix + "router.weight": ParamInfo((self.E, self.d))}
+            for e in range(self.E):
+                infos[f"{self.prefix}experts.{e}.w1.weight"] = ParamInfo((self.n, self.d))
+                infos[f"{self.prefix}experts.{e}.w2.weight"] = ParamInfo((self.d, self.n))
+            return infos
+
+        def load(self, tensors):
+            self.router = tensors[self.prefix + "router.weight"]
+            self.w1 = [tensors[f"{self.prefix}experts.{e}.w1.weight"] for e in range(self.E)]
+            self.w2 = [tensors[f"{self.prefix}experts.{e}.w2.weight"] for e in range(self.E)]
+
+        def forward(self, xn, step):
+            p = torch.softmax(linear(xn, self.router).float(), dim=-1)
+            top = p.argmax(dim=-1, keepdim=True)
+            gate = torch.zeros_like(p).scatter_(1, top, p.gather(1, top))  # p_e at the chosen expert, 0 elsewhere
+            out = torch.zeros_like(xn, dtype=torch.float32)
+            for e in range(self.E):
+                out += gate[:, e : e + 1] * linear(torch.relu(linear(xn, self.w1[e])), self.w2[e]).float()
+            return out.to(xn.dtype)
+
+    @POSITIONS.register("toy_added_sinusoid", replace=True)
+    class AddedSinusoid(PositionEncoding):
+        """q and k of every head get table[pos] added, table[pos, j] = amp * sin(pos / base^(j / hd) + j)."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.base, self.amp = float(spec.params["base"]), float(spec.params["amplitude"])
+
+        def rotate(self, q, k, step):
+            hd = q.shape[-1]
+            j = torch.arange(hd, device=q.device, dtype=torch.float32)
+            ang = step.tok_pos.float()[:, None] / (self.base ** (j / hd))[None, :] + j[None, :]
+            add = (self.amp * torch.sin(ang)).to(q.dtype)[:, None, :]
+            q += add
+            k += add
+
+    def describe(c):
+        d = c["width"]
+        norm = lambda p: PartSpec("rmsnorm", {"size": d, "eps": c["eps"]}, p)
+        experts = lambda p, n, E: PartSpec("toy_top1_experts", {"hidden_size": d, "intermediate_size": n, "experts": E}, p)
+        att = lambda p, position: PartSpec(
+            "attention", {"hidden_size": d, "num_heads": 3, "num_kv_heads": 1, "head_dim": 24, "window": 0, "position": position}, p)
+        layers = (
+            LayerSpec("prenorm", att("l0.att.", PartSpec("toy_added_sinusoid", {"base": 30.0, "amplitude": 0.5})), experts("l0.moe.", 56, 3),
+                      {"mixer": norm("l0.n1."), "feed_forward": norm("l0.n2.")}),
+            LayerSpec("prenorm", att("l1.att.", PartSpec("rotary", {"rotary_dim": 24, "theta": 80.0, "scaling": RopeScaling(), "interleaved": False})),
+                      experts("l1.moe.", 40, 2), {"mixer": norm("l1.n1."), "feed_forward": norm("l1.n2.")}),
+        )
+        return ModelSpec("ToyRoutedForTests", d, c["vocab"], c["positions"], PartSpec("token_embedding", {"vocab_size": c["vocab"], "hidden_size": d}, "emb."),
+                         layers, (ScheduleEntry(0), ScheduleEntry(1)), norm("final."),
+                         PartSpec("linear_head", {"vocab_size": c["vocab"], "hidden_size": d, "tied_to": "emb.weight"}, "head."), stored_dtype="float32")
+
+    rl.register_architecture(rl.Architecture("ToyRoutedForTests", dict, describe), replace=True)
+    return {"architectures": ["ToyRoutedForTests"], "width": 48, "vocab": 61, "positions": 150, "eps": 1e-6}
+
+
+def toy_routed_plain_logits(cfg, w, tokens):
+    """The second toy model by its formulas, whole sequence, float64; also returns the experts chosen."""
+    T = len(tokens)
+    x = w["emb.weight"].double()[torch.tensor(tokens)]
+    pos = torch.arange(T)
+    chosen = []
+    for layer in (0, 1):
+        p = f"l{layer}."
+        xn = plain_rmsnorm(x, w[p + "n1.weight"].double(), cfg["eps"])
+        q = (xn @ w[p + "att.q_proj.weight"].double().T).view(T, 3, 24)
+        k = (xn @ w[p + "att.k_proj.weight"].double().T).view(T, 1, 24)
+        v = (xn @ w[p + "att.v_proj.weight"].double().T).view(T, 1, 24)
+        if layer == 0:
+            j = torch.arange(24, dtype=torch.float64)
+            add = 0.5 * torch.sin(pos.double()[:, None] / (30.0 ** (j / 24))[None, :] + j[None, :])
+            q, k = q + add[:, None, :], k + add[:, None, :]
+        else:
+            inv = torch.tensor([80.0 ** (-2 * i / 24) for i in range(12)])
+            q, k = plain_rope(q, pos, inv, False), plain_rope(k, pos, inv, False)
+        x = x + plain_attention(q, k, v, 0).reshape(T, 72) @ w[p + "att.o_proj.weight"].double().T
+        xn = plain_rmsnorm(x, w[p + "n2.weight"].double(), cfg["eps"])
+        prob = torch.softmax(xn @ w[p + "moe.router.weight"].double().T, dim=-1)
+        top = prob.argmax(dim=-1)
+        chosen.append(top)
+        ff = torch.zeros_like(x)
+        for t in range(T):
+            e = int(top[t])
+            h = torch.relu(xn[t] @ w[f"{p}moe.experts.{e}.w1.weight"].double().T)
+            ff[t] = prob[t, e] * (h @ w[f"{p}moe.experts.{e}.w2.weight"].double().T)
+        x = x + ff
+    return plain_rmsnorm(x, w["final.weight"].double(), cfg["eps"]) @ w["emb.weight"].double().T, chosen
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_toy_architecture_with_routed_experts_and_added_positions(tmp_path, graphs):
+    """A feed-forward with routing and a position encoding of another kind, registered from here,
+    built from a configuration, loaded from a model folder and stepped (prompts of unequal lengths,
+    then token by token, twice in reused slots) without a change to the library's files."""
+    import rusty_llama_b200 as rl
+    from conftest import read_weights
+
+    cfg = register_toy_routed()
+    model_dir = rl.write_random_model(str(tmp_path / "toy_routed"), cfg, seed=11, std=0.25, norm_jitter=0.1)
+    w = read_weights(model_dir)
+    assert "l0.moe.experts.2.w1.weight" in w and "l1.moe.router.weight" in w and "head.weight" not in w
+    llm = rl.load(model_dir, dtype="float32", max_tokens=64 * 5, max_seqs=2, use_graphs=graphs)
+    rng = np.random.default_rng(8)
+    a, b = rng.integers(0, 61, 90).tolist(), rng.integers(0, 61, 21).tolist()
+    (ref_a, chosen_a), (ref_b, _) = toy_routed_plain_logits(cfg, w, a), toy_routed_plain_logits(cfg, w, b)
+    # the routing is exercised: every expert of both layers is chosen by some token
+    assert set(chosen_a[0].tolist()) == {0, 1, 2} and set(chosen_a[1].tolist()) == {0, 1}
+
+    def near(got, ref):
+        err = float((got.double().cpu() - ref).abs().max())
+        assert err <= 5e-5 * float(ref.abs().max()) + 1e-6, err
+
+    for round_ in range(2):
+        sa, sb = llm.open_sequence(), llm.open_sequence()
+        out = llm.step([rl.StepEntry(sa, a[:50], list(range(50))), rl.StepEntry(sb, b[:4], list(range(4)))])
+        near(out[:50], ref_a[:50])
+        near(out[50:], ref_b[:4])
+        pa, pb = 50, 4
+        while pa < 90:
+            entries = [rl.StepEntry(sa, [a[pa]], [0])]
+            if pb < 21:
+                entries.append(rl.StepEntry(sb, [b[pb]], [0]))
+            out = llm.step(entries)
+            near(out[0], ref_a[pa])
+            if pb < 21:
+                near(out[1], ref_b[pb])
+                pb += 1
+                if pb == 21:
+                    llm.close_sequence(sb)
+            pa += 1
+        llm.close_sequence(sa)
+        llm.engine.cache.check_consistent()
+    outs = llm.generate([a[:10], b[:3]], max_new_tokens=5, temperature=0.0, stop_token_ids=[])
+    assert [len(o) for o in outs] == [5, 5]
