@@ -217,3 +217,24 @@ def test_sequence_seeds():
     assert sequence_seed(12345, 0) == 12345 and sequence_seed(0, 0) == 1
     seeds = {sequence_seed(12345, i) for i in range(100)}
     assert len(seeds) == 100 and 0 not in seeds
+
+
+def test_command_line_options_follow_the_reference(tmp_path):
+    """-t -p -s -n -i with the reference's names, meanings and defaults (src/main.rs:24-66)."""
+    from rusty_llama_b200.cli import main, parse_args, parse_prompts
+
+    a = parse_args(["some/dir"])
+    assert (a["temperature"], a["top_p"], a["seed"], a["steps"], a["prompt"], a["dtype"]) == (1.0, 0.9, None, 256, "", "bfloat16")
+    a = parse_args(["m", "-t", "0", "-p", "0.5", "-s", "42", "-n", "17", "-i", "1, 2 3", "--dtype", "float32"])
+    assert (a["temperature"], a["top_p"], a["seed"], a["steps"], a["prompt"], a["dtype"]) == (0.0, 0.5, 42, 17, "1, 2 3", "float32")
+    assert parse_prompts("1, 2 3") == [[1, 2, 3]]
+    f = tmp_path / "prompts.txt"
+    f.write_text("5 6\n\n7,8,9\n")
+    assert parse_prompts("@" + str(f)) == [[5, 6], [7, 8, 9]]
+    with pytest.raises(SystemExit, match="unknown option"):
+        parse_args(["m", "-z", "tok.bin"])
+    with pytest.raises(SystemExit, match="missing value"):
+        parse_args(["m", "-t"])
+    with pytest.raises(SystemExit, match="bad value"):
+        parse_args(["m", "-n", "many"])
+    assert main(["m", "-n", "4"]) == 1  # an empty prompt is an error before anything is loaded (src/main.rs:294-296)

@@ -245,3 +245,29 @@ def test_launching_ahead_changes_no_token(dtype, temperature, llms):
         assert llm.engine.cache.n_open == 0 and llm.engine.cache.pages_free() == free
         llm.engine.cache.check_consistent()
     assert any(r.finish_reason == "stop_token" for r in b)
+
+
+def test_command_line_generates_what_the_entry_point_generates(tmp_path, capsys, tiny_weights):
+    """bin/rusty_llama's main on a model folder: `-n` counts positions, prompt included; ids on standard
+    output, one line per prompt; the rate on standard error."""
+    import rusty_llama_b200 as rl
+    from rusty_llama_b200.cli import main
+
+    cfg = TINY["A"][0]
+    model_dir = rl.write_random_model(str(tmp_path / "m"), cfg, seed=3)
+    prompts = tmp_path / "p.txt"
+    prompts.write_text("5 17 3 9\n7, 7\n")
+    assert main([model_dir, "-t", "0", "-n", "12", "-i", "@" + str(prompts), "--dtype", "float32", "--max-tokens", "256"]) == 0
+    out, err = capsys.readouterr()
+    lines = [[int(t) for t in ln.split()] for ln in out.splitlines()]
+    assert len(lines) == 2 and len(lines[0]) <= 8 and len(lines[1]) <= 10  # 12 positions each, 4 and 2 of them the prompt
+    assert "tokens" in err and "tok/s" in err
+    llm = rl.load(model_dir, dtype="float32", max_tokens=256)
+    assert llm.generate([[5, 17, 3, 9], [7, 7]], steps=12, temperature=0.0) == lines
+    # without the model's stop tokens the count is exact
+    assert [len(o) for o in llm.generate([[5, 17, 3, 9], [7, 7]], steps=12, temperature=0.0, stop_token_ids=[])] == [8, 10]
+    # sampled, with a seed: the same call twice gives the same ids
+    assert main([model_dir, "-t", "0.9", "-p", "0.8", "-s", "5", "-n", "9", "-i", "1 2 3", "--max-tokens", "256"]) == 0
+    first = capsys.readouterr().out
+    assert main([model_dir, "-t", "0.9", "-p", "0.8", "-s", "5", "-n", "9", "-i", "1 2 3", "--max-tokens", "256"]) == 0
+    assert capsys.readouterr().out == first and len(first.split()) <= 6
