@@ -107,6 +107,8 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
   }
 
   pdl_trigger();
+  if (threadIdx.x == CONSUMER_WARPS * 32)  // the copying lane: have the tensor map on its way before the barriers are set up
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
   const int first_item = (int)((long long)blockIdx.x * items / gridDim.x);
   const int end_item = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
 

@@ -271,3 +271,37 @@ def test_command_line_generates_what_the_entry_point_generates(tmp_path, capsys,
     first = capsys.readouterr().out
     assert main([model_dir, "-t", "0.9", "-p", "0.8", "-s", "5", "-n", "9", "-i", "1 2 3", "--max-tokens", "256"]) == 0
     assert capsys.readouterr().out == first and len(first.split()) <= 6
+
+
+def test_one_layer_at_the_sizes_of_the_benchmark(tmp_path):
+    """The benchmark's layer sizes (width 4096, 32 / 8 heads of 128, feed-forward 14336, llama3 rope
+    scaling) with one layer and a smaller vocabulary, in bfloat16: two prompts of unequal lengths in one
+    step, then tokens one by one with and without graphs.  This is where the kernels that only these sizes
+    select are checked inside a model: the TMA-fed streaming product at k = 4096 and 14336 (in slices), the
+    tcgen05 product and prompt attention, the four-warp decode attention with its splits."""
+    import bench
+    import rusty_llama_b200 as rl
+    from conftest import read_weights
+
+    cfg = dict(bench.load_config())
+    cfg.update(num_hidden_layers=1, vocab_size=8200, max_position_embeddings=1024)
+    model_dir = rl.write_random_model(str(tmp_path / "big"), cfg, seed=21, std=0.03, norm_jitter=0.1)
+    w = read_weights(model_dir)
+    rng = np.random.default_rng(4)
+    a, b = rng.integers(0, 8200, 580).tolist(), rng.integers(0, 8200, 71).tolist()  # a: long enough for four key splits
+    refs = plain_all_logits(cfg, w, "bfloat16", {"a": a, "b": b})
+    for graphs in (True, False):
+        llm = rl.load(model_dir, dtype="bfloat16", max_tokens=64 * 12, max_seqs=2, use_graphs=graphs)
+        sa, sb = llm.open_sequence(), llm.open_sequence()
+        out = llm.step([rl.StepEntry(sa, a[:574], [0, 77, 573]), rl.StepEntry(sb, b[:65], [64])]).cpu().numpy()
+        check_logits(out[:3], refs["a"][[0, 77, 573]], "bfloat16", "prompt a")
+        check_logits(out[3:], refs["b"][[64]], "bfloat16", "prompt b")
+        for i in range(6):
+            out = llm.step([rl.StepEntry(sa, [a[574 + i]], [0]), rl.StepEntry(sb, [b[65 + i]], [0])]).cpu().numpy()
+            check_logits(out[:1], refs["a"][[574 + i]], "bfloat16", f"decode a {i} (graphs={graphs})")
+            check_logits(out[1:], refs["b"][[65 + i]], "bfloat16", f"decode b {i} (graphs={graphs})")
+        llm.close_sequence(sa)
+        llm.close_sequence(sb)
+        llm.engine.check_device_status()
+        del llm
+        torch.cuda.empty_cache()
