@@ -110,8 +110,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   for (int i = threadIdx.x; i < HEADS * Q_STRIDE / 2; i += NUM_THREADS) reinterpret_cast<uint32_t*>(q_s)[i] = 0u;
   __syncthreads();
   pdl_trigger();
-  pdl_wait();  // the newest key and value and the queries are the previous kernel's output
 
+  // Lengths and page tables were uploaded before the step's first kernel; the kernel before this one
+  // writes the queries and the newest position's key and value, nothing else that is read here.
   const int kv_len = seq_len[s];
   const int pos = kv_len - 1;
   const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
@@ -125,10 +126,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (warp == PRODUCT_WARPS) {
     // ---------------- copies
     if (lane == 0 && !*(volatile int*)&bars.abort_flag) {
-      const uint32_t ring_addr = smem_u32(ring);
       int issued = 0;
+      bool waited = false;
       for (int tile = my_lo; tile <= my_hi; ++tile, ++issued) {
         const int st = issued % STAGES, round = issued / STAGES;
+        // pages before the sequence's last one are older than this step: their copies start while the
+        // kernel before this one is still running
+        if (!waited && (tile == tile_hi || round > 0)) {
+          pdl_wait();
+          waited = true;
+        }
         if (round > 0 && !mbar_wait(&bars.empty[st], (round - 1) & 1)) {
           atomicExch(status, 51);
           bars.abort_flag = 1;
@@ -137,7 +144,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (*(volatile int*)&bars.abort_flag) break;
         const int page = table[tile];
         unsigned char* dst = ring + (size_t)st * STAGE_BYTES;
-        (void)ring_addr;
         mbar_expect_tx(&bars.full[st], STAGE_BYTES);
         tma_load_4d(dst, &map_k, &bars.full[st], 0, 0, kh, page);
         tma_load_4d(dst + HALF_BYTES, &map_k, &bars.full[st], 64, 0, kh, page);
@@ -152,6 +158,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     return;  // the product warps meet at a barrier of their own
   }
 
+  pdl_wait();  // the queries are the previous kernel's output, and it may still read this one's scratch
   // ---------------- products
   const int g = lane >> 2, t4 = lane & 3;
   {
