@@ -264,7 +264,7 @@ def run_ours(args) -> dict:
             "unit": "tokens/s",
             "h2d_bytes_per_step": meta_ints,
             "d2h_bytes_per_step": 4 * batch,
-            "what": "LLM.generate decode phase, greedy, host lists in and out, host clock",
+            "what": "LLM.generate decode phase, greedy, host lists in and out, host clock; starts right after the prompt step, whose power-capped SM clock takes about 130 ms to recover",
             "host_ms_per_step_in_step_call": round(1000.0 * st.decode_step_call_seconds / max(st.decode_steps, 1), 4),
             "host_ms_per_step_in_sample_call": round(1000.0 * st.decode_sample_call_seconds / max(st.decode_steps, 1), 4),
         },

@@ -223,7 +223,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     };
     pdl_wait();  // the activations are the previous kernel's output, and it may still read ours
     for (int item = first_item; item < end_item && ok; ++item, ++done_items) {
-      const int slice = item / units, unit = item - slice * units;
+      const int slice = item / units;
       const int kbeg = slice * slice_len, klen = min(slice_len, K - kbeg);
       if (slice != loaded_slice) {
         // this lane's pieces of the activations of the slice, zero where there is no row or no k
