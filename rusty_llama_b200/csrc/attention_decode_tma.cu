@@ -15,6 +15,12 @@
 // At the end the four warps' partial results are merged in shared memory (in warp order) and the
 // block writes one partial (max as a base-2 exponent, sum, unnormalised output) per head to
 // scratch; the merge kernel adds the splits in split order.
+// Fused position encoding and cache write (fuse > 0): the step's rotary kernel is left out and this
+// kernel does its work where the data passes anyway.  The queries are turned by their position's
+// angles as they are put into shared memory; the block whose split holds the sequence's last page
+// takes the new token's raw key and value from the projection's output, turns the key, puts both
+// into its copy of the page in shared memory (the warp that owns that row does it, nobody else
+// reads the row) and, for the next steps, into the cache.  Same formulas as rope.cu.
 // Two blocks share an SM (99 KB of shared memory each): 192 KB of keys and values in flight per SM,
 // eight product warps.
 //
@@ -38,7 +44,9 @@ RL_DEFINE_ERROR_TEXT()
 struct DecodeBarriers {
   uint64_t full[STAGES], empty[STAGES];
   int abort_flag;
+  float cs[HD / 2], sn[HD / 2];  // cosine and sine of the new position's angles (fused rotary)
 };
+static_assert(sizeof(DecodeBarriers) <= 1024, "the small items must fit their area");
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -75,7 +83,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table, int table_width,
                        const int* __restrict__ seq_len, float* __restrict__ part_o, float* __restrict__ part_ml, int H,
-                       int K, int window, float scale_log2, int n_splits, int* __restrict__ status) {
+                       int K, int window, float scale_log2, int n_splits, int* __restrict__ status,
+                       int fuse, bf16* __restrict__ k_pages_w, bf16* __restrict__ v_pages_w,
+                       const float* __restrict__ inv_freq, int rot, int interleaved) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -158,6 +168,17 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     return;  // the product warps meet at a barrier of their own
   }
 
+  const int half_rot = rot >> 1;
+  if (fuse) {
+    // angles of the new token's position, once per block (32-bit product, accurate sincosf); they depend
+    // on the position alone, so this runs while the kernel before this one is still at work
+    for (int j = threadIdx.x; j < half_rot; j += PRODUCT_WARPS * 32) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
+      bars.cs[j] = cs;
+      bars.sn[j] = sn;
+    }
+  }
   pdl_wait();  // the queries are the previous kernel's output, and it may still read this one's scratch
   // ---------------- products
   const int g = lane >> 2, t4 = lane & 3;
@@ -167,6 +188,17 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (r < n_heads)
       *reinterpret_cast<uint4*>(q_s + (size_t)r * Q_STRIDE + piece * 8) =
           __ldcg(reinterpret_cast<const uint4*>(q + (size_t)s * q_stride + (size_t)(h0 + r) * HD + piece * 8));
+  }
+  if (fuse) {
+    product_warps_sync();  // the queries and the angles are in shared memory
+    for (int idx = threadIdx.x; idx < n_heads * half_rot; idx += PRODUCT_WARPS * 32) {
+      const int r = idx / half_rot, j = idx - r * half_rot;
+      const int d0 = interleaved ? 2 * j : j, d1 = interleaved ? 2 * j + 1 : j + half_rot;
+      bf16* row = q_s + (size_t)r * Q_STRIDE;
+      const float a = __bfloat162float(row[d0]), b = __bfloat162float(row[d1]);
+      row[d0] = __float2bfloat16_rn(a * bars.cs[j] - b * bars.sn[j]);
+      row[d1] = __float2bfloat16_rn(a * bars.sn[j] + b * bars.cs[j]);
+    }
   }
   product_warps_sync();
   uint32_t qf[HD / 16][2];  // Q^T as B fragments: (dims kk*16 + 2*t4 [+8], head g)
@@ -206,6 +238,30 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       break;
     }
     const uint32_t k_s = smem_u32(ring) + st * STAGE_BYTES, v_s = k_s + 2 * HALF_BYTES;
+    if (fuse == 2 && tile == tile_hi && warp == ((pos & (PAGE - 1)) >> 4)) {
+      // the new token's key and value: from the projection's output into this block's copy of the page
+      // and (one block per kv head) into the cache
+      const int row = pos & (PAGE - 1);
+      const bf16* k_raw = q + (size_t)s * q_stride + (size_t)(H + kh) * HD;
+      const bf16* v_raw = k_raw + (size_t)K * HD;
+      unsigned char* k_tile = ring + (size_t)st * STAGE_BYTES;
+      unsigned char* v_tile = k_tile + 2 * HALF_BYTES;
+      const size_t cache_row = (((size_t)table[tile] * K + kh) * PAGE + row) * HD;
+      const bool to_cache = g0 == 0;
+      auto put = [&](unsigned char* tile_base, bf16* pages, int d, bf16 v) {
+        *reinterpret_cast<bf16*>(tile_base + (d >> 6) * HALF_BYTES + swz(row, (d & 63) >> 3) + (d & 7) * 2) = v;
+        if (to_cache) pages[cache_row + d] = v;
+      };
+      for (int j = lane; j < half_rot; j += 32) {
+        const int d0 = interleaved ? 2 * j : j, d1 = interleaved ? 2 * j + 1 : j + half_rot;
+        const float a = __bfloat162float(k_raw[d0]), b = __bfloat162float(k_raw[d1]);
+        put(k_tile, k_pages_w, d0, __float2bfloat16_rn(a * bars.cs[j] - b * bars.sn[j]));
+        put(k_tile, k_pages_w, d1, __float2bfloat16_rn(a * bars.sn[j] + b * bars.cs[j]));
+      }
+      for (int d = rot + lane; d < HD; d += 32) put(k_tile, k_pages_w, d, k_raw[d]);
+      for (int d = lane; d < HD; d += 32) put(v_tile, v_pages_w, d, v_raw[d]);
+      __syncwarp();
+    }
 
     // ---- S^T = K Q^T: this warp's 16 keys x 8 heads
     float s_acc[4] = {0.f, 0.f, 0.f, 0.f};  // (key g [+8], head 2*t4 [+1])
@@ -394,10 +450,16 @@ RL_API int rl_attn_decode_tma_head_dim() { return HD; }
 // n_seqs*H*n_splits*2), plus the number of cache pages and a status word: one int in device memory,
 // 0 before the call; non-zero afterwards means that a bounded wait expired (51 the copying lane, 52 a
 // product warp; 56: shared memory not aligned) and the output is not valid.
+// fuse: 0 = the queries are already position-encoded and the new key and value already in the cache;
+// 1 = turn the queries here (the cache is another layer's and complete); 2 = turn the queries, and take
+// the new token's key and value from q's rows (keys at column H * hd, values at (H + K) * hd), turn the
+// key and store both (k_pages and v_pages are written).  inv_freq: rot / 2 angles per position; rot = 0
+// means no rotation at all (then fuse = 2 only stores).
 RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
                               const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
                               void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
-                              float scale, int n_splits, int* status, cudaStream_t stream) {
+                              float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
+                              int interleaved, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
   if (hd != HD) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for %d", hd, HD);
   if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
@@ -406,6 +468,9 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
   if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
+  if (fuse < 0 || fuse > 2 || rot < 0 || rot > HD || (rot & 1) || (fuse && rot > 0 && inv_freq == nullptr))
+    RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d%s", fuse, rot, inv_freq ? "" : " and no angles");
+  if (fuse == 2 && q_stride < (H + 2 * K) * HD) RL_REFUSE(13, "attn_decode_tma: rows of %d hold no key and value behind %d query heads", q_stride, H);
   EncodeTiledFn enc = encode_tiled();
   if (!enc) RL_REFUSE(9, "attn_decode_tma: cuTensorMapEncodeTiled is not available");
   CUtensorMap map_k, map_v;
@@ -425,7 +490,9 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   const int G = H / K;
   dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, SMEM_BYTES, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
-                            table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status));
+                            table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
+                            fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
+                            interleaved));
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_tma_merge_kernel, grid2, HD, 0, stream, (const float*)part_o, (const float*)part_ml,
                             (bf16*)out, out_stride, H, n_splits));

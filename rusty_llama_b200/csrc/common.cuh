@@ -40,8 +40,38 @@ static thread_local char rl_error_buf[512] = {0};
     return 0;                                                                      \
   } while (0)
 
-#define RL_DEFINE_ERROR_TEXT() \
-  RL_API const char* rl_error_text() { return rl_error_buf; }
+// Profiling aid, compiled in only with -DRL_TRACE (RUSTY_LLAMA_NVCC_EXTRA="-DRL_TRACE"): the first
+// thread of a kernel's first block notes the time at which its dependency wait returned, i.e. when the
+// kernel before it had finished, in a buffer that the host hands to every library with rl_trace_set.
+// The differences between successive notes are the kernels' durations inside a replayed graph, where
+// no profiler can look without serialising them.
+#ifdef RL_TRACE
+static __device__ unsigned long long* rl_trace_buf = nullptr;
+static __device__ unsigned int* rl_trace_count = nullptr;
+static __device__ unsigned int rl_trace_cap = 0;
+#define RL_DEFINE_TRACE()                                                                             \
+  RL_API int rl_trace_set(void* buf, void* count, unsigned int cap) {                                 \
+    cudaError_t e = cudaMemcpyToSymbol(rl_trace_buf, &buf, sizeof(void*));                            \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(rl_trace_count, &count, sizeof(void*));              \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(rl_trace_cap, &cap, sizeof(unsigned int));           \
+    return (int)e;                                                                                    \
+  }
+__device__ __forceinline__ void rl_trace_mark() {
+  if (threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && rl_trace_buf != nullptr) {
+    const unsigned int i = atomicAdd(rl_trace_count, 1u);
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (i < rl_trace_cap) rl_trace_buf[i] = t;
+  }
+}
+#else
+#define RL_DEFINE_TRACE()
+__device__ __forceinline__ void rl_trace_mark() {}
+#endif
+
+#define RL_DEFINE_ERROR_TEXT()                                 \
+  RL_API const char* rl_error_text() { return rl_error_buf; } \
+  RL_DEFINE_TRACE()
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
@@ -167,7 +197,10 @@ __device__ __forceinline__ void store4<bf16>(bf16* p, const float* f) {
 // persistent streaming product then requests its first ring of weights (200 KB per SM) while the
 // norm, rotary or attention kernel before it is still at work.  Measured on the decode step of an
 // 8B model at batch 8: 4.43 ms without, 4.01 ms with.  RL_PDL=0 in the environment turns it off.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  rl_trace_mark();
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Called first thing by the kernels of a decode step: once every block of a kernel has started, its
 // successor (if launched with the programmatic attribute) may become resident and do what does not

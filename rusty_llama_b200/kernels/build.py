@@ -33,6 +33,9 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "--shared", "-Xcompiler", "-fPIC",
 ]
+# more flags for experiments (for instance -DRL_TRACE, see csrc/common.cuh); they are part of a
+# library's fingerprint, so give such builds a folder of their own with RUSTY_LLAMA_BUILD_DIR
+NVCC_FLAGS += os.environ.get("RUSTY_LLAMA_NVCC_EXTRA", "").split()
 
 _lock = threading.Lock()
 _dir_lock = threading.Lock()

@@ -280,9 +280,15 @@ def attn_decode_scratch_floats(n_seqs: int, num_heads: int, head_dim: int, n_spl
 def attn_decode(
     q: torch.Tensor, k_pages, v_pages, block_table, seq_len, num_heads: int, num_kv_heads: int, head_dim: int,
     n_splits: int, scratch: torch.Tensor, window: int = 0, scale: Optional[float] = None,
-    out: Optional[torch.Tensor] = None, impl: str = "auto",
+    out: Optional[torch.Tensor] = None, impl: str = "auto", fuse: int = 0,
+    inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False,
 ) -> torch.Tensor:
     """One query token per sequence over keys 0..seq_len-1, the key range cut into `n_splits`.
+
+    fuse (the "tma" kernel only): 0 = q is position-encoded and the new key and value are in the cache
+    (what `rope_kv_write` leaves); 1 = q's rows are raw projections, the kernel turns the queries by
+    `inv_freq` / `rotary_dim` / `interleaved`; 2 = as 1, and the kernel also takes the new token's key and
+    value from q's rows, turns the key and stores both into the cache (k_pages and v_pages are written).
 
     scratch: float32 tensor of at least attn_decode_scratch_floats(...) elements.
     impl: "warp" = one-warp blocks that copy their own tiles, "tma" = four-warp blocks on a TMA-fed
@@ -310,6 +316,14 @@ def attn_decode(
     _need(impl in ("auto", "warp", "tma"), f"attn_decode: unknown impl {impl!r}")
     if impl == "auto":
         impl = "tma" if (head_dim == ATTN_DECODE_TMA_HEAD_DIM and q.dtype == torch.bfloat16) else "warp"
+    _need(fuse in (0, 1, 2), f"attn_decode: fuse={fuse}")
+    if fuse:
+        _need(impl == "tma", "attn_decode: only the TMA kernel fuses the position encoding")
+        if rotary_dim:
+            _cuda(inv_freq, "attn_decode inv_freq", torch.float32)
+            _need(inv_freq.numel() >= rotary_dim // 2, "attn_decode: too few angles for the rotary size")
+        if fuse == 2:
+            _need(q.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim, "attn_decode: q rows hold no key and value")
     if impl == "tma":
         _need(q.dtype == torch.bfloat16, "attn_decode: the TMA kernel is bfloat16 only")
         status = _tc_status_word(q.device)
@@ -318,7 +332,8 @@ def attn_decode(
             _p(q), c_int(qs), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
             c_int(block_table.shape[1]), _p(seq_len), part_o, part_ml, _p(out), c_int(out.stride(0)), c_int(S),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
-            c_int(n_splits), _p(status), _stream(),
+            c_int(n_splits), _p(status), c_int(fuse), _p(inv_freq) if (fuse and rotary_dim) else c_void_p(0), c_int(rotary_dim if fuse else 0),
+            c_int(1 if interleaved else 0), _stream(),
         )
         _check(lib, rc, "attn_decode_tma", kernels=2)
         return out

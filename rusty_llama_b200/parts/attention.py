@@ -97,7 +97,13 @@ class Attention(Mixer):
             qkv = linear(xn, self.w_qkv[: self.qd])
         else:
             qkv = linear(xn, self.w_qkv)
-        self.position.write_qk(qkv, step, cache, self.H, self.K, self.hd, write_kv=not shared_cache)
+        # a decode step of a bfloat16 run at head size 128: the attention kernel turns the queries and the
+        # new key and stores key and value itself, if the position encoding is one it knows how to apply
+        fusion = None
+        if step.decode_only and self.rt.dtype == torch.bfloat16 and self.hd == ops.ATTN_DECODE_TMA_HEAD_DIM:
+            fusion = self.position.decode_fusion()
+        if fusion is None:
+            self.position.write_qk(qkv, step, cache, self.H, self.K, self.hd, write_kv=not shared_cache)
         if self.rt.dtype == torch.float32:
             a = ops.attn_generic(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos,
@@ -111,6 +117,8 @@ class Attention(Mixer):
             a = ops.attn_decode(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_len, self.H, self.K, self.hd,
                 n_splits, scratch, window=self.window, scale=self.scale,
+                **({} if fusion is None else dict(
+                    fuse=1 if shared_cache else 2, inv_freq=fusion[0], rotary_dim=fusion[1], interleaved=fusion[2])),
             )
         elif self.hd == ops.FLASH_TC_HEAD_DIM:
             a = ops.flash_prefill_tc(

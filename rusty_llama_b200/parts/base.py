@@ -176,6 +176,12 @@ class PositionEncoding(Part):
         """Encode positions into q[T, H, hd] and k[T, K, hd] in place."""
         raise NotImplementedError
 
+    def decode_fusion(self):
+        """None, or (inv_freq, rotary_dim, interleaved) if this encoding is a rotation by angles
+        position * inv_freq[j] of `rotary_dim` leading dimensions (0 = none at all): a mixer may then
+        leave `write_qk` out of a decode step and have its attention kernel do the same work."""
+        return None
+
     def write_qk(self, qkv: torch.Tensor, step, kv, num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool) -> None:
         from ..kernels import ops
 

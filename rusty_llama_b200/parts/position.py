@@ -37,6 +37,9 @@ class Rotary(PositionEncoding):
     def rotate(self, q, k, step):
         raise NotImplementedError("Rotary encodes positions inside write_qk")
 
+    def decode_fusion(self):
+        return self.inv_freq, self.rotary_dim, self.interleaved
+
 
 @POSITIONS.register("none")
 class NoPosition(PositionEncoding):
@@ -44,3 +47,6 @@ class NoPosition(PositionEncoding):
 
     def rotate(self, q, k, step):
         return None
+
+    def decode_fusion(self):
+        return None, 0, False

@@ -313,6 +313,55 @@ def test_attn_decode_tma(ops, H, K, n_splits, window):
     assert torch.isnan(scratch[-7:]).all()  # the kernel stays inside the scratch it asked for
 
 
+@pytest.mark.parametrize("H, K", [(8, 2), (32, 8), (24, 1)])
+@pytest.mark.parametrize("rot, interleaved", [(128, False), (128, True), (64, False), (0, False)])
+@pytest.mark.parametrize("n_splits, window", [(1, 0), (4, 0), (3, 150)])
+def test_attn_decode_tma_with_rotary_and_cache_write_fused(ops, H, K, rot, interleaved, n_splits, window):
+    """fuse = 2 against the two kernels it stands for (rope_kv_write, then attention): the same keys
+    and values end up in the cache, bit for bit, at a page's first and last slot and in every warp's
+    quarter of a page, and the same attention comes out; fuse = 1 turns the queries only."""
+    hd = 128
+    lens = [1, 64, 65, 300, 128, 1000, 17, 81, 112]
+    S = len(lens)
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=9)
+    g = torch.Generator().manual_seed(rot + H)
+    raw = bf16_round(torch.randn(S, (H + 2 * K) * hd, generator=g)).to(torch.bfloat16).to(DEV)
+    inv_freq = (10000.0 ** (-torch.arange(0, max(rot, 2), 2, dtype=torch.float32) / max(rot, 2))).to(DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tok_pos = (seq_len - 1).contiguous()
+    tok_seq = torch.arange(S, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(ops.attn_decode_scratch_floats(S, H, hd, n_splits), device=DEV)
+    # the two-kernel way, on copies
+    qkv_a, k_a, v_a = raw.clone(), kv.k_pages.clone(), kv.v_pages.clone()
+    ops.rope_kv_write(qkv_a, tok_pos, tok_seq, kv.table, k_a, v_a, inv_freq if rot else None, H, K, hd, rot, interleaved, write_kv=True)
+    out_a = ops.attn_decode(qkv_a, k_a, v_a, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window, impl="tma").clone()
+    # the fused way: the new position's slot holds junk before the call
+    qkv_b, k_b, v_b = raw.clone(), kv.k_pages.clone(), kv.v_pages.clone()
+    out_b = ops.attn_decode(qkv_b, k_b, v_b, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window, impl="tma",
+                            fuse=2, inv_freq=inv_freq, rotary_dim=rot, interleaved=interleaved)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert torch.equal(k_b, k_a) and torch.equal(v_b, v_a)  # the cache holds what the rotary kernel would have stored
+    assert torch.equal(qkv_b, raw)  # the projection's output is only read
+    assert torch.equal(out_b, out_a)
+    # and the two-kernel way is right: against the plain formula for one sequence
+    s = 3
+    q_rot = qkv_a[s : s + 1, : H * hd].float().cpu().view(1, H, hd)
+    k_all = torch.stack([k_a[int(kv.table[s, p // PAGE]), :, p % PAGE].float().cpu() for p in range(lens[s])])  # [len, K, hd]
+    ref = torch.zeros(H, hd, dtype=torch.float64)
+    lo = max(0, lens[s] - window) if window else 0
+    for h in range(H):
+        kh = h // (H // K)
+        sc = (k_all[lo:, kh].double() @ q_rot[0, h].double()) / math.sqrt(hd)
+        vv = torch.stack([v_a[int(kv.table[s, p // PAGE]), kh, p % PAGE].float().cpu() for p in range(lo, lens[s])]).double()
+        ref[h] = torch.softmax(sc, dim=0) @ vv
+    close_bf16(out_b[s].view(H, hd), ref)
+    # queries only (the cache is complete, as when a layer reads another layer's cache)
+    out_c = ops.attn_decode(raw.clone(), k_a, v_a, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window, impl="tma",
+                            fuse=1, inv_freq=inv_freq, rotary_dim=rot, interleaved=interleaved)
+    assert torch.equal(out_c, out_a)
+
+
 def test_attn_decode_tma_finds_a_far_key(ops):
     """One key far back among hundreds carries almost all the weight: a kernel that skips a page, a
     split, a warp's 16 keys or a swizzled piece returns something else entirely."""
