@@ -20,7 +20,7 @@ The reference keeps the same seams as `Backend` trait methods
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Mapping, Optional, Tuple
+from typing import List, Callable, Dict, Mapping, Optional, Tuple
 
 import torch
 
@@ -34,18 +34,26 @@ class Workspace:
 
     Kernels that need global memory beyond their inputs and outputs (the split
     partials of decode attention, the probabilities of the sampler) take it
-    from here, so that a replayed CUDA graph always sees the same addresses."""
+    from here, so that a replayed CUDA graph always sees the same addresses.  A tensor that
+    has to grow is replaced, but the old one is kept for good: graphs captured while it was
+    current still write to its address when they are replayed."""
 
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        self._retired: List[torch.Tensor] = []
 
-    def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, numel: int, dtype: torch.dtype, zeroed: bool = False) -> torch.Tensor:
+        """zeroed: the tensor starts as zeros and its users leave it as zeros (counters that the
+        kernels reset themselves); such a name must always be asked for with zeroed=True."""
         buf = self._bufs.get(name)
         if buf is None or buf.numel() < numel or buf.dtype != dtype:
-            if torch.cuda.is_current_stream_capturing():
+            if self.device.type == "cuda" and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(f"workspace '{name}' would have to grow during graph capture")
-            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            if buf is not None:
+                self._retired.append(buf)
+            make = torch.zeros if zeroed else torch.empty
+            buf = make(max(numel, 1), dtype=dtype, device=self.device)
             self._bufs[name] = buf
         return buf
 

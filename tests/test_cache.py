@@ -154,3 +154,20 @@ def test_block_table_lists_pages_in_position_order():
     assert t.dtype == np.int32 and t.shape == (2, 4)
     assert list(t[1, :2]) == c.kv_groups[0].pages[a] and t[0, 0] == c.kv_groups[0].pages[b][0]
     assert len(set(c.kv_groups[0].pages[a]) | set(c.kv_groups[0].pages[b])) == 3
+
+
+def test_workspace_keeps_what_replayed_graphs_may_still_write_to():
+    """A scratch tensor that has to grow is replaced, never freed: a graph captured earlier still uses
+    the old address.  Zeroed tensors start as zeros."""
+    from rusty_llama_b200.parts import Workspace
+
+    ws = Workspace(torch.device("cpu"))
+    a = ws.get("scratch", 10, torch.float32)
+    assert ws.get("scratch", 8, torch.float32) is a  # large enough: the same tensor
+    ptr = a.data_ptr()
+    del a
+    b = ws.get("scratch", 1000, torch.float32)
+    assert b.numel() >= 1000 and b.data_ptr() != ptr
+    assert any(t.data_ptr() == ptr for t in ws._retired)  # still owned, so nothing else can be given its memory
+    c = ws.get("counters", 16, torch.int32, zeroed=True)
+    assert c.dtype == torch.int32 and int(c.abs().sum()) == 0
