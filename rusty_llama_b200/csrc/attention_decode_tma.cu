@@ -44,6 +44,7 @@ RL_DEFINE_ERROR_TEXT()
 struct DecodeBarriers {
   uint64_t full[STAGES], empty[STAGES];
   int abort_flag;
+  int last;  // this block is the last of its group's splits to finish
   float cs[HD / 2], sn[HD / 2];  // cosine and sine of the new position's angles (fused rotary)
 };
 static_assert(sizeof(DecodeBarriers) <= 1024, "the small items must fit their area");
@@ -85,7 +86,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const int* __restrict__ seq_len, float* __restrict__ part_o, float* __restrict__ part_ml, int H,
                        int K, int window, float scale_log2, int n_splits, int* __restrict__ status,
                        int fuse, bf16* __restrict__ k_pages_w, bf16* __restrict__ v_pages_w,
-                       const float* __restrict__ inv_freq, int rot, int interleaved) {
+                       const float* __restrict__ inv_freq, int rot, int interleaved,
+                       unsigned int* __restrict__ counters, bf16* __restrict__ out, int out_stride) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -364,22 +366,77 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         mw[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - M);
         l += mw[w] * merge_ml[(w * HEADS + head) * 2 + 1];
       }
-      const size_t slot = ((size_t)s * H + h0 + head) * n_splits + split;
-      if (d0 == 0) {
-        part_ml[slot * 2] = M;  // -inf when the split held no key at all (an empty split)
-        part_ml[slot * 2 + 1] = l;
-      }
-      float* po = part_o + slot * HD;
+      if (counters != nullptr && n_splits == 1) {
+        // the only split: this is the result
+        const float inv = 1.0f / l;
+        bf16* orow = out + (size_t)s * out_stride + (size_t)(h0 + head) * HD;
 #pragma unroll
-      for (int j = 0; j < HD / 16; ++j) {
-        const int d = d0 + 16 * j;
-        float o = 0.f;
+        for (int j = 0; j < HD / 16; ++j) {
+          const int d = d0 + 16 * j;
+          float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < PRODUCT_WARPS; ++w) o += mw[w] * merge_o[(size_t)(w * HEADS + head) * O_STRIDE + d];
-        po[d] = o;
+          for (int w = 0; w < PRODUCT_WARPS; ++w) o += mw[w] * merge_o[(size_t)(w * HEADS + head) * O_STRIDE + d];
+          orow[d] = __float2bfloat16_rn(o * inv);
+        }
+      } else {
+        const size_t slot = ((size_t)s * H + h0 + head) * n_splits + split;
+        if (d0 == 0) {
+          part_ml[slot * 2] = M;  // -inf when the split held no key at all (an empty split)
+          part_ml[slot * 2 + 1] = l;
+        }
+        float* po = part_o + slot * HD;
+#pragma unroll
+        for (int j = 0; j < HD / 16; ++j) {
+          const int d = d0 + 16 * j;
+          float o = 0.f;
+#pragma unroll
+          for (int w = 0; w < PRODUCT_WARPS; ++w) o += mw[w] * merge_o[(size_t)(w * HEADS + head) * O_STRIDE + d];
+          po[d] = o;
+        }
       }
     }
   }
+  if (counters == nullptr || n_splits == 1) return;
+
+  // ---- the block that finishes last among the splits of its (sequence, head group) adds them up, in
+  // split order, exactly as the merge kernel would: out = sum_i 2^(m_i - M) o_i / sum_i 2^(m_i - M) l_i.
+  // Its partial results are made visible before the ticket is drawn, and the last one reads the others'
+  // only after it has seen every ticket drawn.
+  __threadfence();
+  product_warps_sync();
+  unsigned int* counter = counters + (size_t)s * gridDim.y + blockIdx.y;
+  if (threadIdx.x == 0) bars.last = (atomicAdd(counter, 1u) == (unsigned int)n_splits - 1u) ? 1 : 0;
+  product_warps_sync();
+  if (!bars.last) return;
+  __threadfence();
+  {
+    const int head = threadIdx.x >> 4, d0 = threadIdx.x & 15;
+    if (head < n_heads) {
+      const float* ml = part_ml + ((size_t)s * H + h0 + head) * n_splits * 2;
+      const float* po = part_o + ((size_t)s * H + h0 + head) * n_splits * HD;
+      float M = -INFINITY;
+      for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(ml + 2 * i));
+      float denom = 0.f;
+      for (int i = 0; i < n_splits; ++i) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(ml + 2 * i));
+        denom += ((v.x == -INFINITY) ? 0.f : exp2f(v.x - M)) * v.y;
+      }
+      const float inv = 1.0f / denom;
+      float o[HD / 16];
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) o[j] = 0.f;
+      for (int i = 0; i < n_splits; ++i) {
+        const float mi = __ldcg(ml + 2 * i);
+        const float wi = ((mi == -INFINITY) ? 0.f : exp2f(mi - M)) * inv;
+#pragma unroll
+        for (int j = 0; j < HD / 16; ++j) o[j] += wi * __ldcg(po + (size_t)i * HD + d0 + 16 * j);
+      }
+      bf16* orow = out + (size_t)s * out_stride + (size_t)(h0 + head) * HD;
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) orow[d0 + 16 * j] = __float2bfloat16_rn(o[j]);
+    }
+  }
+  if (threadIdx.x == 0) *counter = 0u;  // ready for the next call
 }
 
 // out[s, h, :] = sum_split 2^(m_split - M) o_split / sum_split 2^(m_split - M) l_split, in split order.
@@ -455,11 +512,14 @@ RL_API int rl_attn_decode_tma_head_dim() { return HD; }
 // the new token's key and value from q's rows (keys at column H * hd, values at (H + K) * hd), turn the
 // key and store both (k_pages and v_pages are written).  inv_freq: rot / 2 angles per position; rot = 0
 // means no rotation at all (then fuse = 2 only stores).
+// counters: null, or n_seqs * (K * groups of 8 heads) zeros in device memory: the splits are then added
+// up by the block that finishes last (no merge kernel is launched) and the counters are zeros again
+// when the kernel ends.
 RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
                               const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
                               void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
                               float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
-                              int interleaved, cudaStream_t stream) {
+                              int interleaved, unsigned int* counters, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
   if (hd != HD) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for %d", hd, HD);
   if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
@@ -492,7 +552,8 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, SMEM_BYTES, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
                             table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
                             fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
-                            interleaved));
+                            interleaved, counters, (bf16*)out, out_stride));
+  if (counters != nullptr) return 0;
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_tma_merge_kernel, grid2, HD, 0, stream, (const float*)part_o, (const float*)part_ml,
                             (bf16*)out, out_stride, H, n_splits));

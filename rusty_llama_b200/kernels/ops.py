@@ -282,8 +282,13 @@ def attn_decode(
     n_splits: int, scratch: torch.Tensor, window: int = 0, scale: Optional[float] = None,
     out: Optional[torch.Tensor] = None, impl: str = "auto", fuse: int = 0,
     inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False,
+    counters: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One query token per sequence over keys 0..seq_len-1, the key range cut into `n_splits`.
+
+    counters (the "tma" kernel only): int32 zeros, one per sequence and group of 8 query heads of a kv
+    head; with them the splits are added up by the block that finishes last instead of by a second
+    kernel, and the counters are zeros again afterwards.
 
     fuse (the "tma" kernel only): 0 = q is position-encoded and the new key and value are in the cache
     (what `rope_kv_write` leaves); 1 = q's rows are raw projections, the kernel turns the queries by
@@ -324,6 +329,11 @@ def attn_decode(
             _need(inv_freq.numel() >= rotary_dim // 2, "attn_decode: too few angles for the rotary size")
         if fuse == 2:
             _need(q.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim, "attn_decode: q rows hold no key and value")
+    if counters is not None:
+        _need(impl == "tma", "attn_decode: only the TMA kernel adds the splits up itself")
+        _cuda(counters, "attn_decode counters", torch.int32)
+        groups = num_kv_heads * ((num_heads // num_kv_heads + 7) // 8)
+        _need(counters.numel() >= S * groups, f"attn_decode: {counters.numel()} counters, {S * groups} needed")
     if impl == "tma":
         _need(q.dtype == torch.bfloat16, "attn_decode: the TMA kernel is bfloat16 only")
         status = _tc_status_word(q.device)
@@ -333,9 +343,9 @@ def attn_decode(
             c_int(block_table.shape[1]), _p(seq_len), part_o, part_ml, _p(out), c_int(out.stride(0)), c_int(S),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
             c_int(n_splits), _p(status), c_int(fuse), _p(inv_freq) if (fuse and rotary_dim) else c_void_p(0), c_int(rotary_dim if fuse else 0),
-            c_int(1 if interleaved else 0), _stream(),
+            c_int(1 if interleaved else 0), _p(counters) if counters is not None else c_void_p(0), _stream(),
         )
-        _check(lib, rc, "attn_decode_tma", kernels=2)
+        _check(lib, rc, "attn_decode_tma", kernels=1 if counters is not None else 2)
         return out
     lib = build.load("attention_decode")
     rc = lib.rl_attn_decode(

@@ -114,9 +114,16 @@ class Attention(Mixer):
             scratch = self.rt.workspace.get(
                 "attn_decode", ops.attn_decode_scratch_floats(step.n_seqs, self.H, self.hd, n_splits), torch.float32
             )
+            # With one split per sequence the attention kernel writes the result itself.  With more, a
+            # second kernel adds the splits up: letting the block that finishes last do that (the kernel
+            # can) measured slower at batch 1 and 8 (its serial tail costs more than the small kernel).
+            counters = None
+            if self.hd == ops.ATTN_DECODE_TMA_HEAD_DIM and n_splits == 1:
+                groups = self.K * ((self.H // self.K + _DECODE_HEADS_PER_BLOCK - 1) // _DECODE_HEADS_PER_BLOCK)
+                counters = self.rt.workspace.get("attn_decode_counters", step.n_seqs * groups, torch.int32, zeroed=True)
             a = ops.attn_decode(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_len, self.H, self.K, self.hd,
-                n_splits, scratch, window=self.window, scale=self.scale,
+                n_splits, scratch, window=self.window, scale=self.scale, counters=counters,
                 **({} if fusion is None else dict(
                     fuse=1 if shared_cache else 2, inv_freq=fusion[0], rotary_dim=fusion[1], interleaved=fusion[2])),
             )

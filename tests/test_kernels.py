@@ -362,6 +362,35 @@ def test_attn_decode_tma_with_rotary_and_cache_write_fused(ops, H, K, rot, inter
     assert torch.equal(out_c, out_a)
 
 
+@pytest.mark.parametrize("H, K", [(8, 2), (32, 8), (24, 1)])
+@pytest.mark.parametrize("n_splits, window", [(1, 0), (4, 0), (64, 0), (3, 150)])
+def test_attn_decode_tma_adds_its_splits_up_itself(ops, H, K, n_splits, window):
+    """With counters the block that finishes last merges the splits: the same result as with the merge
+    kernel, call after call (the counters are zeros again each time), also with splits that hold no key."""
+    hd = 128
+    lens = [1, 64, 65, 300, 128, 1000, 17]
+    S = len(lens)
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=6)
+    q = bf16_round(torch.randn(S, (H + 2 * K) * hd)).to(torch.bfloat16).to(DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(ops.attn_decode_scratch_floats(S, H, hd, n_splits), device=DEV)
+    two = ops.attn_decode(q, kv.k_pages, kv.v_pages, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window, impl="tma").clone()
+    groups = K * ((H // K + 7) // 8)
+    counters = torch.zeros(S * groups + 3, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        one = ops.attn_decode(q, kv.k_pages, kv.v_pages, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window, impl="tma",
+                              counters=counters, out=torch.full((S, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV))
+        torch.cuda.synchronize()
+        ops.tc_status_check()
+        assert int(counters.abs().sum()) == 0
+        close_bf16(one, two.double())
+        assert float((one.float() - two.float()).abs().max()) <= 2.0 ** -7 * float(two.float().abs().max())  # sums in another order at most
+    ref = torch.cat([
+        ref_attention_rows(q[s : s + 1, : H * hd].float().cpu().view(1, H, hd), kv, s, [lens[s] - 1], window) for s in range(S)
+    ]).view(S, H * hd)
+    close_bf16(one, ref)
+
+
 def test_attn_decode_tma_finds_a_far_key(ops):
     """One key far back among hundreds carries almost all the weight: a kernel that skips a page, a
     split, a warp's 16 keys or a swizzled piece returns something else entirely."""
