@@ -18,6 +18,11 @@
 // columns past M, N and K are zero-filled by TMA on the way in and masked on the way out, so any
 // M and N work; K and the row strides of x and w must be multiples of 8 (16-byte TMA rows).
 //
+// Tile width.  With few rows (a decode step of 9 to 128 sequences) the product is a stream of
+// weights, and 256-wide tiles may be too few to give every SM one (6144 features: 24 tiles).  The
+// launcher then narrows the tiles (`bn`, a multiple of 16 from 16 to 256) so that they fill one wave;
+// the stages and accumulators keep their places for 256 columns and a narrower tile uses part of them.
+//
 // Every wait on an mbarrier is bounded (about one second of polling): on expiry the waiter
 // records a code in `status[0]`, the block drains, frees its tensor memory and returns.
 #include "tc_common.cuh"
@@ -101,7 +106,7 @@ __device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32],
 template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int k_splits,
+               TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int k_splits, int bn,
                int* __restrict__ status) {
   extern __shared__ unsigned char smem_dyn[];
   // the swizzled stages must start on a 1024-byte boundary
@@ -114,7 +119,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   const int n_tiles = tiles_m * tiles_n;
   // a unit of work is one output tile and one slice of the k range (k_splits > 1: each slice
   // writes its own partial result, out[slice][M][ldo], and the consumer adds them)
@@ -150,7 +155,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       bool ok = true;
       for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
         const int tile = unit % n_tiles, ks = unit / n_tiles;
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
         const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
@@ -167,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
           unsigned char* a_dst = stages + (size_t)s * STAGE_BYTES;
           unsigned char* b_dst = a_dst + STAGE_A_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          mbar_expect_tx(&full_bar[s], STAGE_A_BYTES + bn * BK * 2);
           tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
           tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
         }
@@ -182,7 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   } else if (warp == 1) {
     // ---------------- tensor-core issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN);
+      const uint32_t idesc = make_idesc(BM, bn);
       // descriptors differ from stage to stage only in their address field (bytes / 16)
       const uint64_t a_desc0 = make_smem_desc(smem_u32(stages)), b_desc0 = make_smem_desc(smem_u32(stages) + STAGE_A_BYTES);
       uint32_t it = 0, s = 0, phase = 0;  // slices so far; the stage and the parity of its `full` barrier
@@ -242,19 +247,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       if (*(volatile int*)&abort_flag) break;
       tc_fence_after();
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
       const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < (bn + 31) / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
-        if (row < M && col < N) {
+        const int n_valid = min(N - col, bn - c * 32);  // columns of this piece that belong to the tile and the matrix
+        if (row < M && n_valid > 0) {
           if (SWIGLU)
-            store_swiglu16<TO>(out_k + (size_t)row * ldo + (col >> 1), r, (N - col) >> 1, vec_store != 0);
+            store_swiglu16<TO>(out_k + (size_t)row * ldo + (col >> 1), r, n_valid >> 1, vec_store != 0);
           else
-            store_row32<TO>(out_k + (size_t)row * ldo + col, r, N - col, vec_store != 0);
+            store_row32<TO>(out_k + (size_t)row * ldo + col, r, n_valid, vec_store != 0);
         }
       }
       // this half may be overwritten once all four warps have read it
@@ -329,9 +335,25 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
   }
-  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
+  // tiles as wide as they can be while one wave of them still covers the output (see the header)
+  int bn = BN;
+  {
+    const long long tiles_m = (M + BM - 1) / BM;
+    const long long at_full_width = tiles_m * ((N + BN - 1) / BN) * k_splits;
+    // (every tile reads its rows of x again, so narrower tiles cost L2 traffic: measured at 64 rows, a product
+    // with 24 full tiles gains from 128 narrow ones, 29 -> 24 us, one with 112 full tiles does not)
+    if (at_full_width < n_sms / 2) {
+      const long long per_row = n_sms / (tiles_m * k_splits);  // tiles that one row of tiles may have
+      if (per_row >= 1) {
+        long long want = (N + per_row - 1) / per_row;
+        want = ((want + 15) / 16) * 16;
+        bn = (int)(want < 16 ? 16 : (want > BN ? BN : want));
+      }
+    }
+  }
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) * k_splits;
   CUtensorMap map_x, map_w;
-  int e1 = make_map(&map_x, x, M, K, ldx, BM), e2 = make_map(&map_w, w, N, K, ldw, BN);
+  int e1 = make_map(&map_x, x, M, K, ldx, BM), e2 = make_map(&map_w, w, N, K, ldw, bn);
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
   dim3 grid((unsigned)(tiles < n_sms ? tiles : n_sms));
@@ -341,7 +363,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
       RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
     RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store,  \
-                              k_splits, status));                                                                 \
+                              k_splits, bn, status));                                                                 \
   } while (0)
   if (out_dtype == RL_BF16 && swiglu) RL_TC_LAUNCH(bf16, true);
   else if (out_dtype == RL_BF16) RL_TC_LAUNCH(bf16, false);

@@ -148,9 +148,81 @@ def bench_rows(a) -> dict:
     return {"kernel": "add_rmsnorm", "rows": a.rows, "d": d, "us": round(us, 2)}
 
 
+def bench_step_trace(a) -> dict:
+    """Durations of the kernels inside ONE replayed decode step (a CUDA graph with programmatic
+    launches, where a profiler would serialise them): every kernel's first thread notes the time at
+    which its dependency wait returned, i.e. when its predecessor had finished.  Needs libraries built
+    with -DRL_TRACE:
+
+        RUSTY_LLAMA_NVCC_EXTRA=-DRL_TRACE RUSTY_LLAMA_BUILD_DIR=/tmp/rl_trace \\
+            python -m rusty_llama_b200.kernels.microbench step_trace --layers 4 --seqs 8
+    """
+    import ctypes
+
+    from .. import load_random
+    from ..engine import StepEntry
+    from ..parts.attention import decode_splits
+    from . import build as kbuild
+
+    cfg = {
+        "architectures": ["LlamaForCausalLM"], "hidden_size": a.heads * a.head_dim, "intermediate_size": a.ff,
+        "num_hidden_layers": a.layers, "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads, "head_dim": a.head_dim,
+        "vocab_size": a.vocab, "max_position_embeddings": a.ctx + 64, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+        "rope_scaling": None, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+    }
+    llm = load_random(cfg, seed=0, max_tokens=a.seqs * (a.ctx + 128), max_seqs=a.seqs)
+    gen = torch.Generator().manual_seed(0)
+    slots = [llm.open_sequence() for _ in range(a.seqs)]
+    for s in slots:
+        llm.step([StepEntry(s, torch.randint(0, a.vocab, (a.ctx - 60,), generator=gen).tolist(), [])])  # the traced steps stay inside one page-table width
+
+    def decode():
+        return llm.step([StepEntry(s, [5], [0]) for s in slots])
+
+    for _ in range(4):  # a plain run, the capture, replays
+        decode()
+    torch.cuda.synchronize()
+    cap = 8192
+    buf = torch.zeros(cap, dtype=torch.int64, device="cuda:0")
+    count = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    for name in kbuild.loaded_libraries():
+        lib = kbuild.load(name)
+        if not hasattr(lib, "rl_trace_set"):
+            raise SystemExit("the kernel libraries were built without -DRL_TRACE:\n" + bench_step_trace.__doc__)
+        rc = lib.rl_trace_set(ctypes.c_void_p(buf.data_ptr()), ctypes.c_void_p(count.data_ptr()), ctypes.c_uint(cap))
+        if rc:
+            raise SystemExit(f"rl_trace_set of {name} failed with CUDA error {rc}")
+    runs = []
+    for _ in range(a.iters):
+        count.zero_()
+        torch.cuda.synchronize()
+        decode()
+        torch.cuda.synchronize()
+        t = buf[: int(count.item())].cpu().tolist()
+        runs.append([(y - x) / 1000.0 for x, y in zip(t, t[1:])])
+    # the kernels that call the dependency wait, in a step's order; an interval runs from the end of a
+    # kernel's predecessor to its own end (the classifier product and the sampler follow the last mark)
+    fused = a.head_dim == ops.ATTN_DECODE_TMA_HEAD_DIM
+    one_split = decode_splits(a.seqs, a.heads, a.kv_heads, a.ctx, a.head_dim) == 1
+    layer = ["norm1", "qkv"] + ([] if fused else ["rope"]) + ["attention"] + ([] if (fused and one_split) else ["merge"]) + ["o_proj", "norm2", "gate_up", "down"]
+    names = ["embed"] + layer * a.layers + ["final_norm"]
+    if any(len(r) != len(names) for r in runs):
+        raise SystemExit(f"expected {len(names)} intervals per step, got {[len(r) for r in runs]}: the step's kernel list has changed")
+    per = {}
+    for r in runs:
+        for nm, dt in zip(names, r):
+            per.setdefault(nm, []).append(dt)
+    # the median over the steps: a step that crosses into a wider page table runs plainly once more
+    med = lambda v: sorted(v)[len(v) // 2]
+    out = {"kernel": "step_trace", "seqs": a.seqs, "ctx": a.ctx, "layers": a.layers, "us": {k: round(med(v), 2) for k, v in per.items()},
+           "step_spans_us": [round(sum(r), 1) for r in runs]}
+    out["layer_us"] = round(sum(out["us"][k] for k in layer), 1)
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemv", "gemm", "attn_decode", "flash_prefill", "add_rmsnorm"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "attn_decode", "flash_prefill", "add_rmsnorm", "step_trace"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -160,6 +232,9 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=4, help="step_trace: layers of the model")
+    ap.add_argument("--ff", type=int, default=14336, help="step_trace: width of the feed-forward")
+    ap.add_argument("--vocab", type=int, default=128256, help="step_trace: vocabulary")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
     ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream", "tma", "warp"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent TMA-fed kernel; attn_decode: tma or warp = one of its two kernels")
     ap.add_argument("--iters", type=int, default=50)
@@ -169,7 +244,7 @@ def main(argv=None) -> int:
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
     fn = {"gemv": bench_gemv, "gemm": bench_gemm, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
-          "add_rmsnorm": bench_rows}[a.kernel]
+          "add_rmsnorm": bench_rows, "step_trace": bench_step_trace}[a.kernel]
     print(json.dumps(fn(a)))
     return 0
 
