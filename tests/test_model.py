@@ -275,10 +275,11 @@ def test_command_line_generates_what_the_entry_point_generates(tmp_path, capsys,
 
 def test_one_layer_at_the_sizes_of_the_benchmark(tmp_path):
     """The benchmark's layer sizes (width 4096, 32 / 8 heads of 128, feed-forward 14336, llama3 rope
-    scaling) with one layer and a smaller vocabulary, in bfloat16: two prompts of unequal lengths in one
-    step, then tokens one by one with and without graphs.  This is where the kernels that only these sizes
-    select are checked inside a model: the TMA-fed streaming product at k = 4096 and 14336 (in slices), the
-    tcgen05 product and prompt attention, the four-warp decode attention with its splits."""
+    scaling) with one layer and a smaller vocabulary, in bfloat16: prompts of unequal lengths in one
+    step, then tokens one by one, with and without graphs, as a batch of 2 (the streaming products, key
+    splits with a merge kernel) and as a batch of 12 (the tcgen05 product with narrowed tiles and with
+    split k, attention that writes its result itself).  This is where the kernels that only these
+    sizes select are checked inside a model."""
     import bench
     import rusty_llama_b200 as rl
     from conftest import read_weights
@@ -288,20 +289,25 @@ def test_one_layer_at_the_sizes_of_the_benchmark(tmp_path):
     model_dir = rl.write_random_model(str(tmp_path / "big"), cfg, seed=21, std=0.03, norm_jitter=0.1)
     w = read_weights(model_dir)
     rng = np.random.default_rng(4)
-    a, b = rng.integers(0, 8200, 580).tolist(), rng.integers(0, 8200, 71).tolist()  # a: long enough for four key splits
-    refs = plain_all_logits(cfg, w, "bfloat16", {"a": a, "b": b})
+    reqs = {"a": rng.integers(0, 8200, 580).tolist(), "b": rng.integers(0, 8200, 71).tolist()}  # a: long enough for four key splits
+    for i in range(10):
+        reqs[f"s{i}"] = rng.integers(0, 8200, 12 + 3 * i).tolist()
+    refs = plain_all_logits(cfg, w, "bfloat16", reqs)
+    n_decode = 6
     for graphs in (True, False):
-        llm = rl.load(model_dir, dtype="bfloat16", max_tokens=64 * 12, max_seqs=2, use_graphs=graphs)
-        sa, sb = llm.open_sequence(), llm.open_sequence()
-        out = llm.step([rl.StepEntry(sa, a[:574], [0, 77, 573]), rl.StepEntry(sb, b[:65], [64])]).cpu().numpy()
-        check_logits(out[:3], refs["a"][[0, 77, 573]], "bfloat16", "prompt a")
-        check_logits(out[3:], refs["b"][[64]], "bfloat16", "prompt b")
-        for i in range(6):
-            out = llm.step([rl.StepEntry(sa, [a[574 + i]], [0]), rl.StepEntry(sb, [b[65 + i]], [0])]).cpu().numpy()
-            check_logits(out[:1], refs["a"][[574 + i]], "bfloat16", f"decode a {i} (graphs={graphs})")
-            check_logits(out[1:], refs["b"][[65 + i]], "bfloat16", f"decode b {i} (graphs={graphs})")
-        llm.close_sequence(sa)
-        llm.close_sequence(sb)
-        llm.engine.check_device_status()
-        del llm
-        torch.cuda.empty_cache()
+        for names in (["a", "b"], list(reqs)):
+            llm = rl.load(model_dir, dtype="bfloat16", max_tokens=64 * 24, max_seqs=len(names), use_graphs=graphs)
+            slots = {n: llm.open_sequence() for n in names}
+            cut = {n: len(reqs[n]) - n_decode for n in names}
+            out = llm.step([rl.StepEntry(slots[n], reqs[n][: cut[n]], [0, cut[n] - 1]) for n in names]).cpu().numpy()
+            for i, n in enumerate(names):
+                check_logits(out[2 * i : 2 * i + 2], refs[n][[0, cut[n] - 1]], "bfloat16", f"prompt {n}")
+            for t in range(n_decode):
+                out = llm.step([rl.StepEntry(slots[n], [reqs[n][cut[n] + t]], [0]) for n in names]).cpu().numpy()
+                for i, n in enumerate(names):
+                    check_logits(out[i : i + 1], refs[n][[cut[n] + t]], "bfloat16", f"decode {n} {t} (graphs={graphs}, batch {len(names)})")
+            for n in names:
+                llm.close_sequence(slots[n])
+            llm.engine.check_device_status()
+            del llm
+            torch.cuda.empty_cache()
