@@ -87,7 +87,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        int K, int window, float scale_log2, int n_splits, int* __restrict__ status,
                        int fuse, bf16* __restrict__ k_pages_w, bf16* __restrict__ v_pages_w,
                        const float* __restrict__ inv_freq, int rot, int interleaved,
-                       unsigned int* __restrict__ counters, bf16* __restrict__ out, int out_stride) {
+                       unsigned int* __restrict__ counters, bf16* __restrict__ out, int out_stride,
+                       const float* __restrict__ q_parts, int n_parts, long long part_stride) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -187,9 +188,27 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   {
     // this block's queries: HEADS rows of 128 values, 16 bytes per thread
     const int r = threadIdx.x >> 4, piece = threadIdx.x & 15;  // 128 threads = 8 rows x 16 pieces
-    if (r < n_heads)
-      *reinterpret_cast<uint4*>(q_s + (size_t)r * Q_STRIDE + piece * 8) =
-          __ldcg(reinterpret_cast<const uint4*>(q + (size_t)s * q_stride + (size_t)(h0 + r) * HD + piece * 8));
+    if (r < n_heads) {
+      const size_t at = (size_t)s * q_stride + (size_t)(h0 + r) * HD + piece * 8;
+      if (n_parts == 0) {
+        *reinterpret_cast<uint4*>(q_s + (size_t)r * Q_STRIDE + piece * 8) = __ldcg(reinterpret_cast<const uint4*>(q + at));
+      } else {
+        // the projection came as partial sums over slices of k: add them up (32-bit) and round once
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < n_parts; ++p) {
+          const float4 x0 = __ldcg(reinterpret_cast<const float4*>(q_parts + (size_t)p * part_stride + at));
+          const float4 x1 = __ldcg(reinterpret_cast<const float4*>(q_parts + (size_t)p * part_stride + at + 4));
+          v[0] += x0.x; v[1] += x0.y; v[2] += x0.z; v[3] += x0.w;
+          v[4] += x1.x; v[5] += x1.y; v[6] += x1.z; v[7] += x1.w;
+        }
+        uint4 packed;
+        packed.x = pack_bf16(v[0], v[1]);
+        packed.y = pack_bf16(v[2], v[3]);
+        packed.z = pack_bf16(v[4], v[5]);
+        packed.w = pack_bf16(v[6], v[7]);
+        *reinterpret_cast<uint4*>(q_s + (size_t)r * Q_STRIDE + piece * 8) = packed;
+      }
+    }
   }
   if (fuse) {
     product_warps_sync();  // the queries and the angles are in shared memory
@@ -223,6 +242,36 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // rows this lane addresses in the ldmatrix calls: K as A operand (16 keys x 16 dims), V transposed
   const int k_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), k_piece = lane >> 4;      // + 2 * kk
   const int v_row = warp * 16 + (lane & 7) + 8 * (lane >> 4), v_piece = (lane >> 3) & 1;      // + 2 * dt
+  // The warp that owns the new position's row in the sequence's last page reads the new token's raw key
+  // and value now, so that the loads are long done when that page arrives: rotary pairs j = lane, lane + 32,
+  // unrotated dimensions and values d = lane + 32 i.
+  const bool patch_here = fuse == 2 && my_lo <= my_hi && my_hi == tile_hi && warp == ((pos & (PAGE - 1)) >> 4);
+  float new_k[HD / 64][2], new_tail[HD / 32], new_v[HD / 32];
+  if (patch_here) {
+    const size_t k_at = (size_t)s * q_stride + (size_t)(H + kh) * HD, v_at = k_at + (size_t)K * HD;
+    // a raw value of the projection's row, rounded to bfloat16 as the projection would have stored it
+    auto raw = [&](size_t at) -> float {
+      if (n_parts == 0) return __bfloat162float(q[at]);
+      float v = 0.f;
+      for (int p = 0; p < n_parts; ++p) v += __ldcg(q_parts + (size_t)p * part_stride + at);
+      return __bfloat162float(__float2bfloat16_rn(v));
+    };
+#pragma unroll
+    for (int i = 0; i < HD / 64; ++i) {
+      const int j = lane + 32 * i;
+      new_k[i][0] = new_k[i][1] = 0.f;
+      if (j < half_rot) {
+        new_k[i][0] = raw(k_at + (interleaved ? 2 * j : j));
+        new_k[i][1] = raw(k_at + (interleaved ? 2 * j + 1 : j + half_rot));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 32; ++i) {
+      const int d = lane + 32 * i;
+      new_tail[i] = d >= rot ? raw(k_at + d) : 0.f;
+      new_v[i] = raw(v_at + d);
+    }
+  }
   bool ok = true;
   int done = 0;
   for (int tile = my_lo; tile <= my_hi && ok; ++tile, ++done) {
@@ -240,12 +289,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       break;
     }
     const uint32_t k_s = smem_u32(ring) + st * STAGE_BYTES, v_s = k_s + 2 * HALF_BYTES;
-    if (fuse == 2 && tile == tile_hi && warp == ((pos & (PAGE - 1)) >> 4)) {
-      // the new token's key and value: from the projection's output into this block's copy of the page
-      // and (one block per kv head) into the cache
+    if (patch_here && tile == tile_hi) {
+      // the new token's key and value (read before the loop): into this block's copy of the page and (one
+      // block per kv head) into the cache
       const int row = pos & (PAGE - 1);
-      const bf16* k_raw = q + (size_t)s * q_stride + (size_t)(H + kh) * HD;
-      const bf16* v_raw = k_raw + (size_t)K * HD;
       unsigned char* k_tile = ring + (size_t)st * STAGE_BYTES;
       unsigned char* v_tile = k_tile + 2 * HALF_BYTES;
       const size_t cache_row = (((size_t)table[tile] * K + kh) * PAGE + row) * HD;
@@ -254,14 +301,21 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         *reinterpret_cast<bf16*>(tile_base + (d >> 6) * HALF_BYTES + swz(row, (d & 63) >> 3) + (d & 7) * 2) = v;
         if (to_cache) pages[cache_row + d] = v;
       };
-      for (int j = lane; j < half_rot; j += 32) {
-        const int d0 = interleaved ? 2 * j : j, d1 = interleaved ? 2 * j + 1 : j + half_rot;
-        const float a = __bfloat162float(k_raw[d0]), b = __bfloat162float(k_raw[d1]);
-        put(k_tile, k_pages_w, d0, __float2bfloat16_rn(a * bars.cs[j] - b * bars.sn[j]));
-        put(k_tile, k_pages_w, d1, __float2bfloat16_rn(a * bars.sn[j] + b * bars.cs[j]));
+#pragma unroll
+      for (int i = 0; i < HD / 64; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half_rot) {
+          const int d0 = interleaved ? 2 * j : j, d1 = interleaved ? 2 * j + 1 : j + half_rot;
+          put(k_tile, k_pages_w, d0, __float2bfloat16_rn(new_k[i][0] * bars.cs[j] - new_k[i][1] * bars.sn[j]));
+          put(k_tile, k_pages_w, d1, __float2bfloat16_rn(new_k[i][0] * bars.sn[j] + new_k[i][1] * bars.cs[j]));
+        }
       }
-      for (int d = rot + lane; d < HD; d += 32) put(k_tile, k_pages_w, d, k_raw[d]);
-      for (int d = lane; d < HD; d += 32) put(v_tile, v_pages_w, d, v_raw[d]);
+#pragma unroll
+      for (int i = 0; i < HD / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= rot) put(k_tile, k_pages_w, d, __float2bfloat16_rn(new_tail[i]));
+        put(v_tile, v_pages_w, d, __float2bfloat16_rn(new_v[i]));
+      }
       __syncwarp();
     }
 
@@ -512,6 +566,8 @@ RL_API int rl_attn_decode_tma_head_dim() { return HD; }
 // the new token's key and value from q's rows (keys at column H * hd, values at (H + K) * hd), turn the
 // key and store both (k_pages and v_pages are written).  inv_freq: rot / 2 angles per position; rot = 0
 // means no rotation at all (then fuse = 2 only stores).
+// q_parts (with fuse > 0 only): the projection's rows as n_parts float32 partial sums, part p at
+// q_parts + p * part_stride, rows of q_stride values; q is then not read.
 // counters: null, or n_seqs * (K * groups of 8 heads) zeros in device memory: the splits are then added
 // up by the block that finishes last (no merge kernel is launched) and the counters are zeros again
 // when the kernel ends.
@@ -519,17 +575,20 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
                               const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
                               void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
                               float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
-                              int interleaved, unsigned int* counters, cudaStream_t stream) {
+                              int interleaved, unsigned int* counters, const float* q_parts, int n_parts,
+                              long long part_stride, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
   if (hd != HD) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for %d", hd, HD);
   if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
   if (page_size != PAGE) RL_REFUSE(4, "attn_decode_tma: page size %d, this kernel is built for %d", page_size, PAGE);
   if (q_stride % 8) RL_REFUSE(5, "attn_decode_tma: query row stride %d breaks 16-byte alignment", q_stride);
-  if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
+  if (((n_parts > 0 ? (uintptr_t)0 : (uintptr_t)q) | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
   if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
   if (fuse < 0 || fuse > 2 || rot < 0 || rot > HD || (rot & 1) || (fuse && rot > 0 && inv_freq == nullptr))
     RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d%s", fuse, rot, inv_freq ? "" : " and no angles");
+  if (n_parts < 0 || n_parts > 64 || (n_parts > 0 && (q_parts == nullptr || fuse == 0 || ((uintptr_t)q_parts & 15) || part_stride % 4 || q_stride % 4)))
+    RL_REFUSE(14, "attn_decode_tma: %d partial sums need fuse > 0 and 16-byte aligned rows", n_parts);
   if (fuse == 2 && q_stride < (H + 2 * K) * HD) RL_REFUSE(13, "attn_decode_tma: rows of %d hold no key and value behind %d query heads", q_stride, H);
   EncodeTiledFn enc = encode_tiled();
   if (!enc) RL_REFUSE(9, "attn_decode_tma: cuTensorMapEncodeTiled is not available");
@@ -552,7 +611,7 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, SMEM_BYTES, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
                             table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
                             fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
-                            interleaved, counters, (bf16*)out, out_stride));
+                            interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride));
   if (counters != nullptr) return 0;
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_tma_merge_kernel, grid2, HD, 0, stream, (const float*)part_o, (const float*)part_ml,

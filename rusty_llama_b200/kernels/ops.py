@@ -298,12 +298,22 @@ def attn_decode(
     scratch: float32 tensor of at least attn_decode_scratch_floats(...) elements.
     impl: "warp" = one-warp blocks that copy their own tiles, "tma" = four-warp blocks on a TMA-fed
     ring of whole pages (head size 128 only), "auto" = "tma" where it applies, else "warp"."""
-    _cuda(q, "attn_decode q", contiguous=False)
-    qs = _rows(q, "attn_decode q")
-    S = q.shape[0]
-    _need(q.shape[1] >= num_heads * head_dim, "attn_decode: q rows too short")
+    q_parts = None
+    if q.dim() == 3:
+        # the projection as float32 partial sums [parts, S, columns] (a product that was split over k): the
+        # fused TMA kernel adds them up as it reads them
+        _cuda(q, "attn_decode q (partial sums)", torch.float32, contiguous=False)
+        _need(fuse > 0, "attn_decode: partial sums of the projection need fuse > 0")
+        _need(q.stride(2) == 1 and q.stride(1) % 4 == 0 and q.stride(0) % 4 == 0, "attn_decode: partial sums must have dense, 16-byte aligned rows")
+        q_parts, act = q, k_pages.dtype
+        qs, S, q_cols = q.stride(1), q.shape[1], q.shape[2]
+    else:
+        _cuda(q, "attn_decode q", contiguous=False)
+        qs, act = _rows(q, "attn_decode q"), q.dtype
+        S, q_cols = q.shape
+    _need(q_cols >= num_heads * head_dim, "attn_decode: q rows too short")
     _need(q.data_ptr() % 16 == 0, "attn_decode: q is not 16-byte aligned")
-    _check_pages(k_pages, v_pages, q.dtype, num_kv_heads, head_dim, "attn_decode")
+    _check_pages(k_pages, v_pages, act, num_kv_heads, head_dim, "attn_decode")
     _cuda(block_table, "attn_decode block_table", torch.int32)
     _cuda(seq_len, "attn_decode seq_len", torch.int32)
     _need(block_table.dim() == 2 and block_table.shape[0] >= S and seq_len.numel() == S, "attn_decode: metadata sizes")
@@ -311,8 +321,8 @@ def attn_decode(
     need = attn_decode_scratch_floats(S, num_heads, head_dim, n_splits)
     _need(scratch.numel() >= need, f"attn_decode: scratch holds {scratch.numel()} floats, {need} needed")
     if out is None:
-        out = torch.empty((S, num_heads * head_dim), dtype=q.dtype, device=q.device)
-    _cuda(out, "attn_decode out", q.dtype)
+        out = torch.empty((S, num_heads * head_dim), dtype=act, device=q.device)
+    _cuda(out, "attn_decode out", act)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     n_o = S * num_heads * n_splits * head_dim
@@ -320,7 +330,7 @@ def attn_decode(
     part_ml = c_void_p(scratch.data_ptr() + 4 * n_o)
     _need(impl in ("auto", "warp", "tma"), f"attn_decode: unknown impl {impl!r}")
     if impl == "auto":
-        impl = "tma" if (head_dim == ATTN_DECODE_TMA_HEAD_DIM and q.dtype == torch.bfloat16) else "warp"
+        impl = "tma" if (head_dim == ATTN_DECODE_TMA_HEAD_DIM and act == torch.bfloat16) else "warp"
     _need(fuse in (0, 1, 2), f"attn_decode: fuse={fuse}")
     if fuse:
         _need(impl == "tma", "attn_decode: only the TMA kernel fuses the position encoding")
@@ -328,22 +338,25 @@ def attn_decode(
             _cuda(inv_freq, "attn_decode inv_freq", torch.float32)
             _need(inv_freq.numel() >= rotary_dim // 2, "attn_decode: too few angles for the rotary size")
         if fuse == 2:
-            _need(q.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim, "attn_decode: q rows hold no key and value")
+            _need(q_cols >= (num_heads + 2 * num_kv_heads) * head_dim, "attn_decode: q rows hold no key and value")
     if counters is not None:
         _need(impl == "tma", "attn_decode: only the TMA kernel adds the splits up itself")
         _cuda(counters, "attn_decode counters", torch.int32)
         groups = num_kv_heads * ((num_heads // num_kv_heads + 7) // 8)
         _need(counters.numel() >= S * groups, f"attn_decode: {counters.numel()} counters, {S * groups} needed")
+    _need(q_parts is None or impl == "tma", "attn_decode: only the TMA kernel takes partial sums")
     if impl == "tma":
-        _need(q.dtype == torch.bfloat16, "attn_decode: the TMA kernel is bfloat16 only")
+        _need(act == torch.bfloat16, "attn_decode: the TMA kernel is bfloat16 only")
         status = _tc_status_word(q.device)
         lib = build.load("attention_decode_tma")
         rc = lib.rl_attn_decode_tma(
-            _p(q), c_int(qs), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
+            c_void_p(0) if q_parts is not None else _p(q), c_int(qs), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
             c_int(block_table.shape[1]), _p(seq_len), part_o, part_ml, _p(out), c_int(out.stride(0)), c_int(S),
             c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
             c_int(n_splits), _p(status), c_int(fuse), _p(inv_freq) if (fuse and rotary_dim) else c_void_p(0), c_int(rotary_dim if fuse else 0),
-            c_int(1 if interleaved else 0), _p(counters) if counters is not None else c_void_p(0), _stream(),
+            c_int(1 if interleaved else 0), _p(counters) if counters is not None else c_void_p(0),
+            _p(q_parts) if q_parts is not None else c_void_p(0), c_int(0 if q_parts is None else q_parts.shape[0]),
+            c_ll(0 if q_parts is None else q_parts.stride(0)), _stream(),
         )
         _check(lib, rc, "attn_decode_tma", kernels=1 if counters is not None else 2)
         return out

@@ -21,6 +21,7 @@ _DECODE_HEADS_PER_BLOCK = 8
 
 # the four-warp kernel for head size 128: two blocks per SM; a split shorter than four pages costs
 # more in the merge than it gains (measured at one sequence of 4096: 16 splits 7.5 us, 37 splits 8.8)
+_QKV_PARTIALS_MAX_ROWS = 32
 _DECODE_TMA_TARGET_BLOCKS = 296
 _DECODE_TMA_MIN_PAGES = 4
 
@@ -92,16 +93,17 @@ class Attention(Mixer):
         self.w_o = tensors[p + "o_proj.weight"].contiguous()
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
-        if shared_cache:
-            # the keys and values are another run's: project the queries only
-            qkv = linear(xn, self.w_qkv[: self.qd])
-        else:
-            qkv = linear(xn, self.w_qkv)
         # a decode step of a bfloat16 run at head size 128: the attention kernel turns the queries and the
         # new key and stores key and value itself, if the position encoding is one it knows how to apply
         fusion = None
         if step.decode_only and self.rt.dtype == torch.bfloat16 and self.hd == ops.ATTN_DECODE_TMA_HEAD_DIM:
             fusion = self.position.decode_fusion()
+        # the keys and values may be another run's: then only the queries are projected.  The fused attention
+        # kernel also takes the projection as partial sums over slices of k, which lets a product with few
+        # output tiles use all SMs (measured at the 8B sizes: 3 % of the step gained at 16 and 24 sequences,
+        # 3 % lost at 64, where every block would add up its own partial sums)
+        w = self.w_qkv[: self.qd] if shared_cache else self.w_qkv
+        qkv = linear_to_stream(xn, w) if (fusion is not None and xn.shape[0] <= _QKV_PARTIALS_MAX_ROWS) else linear(xn, w)
         if fusion is None:
             self.position.write_qk(qkv, step, cache, self.H, self.K, self.hd, write_kv=not shared_cache)
         if self.rt.dtype == torch.float32:

@@ -391,6 +391,40 @@ def test_attn_decode_tma_adds_its_splits_up_itself(ops, H, K, n_splits, window):
     close_bf16(one, ref)
 
 
+@pytest.mark.parametrize("parts", [1, 3])
+@pytest.mark.parametrize("fuse", [1, 2])
+def test_attn_decode_tma_takes_the_projection_as_partial_sums(ops, parts, fuse):
+    """The fused kernel fed with float32 partial sums [parts, S, columns] of the projection against the
+    same kernel fed with their bfloat16 sum: the same cache contents and the same result, bit for bit."""
+    H, K, hd, rot = 8, 2, 128, 128
+    lens = [1, 64, 65, 300, 128, 17]
+    S = len(lens)
+    kv = PagedKV(lens, K, hd, torch.bfloat16, seed=12)
+    g = torch.Generator().manual_seed(parts)
+    pieces = torch.randn(parts, S, (H + 2 * K) * hd, generator=g).to(DEV)
+    whole = pieces.sum(dim=0) if parts > 1 else pieces[0]
+    # the sum the kernel makes: part after part in 32-bit
+    acc = torch.zeros_like(pieces[0])
+    for p in range(parts):
+        acc = acc + pieces[p]
+    raw = acc.to(torch.bfloat16)
+    inv_freq = (10000.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / rot)).to(DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(ops.attn_decode_scratch_floats(S, H, hd, 2), device=DEV)
+    k_a, v_a, k_b, v_b = kv.k_pages.clone(), kv.v_pages.clone(), kv.k_pages.clone(), kv.v_pages.clone()
+    kw = dict(impl="tma", fuse=fuse, inv_freq=inv_freq, rotary_dim=rot, interleaved=False)
+    out_a = ops.attn_decode(raw, k_a, v_a, kv.table, seq_len, H, K, hd, 2, scratch, **kw).clone()
+    out_b = ops.attn_decode(pieces, k_b, v_b, kv.table, seq_len, H, K, hd, 2, scratch, **kw)
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert out_b.dtype == torch.bfloat16 and torch.equal(out_b, out_a)
+    assert torch.equal(k_b, k_a) and torch.equal(v_b, v_a)
+    if fuse == 2:
+        assert not torch.equal(k_a, kv.k_pages)  # the new keys were stored
+    with pytest.raises(Exception, match="fuse > 0"):
+        ops.attn_decode(pieces, k_b, v_b, kv.table, seq_len, H, K, hd, 2, scratch, impl="tma")
+
+
 def test_attn_decode_tma_finds_a_far_key(ops):
     """One key far back among hundreds carries almost all the weight: a kernel that skips a page, a
     split, a warp's 16 keys or a swizzled piece returns something else entirely."""
