@@ -517,6 +517,43 @@ def test_flash_prefill_tc(ops, H, K, window):
     close_bf16(out, torch.cat(refs).view(T, H * hd))
 
 
+def test_long_context_attention_kernels_at_head_size_128(ops):
+    """20 000 cached positions (313 pages in a scrambled table): a chunk of 200 prompt rows appended far
+    into the sequence through the tcgen05 kernel, then a decode row through the TMA kernel with few and
+    many key splits, with and without a window.  One key far back (position 77) is made to matter, so
+    that a page skipped hundreds of pages away would show."""
+    H, K, hd = 4, 2, 128
+    n, q_len = 20000, 200
+    kv = PagedKV([n], K, hd, torch.bfloat16, seed=31, extra_pages=5)
+    g = torch.Generator().manual_seed(7)
+    q = bf16_round(torch.randn(q_len, (H + 2 * K) * hd, generator=g))
+    far = 77
+    boost = bf16_round(q[-1, :hd] * 0.6)  # along the last row's first head
+    kv.k[0][far, 0] = boost
+    kv.k_pages[int(kv.table[0, far // PAGE]), 0, far % PAGE] = boost.to(torch.bfloat16).to(DEV)
+    qd = q.to(torch.bfloat16).to(DEV)
+    pos0 = n - q_len
+    for window in (0, 5000):
+        out = ops.flash_prefill_tc(qd, kv.k_pages, kv.v_pages, kv.table, torch.tensor([0, q_len], dtype=torch.int32, device=DEV),
+                                   torch.tensor([pos0], dtype=torch.int32, device=DEV), q_len, H, K, hd, window=window)
+        torch.cuda.synchronize()
+        ops.tc_status_check()
+        rows = [0, 63, 64, 127, 128, 199]
+        ref = ref_attention_rows(q[rows, : H * hd].view(len(rows), H, hd), kv, 0, [pos0 + r for r in rows], window).view(len(rows), H * hd)
+        close_bf16(out[rows], ref)
+        for n_splits in (3, 64):
+            scratch = torch.empty(ops.attn_decode_scratch_floats(1, H, hd, n_splits), device=DEV)
+            dec = ops.attn_decode(qd[-1:], kv.k_pages, kv.v_pages, kv.table, torch.tensor([n], dtype=torch.int32, device=DEV),
+                                  H, K, hd, n_splits, scratch, window=window, impl="tma")
+            torch.cuda.synchronize()
+            ops.tc_status_check()
+            close_bf16(dec, ref[-1:])
+    # without a window the far key carries visible weight in the last row's first head
+    full = ref_attention_rows(q[-1:, : H * hd].view(1, H, hd), kv, 0, [n - 1], 0).view(H, hd)
+    near = ref_attention_rows(q[-1:, : H * hd].view(1, H, hd), kv, 0, [n - 1], 5000).view(H, hd)
+    assert float((full[0] - near[0]).abs().max()) > 0.05
+
+
 def test_flash_prefill_tc_each_key_and_dimension_lands_where_it_should(ops):
     """Values that name their own key and dimension, queries that each pick one key: any mix-up of pages,
     swizzled pieces, k steps or the transposed V operand shows as a wrong number, not as noise."""
