@@ -87,7 +87,10 @@ __device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32],
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
-    h[i] = g * (1.0f / (1.0f + expf(-g))) * u;
+    // exp and the division by the hardware's approximations (a few units in the last place of 32 bits,
+    // far below the bfloat16 rounding that follows): the accurate forms cost a row's thread about 8 us per
+    // tile, which a step with one tile per SM cannot hide behind the next tile's products
+    h[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
   }
   if (vec && n_valid >= 16) {
 #pragma unroll
