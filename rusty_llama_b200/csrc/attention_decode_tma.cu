@@ -243,33 +243,30 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int k_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), k_piece = lane >> 4;      // + 2 * kk
   const int v_row = warp * 16 + (lane & 7) + 8 * (lane >> 4), v_piece = (lane >> 3) & 1;      // + 2 * dt
   // The warp that owns the new position's row in the sequence's last page reads the new token's raw key
-  // and value now, so that the loads are long done when that page arrives: rotary pairs j = lane, lane + 32,
-  // unrotated dimensions and values d = lane + 32 i.
+  // and value now, so that the loads are long done when that page arrives: lane l takes dimensions
+  // 4 l .. 4 l + 3 of both, one 8-byte load each (or one 16-byte load per partial sum, all independent).
   const bool patch_here = fuse == 2 && my_lo <= my_hi && my_hi == tile_hi && warp == ((pos & (PAGE - 1)) >> 4);
-  float new_k[HD / 64][2], new_tail[HD / 32], new_v[HD / 32];
+  float new_k[4] = {0.f, 0.f, 0.f, 0.f}, new_v[4] = {0.f, 0.f, 0.f, 0.f};
   if (patch_here) {
-    const size_t k_at = (size_t)s * q_stride + (size_t)(H + kh) * HD, v_at = k_at + (size_t)K * HD;
-    // a raw value of the projection's row, rounded to bfloat16 as the projection would have stored it
-    auto raw = [&](size_t at) -> float {
-      if (n_parts == 0) return __bfloat162float(q[at]);
-      float v = 0.f;
-      for (int p = 0; p < n_parts; ++p) v += __ldcg(q_parts + (size_t)p * part_stride + at);
-      return __bfloat162float(__float2bfloat16_rn(v));
-    };
-#pragma unroll
-    for (int i = 0; i < HD / 64; ++i) {
-      const int j = lane + 32 * i;
-      new_k[i][0] = new_k[i][1] = 0.f;
-      if (j < half_rot) {
-        new_k[i][0] = raw(k_at + (interleaved ? 2 * j : j));
-        new_k[i][1] = raw(k_at + (interleaved ? 2 * j + 1 : j + half_rot));
+    const size_t k_at = (size_t)s * q_stride + (size_t)(H + kh) * HD + 4 * lane, v_at = k_at + (size_t)K * HD;
+    if (n_parts == 0) {
+      const uint2 kr = __ldcg(reinterpret_cast<const uint2*>(q + k_at)), vr = __ldcg(reinterpret_cast<const uint2*>(q + v_at));
+      const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
+      const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x)), v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+      new_k[0] = k0.x; new_k[1] = k0.y; new_k[2] = k1.x; new_k[3] = k1.y;
+      new_v[0] = v0.x; new_v[1] = v0.y; new_v[2] = v1.x; new_v[3] = v1.y;
+    } else {
+      for (int p = 0; p < n_parts; ++p) {
+        const float4 kp = __ldcg(reinterpret_cast<const float4*>(q_parts + (size_t)p * part_stride + k_at));
+        const float4 vp = __ldcg(reinterpret_cast<const float4*>(q_parts + (size_t)p * part_stride + v_at));
+        new_k[0] += kp.x; new_k[1] += kp.y; new_k[2] += kp.z; new_k[3] += kp.w;
+        new_v[0] += vp.x; new_v[1] += vp.y; new_v[2] += vp.z; new_v[3] += vp.w;
       }
-    }
 #pragma unroll
-    for (int i = 0; i < HD / 32; ++i) {
-      const int d = lane + 32 * i;
-      new_tail[i] = d >= rot ? raw(k_at + d) : 0.f;
-      new_v[i] = raw(v_at + d);
+      for (int e = 0; e < 4; ++e) {  // rounded to bfloat16 as the projection would have stored them
+        new_k[e] = __bfloat162float(__float2bfloat16_rn(new_k[e]));
+        new_v[e] = __bfloat162float(__float2bfloat16_rn(new_v[e]));
+      }
     }
   }
   bool ok = true;
@@ -290,31 +287,41 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     const uint32_t k_s = smem_u32(ring) + st * STAGE_BYTES, v_s = k_s + 2 * HALF_BYTES;
     if (patch_here && tile == tile_hi) {
-      // the new token's key and value (read before the loop): into this block's copy of the page and (one
-      // block per kv head) into the cache
+      // the new token's key and value (read before the loop): the key turned by the position's angles,
+      // both into this block's copy of the page and (one block per kv head) into the cache
       const int row = pos & (PAGE - 1);
-      unsigned char* k_tile = ring + (size_t)st * STAGE_BYTES;
-      unsigned char* v_tile = k_tile + 2 * HALF_BYTES;
-      const size_t cache_row = (((size_t)table[tile] * K + kh) * PAGE + row) * HD;
-      const bool to_cache = g0 == 0;
-      auto put = [&](unsigned char* tile_base, bf16* pages, int d, bf16 v) {
-        *reinterpret_cast<bf16*>(tile_base + (d >> 6) * HALF_BYTES + swz(row, (d & 63) >> 3) + (d & 7) * 2) = v;
-        if (to_cache) pages[cache_row + d] = v;
-      };
+      const int hq = half_rot >> 2;  // lanes between the two halves of a pair (neighbour layout)
+      float o[4];
 #pragma unroll
-      for (int i = 0; i < HD / 64; ++i) {
-        const int j = lane + 32 * i;
-        if (j < half_rot) {
-          const int d0 = interleaved ? 2 * j : j, d1 = interleaved ? 2 * j + 1 : j + half_rot;
-          put(k_tile, k_pages_w, d0, __float2bfloat16_rn(new_k[i][0] * bars.cs[j] - new_k[i][1] * bars.sn[j]));
-          put(k_tile, k_pages_w, d1, __float2bfloat16_rn(new_k[i][0] * bars.sn[j] + new_k[i][1] * bars.cs[j]));
+      for (int e = 0; e < 4; ++e) {
+        const int d = 4 * lane + e;
+        // the partner's raw value: from the lane that holds dimension d + half_rot or d - half_rot
+        const float up = __shfl_sync(0xffffffffu, new_k[e], (lane + hq) & 31), dn = __shfl_sync(0xffffffffu, new_k[e], (lane - hq) & 31);
+        float r = new_k[e];
+        if (d < rot) {
+          if (interleaved) {
+            const int j = d >> 1;
+            const float other = new_k[e ^ 1];
+            r = (d & 1) ? other * bars.sn[j] + new_k[e] * bars.cs[j] : new_k[e] * bars.cs[j] - other * bars.sn[j];
+          } else if (d < half_rot) {
+            r = new_k[e] * bars.cs[d] - up * bars.sn[d];
+          } else {
+            r = dn * bars.sn[d - half_rot] + new_k[e] * bars.cs[d - half_rot];
+          }
         }
+        o[e] = r;
       }
-#pragma unroll
-      for (int i = 0; i < HD / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d >= rot) put(k_tile, k_pages_w, d, __float2bfloat16_rn(new_tail[i]));
-        put(v_tile, v_pages_w, d, __float2bfloat16_rn(new_v[i]));
+      const int d0 = 4 * lane;
+      const uint32_t in_tile = (d0 >> 6) * HALF_BYTES + swz(row, (d0 & 63) >> 3) + (d0 & 7) * 2;
+      const uint2 k_packed = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+      const uint2 v_packed = make_uint2(pack_bf16(new_v[0], new_v[1]), pack_bf16(new_v[2], new_v[3]));
+      unsigned char* k_tile = ring + (size_t)st * STAGE_BYTES;
+      *reinterpret_cast<uint2*>(k_tile + in_tile) = k_packed;
+      *reinterpret_cast<uint2*>(k_tile + 2 * HALF_BYTES + in_tile) = v_packed;
+      if (g0 == 0) {
+        const size_t cache_at = (((size_t)table[tile] * K + kh) * PAGE + row) * HD + d0;
+        *reinterpret_cast<uint2*>(k_pages_w + cache_at) = k_packed;
+        *reinterpret_cast<uint2*>(v_pages_w + cache_at) = v_packed;
       }
       __syncwarp();
     }
@@ -585,8 +592,8 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   if (((n_parts > 0 ? (uintptr_t)0 : (uintptr_t)q) | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
   if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
-  if (fuse < 0 || fuse > 2 || rot < 0 || rot > HD || (rot & 1) || (fuse && rot > 0 && inv_freq == nullptr))
-    RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d%s", fuse, rot, inv_freq ? "" : " and no angles");
+  if (fuse < 0 || fuse > 2 || rot < 0 || rot > HD || (rot & 7) || (fuse && rot > 0 && inv_freq == nullptr))
+    RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d (a multiple of 8 up to the head size)%s", fuse, rot, inv_freq ? "" : " and no angles");
   if (n_parts < 0 || n_parts > 64 || (n_parts > 0 && (q_parts == nullptr || fuse == 0 || ((uintptr_t)q_parts & 15) || part_stride % 4 || q_stride % 4)))
     RL_REFUSE(14, "attn_decode_tma: %d partial sums need fuse > 0 and 16-byte aligned rows", n_parts);
   if (fuse == 2 && q_stride < (H + 2 * K) * HD) RL_REFUSE(13, "attn_decode_tma: rows of %d hold no key and value behind %d query heads", q_stride, H);

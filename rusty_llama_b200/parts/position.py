@@ -38,6 +38,8 @@ class Rotary(PositionEncoding):
         raise NotImplementedError("Rotary encodes positions inside write_qk")
 
     def decode_fusion(self):
+        if self.rotary_dim % 8:  # the fused kernel moves a pair's halves between lanes in steps of four values
+            return None
         return self.inv_freq, self.rotary_dim, self.interleaved
 
 
