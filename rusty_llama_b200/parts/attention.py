@@ -21,7 +21,7 @@ _DECODE_HEADS_PER_BLOCK = 8
 
 # the four-warp kernel for head size 128: two blocks per SM; a split shorter than four pages costs
 # more in the merge than it gains (measured at one sequence of 4096: 16 splits 7.5 us, 37 splits 8.8)
-_QKV_PARTIALS_MAX_ROWS = 32
+_QKV_PARTIALS_MAX_ROWS = 128
 _DECODE_TMA_TARGET_BLOCKS = 296
 _DECODE_TMA_MIN_PAGES = 4
 
@@ -100,8 +100,7 @@ class Attention(Mixer):
             fusion = self.position.decode_fusion()
         # the keys and values may be another run's: then only the queries are projected.  The fused attention
         # kernel also takes the projection as partial sums over slices of k, which lets a product with few
-        # output tiles use all SMs (measured at the 8B sizes: 3 % of the step gained at 16 and 24 sequences,
-        # 3 % lost at 64, where every block would add up its own partial sums)
+        # output tiles use all SMs (measured at the 8B sizes: 3 % of the step gained at 16, 24 and 64 sequences)
         w = self.w_qkv[: self.qd] if shared_cache else self.w_qkv
         qkv = linear_to_stream(xn, w) if (fusion is not None and xn.shape[0] <= _QKV_PARTIALS_MAX_ROWS) else linear(xn, w)
         if fusion is None:
