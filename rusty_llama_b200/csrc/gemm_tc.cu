@@ -20,8 +20,8 @@
 //
 // Tile width.  With few rows (a decode step of 9 to 128 sequences) the product is a stream of
 // weights, and 256-wide tiles may be too few to give every SM one (6144 features: 24 tiles).  The
-// launcher then narrows the tiles (`bn`, a multiple of 16 from 16 to 256) so that they fill one wave;
-// the stages and accumulators keep their places for 256 columns and a narrower tile uses part of them.
+// launcher then narrows the tiles (`bn`, a multiple of 16 from 16 to 256) so that they fill one wave.
+// The stages and accumulators keep their places for 256 columns and a narrower tile uses part of them.
 //
 // Every wait on an mbarrier is bounded (about one second of polling): on expiry the waiter
 // records a code in `status[0]`, the block drains, frees its tensor memory and returns.
@@ -338,7 +338,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
   }
-  // tiles as wide as they can be while one wave of them still covers the output (see the header)
+  // the tile width: see the header
   int bn = BN;
   {
     const long long tiles_m = (M + BM - 1) / BM;
@@ -353,6 +353,8 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
         bn = (int)(want < 16 ? 16 : (want > BN ? BN : want));
       }
     }
+    // (Narrowing the tiles of a product with several rounds of tiles, so that the last round is fuller, was
+    // measured and does not pay: at 2048 rows a width of 240 instead of 256 took 390 us instead of 350.)
   }
   const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) * k_splits;
   CUtensorMap map_x, map_w;
