@@ -26,6 +26,7 @@
 //
 // Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
 #include "tc_common.cuh"
+#include "attention_merge.cuh"
 
 RL_DEFINE_ERROR_TEXT()
 
@@ -500,68 +501,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (threadIdx.x == 0) *counter = 0u;  // ready for the next call
 }
 
-// out[s, h, :] = sum_split 2^(m_split - M) o_split / sum_split 2^(m_split - M) l_split, in split order.
-// One block per (sequence, head); at most 64 splits.
-__global__ void attn_decode_tma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                             bf16* __restrict__ out, int out_stride, int H, int n_splits) {
-  __shared__ float w_s[64];
-  pdl_trigger();
-  pdl_wait();
-  const int h = blockIdx.x, s = blockIdx.y;
-  const float* ml = part_ml + ((size_t)s * H + h) * n_splits * 2;
-  const float* po = part_o + ((size_t)s * H + h) * n_splits * HD;
-  if (threadIdx.x < 32) {
-    const int lane = threadIdx.x;
-    float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
-    if (lane < n_splits) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(ml + 2 * lane));
-      m0 = v.x;
-      l0 = v.y;
-    }
-    if (lane + 32 < n_splits) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(ml + 2 * (lane + 32)));
-      m1 = v.x;
-      l1 = v.y;
-    }
-    const float M = warp_max(fmaxf(m0, m1));
-    const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M);
-    const float w1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - M);
-    const float inv = 1.0f / warp_sum(w0 * l0 + w1 * l1);
-    w_s[lane] = w0 * inv;
-    w_s[lane + 32] = w1 * inv;
-  }
-  __syncthreads();
-  const int d = threadIdx.x;  // HD threads
-  float o = 0.f;
-  int i = 0;
-  for (; i + 4 <= n_splits; i += 4) {
-    const float v0 = __ldcg(po + (size_t)i * HD + d), v1 = __ldcg(po + (size_t)(i + 1) * HD + d);
-    const float v2 = __ldcg(po + (size_t)(i + 2) * HD + d), v3 = __ldcg(po + (size_t)(i + 3) * HD + d);
-    o += w_s[i] * v0;
-    o += w_s[i + 1] * v1;
-    o += w_s[i + 2] * v2;
-    o += w_s[i + 3] * v3;
-  }
-  for (; i < n_splits; ++i) o += w_s[i] * __ldcg(po + (size_t)i * HD + d);
-  out[(size_t)s * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(o);
-}
-
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = (EncodeTiledFn)p;
-  return fn;
-}
-
 RL_API int rl_attn_decode_tma_head_dim() { return HD; }
 
 // Same arguments as rl_attn_decode (scratch: part_o of n_seqs*H*n_splits*hd floats, part_ml of
@@ -597,19 +537,9 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   if (n_parts < 0 || n_parts > 64 || (n_parts > 0 && (q_parts == nullptr || fuse == 0 || ((uintptr_t)q_parts & 15) || part_stride % 4 || q_stride % 4)))
     RL_REFUSE(14, "attn_decode_tma: %d partial sums need fuse > 0 and 16-byte aligned rows", n_parts);
   if (fuse == 2 && q_stride < (H + 2 * K) * HD) RL_REFUSE(13, "attn_decode_tma: rows of %d hold no key and value behind %d query heads", q_stride, H);
-  EncodeTiledFn enc = encode_tiled();
-  if (!enc) RL_REFUSE(9, "attn_decode_tma: cuTensorMapEncodeTiled is not available");
   CUtensorMap map_k, map_v;
-  for (int which = 0; which < 2; ++which) {
-    cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)PAGE, (cuuint64_t)K, (cuuint64_t)n_pages};
-    cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)PAGE * HD * 2, (cuuint64_t)K * PAGE * HD * 2};
-    cuuint32_t box[4] = {64, PAGE, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_pages : k_pages), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      RL_REFUSE(10, "attn_decode_tma: cannot describe the cache pages to TMA");
-  }
+  if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
+    RL_REFUSE(10, "attn_decode_tma: cannot describe the cache pages to TMA");
   auto kern = attn_decode_tma_kernel;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     RL_REFUSE(11, "attn_decode_tma: cannot get %d bytes of shared memory", SMEM_BYTES);
@@ -621,7 +551,7 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
                             interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride));
   if (counters != nullptr) return 0;
   dim3 grid2(H, n_seqs);
-  RL_LAUNCH_CHECK(rl_launch(attn_decode_tma_merge_kernel, grid2, HD, 0, stream, (const float*)part_o, (const float*)part_ml,
-                            (bf16*)out, out_stride, H, n_splits));
+  RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
+                            (bf16*)out, out_stride, H, HD, n_splits));
   return 0;
 }

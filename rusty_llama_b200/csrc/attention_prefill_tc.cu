@@ -396,21 +396,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = (EncodeTiledFn)p;
-  return fn;
-}
-
 RL_API int rl_flash_prefill_tc_head_dim() { return HD; }
 
 // status: one int in device memory, 0 before the call; afterwards non-zero means that a bounded wait
@@ -428,28 +413,11 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) RL_REFUSE(6, "flash_prefill_tc: operands must be 16-byte aligned");
   if (H > 65535 || n_seqs > 65535) RL_REFUSE(7, "flash_prefill_tc: H=%d or S=%d exceeds 65535", H, n_seqs);
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "flash_prefill_tc: bad window or scale, or no status word");
-  EncodeTiledFn enc = encode_tiled();
-  if (!enc) RL_REFUSE(9, "flash_prefill_tc: cuTensorMapEncodeTiled is not available");
   CUtensorMap map_q, map_k, map_v;
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)q_stride, (cuuint64_t)n_tokens};
-    cuuint64_t strides[1] = {(cuuint64_t)q_stride * 2};
-    cuuint32_t box[2] = {64, BMQ};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
-  }
-  for (int which = 0; which < 2; ++which) {
-    cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)PAGE, (cuuint64_t)K, (cuuint64_t)n_pages};
-    cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)PAGE * HD * 2, (cuuint64_t)K * PAGE * HD * 2};
-    cuuint32_t box[4] = {64, PAGE, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_pages : k_pages), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      RL_REFUSE(11, "flash_prefill_tc: cannot describe the cache pages to TMA");
-  }
+  if (make_matrix_map(&map_q, q, n_tokens, q_stride, q_stride, BMQ))
+    RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
+  if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
+    RL_REFUSE(11, "flash_prefill_tc: cannot describe the cache pages to TMA");
   const size_t smem = SMEM_BYTES;
   auto kern = flash_prefill_tc_kernel;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

@@ -278,35 +278,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = (EncodeTiledFn)p;
-  return fn;
-}
-
-// rows x K bfloat16 matrix with row stride ld (elements); boxes of `box_rows` rows x 64 columns, 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-  EncodeTiledFn enc = encode_tiled();
-  if (!enc) return 1;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 2;
-}
-
 // status: one int in device memory, 0 before the call; non-zero afterwards means a bounded wait expired
 // (1 producer, 2 tensor-core issuer waiting for data, 3 epilogue, 4 tensor-core issuer waiting for the
 // epilogue) and the output is not valid.
@@ -358,7 +329,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   }
   const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) * k_splits;
   CUtensorMap map_x, map_w;
-  int e1 = make_map(&map_x, x, M, K, ldx, BM), e2 = make_map(&map_w, w, N, K, ldw, bn);
+  int e1 = make_matrix_map(&map_x, x, M, K, ldx, BM), e2 = make_matrix_map(&map_w, w, N, K, ldw, bn);
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
   dim3 grid((unsigned)(tiles < n_sms ? tiles : n_sms));

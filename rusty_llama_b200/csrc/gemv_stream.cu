@@ -287,21 +287,6 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = (EncodeTiledFn)p;
-  return fn;
-}
-
 // How the kernel cuts k: k per slice (a multiple of KC, at most MAX_SLICE) and the slices that
 // result from at least k_slices of them.
 static void plan(int K, int k_slices, int* slice_len, int* slices) {
