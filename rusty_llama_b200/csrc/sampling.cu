@@ -6,12 +6,15 @@
 // logits back; here only the chosen token ids leave the device.
 //
 // One block per row.  The nucleus is found without sorting: the probability
-// that closes it is located by a bisection over the bit patterns of positive
-// floats (their integer order is their numeric order), each probe being one
-// masked sum over the row; equal probabilities are taken in index order.
-// Sums are tree sums, so a draw that lands within rounding of a boundary of the
-// cumulative distribution may pick the neighbouring token of the sequential
-// 32-bit sum the reference does.
+// that closes it is located digit by digit in the bit patterns of positive
+// floats (their integer order is their numeric order): four sweeps over the
+// row, each a histogram of probability mass over the next eight bits, instead
+// of one sweep per bit.  The masses are added as 64-bit fixed-point numbers
+// (2^-44), so the histogram's atomic additions give the same sums in whatever
+// order they happen and a row of 128k probabilities is summed more exactly than
+// in 32-bit floats; equal probabilities are taken in index order.  A draw that
+// lands within rounding of a boundary of the cumulative distribution may pick
+// the neighbouring token of the sequential 32-bit sum the reference does.
 #include "common.cuh"
 
 RL_DEFINE_ERROR_TEXT()
@@ -88,6 +91,50 @@ RL_API int rl_argmax(const float* logits, long long row_stride, int n_rows, int 
   RL_LAUNCH_RESULT();
 }
 
+// ---------------------------------------------------------------- sweeps over a row
+// f(value, index) for every element of p[0..n), every thread of the block taking part.  A block that
+// scans a row of 128k values alone is bound by how many loads it has in flight, so an aligned row is
+// read four values per load, four loads ahead.  The order in which a thread meets its elements is not
+// the index order.
+template <typename F>
+__device__ __forceinline__ void sweep(const float* p, int n, F f) {
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    const int n4 = n >> 2;
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    int i = threadIdx.x;
+    for (; i + 3 * (int)blockDim.x < n4; i += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = p4[i + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int base = 4 * (i + u * blockDim.x);
+        f(v[u].x, base);
+        f(v[u].y, base + 1);
+        f(v[u].z, base + 2);
+        f(v[u].w, base + 3);
+      }
+    }
+    for (; i < n4; i += blockDim.x) {
+      const float4 v = p4[i];
+      f(v.x, 4 * i);
+      f(v.y, 4 * i + 1);
+      f(v.z, 4 * i + 2);
+      f(v.w, 4 * i + 3);
+    }
+    for (int j = 4 * n4 + threadIdx.x; j < n; j += blockDim.x) f(p[j], j);
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) f(p[i], i);
+  }
+}
+
+// The part of a row that one warp owns when the row is cut into 32 contiguous parts (index order matters).
+__device__ __forceinline__ void warp_range(int n, int warp, int n_warps, int& begin, int& end) {
+  const int per = (((n + n_warps - 1) / n_warps) + 31) & ~31;  // whole tiles of 32
+  begin = min(n, warp * per);
+  end = min(n, begin + per);
+}
+
 // ---------------------------------------------------------------- sampling
 
 // Sum and count of the probabilities p[i] >= lo (as bit patterns) that also pass `floor_bits`.
@@ -95,110 +142,189 @@ __device__ __forceinline__ void masked_sum(const float* p, int n, uint32_t lo_bi
                                            int& count) {
   float s = 0.f;
   float c = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = p[i];
+  sweep(p, n, [&](float v, int) {
     if (__float_as_uint(v) >= lo_bits) {
       s += v;
       c += 1.f;
     }
-  }
+  });
   sum = block_sum(s, red);
   count = (int)block_sum(c, red);
 }
 
-// Largest bit pattern b in [lo, hi) such that the mass of {p >= b} exceeds `limit`;
-// the caller guarantees that lo qualifies and hi does not.
-__device__ uint32_t bisect_mass(const float* p, int n, uint32_t lo, uint32_t hi, float limit, float* red) {
-  while (hi - lo > 1) {
-    const uint32_t mid = lo + ((hi - lo) >> 1);
-    float s;
-    int c;
-    masked_sum(p, n, mid, red, s, c);
-    if (s > limit) lo = mid; else hi = mid;
+// Fixed-point masses: a probability as a multiple of 2^-44 (the sum of a whole row stays below 2^45).
+#define MASS_ONE 17592186044416.0  // 2^44
+__device__ __forceinline__ unsigned long long to_mass(float v) { return (unsigned long long)((double)v * MASS_ONE + 0.5); }
+__device__ __forceinline__ float from_mass(unsigned long long m) { return (float)((double)m / MASS_ONE); }
+
+#define HIST_COPIES 16   // two warps share a copy of the histogram
+#define HIST_BINS 256
+
+// Among the probabilities whose bit pattern is at least `lo_bits`: the value v* with
+// mass{p > v*} <= limit < mass{p >= v*} (the caller guarantees that their whole mass exceeds `limit`;
+// if rounding says otherwise the smallest of them is returned).  Returns v*'s bit pattern and leaves
+// mass{p > v*} in *mass_gt.  hist: HIST_COPIES * HIST_BINS 64-bit words of shared memory; bins: HIST_BINS more.
+__device__ uint32_t select_mass(const float* p, int n, uint32_t lo_bits, float limit, unsigned long long* hist,
+                                unsigned long long* bins, float* mass_gt) {
+  __shared__ uint32_t sel_prefix;
+  __shared__ unsigned long long sel_above;
+  const unsigned long long limit_m = to_mass(fmaxf(limit, 0.f));
+  uint32_t prefix = 0, prefix_mask = 0;
+  unsigned long long above = 0;  // mass of the candidates above the prefix's range
+  unsigned long long* mine = hist + (threadIdx.x >> 6) * HIST_BINS;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < HIST_COPIES * HIST_BINS; i += blockDim.x) hist[i] = 0ull;
+    __syncthreads();
+    sweep(p, n, [&](float v, int) {
+      const uint32_t key = __float_as_uint(v);
+      if (key >= lo_bits && (key & prefix_mask) == prefix) atomicAdd(&mine[(key >> shift) & (HIST_BINS - 1)], to_mass(v));
+    });
+    __syncthreads();
+    if (threadIdx.x < HIST_BINS) {
+      unsigned long long m = 0;
+#pragma unroll
+      for (int c = 0; c < HIST_COPIES; ++c) m += hist[c * HIST_BINS + threadIdx.x];
+      bins[threadIdx.x] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long acc = above;
+      int chosen = -1, lowest = -1;
+      for (int d = HIST_BINS - 1; d >= 0; --d) {
+        if (bins[d] == 0ull) continue;
+        lowest = d;
+        if (acc + bins[d] > limit_m) {
+          chosen = d;
+          break;
+        }
+        acc += bins[d];
+      }
+      if (chosen < 0) {  // rounding: the candidates' mass does not exceed the limit after all
+        chosen = max(lowest, 0);
+        acc -= lowest >= 0 ? bins[lowest] : 0ull;
+      }
+      sel_prefix = prefix | ((uint32_t)chosen << shift);
+      sel_above = acc;
+    }
+    __syncthreads();
+    prefix = sel_prefix;
+    above = sel_above;
+    prefix_mask |= (uint32_t)(HIST_BINS - 1) << shift;
+    __syncthreads();
   }
-  return lo;
+  *mass_gt = from_mass(above);
+  return prefix;
+}
+
+// How many probabilities have exactly the bit pattern `bits`.
+__device__ int count_equal(const float* p, int n, uint32_t bits, float* red) {
+  float c = 0.f;
+  sweep(p, n, [&](float v, int) { c += (__float_as_uint(v) == bits) ? 1.f : 0.f; });
+  return (int)block_sum(c, red);
 }
 
 // Smallest probability that is >= the pattern `b` (the value that closes the set).
 __device__ float min_at_least(const float* p, int n, uint32_t b, float* red) {
   float m = INFINITY;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = p[i];
+  sweep(p, n, [&](float v, int) {
     if (__float_as_uint(v) >= b) m = fminf(m, v);
-  }
+  });
   return -block_max(-m, red);
 }
 
 // Index of the j-th (from 0) element equal to `v`, in index order; -1 if there are fewer.
+// Each warp counts the matches in its contiguous part of the row (coalesced loads); the warp whose part
+// holds the j-th match then walks it in tiles of 32, a ballot per tile.
 __device__ int kth_equal(const float* p, int n, float v, int j, int* sh_int) {
-  const int per = (n + blockDim.x - 1) / blockDim.x;
-  const int begin = threadIdx.x * per, end = min(n, begin + per);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  int begin, end;
+  warp_range(n, warp, n_warps, begin, end);
   int mine = 0;
-  for (int i = begin; i < end; ++i) mine += (p[i] == v);
+  for (int i = begin + lane; i < end; i += 32) mine += (p[i] == v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
   __syncthreads();
-  sh_int[threadIdx.x] = mine;
+  if (lane == 0) sh_int[warp] = mine;
+  if (threadIdx.x == 0) sh_int[n_warps + 2] = -1;
   __syncthreads();
-  // the thread whose range holds the j-th match finds it; a serial prefix over 1024 counts is cheap
   if (threadIdx.x == 0) {
     int before = 0, owner = -1;
-    for (int t = 0; t < (int)blockDim.x; ++t) {
-      if (j < before + sh_int[t]) { owner = t; break; }
-      before += sh_int[t];
+    for (int w = 0; w < n_warps; ++w) {
+      if (j < before + sh_int[w]) { owner = w; break; }
+      before += sh_int[w];
     }
-    sh_int[blockDim.x] = owner;
-    sh_int[blockDim.x + 1] = before;
+    sh_int[n_warps] = owner;
+    sh_int[n_warps + 1] = before;
   }
   __syncthreads();
-  const int owner = sh_int[blockDim.x], before = sh_int[blockDim.x + 1];
-  __syncthreads();
-  if (owner < 0) return -1;
-  if ((int)threadIdx.x == owner) {
-    int seen = before, found = -1;
-    for (int i = begin; i < end; ++i)
-      if (p[i] == v) {
-        if (seen == j) { found = i; break; }
-        ++seen;
+  const int owner = sh_int[n_warps];
+  if (warp == owner) {
+    int seen = sh_int[n_warps + 1];
+    for (int base = begin; base < end; base += 32) {
+      const int i = base + lane;
+      const unsigned hits = __ballot_sync(0xffffffffu, i < end && p[i] == v);
+      const int c = __popc(hits);
+      if (j < seen + c) {
+        // the (j - seen)-th set bit of hits
+        unsigned h = hits;
+        for (int k = 0; k < j - seen; ++k) h &= h - 1;
+        if (lane == 0) sh_int[n_warps + 2] = base + __ffs(h) - 1;
+        break;
       }
-    sh_int[blockDim.x + 2] = found;
+      seen += c;
+    }
   }
   __syncthreads();
-  const int found = sh_int[blockDim.x + 2];
+  const int found = sh_int[n_warps + 2];
   __syncthreads();
   return found;
 }
 
 // First index, in index order, whose running sum of p exceeds `target`; n-1 if none.
+// The same two levels: sums of the warps' parts, then the owning warp walks its part in tiles of 32
+// with a prefix sum by shuffles.
 __device__ int first_cdf_above(const float* p, int n, float target, float* sh_f, int* sh_int) {
-  const int per = (n + blockDim.x - 1) / blockDim.x;
-  const int begin = threadIdx.x * per, end = min(n, begin + per);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  int begin, end;
+  warp_range(n, warp, n_warps, begin, end);
   float mine = 0.f;
-  for (int i = begin; i < end; ++i) mine += p[i];
+  for (int i = begin + lane; i < end; i += 32) mine += p[i];
+  mine = warp_sum(mine);
   __syncthreads();
-  sh_f[threadIdx.x] = mine;
+  if (lane == 0) sh_f[warp] = mine;
   __syncthreads();
   if (threadIdx.x == 0) {
     float before = 0.f;
     int owner = -1;
-    for (int t = 0; t < (int)blockDim.x; ++t) {
-      if (target < before + sh_f[t]) { owner = t; break; }
-      before += sh_f[t];
+    for (int w = 0; w < n_warps; ++w) {
+      if (target < before + sh_f[w]) { owner = w; break; }
+      before += sh_f[w];
     }
     sh_int[0] = owner;
-    sh_f[blockDim.x] = before;
+    sh_int[1] = n - 1;
+    sh_f[n_warps] = before;
   }
   __syncthreads();
   const int owner = sh_int[0];
-  const float before = sh_f[blockDim.x];
-  __syncthreads();
-  if (owner < 0) return n - 1;
-  if ((int)threadIdx.x == owner) {
-    float cdf = before;
-    int found = end - 1;
-    for (int i = begin; i < end; ++i) {
-      cdf += p[i];
-      if (target < cdf) { found = i; break; }
+  if (warp == owner) {
+    float before = sh_f[n_warps];
+    int found = end - 1;  // rounding may leave the target just above the part's own sum
+    for (int base = begin; base < end; base += 32) {
+      const int i = base + lane;
+      float x = i < end ? p[i] : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {  // inclusive prefix sum over the tile
+        const float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      const unsigned over = __ballot_sync(0xffffffffu, i < end && target < before + x);
+      if (over) {
+        found = base + __ffs(over) - 1;
+        break;
+      }
+      before += __shfl_sync(0xffffffffu, x, 31);
     }
-    sh_int[1] = found;
+    if (lane == 0) sh_int[1] = found;
   }
   __syncthreads();
   const int found = sh_int[1];
@@ -215,6 +341,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
   __shared__ float sh_f[SAMPLE_THREADS + 1];
   __shared__ int sh_int[SAMPLE_THREADS + 3];
   __shared__ float coin_s;
+  __shared__ unsigned long long hist[HIST_COPIES * HIST_BINS];
+  __shared__ unsigned long long hist_bins[HIST_BINS];
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   float* p = probs + (size_t)r * n;
@@ -232,17 +360,18 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
   }
 
   // softmax of logits / t (src/sampler.rs:58-73, :101-106)
-  float mx = -INFINITY;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, row[i] / temperature);
-  mx = block_max(mx, red);
+  float mx = -INFINITY;  // the largest logit / t is the largest logit, divided (t > 0): one division, not n
+  sweep(row, n, [&](float v, int) { mx = fmaxf(mx, v); });
+  mx = block_max(mx, red) / temperature;
   float part = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float e = expf(row[i] / temperature - mx);
+  sweep(row, n, [&](float v, int i) {
+    const float e = expf(v / temperature - mx);
     p[i] = e;
     part += e;
-  }
+  });
   const float inv = 1.0f / block_sum(part, red);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] *= inv;
+  __syncthreads();
+  sweep(p, n, [&](float v, int i) { p[i] = v * inv; });
   __syncthreads();
   const float coin = coin_s;
 
@@ -259,10 +388,6 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
     if (kept == 0) {
       chosen = block_argmax(row, n, temperature, sh_arg);  // (src/sampler.rs:135-144)
     } else {
-      float pmax = 0.f;
-      for (int i = threadIdx.x; i < n; i += blockDim.x) pmax = fmaxf(pmax, p[i]);
-      pmax = block_max(pmax, red);
-      const uint32_t top_bits = __float_as_uint(pmax) + 1u;
       // the value that closes the nucleus, the mass above it, and how many of its equals are in
       float v_min, mass_gt;
       int ties_in;
@@ -273,12 +398,9 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
         masked_sum(p, n, __float_as_uint(v_min) + 1u, red, mass_gt, c_gt);
         ties_in = c_ge - c_gt;
       } else {
-        const uint32_t b = bisect_mass(p, n, cutoff_bits, top_bits, top_p, red);
-        v_min = min_at_least(p, n, b, red);
-        float s_ge; int c_ge, c_gt;
-        masked_sum(p, n, __float_as_uint(v_min), red, s_ge, c_ge);
-        masked_sum(p, n, __float_as_uint(v_min) + 1u, red, mass_gt, c_gt);
-        const int ties = c_ge - c_gt;
+        const uint32_t v_bits = select_mass(p, n, cutoff_bits, top_p, hist, hist_bins, &mass_gt);
+        v_min = __uint_as_float(v_bits);
+        const int ties = count_equal(p, n, v_bits, red);
         int need = (int)floorf((top_p - mass_gt) / v_min) + 1;  // smallest count whose sum exceeds top_p
         ties_in = min(max(need, 1), ties);
       }
@@ -291,13 +413,12 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
         chosen = kth_equal(p, n, v_min, j, sh_int);
       } else {
         // largest value whose "at least" mass exceeds the target, within the part above v_min
-        const uint32_t b = bisect_mass(p, n, __float_as_uint(v_min) + 1u, top_bits, target, red);
-        const float v_sel = min_at_least(p, n, b, red);
-        float s_ge, s_gt; int c_ge, c_gt;
-        masked_sum(p, n, __float_as_uint(v_sel), red, s_ge, c_ge);
-        masked_sum(p, n, __float_as_uint(v_sel) + 1u, red, s_gt, c_gt);
+        float s_gt;
+        const uint32_t sel_bits = select_mass(p, n, __float_as_uint(v_min) + 1u, target, hist, hist_bins, &s_gt);
+        const float v_sel = __uint_as_float(sel_bits);
+        const int equals = count_equal(p, n, sel_bits, red);
         int j = (int)floorf((target - s_gt) / v_sel);
-        j = min(max(j, 0), c_ge - c_gt - 1);
+        j = min(max(j, 0), equals - 1);
         chosen = kth_equal(p, n, v_sel, j, sh_int);
       }
       if (chosen < 0) chosen = block_argmax(row, n, temperature, sh_arg);
