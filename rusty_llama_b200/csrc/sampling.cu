@@ -5,7 +5,10 @@
 // is kept per sequence.  The reference samples on the host after copying the
 // logits back; here only the chosen token ids leave the device.
 //
-// One block per row.  The nucleus is found without sorting: the probability
+// A row is shared by a team of blocks (a thread-block cluster of up to 8, each on an SM of its own,
+// each sweeping its part of the row; sums, histograms and counts meet through distributed shared
+// memory): one block alone took 0.29 ms for a row of 128k, a quarter of it per sweep waiting on its
+// own loads.  The nucleus is found without sorting: the probability
 // that closes it is located digit by digit in the bit patterns of positive
 // floats (their integer order is their numeric order): four sweeps over the
 // row, each a histogram of probability mass over the next eight bits, instead
@@ -15,7 +18,11 @@
 // in 32-bit floats; equal probabilities are taken in index order.  A draw that
 // lands within rounding of a boundary of the cumulative distribution may pick
 // the neighbouring token of the sequential 32-bit sum the reference does.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 RL_DEFINE_ERROR_TEXT()
 
@@ -91,24 +98,26 @@ RL_API int rl_argmax(const float* logits, long long row_stride, int n_rows, int 
   RL_LAUNCH_RESULT();
 }
 
-// ---------------------------------------------------------------- sweeps over a row
-// f(value, index) for every element of p[0..n), every thread of the block taking part.  A block that
-// scans a row of 128k values alone is bound by how many loads it has in flight, so an aligned row is
-// read four values per load, four loads ahead.  The order in which a thread meets its elements is not
-// the index order.
+// ---------------------------------------------------------------- sweeps over a part of a row
+// f(value, index) for every element of p[begin..end), every thread of the block taking part.  A block
+// that scans its part alone is bound by how many loads it has in flight, so an aligned part is read
+// four values per load, four loads ahead.  The order in which a thread meets its elements is not the
+// index order.
 template <typename F>
-__device__ __forceinline__ void sweep(const float* p, int n, F f) {
-  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+__device__ __forceinline__ void sweep(const float* p, int begin, int end, F f) {
+  const float* q = p + begin;
+  const int n = end - begin;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) == 0) {
     const int n4 = n >> 2;
-    const float4* p4 = reinterpret_cast<const float4*>(p);
+    const float4* q4 = reinterpret_cast<const float4*>(q);
     int i = threadIdx.x;
     for (; i + 3 * (int)blockDim.x < n4; i += 4 * blockDim.x) {
       float4 v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = p4[i + u * blockDim.x];
+      for (int u = 0; u < 4; ++u) v[u] = q4[i + u * blockDim.x];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int base = 4 * (i + u * blockDim.x);
+        const int base = begin + 4 * (i + u * blockDim.x);
         f(v[u].x, base);
         f(v[u].y, base + 1);
         f(v[u].z, base + 2);
@@ -116,40 +125,94 @@ __device__ __forceinline__ void sweep(const float* p, int n, F f) {
       }
     }
     for (; i < n4; i += blockDim.x) {
-      const float4 v = p4[i];
-      f(v.x, 4 * i);
-      f(v.y, 4 * i + 1);
-      f(v.z, 4 * i + 2);
-      f(v.w, 4 * i + 3);
+      const float4 v = q4[i];
+      const int base = begin + 4 * i;
+      f(v.x, base);
+      f(v.y, base + 1);
+      f(v.z, base + 2);
+      f(v.w, base + 3);
     }
-    for (int j = 4 * n4 + threadIdx.x; j < n; j += blockDim.x) f(p[j], j);
+    for (int j = 4 * n4 + threadIdx.x; j < n; j += blockDim.x) f(q[j], begin + j);
   } else {
-    for (int i = threadIdx.x; i < n; i += blockDim.x) f(p[i], i);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) f(q[i], begin + i);
   }
 }
 
-// The part of a row that one warp owns when the row is cut into 32 contiguous parts (index order matters).
-__device__ __forceinline__ void warp_range(int n, int warp, int n_warps, int& begin, int& end) {
-  const int per = (((n + n_warps - 1) / n_warps) + 31) & ~31;  // whole tiles of 32
-  begin = min(n, warp * per);
-  end = min(n, begin + per);
-}
+// ---------------------------------------------------------------- the team of blocks that shares a row
+#define TEAM_MAX 8
+#define HIST_COPIES 16   // two warps share a copy of the histogram
+#define HIST_BINS 256
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+static_assert(SAMPLE_WARPS == 32, "the warps' totals are scanned by one warp, a lane each");
+
+// What the blocks of a team leave for one another in their own shared memory.  Everything that is
+// exchanged has two places used in turn, so that one cluster barrier per exchange is enough: a block can
+// only write a place for the second time after a later barrier, which every reader of the first round
+// has reached.
+struct Exchange {
+  float f[2][4];
+  int i[2][4];
+  unsigned long long bins[2][HIST_BINS];
+};
+
+struct Team {
+  cg::cluster_group cluster;
+  int rank, size;
+  int begin, end;   // this block's part of the row, in index order by rank
+  Exchange* x;      // this block's own
+  int turn;
+  float* red;       // 32 floats for block-wide reductions
+
+  __device__ __forceinline__ const Exchange* of(int r) const { return cluster.map_shared_rank(x, r); }
+
+  // sums of a and b over the whole row (every block gets the same values: added in rank order)
+  __device__ void sum2(float a, float b, float& A, float& B) {
+    a = block_sum(a, red);
+    b = block_sum(b, red);
+    if (threadIdx.x == 0) {
+      x->f[turn][0] = a;
+      x->f[turn][1] = b;
+    }
+    cluster.sync();
+    A = 0.f;
+    B = 0.f;
+    for (int r = 0; r < size; ++r) {
+      A += of(r)->f[turn][0];
+      B += of(r)->f[turn][1];
+    }
+    turn ^= 1;
+  }
+  __device__ float sum(float a) {
+    float A, B;
+    sum2(a, 0.f, A, B);
+    return A;
+  }
+  __device__ float maximum(float a) {
+    a = block_max(a, red);
+    if (threadIdx.x == 0) x->f[turn][0] = a;
+    cluster.sync();
+    float A = -INFINITY;
+    for (int r = 0; r < size; ++r) A = fmaxf(A, of(r)->f[turn][0]);
+    turn ^= 1;
+    return A;
+  }
+};
 
 // ---------------------------------------------------------------- sampling
 
-// Sum and count of the probabilities p[i] >= lo (as bit patterns) that also pass `floor_bits`.
-__device__ __forceinline__ void masked_sum(const float* p, int n, uint32_t lo_bits, float* red, float& sum,
-                                           int& count) {
+// Sum and count of the probabilities whose bit pattern is at least `lo_bits`.
+__device__ __forceinline__ void masked_sum(Team& tm, const float* p, uint32_t lo_bits, float& sum, int& count) {
   float s = 0.f;
   float c = 0.f;
-  sweep(p, n, [&](float v, int) {
+  sweep(p, tm.begin, tm.end, [&](float v, int) {
     if (__float_as_uint(v) >= lo_bits) {
       s += v;
       c += 1.f;
     }
   });
-  sum = block_sum(s, red);
-  count = (int)block_sum(c, red);
+  float C;
+  tm.sum2(s, c, sum, C);
+  count = (int)C;
 }
 
 // Fixed-point masses: a probability as a multiple of 2^-44 (the sum of a whole row stays below 2^45).
@@ -157,15 +220,13 @@ __device__ __forceinline__ void masked_sum(const float* p, int n, uint32_t lo_bi
 __device__ __forceinline__ unsigned long long to_mass(float v) { return (unsigned long long)((double)v * MASS_ONE + 0.5); }
 __device__ __forceinline__ float from_mass(unsigned long long m) { return (float)((double)m / MASS_ONE); }
 
-#define HIST_COPIES 16   // two warps share a copy of the histogram
-#define HIST_BINS 256
-
 // Among the probabilities whose bit pattern is at least `lo_bits`: the value v* with
 // mass{p > v*} <= limit < mass{p >= v*} (the caller guarantees that their whole mass exceeds `limit`;
 // if rounding says otherwise the smallest of them is returned).  Returns v*'s bit pattern and leaves
-// mass{p > v*} in *mass_gt.  hist: HIST_COPIES * HIST_BINS 64-bit words of shared memory; bins: HIST_BINS more.
-__device__ uint32_t select_mass(const float* p, int n, uint32_t lo_bits, float limit, unsigned long long* hist,
-                                unsigned long long* bins, float* mass_gt) {
+// mass{p > v*} in *mass_gt.  hist: HIST_COPIES * HIST_BINS 64-bit words of shared memory.
+// Every block of the team walks the same bins in the same order and so takes the same decisions.
+__device__ uint32_t select_mass(Team& tm, const float* p, uint32_t lo_bits, float limit, unsigned long long* hist,
+                                unsigned long long* total_bins, float* mass_gt) {
   __shared__ uint32_t sel_prefix;
   __shared__ unsigned long long sel_above;
   const unsigned long long limit_m = to_mass(fmaxf(limit, 0.f));
@@ -175,7 +236,7 @@ __device__ uint32_t select_mass(const float* p, int n, uint32_t lo_bits, float l
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < HIST_COPIES * HIST_BINS; i += blockDim.x) hist[i] = 0ull;
     __syncthreads();
-    sweep(p, n, [&](float v, int) {
+    sweep(p, tm.begin, tm.end, [&](float v, int) {
       const uint32_t key = __float_as_uint(v);
       if (key >= lo_bits && (key & prefix_mask) == prefix) atomicAdd(&mine[(key >> shift) & (HIST_BINS - 1)], to_mass(v));
     });
@@ -184,27 +245,63 @@ __device__ uint32_t select_mass(const float* p, int n, uint32_t lo_bits, float l
       unsigned long long m = 0;
 #pragma unroll
       for (int c = 0; c < HIST_COPIES; ++c) m += hist[c * HIST_BINS + threadIdx.x];
-      bins[threadIdx.x] = m;
+      tm.x->bins[tm.turn][threadIdx.x] = m;
     }
+    tm.cluster.sync();
+    if (threadIdx.x < HIST_BINS) {
+      unsigned long long m = 0;
+      for (int r = 0; r < tm.size; ++r) m += tm.of(r)->bins[tm.turn][threadIdx.x];
+      total_bins[threadIdx.x] = m;
+    }
+    tm.turn ^= 1;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long acc = above;
-      int chosen = -1, lowest = -1;
-      for (int d = HIST_BINS - 1; d >= 0; --d) {
-        if (bins[d] == 0ull) continue;
-        lowest = d;
-        if (acc + bins[d] > limit_m) {
-          chosen = d;
-          break;
+    if (threadIdx.x < 32) {
+      // warp 0 walks the bins from the top: lane l owns bins 8l .. 8l+7; the masses above a lane's bins
+      // come from a suffix sum over the lanes, then each lane walks its own eight
+      const int lane = threadIdx.x;
+      unsigned long long own[8], lane_total = 0;
+      unsigned nonzero = 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        own[e] = total_bins[8 * lane + e];
+        lane_total += own[e];
+        nonzero |= (own[e] != 0ull) << e;
+      }
+      unsigned long long higher = lane_total;  // inclusive suffix sum over lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long y = __shfl_down_sync(0xffffffffu, higher, o);
+        if (lane + o < 32) higher += y;
+      }
+      unsigned long long acc = above + higher - lane_total;
+      int hit = -1;
+      unsigned long long acc_hit = 0;
+#pragma unroll
+      for (int e = 7; e >= 0; --e) {
+        if (hit < 0 && own[e] != 0ull && acc + own[e] > limit_m) {
+          hit = e;
+          acc_hit = acc;
         }
-        acc += bins[d];
+        acc += own[e];
       }
-      if (chosen < 0) {  // rounding: the candidates' mass does not exceed the limit after all
-        chosen = max(lowest, 0);
-        acc -= lowest >= 0 ? bins[lowest] : 0ull;
+      const unsigned hits = __ballot_sync(0xffffffffu, hit >= 0);
+      const unsigned filled = __ballot_sync(0xffffffffu, nonzero != 0u);
+      if (hits) {
+        if (lane == 31 - __clz(hits)) {  // the highest lane with a hit holds the first bin from the top
+          sel_prefix = prefix | ((uint32_t)(8 * lane + hit) << shift);
+          sel_above = acc_hit;
+        }
+      } else if (filled) {  // rounding: the candidates' mass does not exceed the limit after all
+        if (lane == __ffs(filled) - 1) {
+          const int e = __ffs(nonzero) - 1;  // the lowest bin that holds anything
+          // (the bins below e in this lane and all lower lanes are empty, so `higher` is all the mass)
+          sel_prefix = prefix | ((uint32_t)(8 * lane + e) << shift);
+          sel_above = above + higher - own[e];
+        }
+      } else if (lane == 0) {
+        sel_prefix = prefix;
+        sel_above = above;
       }
-      sel_prefix = prefix | ((uint32_t)chosen << shift);
-      sel_above = acc;
     }
     __syncthreads();
     prefix = sel_prefix;
@@ -217,138 +314,220 @@ __device__ uint32_t select_mass(const float* p, int n, uint32_t lo_bits, float l
 }
 
 // How many probabilities have exactly the bit pattern `bits`.
-__device__ int count_equal(const float* p, int n, uint32_t bits, float* red) {
+__device__ int count_equal(Team& tm, const float* p, uint32_t bits) {
   float c = 0.f;
-  sweep(p, n, [&](float v, int) { c += (__float_as_uint(v) == bits) ? 1.f : 0.f; });
-  return (int)block_sum(c, red);
+  sweep(p, tm.begin, tm.end, [&](float v, int) { c += (__float_as_uint(v) == bits) ? 1.f : 0.f; });
+  return (int)tm.sum(c);
 }
 
-// Smallest probability that is >= the pattern `b` (the value that closes the set).
-__device__ float min_at_least(const float* p, int n, uint32_t b, float* red) {
+// Smallest probability whose bit pattern is at least `b` (the value that closes the set).
+__device__ float min_at_least(Team& tm, const float* p, uint32_t b) {
   float m = INFINITY;
-  sweep(p, n, [&](float v, int) {
+  sweep(p, tm.begin, tm.end, [&](float v, int) {
     if (__float_as_uint(v) >= b) m = fminf(m, v);
   });
-  return -block_max(-m, red);
+  return -tm.maximum(-m);
 }
 
-// Index of the j-th (from 0) element equal to `v`, in index order; -1 if there are fewer.
-// Each warp counts the matches in its contiguous part of the row (coalesced loads); the warp whose part
-// holds the j-th match then walks it in tiles of 32, a ballot per tile.
-__device__ int kth_equal(const float* p, int n, float v, int j, int* sh_int) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+// The part of a block's part that one of its warps owns (contiguous, whole tiles of 32: index order matters).
+__device__ __forceinline__ void warp_range(const Team& tm, int warp, int& begin, int& end) {
+  const int n = tm.end - tm.begin;
+  const int per = (((n + SAMPLE_WARPS - 1) / SAMPLE_WARPS) + 31) & ~31;
+  begin = tm.begin + min(n, warp * per);
+  end = min(tm.end, begin + per);
+}
+
+// Index of the j-th (from 0) element equal to `v`, in index order; -1 if there are fewer.  With
+// `clamp`, j is first brought into 0 .. (number of equals - 1).
+// Every warp of every block counts the matches in its contiguous part (coalesced loads).  The counts are
+// added up in index order on two levels, the warps of a block by a scan in its first warp and the blocks
+// by a scan that every warp makes for itself from the exchanged totals; the warp whose part holds the
+// j-th match walks it in tiles of 32, a ballot per tile, and the whole team reads the answer from that block.
+__device__ int kth_equal(Team& tm, const float* p, float v, int j, bool clamp) {
+  __shared__ int found_s;
+  __shared__ int warp_incl[SAMPLE_WARPS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int begin, end;
-  warp_range(n, warp, n_warps, begin, end);
+  warp_range(tm, warp, begin, end);
   int mine = 0;
   for (int i = begin + lane; i < end; i += 32) mine += (p[i] == v);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if (lane == 0) warp_incl[warp] = mine;
+  if (threadIdx.x == 0) found_s = -1;
   __syncthreads();
-  if (lane == 0) sh_int[warp] = mine;
-  if (threadIdx.x == 0) sh_int[n_warps + 2] = -1;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int before = 0, owner = -1;
-    for (int w = 0; w < n_warps; ++w) {
-      if (j < before + sh_int[w]) { owner = w; break; }
-      before += sh_int[w];
+  if (warp == 0) {
+    int x = warp_incl[lane];  // SAMPLE_WARPS == 32
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
     }
-    sh_int[n_warps] = owner;
-    sh_int[n_warps + 1] = before;
+    warp_incl[lane] = x;
+    if (lane == 31) tm.x->i[tm.turn][1] = x;
   }
-  __syncthreads();
-  const int owner = sh_int[n_warps];
-  if (warp == owner) {
-    int seen = sh_int[n_warps + 1];
-    for (int base = begin; base < end; base += 32) {
-      const int i = base + lane;
-      const unsigned hits = __ballot_sync(0xffffffffu, i < end && p[i] == v);
-      const int c = __popc(hits);
-      if (j < seen + c) {
-        // the (j - seen)-th set bit of hits
-        unsigned h = hits;
-        for (int k = 0; k < j - seen; ++k) h &= h - 1;
-        if (lane == 0) sh_int[n_warps + 2] = base + __ffs(h) - 1;
-        break;
+  tm.cluster.sync();
+  const int tot = lane < tm.size ? tm.of(lane)->i[tm.turn][1] : 0;
+  int incl = tot;
+#pragma unroll
+  for (int o = 1; o < TEAM_MAX; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  const int total = __shfl_sync(0xffffffffu, incl, tm.size - 1);
+  if (clamp) j = min(max(j, 0), total - 1);
+  const unsigned hit = __ballot_sync(0xffffffffu, lane < tm.size && j >= incl - tot && j < incl);
+  const int owner_rank = hit ? __ffs(hit) - 1 : -1;
+  if (owner_rank == tm.rank) {
+    const int jj = j - __shfl_sync(0xffffffffu, incl - tot, owner_rank);
+    int seen = warp ? warp_incl[warp - 1] : 0;
+    if (jj >= seen && jj < warp_incl[warp]) {
+      for (int base = begin; base < end; base += 32) {
+        const int i = base + lane;
+        const unsigned hits = __ballot_sync(0xffffffffu, i < end && p[i] == v);
+        const int c = __popc(hits);
+        if (jj < seen + c) {
+          unsigned h = hits;
+          for (int k = 0; k < jj - seen; ++k) h &= h - 1;  // drop the matches before the wanted one
+          if (lane == 0) found_s = base + __ffs(h) - 1;
+          break;
+        }
+        seen += c;
       }
-      seen += c;
     }
   }
   __syncthreads();
-  const int found = sh_int[n_warps + 2];
-  __syncthreads();
+  if (threadIdx.x == 0) tm.x->i[tm.turn][0] = found_s;
+  tm.cluster.sync();
+  const int found = owner_rank < 0 ? -1 : tm.of(owner_rank)->i[tm.turn][0];
+  tm.turn ^= 1;
   return found;
 }
 
 // First index, in index order, whose running sum of p exceeds `target`; n-1 if none.
-// The same two levels: sums of the warps' parts, then the owning warp walks its part in tiles of 32
+// The same two levels with sums in the place of counts; the owning warp walks its part in tiles of 32
 // with a prefix sum by shuffles.
-__device__ int first_cdf_above(const float* p, int n, float target, float* sh_f, int* sh_int) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+__device__ int first_cdf_above(Team& tm, const float* p, int n, float target) {
+  __shared__ int found_s;
+  __shared__ float warp_incl[SAMPLE_WARPS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int begin, end;
-  warp_range(n, warp, n_warps, begin, end);
+  warp_range(tm, warp, begin, end);
   float mine = 0.f;
   for (int i = begin + lane; i < end; i += 32) mine += p[i];
   mine = warp_sum(mine);
+  if (lane == 0) warp_incl[warp] = mine;
+  if (threadIdx.x == 0) found_s = n - 1;
   __syncthreads();
-  if (lane == 0) sh_f[warp] = mine;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float before = 0.f;
-    int owner = -1;
-    for (int w = 0; w < n_warps; ++w) {
-      if (target < before + sh_f[w]) { owner = w; break; }
-      before += sh_f[w];
-    }
-    sh_int[0] = owner;
-    sh_int[1] = n - 1;
-    sh_f[n_warps] = before;
-  }
-  __syncthreads();
-  const int owner = sh_int[0];
-  if (warp == owner) {
-    float before = sh_f[n_warps];
-    int found = end - 1;  // rounding may leave the target just above the part's own sum
-    for (int base = begin; base < end; base += 32) {
-      const int i = base + lane;
-      float x = i < end ? p[i] : 0.f;
+  if (warp == 0) {
+    float x = warp_incl[lane];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {  // inclusive prefix sum over the tile
-        const float y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x += y;
-      }
-      const unsigned over = __ballot_sync(0xffffffffu, i < end && target < before + x);
-      if (over) {
-        found = base + __ffs(over) - 1;
-        break;
-      }
-      before += __shfl_sync(0xffffffffu, x, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
     }
-    if (lane == 0) sh_int[1] = found;
+    warp_incl[lane] = x;
+    if (lane == 31) tm.x->f[tm.turn][1] = x;
+  }
+  tm.cluster.sync();
+  const float tot = lane < tm.size ? tm.of(lane)->f[tm.turn][1] : 0.f;
+  float incl = tot;
+#pragma unroll
+  for (int o = 1; o < TEAM_MAX; o <<= 1) {
+    const float y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  const float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+  const unsigned hit = __ballot_sync(0xffffffffu, lane < tm.size && target < incl);
+  const int owner_rank = hit ? __ffs(hit) - 1 : -1;
+  if (owner_rank == tm.rank) {
+    const float before_rank = owner_rank ? __shfl_sync(0xffffffffu, excl, owner_rank) : 0.f;
+    // the first warp whose running sum passes the target (rounding may leave it just above the block's
+    // own sum: then the last warp, and the last index of its part)
+    const unsigned whit = __ballot_sync(0xffffffffu, target < before_rank + warp_incl[lane]);
+    const int owner_warp = whit ? __ffs(whit) - 1 : SAMPLE_WARPS - 1;
+    if (warp == owner_warp) {
+      float before = before_rank + (warp ? warp_incl[warp - 1] : 0.f);
+      int found = max(end - 1, 0);
+      for (int base = begin; base < end; base += 32) {
+        const int i = base + lane;
+        float x = i < end ? p[i] : 0.f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {  // inclusive prefix sum over the tile
+          const float y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        const unsigned over = __ballot_sync(0xffffffffu, i < end && target < before + x);
+        if (over) {
+          found = base + __ffs(over) - 1;
+          break;
+        }
+        before += __shfl_sync(0xffffffffu, x, 31);
+      }
+      if (lane == 0) found_s = found;
+    }
   }
   __syncthreads();
-  const int found = sh_int[1];
-  __syncthreads();
+  if (threadIdx.x == 0) tm.x->i[tm.turn][0] = found_s;
+  tm.cluster.sync();
+  const int found = owner_rank < 0 ? n - 1 : tm.of(owner_rank)->i[tm.turn][0];
+  tm.turn ^= 1;
   return found;
 }
 
+// The argmax of logits / t over the whole row, last of equal maxima.
+__device__ int team_argmax(Team& tm, const float* row, float t, ArgMax* sh) {
+  ArgMax best = {-INFINITY, -1};
+  sweep(row, tm.begin, tm.end, [&](float v, int i) { best = better(best, ArgMax{v / t, i}); });
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other;
+    other.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+    other.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+    best = better(best, other);
+  }
+  __syncthreads();
+  if (lane == 0) sh[warp] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ArgMax r = sh[0];
+    for (int w = 1; w < SAMPLE_WARPS; ++w) r = better(r, sh[w]);
+    tm.x->f[tm.turn][0] = r.v;
+    tm.x->i[tm.turn][0] = r.i;
+  }
+  tm.cluster.sync();
+  ArgMax all = {-INFINITY, -1};
+  for (int r = 0; r < tm.size; ++r) all = better(all, ArgMax{tm.of(r)->f[tm.turn][0], tm.of(r)->i[tm.turn][0]});
+  tm.turn ^= 1;
+  return all.i;
+}
+
+// grid: (team size, rows), clusters of (team size, 1, 1)
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int n, float temperature, float top_p,
               unsigned long long* __restrict__ rng_states, const int* __restrict__ rng_index,
               float* __restrict__ probs, int* __restrict__ out) {
   __shared__ float red[32];
   __shared__ ArgMax sh_arg[32];
-  __shared__ float sh_f[SAMPLE_THREADS + 1];
-  __shared__ int sh_int[SAMPLE_THREADS + 3];
-  __shared__ float coin_s;
+  __shared__ Exchange exchange;
   __shared__ unsigned long long hist[HIST_COPIES * HIST_BINS];
-  __shared__ unsigned long long hist_bins[HIST_BINS];
-  const int r = blockIdx.x;
+  __shared__ unsigned long long total_bins[HIST_BINS];
+  Team tm = {cg::this_cluster(), 0, 0, 0, 0, &exchange, 0, red};
+  tm.rank = (int)tm.cluster.block_rank();
+  tm.size = (int)tm.cluster.num_blocks();
+  {
+    const int per = (((n + tm.size - 1) / tm.size) + 3) & ~3;  // parts that keep the row's 16-byte alignment
+    tm.begin = min(n, tm.rank * per);
+    tm.end = min(n, tm.begin + per);
+  }
+  const int r = blockIdx.y;
   const float* row = logits + (size_t)r * row_stride;
   float* p = probs + (size_t)r * n;
 
-  // one draw per sampled token (src/sampler.rs:176-187)
-  if (threadIdx.x == 0) {
+  // one draw per sampled token (src/sampler.rs:176-187): the first block draws, the others read it after
+  // the first exchange below
+  if (tm.rank == 0 && threadIdx.x == 0) {
     unsigned long long* st = rng_states + rng_index[r];
     unsigned long long s = *st;
     s ^= s >> 12;
@@ -356,51 +535,51 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
     s ^= s >> 27;
     *st = s;
     const uint32_t u = (uint32_t)((s * 0x2545F4914F6CDD1DULL) >> 32);
-    coin_s = (float)(u >> 8) / 16777216.0f;
+    exchange.f[0][3] = (float)(u >> 8) / 16777216.0f;
   }
 
   // softmax of logits / t (src/sampler.rs:58-73, :101-106)
   float mx = -INFINITY;  // the largest logit / t is the largest logit, divided (t > 0): one division, not n
-  sweep(row, n, [&](float v, int) { mx = fmaxf(mx, v); });
-  mx = block_max(mx, red) / temperature;
+  sweep(row, tm.begin, tm.end, [&](float v, int) { mx = fmaxf(mx, v); });
+  mx = tm.maximum(mx) / temperature;  // (turn 0: the coin lies in the same place of the first block)
+  const float coin = tm.of(0)->f[0][3];
   float part = 0.f;
-  sweep(row, n, [&](float v, int i) {
+  sweep(row, tm.begin, tm.end, [&](float v, int i) {
     const float e = expf(v / temperature - mx);
     p[i] = e;
     part += e;
   });
-  const float inv = 1.0f / block_sum(part, red);
+  const float inv = 1.0f / tm.sum(part);
   __syncthreads();
-  sweep(p, n, [&](float v, int i) { p[i] = v * inv; });
+  sweep(p, tm.begin, tm.end, [&](float v, int i) { p[i] = v * inv; });
   __syncthreads();
-  const float coin = coin_s;
 
   int chosen;
   if (!(top_p > 0.f && top_p < 1.f)) {
-    chosen = first_cdf_above(p, n, coin, sh_f, sh_int);
+    chosen = first_cdf_above(tm, p, n, coin);
   } else {
     // candidates must reach (1 - top_p) / (n - 1) (src/sampler.rs:127-134)
     const float cutoff = (1.0f - top_p) / (float)max(n - 1, 1);
     const uint32_t cutoff_bits = __float_as_uint(cutoff);
     float kept_mass;
     int kept;
-    masked_sum(p, n, cutoff_bits, red, kept_mass, kept);
+    masked_sum(tm, p, cutoff_bits, kept_mass, kept);
     if (kept == 0) {
-      chosen = block_argmax(row, n, temperature, sh_arg);  // (src/sampler.rs:135-144)
+      chosen = team_argmax(tm, row, temperature, sh_arg);  // (src/sampler.rs:135-144)
     } else {
       // the value that closes the nucleus, the mass above it, and how many of its equals are in
       float v_min, mass_gt;
       int ties_in;
       if (!(kept_mass > top_p)) {  // the mass never exceeds top_p: everything kept stays (:150-158)
-        v_min = min_at_least(p, n, cutoff_bits, red);
+        v_min = min_at_least(tm, p, cutoff_bits);
         float s_ge; int c_ge, c_gt;
-        masked_sum(p, n, __float_as_uint(v_min), red, s_ge, c_ge);
-        masked_sum(p, n, __float_as_uint(v_min) + 1u, red, mass_gt, c_gt);
+        masked_sum(tm, p, __float_as_uint(v_min), s_ge, c_ge);
+        masked_sum(tm, p, __float_as_uint(v_min) + 1u, mass_gt, c_gt);
         ties_in = c_ge - c_gt;
       } else {
-        const uint32_t v_bits = select_mass(p, n, cutoff_bits, top_p, hist, hist_bins, &mass_gt);
+        const uint32_t v_bits = select_mass(tm, p, cutoff_bits, top_p, hist, total_bins, &mass_gt);
         v_min = __uint_as_float(v_bits);
-        const int ties = count_equal(p, n, v_bits, red);
+        const int ties = count_equal(tm, p, v_bits);
         int need = (int)floorf((top_p - mass_gt) / v_min) + 1;  // smallest count whose sum exceeds top_p
         ties_in = min(max(need, 1), ties);
       }
@@ -410,21 +589,20 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
         // falls among the equals that close the nucleus
         int j = (int)floorf((target - mass_gt) / v_min);
         j = min(max(j, 0), ties_in - 1);
-        chosen = kth_equal(p, n, v_min, j, sh_int);
+        chosen = kth_equal(tm, p, v_min, j, false);
       } else {
         // largest value whose "at least" mass exceeds the target, within the part above v_min
         float s_gt;
-        const uint32_t sel_bits = select_mass(p, n, __float_as_uint(v_min) + 1u, target, hist, hist_bins, &s_gt);
+        const uint32_t sel_bits = select_mass(tm, p, __float_as_uint(v_min) + 1u, target, hist, total_bins, &s_gt);
         const float v_sel = __uint_as_float(sel_bits);
-        const int equals = count_equal(p, n, sel_bits, red);
-        int j = (int)floorf((target - s_gt) / v_sel);
-        j = min(max(j, 0), equals - 1);
-        chosen = kth_equal(p, n, v_sel, j, sh_int);
+        const int j = (int)floorf((target - s_gt) / v_sel);
+        chosen = kth_equal(tm, p, v_sel, j, true);  // j brought into the number of equals
       }
-      if (chosen < 0) chosen = block_argmax(row, n, temperature, sh_arg);
+      if (chosen < 0) chosen = team_argmax(tm, row, temperature, sh_arg);
     }
   }
-  if (threadIdx.x == 0) out[r] = chosen;
+  if (tm.rank == 0 && threadIdx.x == 0) out[r] = chosen;
+  tm.cluster.sync();  // nobody leaves while a team mate may still read its shared memory
 }
 
 // probs: scratch of n_rows * n floats.  rng_states[rng_index[r]] is read and advanced for row r.
@@ -434,7 +612,22 @@ RL_API int rl_sample(const float* logits, long long row_stride, int n_rows, int 
   if (n_rows <= 0 || n <= 0) RL_REFUSE(1, "sample: rows=%d n=%d", n_rows, n);
   if (!(temperature > 0.f)) RL_REFUSE(2, "sample: temperature %f is not positive (0 is the argmax kernel's)", temperature);
   if (!rng_states || !rng_index || !probs) RL_REFUSE(3, "sample: missing random state or scratch");
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, n, temperature, top_p, rng_states,
-                                                        rng_index, probs, out);
-  RL_LAUNCH_RESULT();
+  if (n_rows > 65535) RL_REFUSE(4, "sample: %d rows exceed 65535", n_rows);
+  // a team member should have a few thousand values to sweep, or the exchanges cost more than they save
+  int team = 1;
+  while (team < TEAM_MAX && n / (2 * team) >= 4096) team *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(team, n_rows);
+  cfg.blockDim = dim3(SAMPLE_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = team;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  RL_LAUNCH_CHECK(cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, n, temperature, top_p, rng_states, rng_index, probs, out));
+  return 0;
 }

@@ -876,6 +876,37 @@ def test_sample_follows_the_plain_sampler(ops, n, temperature, top_p):
     assert np.array_equal(states.cpu().numpy().view(np.uint64), want_states)
 
 
+@pytest.mark.parametrize("n, temperature, top_p", [(9000, 0.8, 0.5), (20000, 1.0, 0.0), (40001, 0.9, 0.9), (40001, 1.5, 0.99)])
+def test_sample_rows_shared_by_several_blocks(ops, n, temperature, top_p):
+    """Rows long enough that 2, 4 and 8 blocks share one (a length that is no multiple of 4 among them):
+    the blocks' sums, histograms and counts have to meet in index order."""
+    rows = 4
+    g = torch.Generator().manual_seed(n)
+    logits = torch.randn(rows, n, generator=g) * 2.5
+    logits[1] = torch.round(logits[1] * 2) / 2  # many equal probabilities, spread over all blocks
+    logits[2, n - 2] = 30.0  # one dominant token in the last block's part
+    logits[3, :] = -20.0
+    logits[3, [1, n // 2, n - 1]] = torch.tensor([3.0, 3.0, 3.0])  # equals in the first, a middle and the last part
+    seeds = [4242, 17, 3, 2**62 + 11]
+    states = torch.from_numpy(np.array(seeds, dtype=np.uint64).view(np.int64).copy()).to(DEV)
+    index = torch.arange(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * n, device=DEV)
+    rngs = [PlainRng(s) for s in seeds]
+    ld = logits.to(DEV)
+    draws = 5
+    for d in range(draws):
+        got = ops.sample(ld, temperature, top_p, states, index, scratch).cpu().tolist()
+        want = [plain_sample(logits[r].tolist(), temperature, top_p, rngs[r]) for r in range(rows)]
+        assert got[0] == want[0] and got[2] == want[2], f"draw {d}: {got} against {want}"
+        # equal probabilities are ordered by the reference's unstable sort, here by index: the draw lands
+        # on the same value, maybe at another index
+        assert logits[1, got[1]] == logits[1, want[1]]
+        # the three equal tokens hold nearly all the mass: whichever the coin picks, it is one of them
+        assert got[3] in (1, n // 2, n - 1) and want[3] in (1, n // 2, n - 1)
+    want_states = np.array([r.state for r in rngs], dtype=np.uint64)
+    assert np.array_equal(states.cpu().numpy().view(np.uint64), want_states)
+
+
 def test_sample_rows_without_ties_agree_exactly(ops):
     n, rows = 2000, 8
     logits = torch.randn(rows, n, generator=torch.Generator().manual_seed(5)) * 3
