@@ -5,7 +5,9 @@ persistent TMA-fed streaming kernel for up to 8 rows (a decode step; the older r
 kernel where k is no multiple of 64) and the TMA + tcgen05 kernel above that (a prompt step).  The
 reference makes the same split, its own GEMV kernels for decode and a cuBLASLt call for prompts
 (src/backend/cuda.rs:354-442, :717-758); `use_library_gemm(True)` puts the vendor GEMM
-(torch.matmul) in the place of the tcgen05 kernel, for comparisons only.
+(torch.matmul) in the place of the tcgen05 kernel, for comparisons only.  Those kernels move rows in
+16-byte pieces; a product whose k is no multiple of 8, or whose rows do not start on 16 bytes, goes to a
+plain FMA kernel instead (slow, but every size that a configuration allows has to run).
 """
 
 from __future__ import annotations
@@ -36,6 +38,13 @@ def _streams(M: int, K: int, whole: bool) -> bool:
     return slices == 1 or (slices > 1 and not whole)
 
 
+def _odd(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the operands' rows cannot be moved in 16-byte pieces."""
+    return bool(
+        x.shape[1] % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16
+    )
+
+
 def use_library_gemm(on: bool) -> None:
     """Route bfloat16 products of more than 64 rows through torch.matmul instead of `gemm_tc`."""
     global _library_gemm
@@ -53,6 +62,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
     M, K = x.shape
+    if _odd(x, w):
+        return ops.gemm_bf16_any(x, w, out_dtype)
     if M <= STREAM_MAX_ROWS:
         if _streams(M, K, whole=True):
             return ops.gemv_stream(x, w, out_dtype)
@@ -73,6 +84,8 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     the product's 32-bit sums go through the activation before anything is rounded or stored."""
     if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
         raise KernelError(f"linear_swiglu: bfloat16 only, got {x.dtype} x {w_gate_up.dtype}")
+    if _odd(x, w_gate_up):
+        return ops.gemm_bf16_any(x, w_gate_up, torch.bfloat16, swiglu=True)
     if x.shape[0] <= STREAM_MAX_ROWS:
         if _streams(x.shape[0], x.shape[1], whole=True):
             return ops.gemv_stream(x, w_gate_up, torch.bfloat16, swiglu=True)
@@ -91,7 +104,7 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     returned, which the next norm's kernel adds up in 32-bit; otherwise the same as `linear`."""
     M, K = x.shape
     N = w.shape[0]
-    if x.dtype != torch.bfloat16:
+    if x.dtype != torch.bfloat16 or _odd(x, w):
         return linear(x, w)
     if M <= STREAM_MAX_ROWS and _streams(M, K, whole=False):
         # as few slices of k as the kernel allows (each costs a partial result to write and to add)

@@ -462,6 +462,29 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
     return out
 
 
+def gemm_bf16_any(
+    x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False
+) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for bfloat16 operands of any k and alignment, 32-bit sums on the
+    CUDA cores: the slow kernel behind the shapes that the 16-byte-row kernels refuse.
+
+    swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums."""
+    _cuda(x, "gemm_bf16_any x", torch.bfloat16, contiguous=False)
+    _cuda(w, "gemm_bf16_any w", torch.bfloat16, contiguous=False)
+    ldx, ldw = _rows(x, "gemm_bf16_any x"), _rows(w, "gemm_bf16_any w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, f"gemm_bf16_any: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+    lib = build.load("gemm_f32")
+    rc = lib.rl_gemm_bf16_any(
+        _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_bf16_any out")), c_int(out.shape[1]),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream(),
+    )
+    _check(lib, rc, "gemm_bf16_any")
+    return out
+
+
 def gemv_bf16(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
     swiglu: bool = False, k_splits: int = 1,

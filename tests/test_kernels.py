@@ -834,6 +834,26 @@ def test_gemv_bf16_refuses_what_it_cannot_do(ops):
         ops.gemv_bf16(x.cpu(), w.cpu())
 
 
+@pytest.mark.parametrize("M, N, K", [(1, 34, 100), (7, 258, 250), (70, 130, 129), (200, 66, 1001)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_gemm_bf16_any_takes_every_k(ops, M, N, K, swiglu):
+    """The plain FMA kernel behind the shapes that the 16-byte-row kernels refuse: any k, rows that start
+    anywhere."""
+    g = torch.Generator().manual_seed(M * N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    if swiglu:
+        gate, up = ref[:, 0::2], ref[:, 1::2]
+        ref = gate / (1 + torch.exp(-gate)) * up
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = ops.gemm_bf16_any(x.to(DEV), w.to(DEV), out_dtype, swiglu=swiglu).cpu().double()
+        assert got.shape == ref.shape
+        err = (got - ref).abs().max().item()
+        bound = 2e-5 * ref.abs().max().item() + (ref.abs().max().item() * 2 ** -8 if out_dtype == torch.bfloat16 else 0)
+        assert err <= bound + 1e-6, f"{out_dtype}: {err} against {bound}"
+
+
 # --------------------------------------------------------------------------- sampling
 def test_argmax_last_of_ties(ops):
     logits = torch.randn(6, 1000)
