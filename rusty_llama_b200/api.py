@@ -12,7 +12,7 @@ from typing import Callable, List, Mapping, Optional, Sequence, Union
 import torch
 
 from .config.llama import read_config_json
-from .engine import Engine, GenerationResult, GenerationStats, StepEntry, generate
+from .engine import Engine, GenerationStats, StepEntry, generate
 from .errors import StepError
 from .models.model import Model
 from .sampling import Sampler, SamplingParams

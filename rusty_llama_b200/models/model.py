@@ -7,7 +7,7 @@ code and branches on the architecture; here the walk follows data.
 
 from __future__ import annotations
 
-from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+from typing import Dict, List, Mapping, Sequence, Tuple
 
 import torch
 

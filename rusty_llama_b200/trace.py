@@ -21,8 +21,6 @@ import os
 import sys
 from typing import Dict
 
-import numpy as np
-
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)

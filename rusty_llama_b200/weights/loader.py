@@ -10,7 +10,7 @@ same things tensor by tensor while parsing GGUF (src/model.rs:562-585,
 
 from __future__ import annotations
 
-from typing import Dict, Iterable, Mapping, Optional, Tuple
+from typing import Dict, Mapping, Optional, Tuple
 
 import torch
 

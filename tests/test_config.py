@@ -1,7 +1,6 @@
 """Configuration, registry and rotary tables (no GPU)."""
 
 import json
-import math
 
 import numpy as np
 import pytest

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from plain_llama import PlainRng, plain_argmax, plain_attention, plain_rmsnorm, plain_rope, plain_sample, plain_silu
+from plain_llama import PlainRng, plain_argmax, plain_rmsnorm, plain_rope, plain_sample, plain_silu
 
 pytestmark = pytest.mark.gpu
 

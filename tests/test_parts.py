@@ -2,8 +2,6 @@
 plain formula; and a toy mixer with state of its own, defined here, registered, built and stepped
 without touching the library's files."""
 
-import math
-
 import numpy as np
 import pytest
 import torch
