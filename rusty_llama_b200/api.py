@@ -57,6 +57,12 @@ class LLM:
         on_token: Optional[Callable[[int, int], None]] = None,
         return_results: bool = False,
         launch_ahead: bool = True,
+        top_k: int = 0,
+        min_p: float = 0.0,
+        repeat_penalty: float = 1.0,
+        repeat_last_n: int = 64,
+        frequency_penalty: float = 0.0,
+        presence_penalty: float = 0.0,
     ):
         """Token ids generated after each prompt.
 
@@ -65,13 +71,17 @@ class LLM:
         instead: positions in total, prompt included, clamped to the model's limit
         (src/model.rs:1668); give one of the two (neither: steps = 256).
         temperature 0 is greedy; top_p outside (0, 1) turns the nucleus off; seed None
-        takes the wall clock.  launch_ahead=False makes the loop read every token before it
+        takes the wall clock.  top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty and
+        presence_penalty are the reference's further knobs (`SamplingParams`); setting one selects its
+        longer chain, in which the nucleus is taken before the temperature.  launch_ahead=False makes the loop read every token before it
         starts the next step (same tokens, more idle GPU time)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         batch: List[Sequence[int]] = [prompts] if single else list(prompts)  # type: ignore[list-item]
         if max_new_tokens is not None and steps is not None:
             raise StepError("give max_new_tokens or steps, not both")
-        params = SamplingParams(temperature, top_p, seed)
+        params = SamplingParams(
+            temperature, top_p, seed, top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty
+        )
         stats = GenerationStats()
         if max_new_tokens is None:
             total = min(DEFAULT_STEPS if steps is None else steps, self.engine.max_positions)

@@ -187,6 +187,23 @@ struct Team {
     sum2(a, 0.f, A, B);
     return A;
   }
+  // the largest of unsigned values over the whole row
+  __device__ uint32_t umax(uint32_t a) {
+    a = __reduce_max_sync(0xffffffffu, a);
+    uint32_t* redu = reinterpret_cast<uint32_t*>(red);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) redu[threadIdx.x >> 5] = a;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      a = __reduce_max_sync(0xffffffffu, redu[threadIdx.x]);  // SAMPLE_WARPS == 32
+      if (threadIdx.x == 0) x->i[turn][2] = (int)a;
+    }
+    cluster.sync();
+    uint32_t A = 0;
+    for (int r = 0; r < size; ++r) A = max(A, (uint32_t)of(r)->i[turn][2]);
+    turn ^= 1;
+    return A;
+  }
   __device__ float maximum(float a) {
     a = block_max(a, red);
     if (threadIdx.x == 0) x->f[turn][0] = a;
@@ -220,25 +237,29 @@ __device__ __forceinline__ void masked_sum(Team& tm, const float* p, uint32_t lo
 __device__ __forceinline__ unsigned long long to_mass(float v) { return (unsigned long long)((double)v * MASS_ONE + 0.5); }
 __device__ __forceinline__ float from_mass(unsigned long long m) { return (float)((double)m / MASS_ONE); }
 
-// Among the probabilities whose bit pattern is at least `lo_bits`: the value v* with
-// mass{p > v*} <= limit < mass{p >= v*} (the caller guarantees that their whole mass exceeds `limit`;
-// if rounding says otherwise the smallest of them is returned).  Returns v*'s bit pattern and leaves
-// mass{p > v*} in *mass_gt.  hist: HIST_COPIES * HIST_BINS 64-bit words of shared memory.
+// The elements of a[begin..end) carry a 32-bit key (0: not a candidate) and a 64-bit weight, both from
+// kw(value, index, key, weight).  Finds the key k* with weight{key > k*} <= limit < weight{key >= k*}, digit
+// by digit (8 bits a sweep).  If the candidates' whole weight does not exceed the limit, *fell is set and
+// the smallest key among them is returned (0 if there is no candidate).  Leaves weight{key > k*} in
+// *above_out.  hist: HIST_COPIES * HIST_BINS 64-bit words of shared memory.
 // Every block of the team walks the same bins in the same order and so takes the same decisions.
-__device__ uint32_t select_mass(Team& tm, const float* p, uint32_t lo_bits, float limit, unsigned long long* hist,
-                                unsigned long long* total_bins, float* mass_gt) {
+template <typename KW>
+__device__ uint32_t select_desc(Team& tm, const float* p, KW kw, unsigned long long limit_m, unsigned long long* hist,
+                                unsigned long long* total_bins, unsigned long long* above_out, bool* fell) {
   __shared__ uint32_t sel_prefix;
   __shared__ unsigned long long sel_above;
-  const unsigned long long limit_m = to_mass(fmaxf(limit, 0.f));
+  __shared__ int sel_fell;
   uint32_t prefix = 0, prefix_mask = 0;
   unsigned long long above = 0;  // mass of the candidates above the prefix's range
   unsigned long long* mine = hist + (threadIdx.x >> 6) * HIST_BINS;
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < HIST_COPIES * HIST_BINS; i += blockDim.x) hist[i] = 0ull;
     __syncthreads();
-    sweep(p, tm.begin, tm.end, [&](float v, int) {
-      const uint32_t key = __float_as_uint(v);
-      if (key >= lo_bits && (key & prefix_mask) == prefix) atomicAdd(&mine[(key >> shift) & (HIST_BINS - 1)], to_mass(v));
+    sweep(p, tm.begin, tm.end, [&](float v, int i) {
+      uint32_t key;
+      unsigned long long w;
+      kw(v, i, key, w);
+      if (key != 0u && (key & prefix_mask) == prefix) atomicAdd(&mine[(key >> shift) & (HIST_BINS - 1)], w);
     });
     __syncthreads();
     if (threadIdx.x < HIST_BINS) {
@@ -290,6 +311,7 @@ __device__ uint32_t select_mass(Team& tm, const float* p, uint32_t lo_bits, floa
         if (lane == 31 - __clz(hits)) {  // the highest lane with a hit holds the first bin from the top
           sel_prefix = prefix | ((uint32_t)(8 * lane + hit) << shift);
           sel_above = acc_hit;
+          sel_fell = 0;
         }
       } else if (filled) {  // rounding: the candidates' mass does not exceed the limit after all
         if (lane == __ffs(filled) - 1) {
@@ -297,10 +319,12 @@ __device__ uint32_t select_mass(Team& tm, const float* p, uint32_t lo_bits, floa
           // (the bins below e in this lane and all lower lanes are empty, so `higher` is all the mass)
           sel_prefix = prefix | ((uint32_t)(8 * lane + e) << shift);
           sel_above = above + higher - own[e];
+          sel_fell = 1;
         }
-      } else if (lane == 0) {
+      } else if (lane == 0) {  // no candidate at all
         sel_prefix = prefix;
         sel_above = above;
+        sel_fell = 1;
       }
     }
     __syncthreads();
@@ -309,8 +333,29 @@ __device__ uint32_t select_mass(Team& tm, const float* p, uint32_t lo_bits, floa
     prefix_mask |= (uint32_t)(HIST_BINS - 1) << shift;
     __syncthreads();
   }
-  *mass_gt = from_mass(above);
+  *above_out = above;
+  *fell = sel_fell != 0;
   return prefix;
+}
+
+// Among the probabilities whose bit pattern is at least `lo_bits`: the value v* with
+// mass{p > v*} <= limit < mass{p >= v*} (the caller guarantees that their whole mass exceeds `limit`;
+// if rounding says otherwise the smallest of them is returned).  Returns v*'s bit pattern and leaves
+// mass{p > v*} in *mass_gt.
+__device__ uint32_t select_mass(Team& tm, const float* p, uint32_t lo_bits, float limit, unsigned long long* hist,
+                                unsigned long long* total_bins, float* mass_gt) {
+  unsigned long long above;
+  bool fell;
+  const uint32_t bits = select_desc(
+      tm, p,
+      [&](float v, int, uint32_t& key, unsigned long long& w) {
+        const uint32_t b = __float_as_uint(v);
+        key = b >= lo_bits ? b : 0u;
+        w = to_mass(v);
+      },
+      to_mass(fmaxf(limit, 0.f)), hist, total_bins, &above, &fell);
+  *mass_gt = from_mass(above);
+  return bits;
 }
 
 // How many probabilities have exactly the bit pattern `bits`.
@@ -605,6 +650,266 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
   tm.cluster.sync();  // nobody leaves while a team mate may still read its shared memory
 }
 
+// ---------------------------------------------------------------- the longer chain
+// penalties -> top-k -> top-p -> min-p -> temperature -> draw (or argmax), the order of the reference's
+// chain when any of its further knobs is set (src/sampler.rs:821-931).  Every filter of that chain keeps
+// a prefix of the candidates in descending order, so the survivors are always "all logits above a
+// threshold, and the first E (by index) of those equal to it": the kernel carries (threshold key, E)
+// from stage to stage and never sorts.  Equal logits are taken in index order where the reference's
+// unstable sorts leave the order open.
+
+// Keys: the bit pattern of a float made monotone (larger float, larger key); 0 is never a finite float's.
+__device__ __forceinline__ uint32_t okey(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float unkey(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+struct ChainParams {
+  float temperature, top_p, min_p;
+  float repeat_penalty, frequency_penalty, presence_penalty;
+  int top_k, last_n;
+};
+
+#define HISTORY_MAX 1024  // tokens of history that the penalties can look back on
+
+// f(value, index, sum, count) adds to two running sums; their totals over the whole row come back.
+template <typename F>
+__device__ __forceinline__ void team_sum2(Team& tm, const float* a, F f, float& A, float& B) {
+  float s = 0.f, c = 0.f;
+  sweep(a, tm.begin, tm.end, [&](float v, int i) { f(v, i, s, c); });
+  tm.sum2(s, c, A, B);
+}
+
+// grid: (team size, rows), clusters of (team size, 1, 1).  work: per row 2 * n_pad floats (the penalised
+// logits, then the weights of the current softmax).  history[slot][HISTORY_MAX] with history_count[slot]
+// tokens accepted so far: the ring of the last `last_n` sampled tokens (src/sampler.rs:339-347).
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int n, int n_pad, ChainParams cp,
+                    unsigned long long* __restrict__ rng_states, const int* __restrict__ slot_of_row,
+                    int* __restrict__ history, int* __restrict__ history_count, float* __restrict__ work,
+                    int* __restrict__ out) {
+  __shared__ float red[32];
+  __shared__ ArgMax sh_arg[32];
+  __shared__ Exchange exchange;
+  __shared__ unsigned long long hist[HIST_COPIES * HIST_BINS];
+  __shared__ unsigned long long total_bins[HIST_BINS];
+  __shared__ int ring[HISTORY_MAX];
+  Team tm = {cg::this_cluster(), 0, 0, 0, 0, &exchange, 0, red};
+  tm.rank = (int)tm.cluster.block_rank();
+  tm.size = (int)tm.cluster.num_blocks();
+  {
+    const int per = (((n + tm.size - 1) / tm.size) + 3) & ~3;
+    tm.begin = min(n, tm.rank * per);
+    tm.end = min(n, tm.begin + per);
+  }
+  const int r = blockIdx.y;
+  const int slot = slot_of_row[r];
+  const float* row = logits + (size_t)r * row_stride;
+  float* L = work + (size_t)r * 2 * n_pad;
+  float* q = L + n_pad;
+  const bool draws = cp.temperature != 0.f;
+
+  // one draw per sampled token, none for the argmax (src/sampler.rs:190-193, :225-228)
+  if (draws && tm.rank == 0 && threadIdx.x == 0) {
+    unsigned long long* st = rng_states + slot;
+    unsigned long long s = *st;
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    *st = s;
+    const uint32_t u = (uint32_t)((s * 0x2545F4914F6CDD1DULL) >> 32);
+    exchange.f[0][3] = (float)(u >> 8) / 16777216.0f;
+  }
+
+  // ---- penalties over the ring of accepted tokens (src/sampler.rs:314-337)
+  sweep(row, tm.begin, tm.end, [&](float v, int i) { L[i] = v; });
+  const bool penalties_on = cp.repeat_penalty != 1.f || cp.frequency_penalty != 0.f || cp.presence_penalty != 0.f;
+  const int accepted = cp.last_n > 0 ? history_count[slot] : 0;
+  const int valid = min(accepted, cp.last_n);
+  if (penalties_on && valid > 0) {
+    for (int j = threadIdx.x; j < valid; j += blockDim.x) ring[j] = history[(size_t)slot * HISTORY_MAX + j];
+    __syncthreads();  // (also orders the writes of L above before the changes below)
+    for (int j = threadIdx.x; j < valid; j += blockDim.x) {
+      const int t = ring[j];
+      if (t < tm.begin || t >= tm.end) continue;  // another block's, or no token of this vocabulary
+      int cnt = 0;
+      bool first = true;
+      for (int jj = 0; jj < valid; ++jj) {
+        if (ring[jj] == t) {
+          ++cnt;
+          if (jj < j) first = false;
+        }
+      }
+      if (first) {
+        float l = L[t];
+        l = l > 0.f ? l / cp.repeat_penalty : l * cp.repeat_penalty;
+        l -= (float)cnt * cp.frequency_penalty;
+        l -= cp.presence_penalty;
+        L[t] = l;
+      }
+    }
+  }
+  __syncthreads();
+
+  float mx_l = -INFINITY;
+  sweep(L, tm.begin, tm.end, [&](float v, int) { mx_l = fmaxf(mx_l, v); });
+  mx_l = tm.maximum(mx_l);
+  const float coin = draws ? tm.of(0)->f[0][3] : 0.f;
+
+  // survivors: key > T, and the first E (by index) of key == T; N of them
+  uint32_t T = 0;
+  int E = 0, N = n;
+  bool filtered = false, collapsed = false;
+
+  // ---- top-k (src/sampler.rs:239-251)
+  if (cp.top_k > 0 && cp.top_k < N) {
+    unsigned long long above;
+    bool fell;
+    T = select_desc(
+        tm, L, [&](float v, int, uint32_t& key, unsigned long long& w) { key = okey(v); w = 1ull; },
+        (unsigned long long)(cp.top_k - 1), hist, total_bins, &above, &fell);
+    E = cp.top_k - (int)above;
+    N = cp.top_k;
+    filtered = true;
+  }
+
+  // ---- top-p over the softmax of the survivors (src/sampler.rs:120-160)
+  if (cp.top_p > 0.f && cp.top_p < 1.f) {
+    float sum_gt, unused;
+    team_sum2(tm, L, [&](float v, int, float& s, float&) { if (okey(v) > T) s += expf(v - mx_l); }, sum_gt, unused);
+    const float e_t = E > 0 ? expf(unkey(T) - mx_l) : 0.f;
+    const float inv = 1.0f / (sum_gt + (float)E * e_t);
+    sweep(L, tm.begin, tm.end, [&](float v, int i) { q[i] = expf(v - mx_l) * inv; });
+    __syncthreads();
+    const float q_t = e_t * inv;
+    const float cutoff = (1.0f - cp.top_p) / (float)max(N - 1, 1);
+    float kept_gt_mass, kept_gt_count;
+    team_sum2(tm, L, [&](float v, int i, float& s, float& c) {
+      if (okey(v) > T && q[i] >= cutoff) { s += q[i]; c += 1.f; }
+    }, kept_gt_mass, kept_gt_count);
+    const bool t_in = E > 0 && q_t >= cutoff;
+    const int kept = (int)kept_gt_count + (t_in ? E : 0);
+    const float kept_mass = kept_gt_mass + (t_in ? (float)E * q_t : 0.f);
+    if (kept == 0) {
+      collapsed = true;  // the argmax alone (:135-144)
+    } else if (!(kept_mass > cp.top_p)) {
+      // the mass never exceeds top_p: everything kept stays (:150-158)
+      if (!t_in) {
+        uint32_t inv_key = 0;
+        sweep(L, tm.begin, tm.end, [&](float v, int i) { if (okey(v) > T && q[i] >= cutoff) inv_key = max(inv_key, ~okey(v)); });
+        T = ~tm.umax(inv_key);
+        float cnt, unused2;
+        team_sum2(tm, L, [&](float v, int, float& s, float&) { s += okey(v) == T ? 1.f : 0.f; }, cnt, unused2);
+        E = (int)cnt;
+      }
+    } else {
+      unsigned long long above;
+      bool fell;
+      const uint32_t k_sel = select_desc(
+          tm, L, [&](float v, int i, uint32_t& key, unsigned long long& w) {
+            const uint32_t k = okey(v);
+            key = (k > T && q[i] >= cutoff) ? k : 0u;
+            w = to_mass(q[i]);
+          },
+          to_mass(cp.top_p), hist, total_bins, &above, &fell);
+      if (fell && t_in) {
+        // the nucleus closes among the equals at the old threshold
+        const int need = (int)floorf((cp.top_p - kept_gt_mass) / q_t) + 1;
+        E = min(max(need, 1), E);
+      } else {
+        const float q_sel = expf(unkey(k_sel) - mx_l) * inv;
+        float cnt, unused2;
+        team_sum2(tm, L, [&](float v, int, float& s, float&) { s += okey(v) == k_sel ? 1.f : 0.f; }, cnt, unused2);
+        const int need = (int)floorf((cp.top_p - from_mass(above)) / q_sel) + 1;
+        E = min(max(need, 1), (int)cnt);
+        T = k_sel;
+      }
+    }
+    if (!collapsed) {
+      float cnt_gt, unused3;
+      team_sum2(tm, L, [&](float v, int, float& s, float&) { s += okey(v) > T ? 1.f : 0.f; }, cnt_gt, unused3);
+      N = (int)cnt_gt + E;
+    }
+    filtered = true;
+  }
+
+  // ---- min-p in logit space: logit >= max + ln p, at least one (src/sampler.rs:265-281)
+  if (!collapsed && cp.min_p > 0.f && N >= 2) {
+    const uint32_t tk = okey(mx_l + logf(cp.min_p));
+    if (tk > T) {
+      float c_ge, unused;
+      team_sum2(tm, L, [&](float v, int, float& s, float&) { s += okey(v) >= tk ? 1.f : 0.f; }, c_ge, unused);
+      if ((int)c_ge == 0) {
+        collapsed = true;  // p > 1: the first of the sorted candidates stays, a largest logit
+      } else {
+        uint32_t inv_key = 0;
+        sweep(L, tm.begin, tm.end, [&](float v, int) { if (okey(v) >= tk) inv_key = max(inv_key, ~okey(v)); });
+        T = ~tm.umax(inv_key);
+        float cnt, unused2;
+        team_sum2(tm, L, [&](float v, int, float& s, float&) { s += okey(v) == T ? 1.f : 0.f; }, cnt, unused2);
+        E = (int)cnt;
+        N = (int)c_ge;
+      }
+    }
+    filtered = true;
+  }
+
+  // ---- the choice: argmax (:225-228), or temperature and a draw in the candidates' order (:101-106, :190-215)
+  int chosen;
+  if (collapsed || !draws) {
+    chosen = team_argmax(tm, L, 1.0f, sh_arg);
+  } else {
+    const float t = cp.temperature, mx_t = mx_l / t;
+    float sum_gt, unused;
+    team_sum2(tm, L, [&](float v, int, float& s, float&) { if (okey(v) > T) s += expf(v / t - mx_t); }, sum_gt, unused);
+    const float e_t = E > 0 ? expf(unkey(T) / t - mx_t) : 0.f;
+    const float inv = 1.0f / (sum_gt + (float)E * e_t);
+    sweep(L, tm.begin, tm.end, [&](float v, int i) { q[i] = okey(v) > T || !filtered ? expf(v / t - mx_t) * inv : 0.f; });
+    __syncthreads();
+    const float q_t = e_t * inv;
+    const float target = coin;  // the softmax was just renewed, so the coin is the target (:199-204)
+    if (!filtered) {
+      chosen = first_cdf_above(tm, q, n, target);  // untouched order: by index
+    } else {
+      // descending order: the largest value whose "at least" mass exceeds the target
+      unsigned long long above;
+      bool fell;
+      const uint32_t k_sel = select_desc(
+          tm, L, [&](float v, int i, uint32_t& key, unsigned long long& w) {
+            const uint32_t k = okey(v);
+            key = k > T ? k : 0u;
+            w = to_mass(q[i]);
+          },
+          to_mass(target), hist, total_bins, &above, &fell);
+      if (fell && E > 0) {
+        // among the equals at the threshold (or past the end: the last of them)
+        const float gt_mass = sum_gt * inv;
+        int j = q_t > 0.f ? (int)floorf((target - gt_mass) / q_t) : E - 1;
+        j = min(max(j, 0), E - 1);
+        chosen = kth_equal(tm, L, unkey(T), j, false);
+      } else if (fell) {
+        chosen = kth_equal(tm, L, unkey(k_sel), 0x7fffffff, true);  // past the end: the last candidate
+      } else {
+        const float q_sel = expf(unkey(k_sel) / t - mx_t) * inv;
+        const int j = (int)floorf((target - from_mass(above)) / q_sel);
+        chosen = kth_equal(tm, L, unkey(k_sel), j, true);
+      }
+    }
+    if (chosen < 0) chosen = team_argmax(tm, L, 1.0f, sh_arg);
+  }
+  if (tm.rank == 0 && threadIdx.x == 0) {
+    out[r] = chosen;
+    if (cp.last_n > 0) {  // the chosen token joins the ring (src/sampler.rs:339-347)
+      history[(size_t)slot * HISTORY_MAX + accepted % cp.last_n] = chosen;
+      history_count[slot] = accepted + 1;
+    }
+  }
+  tm.cluster.sync();  // nobody leaves while a team mate may still read its shared memory
+}
+
 // probs: scratch of n_rows * n floats.  rng_states[rng_index[r]] is read and advanced for row r.
 RL_API int rl_sample(const float* logits, long long row_stride, int n_rows, int n, float temperature, float top_p,
                      unsigned long long* rng_states, const int* rng_index, float* probs, int* out,
@@ -629,5 +934,38 @@ RL_API int rl_sample(const float* logits, long long row_stride, int n_rows, int 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   RL_LAUNCH_CHECK(cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, n, temperature, top_p, rng_states, rng_index, probs, out));
+  return 0;
+}
+
+// The longer chain.  work: n_rows * 2 * n_pad floats with n_pad = n rounded up to 4.  history: int
+// [slots][1024] and history_count: int [slots], both indexed by slot_of_row[r], like rng_states.
+RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows, int n, float temperature, float top_p,
+                           int top_k, float min_p, float repeat_penalty, int last_n, float frequency_penalty,
+                           float presence_penalty, unsigned long long* rng_states, const int* slot_of_row,
+                           int* history, int* history_count, float* work, int* out, cudaStream_t stream) {
+  if (n_rows <= 0 || n <= 0) RL_REFUSE(1, "sample_chain: rows=%d n=%d", n_rows, n);
+  if (!(temperature >= 0.f)) RL_REFUSE(2, "sample_chain: temperature %f is negative", temperature);
+  if (!rng_states || !slot_of_row || !work || !history || !history_count) RL_REFUSE(3, "sample_chain: missing random state, history or scratch");
+  if (n_rows > 65535) RL_REFUSE(4, "sample_chain: %d rows exceed 65535", n_rows);
+  if (last_n < 0 || last_n > HISTORY_MAX) RL_REFUSE(5, "sample_chain: a history of %d tokens is outside 0..%d", last_n, HISTORY_MAX);
+  if (top_k < 0 || !(repeat_penalty > 0.f)) RL_REFUSE(6, "sample_chain: top_k %d or repeat penalty %f out of range", top_k, repeat_penalty);
+  ChainParams cp = {temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k, last_n};
+  int team = 1;
+  while (team < TEAM_MAX && n / (2 * team) >= 4096) team *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(team, n_rows);
+  cfg.blockDim = dim3(SAMPLE_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = team;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int n_pad = (n + 3) & ~3;
+  RL_LAUNCH_CHECK(cudaLaunchKernelEx(&cfg, sample_chain_kernel, logits, row_stride, n, n_pad, cp, rng_states, slot_of_row, history,
+                                     history_count, work, out));
   return 0;
 }

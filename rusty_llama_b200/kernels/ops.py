@@ -683,3 +683,44 @@ def sample(
     )
     _check(lib, rc, "sample")
     return out
+
+
+SAMPLE_HISTORY_MAX = 1024
+
+
+def sample_chain(
+    logits: torch.Tensor, temperature: float, top_p: float, top_k: int, min_p: float, repeat_penalty: float,
+    last_n: int, frequency_penalty: float, presence_penalty: float, rng_states: torch.Tensor, slot_of_row: torch.Tensor,
+    history: torch.Tensor, history_count: torch.Tensor, work: torch.Tensor, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One token per row through penalties -> top-k -> top-p -> min-p -> temperature -> draw (temperature 0:
+    the argmax of the penalised logits, no draw).
+
+    Row r belongs to slot slot_of_row[r]: it uses and advances rng_states[slot], reads the last `last_n`
+    chosen tokens of history[slot] (int32 [slots, 1024] with history_count[slot] tokens written so far) for
+    the penalties and appends its choice.  work: float32, at least rows * 2 * (vocabulary rounded up to 4)."""
+    _cuda(logits, "sample_chain logits", torch.float32, contiguous=False)
+    stride = _rows(logits, "sample_chain logits")
+    R, n = logits.shape
+    _cuda(rng_states, "sample_chain rng_states", torch.int64)
+    _cuda(slot_of_row, "sample_chain slot_of_row", torch.int32)
+    _need(slot_of_row.numel() == R, "sample_chain: one slot per row")
+    _cuda(history, "sample_chain history", torch.int32)
+    _cuda(history_count, "sample_chain history_count", torch.int32)
+    _need(history.dim() == 2 and history.shape[1] == SAMPLE_HISTORY_MAX and history.shape[0] == history_count.numel(),
+          f"sample_chain: history must be [slots, {SAMPLE_HISTORY_MAX}] with one count per slot")
+    _cuda(work, "sample_chain work", torch.float32)
+    need = R * 2 * ((n + 3) // 4 * 4)
+    _need(work.numel() >= need, f"sample_chain: work holds {work.numel()} floats, {need} needed")
+    _need(work.data_ptr() % 16 == 0, "sample_chain: work must be 16-byte aligned")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _cuda(out, "sample_chain out", torch.int32)
+    lib = build.load("sampling")
+    rc = lib.rl_sample_chain(
+        _p(logits), c_ll(stride), c_int(R), c_int(n), c_float(temperature), c_float(top_p), c_int(top_k), c_float(min_p),
+        c_float(repeat_penalty), c_int(last_n), c_float(frequency_penalty), c_float(presence_penalty), _p(rng_states),
+        _p(slot_of_row), _p(history), _p(history_count), _p(work), _p(out), _stream(),
+    )
+    _check(lib, rc, "sample_chain")
+    return out

@@ -1,11 +1,15 @@
-"""Choosing next tokens: greedy, temperature and top-p, seeded, one random stream per sequence.
+"""Choosing next tokens: greedy, temperature and top-p, seeded, one random stream per sequence; and
+the reference's longer chain with top-k, min-p and the repetition, frequency and presence penalties.
 
 Semantics are the reference's default chain (src/sampler.rs:801-819): temperature 0
 is the argmax (last of equal maxima, no draw); otherwise logits are divided by the
 temperature, cut to the top-p nucleus when 0 < top_p < 1, and one token is drawn by
-inverse CDF with an xorshift64* generator.  The reference keeps one chain per server
-slot (src/server.rs:288, :513); here the generator states of all sequence slots live
-in one device array and the kernels advance them.
+inverse CDF with an xorshift64* generator.  As soon as top_k, min_p or a penalty is set the
+reference builds another chain, penalties -> top-k -> top-p -> min-p -> temperature -> draw
+(src/sampler.rs:821-931), in which the nucleus is taken before the temperature; so does this
+module.  The reference keeps one chain per server slot (src/server.rs:288, :513); here the
+generator states and the penalties' token histories of all sequence slots live in device arrays
+and the kernels advance them.  Not built: mirostat, XTC, DRY and grammars.
 """
 
 from __future__ import annotations
@@ -46,17 +50,43 @@ def sequence_seed(seed: int, index: int) -> int:
 class SamplingParams:
     """temperature: 0 = greedy (default 1.0).  top_p: nucleus mass, off when <= 0 or >= 1
     (default 0.9).  seed: None = wall clock.  Names and defaults follow the reference's
-    `-t`, `-p`, `-s` (src/main.rs:24-32)."""
+    `-t`, `-p`, `-s` (src/main.rs:24-32).
+
+    top_k: keep the k largest logits, 0 = off.  min_p: keep logits >= max + ln(min_p), 0 = off.
+    repeat_penalty (1 = off), frequency_penalty, presence_penalty (0 = off) act on the tokens among the
+    last repeat_last_n chosen ones (default 64): the reference's `--top-k`, `--min-p`, `--repeat-penalty`,
+    `--repeat-last-n`, `--frequency-penalty`, `--presence-penalty` (src/main.rs:478-485)."""
 
     temperature: float = 1.0
     top_p: float = 0.9
     seed: Optional[int] = None
+    top_k: int = 0
+    min_p: float = 0.0
+    repeat_penalty: float = 1.0
+    repeat_last_n: int = 64
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
 
     def validate(self) -> None:
         if not (self.temperature >= 0.0) or self.temperature == float("inf"):
             raise ConfigError(f"temperature must be finite and >= 0, got {self.temperature}")
         if self.top_p != self.top_p:
             raise ConfigError("top_p is NaN")
+        if self.top_k < 0:
+            raise ConfigError(f"top_k must be >= 0, got {self.top_k}")
+        if self.min_p != self.min_p or not (self.repeat_penalty > 0.0):
+            raise ConfigError(f"min_p {self.min_p} or repeat_penalty {self.repeat_penalty} out of range")
+        if not (0 <= self.repeat_last_n <= ops.SAMPLE_HISTORY_MAX):
+            raise ConfigError(f"repeat_last_n must lie in 0..{ops.SAMPLE_HISTORY_MAX}, got {self.repeat_last_n}")
+
+    @property
+    def penalties_on(self) -> bool:
+        return self.repeat_penalty != 1.0 or self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
+
+    @property
+    def longer_chain(self) -> bool:
+        """Whether the reference would build its longer chain for these values (src/sampler.rs:868-876)."""
+        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on
 
 
 class PendingTokens:
@@ -78,6 +108,10 @@ class Sampler:
         self.device = torch.device(device)
         self.vocab_size = vocab_size
         self.rng_states = torch.ones(max_seqs, dtype=torch.int64, device=self.device)
+        # the penalties' ring of chosen tokens per slot, made when the longer chain is first used
+        self.max_seqs = max_seqs
+        self.history: Optional[torch.Tensor] = None
+        self.history_count = torch.zeros(max_seqs, dtype=torch.int32, device=self.device)
         self._workspace = workspace
         self._scratch: Optional[torch.Tensor] = None
         self._pinned = None
@@ -88,6 +122,7 @@ class Sampler:
         vals = np.array([s or 1 for s in seeds], dtype=np.uint64).view(np.int64)
         idx = torch.tensor(list(slots), dtype=torch.long, device=self.device)
         self.rng_states[idx] = torch.from_numpy(vals).to(self.device)
+        self.history_count[idx] = 0  # a new sequence has chosen nothing yet (src/sampler.rs:349-351)
 
     def begin_fetch(self, tokens: torch.Tensor) -> "PendingTokens":
         """Start copying sampled tokens to the host, now, in stream order: work that is launched
@@ -106,6 +141,8 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, slots: Sequence[int], params: SamplingParams) -> torch.Tensor:
         """int32 [rows] on the device: one token per row of logits[rows, vocab]; row i belongs to slots[i]."""
+        if params.longer_chain:
+            return self._sample_chain(logits, slots, params)
         if params.temperature == 0.0:
             return ops.argmax(logits)
         rows, n = logits.shape
@@ -118,3 +155,21 @@ class Sampler:
             scratch = self._scratch
         index = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
         return ops.sample(logits, params.temperature, params.top_p, self.rng_states, index, scratch)
+
+    def _sample_chain(self, logits: torch.Tensor, slots: Sequence[int], params: SamplingParams) -> torch.Tensor:
+        rows, n = logits.shape
+        need = rows * 2 * ((n + 3) // 4 * 4)
+        if self._workspace is not None:
+            work = self._workspace.get("sample_chain_work", need, torch.float32)
+        else:
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            work = self._scratch
+        if self.history is None:
+            self.history = torch.zeros((self.max_seqs, ops.SAMPLE_HISTORY_MAX), dtype=torch.int32, device=self.device)
+        index = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
+        return ops.sample_chain(
+            logits, params.temperature, params.top_p, params.top_k, params.min_p, params.repeat_penalty,
+            params.repeat_last_n if params.penalties_on else 0, params.frequency_penalty, params.presence_penalty,
+            self.rng_states, index, self.history, self.history_count, work,
+        )

@@ -316,11 +316,13 @@ def plain_generate(
     seed: int = 1,
     stop_token_ids: Sequence[int] = (),
     dtype=torch.float32,
+    chain: Optional["PlainChain"] = None,
 ) -> List[int]:
     """Tokens generated after `prompt`, recomputing the whole sequence each step.
 
     Sample from the last position's logits, stop before emitting a stop token,
-    else feed the token back (src/model.rs:1743-1760).
+    else feed the token back (src/model.rs:1743-1760).  chain: the longer sampler
+    chain in the place of the default one.
     """
     rng = PlainRng(seed)
     seq = list(prompt)
@@ -328,9 +330,104 @@ def plain_generate(
     limit = complete_config(cfg)["max_position_embeddings"]
     while len(out) < max_new_tokens and len(seq) < limit:
         logits = plain_logits(cfg, w, seq, dtype)[-1].to(torch.float32).numpy()
-        tok = plain_sample(logits, temperature, top_p, rng)
+        tok = chain.sample(logits) if chain is not None else plain_sample(logits, temperature, top_p, rng)
         if tok in stop_token_ids:
             break
         out.append(tok)
         seq.append(tok)
     return out
+
+
+class PlainChain:
+    """The reference's longer sampler chain for one sequence: penalties -> top-k -> top-p -> min-p ->
+    temperature -> draw, or -> argmax when the temperature is 0 (src/sampler.rs:877-931).  Candidates are
+    (id, logit, p) records in an array that the stages reorder and shorten, as in the reference; where it
+    sorts with an unstable sort, the stable sort here keeps equal values in index order."""
+
+    def __init__(self, temperature=1.0, top_p=0.9, seed=1, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64,
+                 frequency_penalty=0.0, presence_penalty=0.0):
+        self.t, self.top_p, self.top_k, self.min_p = temperature, top_p, top_k, min_p
+        self.repeat, self.last_n, self.freq, self.present = repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty
+        self.rng = PlainRng(seed)
+        self.ring = []  # the last `last_n` chosen tokens (src/sampler.rs:339-347)
+
+    @staticmethod
+    def _softmax(cands):
+        """p over the live candidates, 32-bit, in array order (src/sampler.rs:58-73)."""
+        l = np.array([c[1] for c in cands], dtype=np.float32)
+        p = _softmax_f32(l)
+        return [(c[0], c[1], p[k]) for k, c in enumerate(cands)]
+
+    def sample(self, logits) -> int:
+        f32 = np.float32
+        cands = [(i, f32(v), f32(0.0)) for i, v in enumerate(np.asarray(logits, dtype=np.float32))]
+        sorted_by_p = False
+        # penalties (src/sampler.rs:314-337)
+        penalties_on = self.repeat != 1.0 or self.freq != 0.0 or self.present != 0.0
+        if penalties_on and self.ring:
+            counts = {}
+            for tok in self.ring:
+                counts[tok] = counts.get(tok, 0) + 1
+            out = []
+            for i, l, p in cands:
+                if i in counts:
+                    l = f32(l / f32(self.repeat)) if l > 0 else f32(l * f32(self.repeat))
+                    l = f32(l - f32(counts[i]) * f32(self.freq))
+                    l = f32(l - f32(self.present))
+                out.append((i, l, p))
+            cands = out
+        # top-k (src/sampler.rs:239-251): the k largest logits; here in descending order
+        if self.top_k != 0 and self.top_k < len(cands):
+            cands = sorted(cands, key=lambda c: -float(c[1]))[: self.top_k]
+        # top-p (src/sampler.rs:120-160)
+        if 0.0 < self.top_p < 1.0:
+            n = len(cands)
+            cands = self._softmax(cands)
+            cutoff = f32((f32(1.0) - f32(self.top_p)) / f32(max(n - 1, 1)))
+            kept = [c for c in cands if c[2] >= cutoff]
+            if not kept:
+                best = plain_argmax([float(c[1]) for c in cands])
+                cands = [cands[best]]
+            else:
+                kept.sort(key=lambda c: -float(c[2]))
+                cumulative, last = f32(0.0), len(kept) - 1
+                for k, c in enumerate(kept):
+                    cumulative = f32(cumulative + c[2])
+                    if cumulative > f32(self.top_p):
+                        last = k
+                        break
+                cands = kept[: last + 1]
+            sorted_by_p = True
+        # min-p (src/sampler.rs:265-281)
+        if self.min_p > 0.0 and len(cands) >= 2:
+            mx = max(float(c[1]) for c in cands)
+            thresh = f32(f32(mx) + f32(np.log(f32(self.min_p))))
+            cands = sorted(cands, key=lambda c: -float(c[1]))
+            above = 0
+            for c in cands:
+                if c[1] >= thresh:
+                    above += 1
+                else:
+                    break
+            cands = cands[: min(max(above, 1), len(cands))]
+            sorted_by_p = False
+        if self.t == 0.0:
+            sel = plain_argmax([float(c[1]) for c in cands])  # (src/sampler.rs:225-228)
+        else:
+            cands = [(i, f32(l / f32(self.t)), p) for i, l, p in cands]  # (:101-106), which also drops `sorted`
+            sorted_by_p = False
+            cands = self._softmax(cands)
+            coin = f32(self.rng.next_f32())
+            target = coin  # (:199-204: only a sorted array scales the coin)
+            cdf, sel = f32(0.0), len(cands) - 1
+            for k, c in enumerate(cands):
+                cdf = f32(cdf + c[2])
+                if target < cdf:
+                    sel = k
+                    break
+        token = cands[sel][0]
+        if self.last_n > 0:
+            if len(self.ring) == self.last_n:
+                self.ring.pop(0)
+            self.ring.append(token)
+        return token

@@ -227,6 +227,11 @@ def test_command_line_options_follow_the_reference(tmp_path):
     assert (a["temperature"], a["top_p"], a["seed"], a["steps"], a["prompt"], a["dtype"]) == (1.0, 0.9, None, 256, "", "bfloat16")
     a = parse_args(["m", "-t", "0", "-p", "0.5", "-s", "42", "-n", "17", "-i", "1, 2 3", "--dtype", "float32"])
     assert (a["temperature"], a["top_p"], a["seed"], a["steps"], a["prompt"], a["dtype"]) == (0.0, 0.5, 42, 17, "1, 2 3", "float32")
+    assert (a["top_k"], a["min_p"], a["repeat_penalty"], a["repeat_last_n"], a["frequency_penalty"], a["presence_penalty"]) == (0, 0.0, 1.0, 64, 0.0, 0.0)  # src/main.rs:478-485
+    a = parse_args(["m", "--top-k", "40", "--min-p", "0.05", "--repeat-penalty", "1.1", "--repeat-last-n", "32", "--frequency-penalty", "0.2", "--presence-penalty", "0.3"])
+    assert (a["top_k"], a["min_p"], a["repeat_penalty"], a["repeat_last_n"], a["frequency_penalty"], a["presence_penalty"]) == (40, 0.05, 1.1, 32, 0.2, 0.3)
+    with pytest.raises(SystemExit, match="unknown option"):
+        parse_args(["m", "--mirostat", "2"])  # not built
     assert parse_prompts("1, 2 3") == [[1, 2, 3]]
     f = tmp_path / "prompts.txt"
     f.write_text("5 6\n\n7,8,9\n")
@@ -238,3 +243,19 @@ def test_command_line_options_follow_the_reference(tmp_path):
     with pytest.raises(SystemExit, match="bad value"):
         parse_args(["m", "-n", "many"])
     assert main(["m", "-n", "4"]) == 1  # an empty prompt is an error before anything is loaded (src/main.rs:294-296)
+
+
+def test_sampling_params_pick_the_chain_as_the_reference_does():
+    """The longer chain is built as soon as one of its knobs leaves its neutral value (src/sampler.rs:868-876)."""
+    from rusty_llama_b200.errors import ConfigError
+    from rusty_llama_b200.sampling import SamplingParams
+
+    assert not SamplingParams(0.8, 0.9, 1).longer_chain
+    assert not SamplingParams(0.8, 0.9, 1, repeat_last_n=8).longer_chain  # a window alone changes nothing
+    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5)):
+        p = SamplingParams(0.8, 0.9, 1, **kw)
+        p.validate()
+        assert p.longer_chain
+    for kw in (dict(top_k=-1), dict(repeat_penalty=0.0), dict(repeat_last_n=5000), dict(min_p=float("nan"))):
+        with pytest.raises(ConfigError):
+            SamplingParams(0.8, 0.9, 1, **kw).validate()

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from plain_llama import PlainRng, plain_argmax, plain_rmsnorm, plain_rope, plain_sample, plain_silu
+from plain_llama import PlainChain, PlainRng, plain_argmax, plain_rmsnorm, plain_rope, plain_sample, plain_silu
 
 pytestmark = pytest.mark.gpu
 
@@ -925,6 +925,87 @@ def test_sample_rows_shared_by_several_blocks(ops, n, temperature, top_p):
         assert got[3] in (1, n // 2, n - 1) and want[3] in (1, n // 2, n - 1)
     want_states = np.array([r.state for r in rngs], dtype=np.uint64)
     assert np.array_equal(states.cpu().numpy().view(np.uint64), want_states)
+
+
+CHAINS = [
+    dict(temperature=0.8, top_p=0.9, top_k=40),
+    dict(temperature=1.0, top_p=0.0, top_k=5),
+    dict(temperature=1.2, top_p=0.95, min_p=0.05),
+    dict(temperature=0.7, top_p=0.0, min_p=0.2, top_k=50),
+    dict(temperature=1.0, top_p=0.9, repeat_penalty=1.3, repeat_last_n=8),
+    dict(temperature=1.0, top_p=0.0, frequency_penalty=0.7, presence_penalty=0.4, repeat_last_n=5),
+    dict(temperature=0.0, top_p=0.9, repeat_penalty=1.5, frequency_penalty=0.3, repeat_last_n=64),
+    dict(temperature=0.9, top_p=0.8, top_k=30, min_p=0.02, repeat_penalty=1.1, presence_penalty=0.2, repeat_last_n=16),
+    dict(temperature=1.0, top_p=0.9, top_k=1),
+    dict(temperature=1.5, top_p=0.3, min_p=1.5),
+]
+
+
+@pytest.mark.parametrize("n", [300, 20001])
+@pytest.mark.parametrize("chain", CHAINS, ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
+def test_sample_chain_follows_the_plain_chain(ops, n, chain):
+    """penalties -> top-k -> top-p -> min-p -> temperature -> draw against the reference's stages run one
+    after the other on the host: rows without equal logits agree draw for draw, the chosen tokens feed the
+    penalties of the next draw, and the generator advances once per drawn token (never for the argmax)."""
+    rows, slots = 3, 5
+    g = torch.Generator().manual_seed(n + len(chain))
+    logits = [torch.randn(rows, n, generator=g) * 2.5 for _ in range(10)]
+    for l in logits:
+        l[1, 7] = 9.0  # a dominant token: penalties have something to push down
+    seeds = [11, 2**40 + 3, 7]
+    slot_of_row = [4, 0, 2]
+    states = torch.ones(slots, dtype=torch.int64, device=DEV)
+    states[slot_of_row] = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    index = torch.tensor(slot_of_row, dtype=torch.int32, device=DEV)
+    history = torch.zeros(slots, 1024, dtype=torch.int32, device=DEV)
+    count = torch.zeros(slots, dtype=torch.int32, device=DEV)
+    work = torch.empty(rows * 2 * ((n + 3) // 4 * 4), device=DEV)
+    c = dict(temperature=1.0, top_p=0.9, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64, frequency_penalty=0.0, presence_penalty=0.0)
+    c.update(chain)
+    penalties = c["repeat_penalty"] != 1.0 or c["frequency_penalty"] != 0.0 or c["presence_penalty"] != 0.0
+    plain = [PlainChain(seed=s, **c) for s in seeds]
+    index_order = c["top_k"] == 0 and c["min_p"] == 0.0 and not (0.0 < c["top_p"] < 1.0) and n > 10000
+    for d, l in enumerate(logits):
+        got = ops.sample_chain(
+            l.to(DEV), c["temperature"], c["top_p"], c["top_k"], c["min_p"], c["repeat_penalty"],
+            c["repeat_last_n"] if penalties else 0, c["frequency_penalty"], c["presence_penalty"], states, index, history, count, work,
+        ).cpu().tolist()
+        want = [plain[r].sample(l[r].tolist()) for r in range(rows)]
+        if got != want and index_order:
+            # a walk over the whole row in index order: the plain chain adds 20001 probabilities one after the
+            # other in 32-bit, the kernel in blocks; a draw within that rounding of a boundary may take the
+            # neighbour.  The penalties then go on from the kernel's token.
+            for r in range(rows):
+                assert abs(got[r] - want[r]) <= 1, f"draw {d}: {got} against {want}"
+                if plain[r].ring:
+                    plain[r].ring[-1] = got[r]
+        else:
+            assert got == want, f"draw {d}: {got} against {want}"
+    want_states = np.array([p.rng.state for p in plain], dtype=np.uint64)
+    assert np.array_equal(states.cpu().numpy().view(np.uint64)[slot_of_row], want_states)
+    if penalties:
+        assert count.cpu().tolist() == [10 if s in slot_of_row else 0 for s in range(slots)]
+
+
+def test_sample_chain_takes_equal_logits_in_index_order(ops):
+    """Equal logits at the edge of top-k and inside the draw: the first by index stay, as in the plain chain's
+    stable sorts."""
+    n = 50
+    logits = torch.full((1, n), -3.0)
+    logits[0, [4, 9, 20, 33, 41]] = 2.0
+    logits[0, 12] = 5.0
+    states = torch.tensor([99], dtype=torch.int64, device=DEV)
+    index = torch.zeros(1, dtype=torch.int32, device=DEV)
+    history = torch.zeros(1, 1024, dtype=torch.int32, device=DEV)
+    count = torch.zeros(1, dtype=torch.int32, device=DEV)
+    work = torch.empty(2 * 52, device=DEV)
+    plain = PlainChain(temperature=2.0, top_p=0.0, seed=99, top_k=4)
+    seen = set()
+    for _ in range(40):
+        got = ops.sample_chain(logits.to(DEV), 2.0, 0.0, 4, 0.0, 1.0, 0, 0.0, 0.0, states, index, history, count, work).item()
+        assert got == plain.sample(logits[0].tolist())
+        seen.add(got)
+    assert seen == {12, 4, 9, 20}  # the largest and the first three of the five equals
 
 
 def test_sample_rows_without_ties_agree_exactly(ops):

@@ -220,6 +220,36 @@ def test_sampled_generation_follows_the_plain_sampler(llms, tiny_weights):
     assert alone == outs[2]  # a sequence's draws do not depend on its neighbours
 
 
+def test_generation_with_the_longer_sampler_chain(llms, tiny_weights):
+    """top-k, min-p and the penalties through the entry point, in 32-bit, against the plain chain fed by the
+    plain model: the kernel keeps each sequence's ring of chosen tokens itself, across steps and batches."""
+    from plain_llama import PlainChain
+    from rusty_llama_b200.sampling import sequence_seed
+
+    name = "A"
+    cfg = TINY[name][0]
+    llm = llms(name, "float32")
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (3, 20, 41)]
+    knobs = dict(temperature=0.9, top_p=0.95, top_k=20, min_p=0.02, repeat_penalty=1.3, repeat_last_n=6, frequency_penalty=0.2, presence_penalty=0.1)
+    outs = llm.generate(prompts, max_new_tokens=24, seed=77, stop_token_ids=[], **knobs)
+    assert outs == llm.generate(prompts, max_new_tokens=24, seed=77, stop_token_ids=[], **knobs)  # the rings start empty again
+    assert outs == llm.generate(prompts, max_new_tokens=24, seed=77, stop_token_ids=[], launch_ahead=False, **knobs)
+    w = rounded_weights(tiny_weights[name], "float32")
+    agree = 0
+    for i, (p, got) in enumerate(zip(prompts, outs)):
+        want = plain_generate(cfg, w, p, 24, stop_token_ids=[], chain=PlainChain(seed=sequence_seed(77, i), **knobs))
+        agree += int(got == want)
+        assert len(got) == 24
+    assert agree >= 2  # a draw within rounding of a boundary parts the streams
+    # greedy with a strong repetition penalty: no token twice within the window, and not the plain greedy's run
+    greedy = llm.generate(prompts[0], max_new_tokens=20, temperature=0.0, stop_token_ids=[])
+    pen = llm.generate(prompts[0], max_new_tokens=20, temperature=0.0, repeat_penalty=50.0, presence_penalty=100.0, repeat_last_n=4, stop_token_ids=[])
+    want = plain_generate(cfg, w, prompts[0], 20, stop_token_ids=[], chain=PlainChain(temperature=0.0, repeat_penalty=50.0, presence_penalty=100.0, repeat_last_n=4))
+    assert pen == want and pen != greedy
+    assert all(pen[k] not in pen[max(0, k - 4) : k] for k in range(len(pen)))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("temperature", [0.0, 0.8])
 def test_launching_ahead_changes_no_token(dtype, temperature, llms):
