@@ -61,12 +61,22 @@ __device__ __forceinline__ void rl_trace_mark() {
     const unsigned int i = atomicAdd(rl_trace_count, 1u);
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (i < rl_trace_cap) rl_trace_buf[i] = t;
+    if (i < rl_trace_cap) rl_trace_buf[i] = t & 0x00ffffffffffffffull;
+  }
+}
+// a note with a number in its top byte, from whichever single thread calls it (block 0 only)
+__device__ __forceinline__ void rl_trace_event(unsigned int id) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && rl_trace_buf != nullptr) {
+    const unsigned int i = atomicAdd(rl_trace_count, 1u);
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (i < rl_trace_cap) rl_trace_buf[i] = ((unsigned long long)id << 56) | (t & 0x00ffffffffffffffull);
   }
 }
 #else
 #define RL_DEFINE_TRACE()
 __device__ __forceinline__ void rl_trace_mark() {}
+__device__ __forceinline__ void rl_trace_event(unsigned int) {}
 #endif
 
 #define RL_DEFINE_ERROR_TEXT()                                 \

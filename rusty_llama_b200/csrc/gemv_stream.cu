@@ -107,6 +107,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
   }
 
   pdl_trigger();
+  if (threadIdx.x == 32) rl_trace_event(1);  // (profiling aid, see common.cuh) block 0 is running
   if (threadIdx.x == CONSUMER_WARPS * 32)  // the copying lane: have the tensor map on its way before the barriers are set up
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
   const int first_item = (int)((long long)blockIdx.x * items / gridDim.x);
@@ -151,8 +152,11 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
           // rows past N and k past K arrive as zeros and count like the rest
           mbar_expect_tx(&bars.full[st], STAGE_BYTES);
           tma_load_3d(ring_addr + st * STAGE_BYTES, &map_w, &bars.full[st], 0, (kbeg + k0) / 64, unit * UNIT_ROWS, pol_w);
+          if (it == 0) rl_trace_event(2);            // first copy issued
+          if (it == STAGES - 1) rl_trace_event(3);   // the ring is full of requests
         }
       }
+      rl_trace_event(7);  // last copy issued
       // nothing may still be writing shared memory when the block ends: if someone gave up, wait
       // (bounded) for the copies that were started
       if (*(volatile int*)&bars.abort_flag)
@@ -198,6 +202,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.red_free[buf]);
+      if (e == 0 && item == end_item - 1) rl_trace_event(8);  // last result stored
     }
   } else {
     // ---------------- products
@@ -237,6 +242,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
             if (HI) xb[s][j] = (k_ok && g + 8 < M) ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)(g + 8) * ldx + kbeg + k)) : zero;
           }
         loaded_slice = slice;
+        if (warp == 0 && lane == 0 && item == first_item) rl_trace_event(4);  // activations requested
       }
       float acc[2 * KB_PER_WARP][4];
 #pragma unroll
@@ -261,6 +267,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.empty[st]);
+            if (warp == 0 && lane == 0 && it == 0) rl_trace_event(5);  // first stage consumed
             ++it;
           }
         }
@@ -283,6 +290,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
       red[buf * (CONSUMER_WARPS * 32) + warp * 32 + lane] = sum4;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.red_full[buf]);
+      if (warp == 0 && lane == 0 && item == end_item - 1) rl_trace_event(6);  // last item's sums handed over
     }
   }
 }

@@ -198,7 +198,9 @@ def bench_step_trace(a) -> dict:
         torch.cuda.synchronize()
         decode()
         torch.cuda.synchronize()
-        t = buf[: int(count.item())].cpu().tolist()
+        raw = buf[: int(count.item())].cpu().tolist()
+        notes = sorted((v & ((1 << 56) - 1), (v >> 56) & 0xFF) for v in raw)  # (time, number); 0: a wait that returned
+        t = [when for when, what in notes if what == 0]
         runs.append([(y - x) / 1000.0 for x, y in zip(t, t[1:])])
     # the kernels that call the dependency wait, in a step's order; an interval runs from the end of a
     # kernel's predecessor to its own end (the classifier product and the sampler follow the last mark)
@@ -217,6 +219,18 @@ def bench_step_trace(a) -> dict:
     out = {"kernel": "step_trace", "seqs": a.seqs, "ctx": a.ctx, "layers": a.layers, "us": {k: round(med(v), 2) for k, v in per.items()},
            "step_spans_us": [round(sum(r), 1) for r in runs]}
     out["layer_us"] = round(sum(out["us"][k] for k in layer), 1)
+    if a.events:
+        # the last traced step's second layer with the numbered notes that some kernels leave besides
+        # (csrc/gemv_stream.cu: 1 block 0 runs, 2 first copy issued, 3 ring full of requests, 4 activations
+        # requested, 5 first stage consumed, 6 last sums handed over, 7 last copy issued, 8 last result
+        # stored); every note is taken after an atomic's round trip, about a microsecond late
+        marks = [i for i, (_, what) in enumerate(notes) if what == 0]
+        lo, hi = marks[1 + len(layer)], marks[min(1 + 2 * len(layer) + 1, len(marks) - 1)]
+        kernel_at = {marks[1 + len(layer) + j]: nm for j, nm in enumerate(layer + layer[:1])}
+        out["events_us"] = [
+            [round((when - notes[lo][0]) / 1000.0, 2), ("wait returned: " + kernel_at.get(i, "?")) if what == 0 else what]
+            for i, (when, what) in enumerate(notes[lo : hi + 1], start=lo)
+        ]
     return out
 
 
@@ -235,6 +249,7 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=4, help="step_trace: layers of the model")
     ap.add_argument("--ff", type=int, default=14336, help="step_trace: width of the feed-forward")
     ap.add_argument("--vocab", type=int, default=128256, help="step_trace: vocabulary")
+    ap.add_argument("--events", action="store_true", help="step_trace: also the numbered notes inside one layer's kernels")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
     ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream", "tma", "warp"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent TMA-fed kernel; attn_decode: tma or warp = one of its two kernels")
     ap.add_argument("--iters", type=int, default=50)
