@@ -147,13 +147,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  // barriers and tensor memory are set up: from here on the kernel reads what its predecessor wrote
+  // Barriers and tensor memory are set up.  The weights are no kernel's output, so the producer asks for
+  // the first ring of them before the dependency wait (they arrive while the kernel before this one
+  // finishes); the activations, and everything the other warps do, come after it.
   pdl_trigger();
-  pdl_wait();
 
   if (warp == 0) {
     // ---------------- producer
     if (lane == 0) {
+      // the same walk over (unit, k block) twice: at most STAGES steps of it for the early weights, then all of it
+      uint32_t early = 0;
+      for (int unit = blockIdx.x; unit < n_units && early < STAGES; unit += gridDim.x) {
+        const int tile = unit % n_tiles, ks = unit / n_tiles;
+        const int n0 = (tile / tiles_m) * bn;
+        const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
+        for (int kb = kb0; kb < kb1 && early < STAGES; ++kb, ++early) {
+          unsigned char* b_dst = stages + (size_t)early * STAGE_BYTES + STAGE_A_BYTES;
+          mbar_expect_tx(&full_bar[early], STAGE_A_BYTES + bn * BK * 2);
+          tma_load_2d(b_dst, &map_w, &full_bar[early], kb * BK, n0);
+        }
+      }
+      pdl_wait();
       uint32_t it = 0;  // slices requested so far, over all tiles of this block
       bool ok = true;
       for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
@@ -175,20 +189,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
           unsigned char* a_dst = stages + (size_t)s * STAGE_BYTES;
           unsigned char* b_dst = a_dst + STAGE_A_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_A_BYTES + bn * BK * 2);
+          if (it >= early) {
+            mbar_expect_tx(&full_bar[s], STAGE_A_BYTES + bn * BK * 2);
+            tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
+          }
           tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
-          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
         }
       }
       // nothing may still be writing shared memory when the block ends: if someone gave up, wait
       // (bounded) for the copies that were started and not consumed
       if (!ok) {
+        // (an early request for weights whose activations were never asked for cannot complete its barrier;
+        // its bytes have long arrived by the time a bounded wait of a second has expired elsewhere)
         const uint32_t first = it > STAGES ? it - STAGES : 0;
         for (uint32_t j = first; j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
       }
     }
   } else if (warp == 1) {
-    // ---------------- tensor-core issuer
+    // ---------------- tensor-core issuer (reads shared and tensor memory only: no wait of its own)
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, bn);
       // descriptors differ from stage to stage only in their address field (bytes / 16)
@@ -234,6 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else {
     // ---------------- epilogue: warps 2..5, each on its quarter of the 128 lanes
+    pdl_wait();  // the kernel before this one may still read the output buffer
     const int quarter = warp & 3;
     int local = 0;
     for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++local) {
