@@ -92,11 +92,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int s = blockIdx.z, h = blockIdx.y;
+  const int s = blockIdx.x / H, h = blockIdx.x % H;
   const int tok0 = seq_start[s];
   const int q_len = seq_start[s + 1] - tok0;
-  // late row tiles have the most keys to visit: they are handed out first
-  const int row0 = (int)(gridDim.x - 1 - blockIdx.x) * BMQ;
+  // Late row tiles have the most keys to visit.  Blocks are handed out in the order of blockIdx.x, then y:
+  // with the row tile in y, the last row tiles of ALL heads and sequences go out first, then the ones before,
+  // and the short tiles fill the gaps at the end (with the heads outermost, the last head's longest tile
+  // started when the others were nearly done: 2048 tokens took 68 us, now 58; 8192 took 654, now 621).
+  const int row0 = (int)(gridDim.y - 1 - blockIdx.y) * BMQ;
   if (row0 >= q_len) return;  // before any barrier or tensor-memory use: the whole block leaves
   const int pos0 = seq_pos0[s];
   const int kh = h / (H / K);
@@ -411,7 +414,8 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   if (page_size != PAGE) RL_REFUSE(4, "flash_prefill_tc: page size %d, this kernel is built for %d", page_size, PAGE);
   if (q_stride % 8 || out_stride % 8) RL_REFUSE(5, "flash_prefill_tc: strides %d/%d break 16-byte alignment", q_stride, out_stride);
   if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) RL_REFUSE(6, "flash_prefill_tc: operands must be 16-byte aligned");
-  if (H > 65535 || n_seqs > 65535) RL_REFUSE(7, "flash_prefill_tc: H=%d or S=%d exceeds 65535", H, n_seqs);
+  if ((long long)H * n_seqs > 0x7fffffffLL || (max_q_len + BMQ - 1) / BMQ > 65535)
+    RL_REFUSE(7, "flash_prefill_tc: H=%d x S=%d blocks or %d query rows exceed the grid", H, n_seqs, max_q_len);
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "flash_prefill_tc: bad window or scale, or no status word");
   CUtensorMap map_q, map_k, map_v;
   if (make_matrix_map(&map_q, q, n_tokens, q_stride, q_stride, BMQ))
@@ -422,7 +426,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   auto kern = flash_prefill_tc_kernel;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     RL_REFUSE(12, "flash_prefill_tc: cannot get %zu bytes of shared memory", smem);
-  dim3 grid((max_q_len + BMQ - 1) / BMQ, H, n_seqs);
+  dim3 grid(H * n_seqs, (max_q_len + BMQ - 1) / BMQ);
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
                             (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status));
   return 0;
