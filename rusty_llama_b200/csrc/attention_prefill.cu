@@ -80,10 +80,12 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __res
   bf16* k_s1 = v_s0 + BN * STRIDE;
   bf16* v_s1 = k_s1 + BN * STRIDE;
 
-  const int s = blockIdx.z, h = blockIdx.y;
+  const int s = blockIdx.x / H, h = blockIdx.x % H;
   const int tok0 = seq_start[s];
   const int q_len = seq_start[s + 1] - tok0;
-  const int row0 = blockIdx.x * BM;  // first query row of this block within the sequence's rows
+  // first query row of this block within the sequence's rows: blocks go out in the order of blockIdx.x, then
+  // y, so the last row tiles of all heads and sequences, which have the most keys to visit, start first
+  const int row0 = (int)(gridDim.y - 1 - blockIdx.y) * BM;
   if (row0 >= q_len) return;
   const int pos0 = seq_pos0[s];
   const int kh = h / (H / K);
@@ -262,7 +264,7 @@ static int launch_prefill(const bf16* q, int q_stride, const bf16* k_pages, cons
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) RL_REFUSE(8, "flash_prefill: cannot get %zu bytes of shared memory", smem);
   }
-  dim3 grid((max_q_len + BM - 1) / BM, H, n_seqs);
+  dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM);
   kern<<<grid, NTHREADS, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0,
                                          out, out_stride, H, K, hd, window, scale * 1.4426950408889634f);
   RL_LAUNCH_RESULT();
@@ -278,7 +280,8 @@ RL_API int rl_flash_prefill(const void* q, int q_stride, const void* k_pages, co
   if (page_size != BN) RL_REFUSE(3, "flash_prefill: page size %d, this kernel is built for %d", page_size, BN);
   if (hd % 8) RL_REFUSE(4, "flash_prefill: head size %d is not a multiple of 8", hd);
   if (q_stride % 8 || out_stride % 2) RL_REFUSE(5, "flash_prefill: strides %d/%d break 16-byte alignment", q_stride, out_stride);
-  if (H > 65535 || n_seqs > 65535) RL_REFUSE(6, "flash_prefill: H=%d or S=%d exceeds 65535", H, n_seqs);
+  if ((long long)H * n_seqs > 0x7fffffffLL || max_q_len / 16 > 65535)
+    RL_REFUSE(6, "flash_prefill: H=%d x S=%d blocks or %d query rows exceed the grid", H, n_seqs, max_q_len);
   if (window < 0) RL_REFUSE(7, "flash_prefill: negative window");
   const bf16* qq = (const bf16*)q;
   const bf16* kp = (const bf16*)k_pages;
