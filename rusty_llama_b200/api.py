@@ -63,6 +63,9 @@ class LLM:
         repeat_last_n: int = 64,
         frequency_penalty: float = 0.0,
         presence_penalty: float = 0.0,
+        mirostat: int = 0,
+        mirostat_lr: float = 0.1,
+        mirostat_ent: float = 5.0,
     ):
         """Token ids generated after each prompt.
 
@@ -73,14 +76,16 @@ class LLM:
         temperature 0 is greedy; top_p outside (0, 1) turns the nucleus off; seed None
         takes the wall clock.  top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty and
         presence_penalty are the reference's further knobs (`SamplingParams`); setting one selects its
-        longer chain, in which the nucleus is taken before the temperature.  launch_ahead=False makes the loop read every token before it
+        longer chain, in which the nucleus is taken before the temperature; mirostat 1 or 2 (with
+        mirostat_lr, mirostat_ent) replaces top_k, top_p and min_p.  launch_ahead=False makes the loop read every token before it
         starts the next step (same tokens, more idle GPU time)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         batch: List[Sequence[int]] = [prompts] if single else list(prompts)  # type: ignore[list-item]
         if max_new_tokens is not None and steps is not None:
             raise StepError("give max_new_tokens or steps, not both")
         params = SamplingParams(
-            temperature, top_p, seed, top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty
+            temperature, top_p, seed, top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty,
+            mirostat, mirostat_lr, mirostat_ent,
         )
         stats = GenerationStats()
         if max_new_tokens is None:

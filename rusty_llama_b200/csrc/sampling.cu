@@ -671,7 +671,12 @@ struct ChainParams {
   float temperature, top_p, min_p;
   float repeat_penalty, frequency_penalty, presence_penalty;
   int top_k, last_n;
+  int mirostat;             // 0, or 1 / 2: the mode that replaces top-k, top-p and min-p (src/sampler.rs:829-866)
+  float mirostat_tau, mirostat_eta;
 };
+
+#define MIROSTAT_M 100  // candidates of the Zipf estimate of mirostat 1 (the reference's mirostat_m)
+#define MIROSTAT_LIST 128
 
 #define HISTORY_MAX 1024  // tokens of history that the penalties can look back on
 
@@ -686,11 +691,12 @@ __device__ __forceinline__ void team_sum2(Team& tm, const float* a, F f, float& 
 // grid: (team size, rows), clusters of (team size, 1, 1).  work: per row 2 * n_pad floats (the penalised
 // logits, then the weights of the current softmax).  history[slot][HISTORY_MAX] with history_count[slot]
 // tokens accepted so far: the ring of the last `last_n` sampled tokens (src/sampler.rs:339-347).
+// mirostat_mu[slot]: the surprise ceiling that mirostat adapts, NaN for a sequence that has not drawn yet.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int n, int n_pad, ChainParams cp,
                     unsigned long long* __restrict__ rng_states, const int* __restrict__ slot_of_row,
-                    int* __restrict__ history, int* __restrict__ history_count, float* __restrict__ work,
-                    int* __restrict__ out) {
+                    int* __restrict__ history, int* __restrict__ history_count, float* __restrict__ mirostat_mu,
+                    float* __restrict__ work, int* __restrict__ out) {
   __shared__ float red[32];
   __shared__ ArgMax sh_arg[32];
   __shared__ Exchange exchange;
@@ -764,8 +770,106 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
   int E = 0, N = n;
   bool filtered = false, collapsed = false;
 
+  // ---- mirostat: temperature first, then its own cut in the place of top-k, top-p and min-p
+  float mu = 0.f;
+  if (cp.mirostat != 0) {
+    __shared__ float cand[MIROSTAT_LIST], all[MIROSTAT_LIST], sorted[MIROSTAT_LIST];
+    __shared__ int cand_n, keep_s;
+    mu = mirostat_mu[slot];
+    if (!(mu == mu)) mu = 2.0f * cp.mirostat_tau;  // a new sequence (src/sampler.rs:379, :451-453)
+    const float t = cp.temperature, mx_t = mx_l / t;
+    float sum_all, unused;
+    team_sum2(tm, L, [&](float v, int, float& s, float&) { s += expf(v / t - mx_t); }, sum_all, unused);
+    const float inv_all = 1.0f / sum_all;
+    sweep(L, tm.begin, tm.end, [&](float v, int i) { q[i] = expf(v / t - mx_t) * inv_all; });
+    __syncthreads();
+    if (cp.mirostat == 2) {
+      // the candidates, in descending order, up to the first whose surprise -log2 p exceeds mu; at least
+      // one (src/sampler.rs:501-506)
+      uint32_t inv_key = 0;
+      sweep(L, tm.begin, tm.end, [&](float v, int i) { if (!(-log2f(q[i]) > mu)) inv_key = max(inv_key, ~okey(v)); });
+      const uint32_t lowest = tm.umax(inv_key);
+      if (lowest != 0u) {
+        T = ~lowest;
+        float cnt, unused2;
+        team_sum2(tm, L, [&](float v, int, float& s, float&) { s += okey(v) == T ? 1.f : 0.f; }, cnt, unused2);
+        E = (int)cnt;
+      } else {  // none: the first of the sorted candidates stays
+        T = okey(mx_l);
+        E = 1;
+      }
+    } else {
+      // mirostat 1: the Zipf exponent from the ratios of the MIROSTAT_M largest probabilities, and from it
+      // the number of candidates that keeps the expected surprise near mu (src/sampler.rs:401-431)
+      const int mm = min(MIROSTAT_M, n);
+      unsigned long long above;
+      bool fell;
+      const uint32_t key_m = select_desc(
+          tm, L, [&](float v, int, uint32_t& key, unsigned long long& w) { key = okey(v); w = 1ull; },
+          (unsigned long long)(mm - 1), hist, total_bins, &above, &fell);
+      if (threadIdx.x == 0) cand_n = 0;
+      __syncthreads();
+      sweep(L, tm.begin, tm.end, [&](float v, int i) {
+        if (okey(v) > key_m) {
+          const int at = atomicAdd(&cand_n, 1);
+          if (at < MIROSTAT_LIST) cand[at] = q[i];
+        }
+      });
+      tm.cluster.sync();
+      // every block gathers all blocks' candidates (fewer than mm) and fills up with the mm-th largest value
+      const float q_m = expf(unkey(key_m) / t - mx_t) * inv_all;
+      if (threadIdx.x < MIROSTAT_LIST) {
+        int j = threadIdx.x;
+        float v = threadIdx.x < mm ? q_m : -1.f;  // (places past mm sort to the end)
+        for (int rk = 0; rk < tm.size; ++rk) {
+          const int c = min(*tm.cluster.map_shared_rank(&cand_n, rk), MIROSTAT_LIST);
+          if (j < c) {
+            v = tm.cluster.map_shared_rank(cand, rk)[j];
+            break;
+          }
+          j -= c;
+        }
+        all[threadIdx.x] = v;
+      }
+      __syncthreads();
+      if (threadIdx.x < MIROSTAT_LIST) {
+        // descending order by counting, for each value, the larger ones and the equal ones before it
+        const float mine = all[threadIdx.x];
+        int place = 0;
+        for (int k = 0; k < MIROSTAT_LIST; ++k) place += (all[k] > mine || (all[k] == mine && k < (int)threadIdx.x)) ? 1 : 0;
+        sorted[place] = mine;
+      }
+      tm.cluster.sync();  // (also: nobody leaves this part while a team mate still reads its list)
+      if (threadIdx.x == 0) {
+        const int bound = min(max(MIROSTAT_M - 1, 0), max(n - 1, 0));
+        double sum_ti_bi = 0.0, sum_ti_sq = 0.0;
+        for (int i = 0; i < bound; ++i) {
+          const double t_i = log((double)(i + 2) / (double)(i + 1));
+          const double b_i = log((double)sorted[i] / (double)sorted[i + 1]);
+          sum_ti_bi += t_i * b_i;
+          sum_ti_sq += t_i * t_i;
+        }
+        const double s_hat = sum_ti_bi / sum_ti_sq;
+        const double epsilon_hat = s_hat - 1.0;
+        const double k = pow((epsilon_hat * pow(2.0, (double)mu)) / (1.0 - pow(-epsilon_hat, (double)n)), 1.0 / s_hat);
+        long long keep = isfinite(k) ? (k >= 9.2e18 ? 0x7fffffffffffffffLL : (k <= -9.2e18 ? -0x7fffffffffffffffLL - 1 : (long long)k)) : 1;
+        keep = keep < 1 ? 1 : keep;
+        keep_s = (int)(keep > n ? n : keep);
+      }
+      __syncthreads();
+      const int keep = keep_s;
+      if (keep < n) {
+        T = select_desc(
+            tm, L, [&](float v, int, uint32_t& key, unsigned long long& w) { key = okey(v); w = 1ull; },
+            (unsigned long long)(keep - 1), hist, total_bins, &above, &fell);
+        E = keep - (int)above;
+      }
+    }
+    filtered = true;
+  }
+
   // ---- top-k (src/sampler.rs:239-251)
-  if (cp.top_k > 0 && cp.top_k < N) {
+  if (cp.mirostat == 0 && cp.top_k > 0 && cp.top_k < N) {
     unsigned long long above;
     bool fell;
     T = select_desc(
@@ -777,7 +881,7 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
   }
 
   // ---- top-p over the softmax of the survivors (src/sampler.rs:120-160)
-  if (cp.top_p > 0.f && cp.top_p < 1.f) {
+  if (cp.mirostat == 0 && cp.top_p > 0.f && cp.top_p < 1.f) {
     float sum_gt, unused;
     team_sum2(tm, L, [&](float v, int, float& s, float&) { if (okey(v) > T) s += expf(v - mx_l); }, sum_gt, unused);
     const float e_t = E > 0 ? expf(unkey(T) - mx_l) : 0.f;
@@ -837,7 +941,7 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
   }
 
   // ---- min-p in logit space: logit >= max + ln p, at least one (src/sampler.rs:265-281)
-  if (!collapsed && cp.min_p > 0.f && N >= 2) {
+  if (cp.mirostat == 0 && !collapsed && cp.min_p > 0.f && N >= 2) {
     const uint32_t tk = okey(mx_l + logf(cp.min_p));
     if (tk > T) {
       float c_ge, unused;
@@ -859,6 +963,7 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
 
   // ---- the choice: argmax (:225-228), or temperature and a draw in the candidates' order (:101-106, :190-215)
   int chosen;
+  float inv_final = 0.f;
   if (collapsed || !draws) {
     chosen = team_argmax(tm, L, 1.0f, sh_arg);
   } else {
@@ -867,6 +972,7 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
     team_sum2(tm, L, [&](float v, int, float& s, float&) { if (okey(v) > T) s += expf(v / t - mx_t); }, sum_gt, unused);
     const float e_t = E > 0 ? expf(unkey(T) / t - mx_t) : 0.f;
     const float inv = 1.0f / (sum_gt + (float)E * e_t);
+    inv_final = inv;
     sweep(L, tm.begin, tm.end, [&](float v, int i) { q[i] = okey(v) > T || !filtered ? expf(v / t - mx_t) * inv : 0.f; });
     __syncthreads();
     const float q_t = e_t * inv;
@@ -902,6 +1008,11 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
   }
   if (tm.rank == 0 && threadIdx.x == 0) {
     out[r] = chosen;
+    if (cp.mirostat != 0) {
+      // mu moves toward the surprise that was observed (src/sampler.rs:446-448, :521-523)
+      const float p_sel = expf(L[chosen] / cp.temperature - mx_l / cp.temperature) * inv_final;
+      mirostat_mu[slot] = mu - cp.mirostat_eta * (-log2f(p_sel) - cp.mirostat_tau);
+    }
     if (cp.last_n > 0) {  // the chosen token joins the ring (src/sampler.rs:339-347)
       history[(size_t)slot * HISTORY_MAX + accepted % cp.last_n] = chosen;
       history_count[slot] = accepted + 1;
@@ -938,18 +1049,24 @@ RL_API int rl_sample(const float* logits, long long row_stride, int n_rows, int 
 }
 
 // The longer chain.  work: n_rows * 2 * n_pad floats with n_pad = n rounded up to 4.  history: int
-// [slots][1024] and history_count: int [slots], both indexed by slot_of_row[r], like rng_states.
+// [slots][1024], history_count: int [slots] and mirostat_mu: float [slots] (may be null without mirostat),
+// all indexed by slot_of_row[r], like rng_states.
 RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows, int n, float temperature, float top_p,
                            int top_k, float min_p, float repeat_penalty, int last_n, float frequency_penalty,
-                           float presence_penalty, unsigned long long* rng_states, const int* slot_of_row,
-                           int* history, int* history_count, float* work, int* out, cudaStream_t stream) {
+                           float presence_penalty, int mirostat, float mirostat_tau, float mirostat_eta,
+                           unsigned long long* rng_states, const int* slot_of_row, int* history, int* history_count,
+                           float* mirostat_mu, float* work, int* out, cudaStream_t stream) {
   if (n_rows <= 0 || n <= 0) RL_REFUSE(1, "sample_chain: rows=%d n=%d", n_rows, n);
   if (!(temperature >= 0.f)) RL_REFUSE(2, "sample_chain: temperature %f is negative", temperature);
   if (!rng_states || !slot_of_row || !work || !history || !history_count) RL_REFUSE(3, "sample_chain: missing random state, history or scratch");
   if (n_rows > 65535) RL_REFUSE(4, "sample_chain: %d rows exceed 65535", n_rows);
   if (last_n < 0 || last_n > HISTORY_MAX) RL_REFUSE(5, "sample_chain: a history of %d tokens is outside 0..%d", last_n, HISTORY_MAX);
   if (top_k < 0 || !(repeat_penalty > 0.f)) RL_REFUSE(6, "sample_chain: top_k %d or repeat penalty %f out of range", top_k, repeat_penalty);
-  ChainParams cp = {temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k, last_n};
+  if (mirostat < 0 || mirostat > 2) RL_REFUSE(7, "sample_chain: mirostat %d is none of 0, 1, 2", mirostat);
+  if (mirostat != 0 && (!(temperature > 0.f) || mirostat_mu == nullptr))
+    RL_REFUSE(8, "sample_chain: mirostat needs a positive temperature (got %f) and its state", temperature);
+  ChainParams cp = {temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k, last_n,
+                    mirostat, mirostat_tau, mirostat_eta};
   int team = 1;
   while (team < TEAM_MAX && n / (2 * team) >= 4096) team *= 2;
   cudaLaunchConfig_t cfg = {};
@@ -966,6 +1083,6 @@ RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows
   cfg.numAttrs = 1;
   const int n_pad = (n + 3) & ~3;
   RL_LAUNCH_CHECK(cudaLaunchKernelEx(&cfg, sample_chain_kernel, logits, row_stride, n, n_pad, cp, rng_states, slot_of_row, history,
-                                     history_count, work, out));
+                                     history_count, mirostat_mu, work, out));
   return 0;
 }

@@ -692,13 +692,16 @@ def sample_chain(
     logits: torch.Tensor, temperature: float, top_p: float, top_k: int, min_p: float, repeat_penalty: float,
     last_n: int, frequency_penalty: float, presence_penalty: float, rng_states: torch.Tensor, slot_of_row: torch.Tensor,
     history: torch.Tensor, history_count: torch.Tensor, work: torch.Tensor, out: Optional[torch.Tensor] = None,
+    mirostat: int = 0, mirostat_tau: float = 5.0, mirostat_eta: float = 0.1, mirostat_mu: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One token per row through penalties -> top-k -> top-p -> min-p -> temperature -> draw (temperature 0:
     the argmax of the penalised logits, no draw).
 
     Row r belongs to slot slot_of_row[r]: it uses and advances rng_states[slot], reads the last `last_n`
     chosen tokens of history[slot] (int32 [slots, 1024] with history_count[slot] tokens written so far) for
-    the penalties and appends its choice.  work: float32, at least rows * 2 * (vocabulary rounded up to 4)."""
+    the penalties and appends its choice.  work: float32, at least rows * 2 * (vocabulary rounded up to 4).
+    mirostat 1 or 2: penalties -> temperature -> mirostat's own cut and draw; mirostat_mu: float32 [slots], NaN
+    for a sequence that has not drawn yet."""
     _cuda(logits, "sample_chain logits", torch.float32, contiguous=False)
     stride = _rows(logits, "sample_chain logits")
     R, n = logits.shape
@@ -716,11 +719,16 @@ def sample_chain(
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     _cuda(out, "sample_chain out", torch.int32)
+    if mirostat:
+        _need(mirostat_mu is not None, "sample_chain: mirostat needs its state")
+        _cuda(mirostat_mu, "sample_chain mirostat_mu", torch.float32)
+        _need(mirostat_mu.numel() == history_count.numel(), "sample_chain: one mirostat state per slot")
     lib = build.load("sampling")
     rc = lib.rl_sample_chain(
         _p(logits), c_ll(stride), c_int(R), c_int(n), c_float(temperature), c_float(top_p), c_int(top_k), c_float(min_p),
-        c_float(repeat_penalty), c_int(last_n), c_float(frequency_penalty), c_float(presence_penalty), _p(rng_states),
-        _p(slot_of_row), _p(history), _p(history_count), _p(work), _p(out), _stream(),
+        c_float(repeat_penalty), c_int(last_n), c_float(frequency_penalty), c_float(presence_penalty), c_int(mirostat),
+        c_float(mirostat_tau), c_float(mirostat_eta), _p(rng_states), _p(slot_of_row), _p(history), _p(history_count),
+        _p(mirostat_mu) if mirostat_mu is not None else c_void_p(0), _p(work), _p(out), _stream(),
     )
     _check(lib, rc, "sample_chain")
     return out

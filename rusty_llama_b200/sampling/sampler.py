@@ -9,7 +9,8 @@ reference builds another chain, penalties -> top-k -> top-p -> min-p -> temperat
 (src/sampler.rs:821-931), in which the nucleus is taken before the temperature; so does this
 module.  The reference keeps one chain per server slot (src/server.rs:288, :513); here the
 generator states and the penalties' token histories of all sequence slots live in device arrays
-and the kernels advance them.  Not built: mirostat, XTC, DRY and grammars.
+and the kernels advance them.  Mirostat 1 and 2 are a mode of that chain (penalties -> temperature ->
+mirostat).  Not built: XTC, DRY and grammars.
 """
 
 from __future__ import annotations
@@ -55,7 +56,9 @@ class SamplingParams:
     top_k: keep the k largest logits, 0 = off.  min_p: keep logits >= max + ln(min_p), 0 = off.
     repeat_penalty (1 = off), frequency_penalty, presence_penalty (0 = off) act on the tokens among the
     last repeat_last_n chosen ones (default 64): the reference's `--top-k`, `--min-p`, `--repeat-penalty`,
-    `--repeat-last-n`, `--frequency-penalty`, `--presence-penalty` (src/main.rs:478-485)."""
+    `--repeat-last-n`, `--frequency-penalty`, `--presence-penalty` (src/main.rs:478-485).
+    mirostat 1 or 2 (`--mirostat`, with `--mirostat-lr` eta and `--mirostat-ent` tau) replaces top-k, top-p
+    and min-p by its own adaptive cut (src/sampler.rs:829-866) and needs a temperature above 0."""
 
     temperature: float = 1.0
     top_p: float = 0.9
@@ -66,6 +69,9 @@ class SamplingParams:
     repeat_last_n: int = 64
     frequency_penalty: float = 0.0
     presence_penalty: float = 0.0
+    mirostat: int = 0
+    mirostat_lr: float = 0.1
+    mirostat_ent: float = 5.0
 
     def validate(self) -> None:
         if not (self.temperature >= 0.0) or self.temperature == float("inf"):
@@ -78,6 +84,10 @@ class SamplingParams:
             raise ConfigError(f"min_p {self.min_p} or repeat_penalty {self.repeat_penalty} out of range")
         if not (0 <= self.repeat_last_n <= ops.SAMPLE_HISTORY_MAX):
             raise ConfigError(f"repeat_last_n must lie in 0..{ops.SAMPLE_HISTORY_MAX}, got {self.repeat_last_n}")
+        if self.mirostat not in (0, 1, 2):
+            raise ConfigError(f"mirostat must be 0, 1 or 2, got {self.mirostat}")
+        if self.mirostat and not (self.temperature > 0.0):
+            raise ConfigError("mirostat divides the logits by the temperature, which must be above 0")
 
     @property
     def penalties_on(self) -> bool:
@@ -86,7 +96,7 @@ class SamplingParams:
     @property
     def longer_chain(self) -> bool:
         """Whether the reference would build its longer chain for these values (src/sampler.rs:868-876)."""
-        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on
+        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on or self.mirostat != 0
 
 
 class PendingTokens:
@@ -112,6 +122,8 @@ class Sampler:
         self.max_seqs = max_seqs
         self.history: Optional[torch.Tensor] = None
         self.history_count = torch.zeros(max_seqs, dtype=torch.int32, device=self.device)
+        # mirostat's surprise ceiling per slot; NaN: not drawn yet (the kernel then starts from 2 tau)
+        self.mirostat_mu = torch.full((max_seqs,), float("nan"), dtype=torch.float32, device=self.device)
         self._workspace = workspace
         self._scratch: Optional[torch.Tensor] = None
         self._pinned = None
@@ -123,6 +135,7 @@ class Sampler:
         idx = torch.tensor(list(slots), dtype=torch.long, device=self.device)
         self.rng_states[idx] = torch.from_numpy(vals).to(self.device)
         self.history_count[idx] = 0  # a new sequence has chosen nothing yet (src/sampler.rs:349-351)
+        self.mirostat_mu[idx] = float("nan")  # (src/sampler.rs:451-453)
 
     def begin_fetch(self, tokens: torch.Tensor) -> "PendingTokens":
         """Start copying sampled tokens to the host, now, in stream order: work that is launched
@@ -172,4 +185,6 @@ class Sampler:
             logits, params.temperature, params.top_p, params.top_k, params.min_p, params.repeat_penalty,
             params.repeat_last_n if params.penalties_on else 0, params.frequency_penalty, params.presence_penalty,
             self.rng_states, index, self.history, self.history_count, work,
+            mirostat=params.mirostat, mirostat_tau=params.mirostat_ent, mirostat_eta=params.mirostat_lr,
+            mirostat_mu=self.mirostat_mu,
         )

@@ -345,7 +345,9 @@ class PlainChain:
     sorts with an unstable sort, the stable sort here keeps equal values in index order."""
 
     def __init__(self, temperature=1.0, top_p=0.9, seed=1, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64,
-                 frequency_penalty=0.0, presence_penalty=0.0):
+                 frequency_penalty=0.0, presence_penalty=0.0, mirostat=0, mirostat_lr=0.1, mirostat_ent=5.0, mirostat_m=100):
+        self.mirostat, self.eta, self.tau, self.m = mirostat, mirostat_lr, mirostat_ent, mirostat_m
+        self.mu = np.float32(2.0) * np.float32(mirostat_ent)  # (src/sampler.rs:379)
         self.t, self.top_p, self.top_k, self.min_p = temperature, top_p, top_k, min_p
         self.repeat, self.last_n, self.freq, self.present = repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty
         self.rng = PlainRng(seed)
@@ -376,6 +378,8 @@ class PlainChain:
                     l = f32(l - f32(self.present))
                 out.append((i, l, p))
             cands = out
+        if self.mirostat:
+            return self._accept(self._mirostat(cands))
         # top-k (src/sampler.rs:239-251): the k largest logits; here in descending order
         if self.top_k != 0 and self.top_k < len(cands):
             cands = sorted(cands, key=lambda c: -float(c[1]))[: self.top_k]
@@ -425,9 +429,53 @@ class PlainChain:
                 if target < cdf:
                     sel = k
                     break
-        token = cands[sel][0]
+        return self._accept(cands[sel][0])
+
+    def _accept(self, token: int) -> int:
         if self.last_n > 0:
             if len(self.ring) == self.last_n:
                 self.ring.pop(0)
             self.ring.append(token)
         return token
+
+    def _mirostat(self, cands) -> int:
+        """penalties (done) -> temperature -> mirostat 1 (src/sampler.rs:401-449) or 2 (:494-524)."""
+        f32 = np.float32
+        cands = [(i, f32(l / f32(self.t)), p) for i, l, p in cands]
+        n = len(cands)
+        cands = self._softmax(sorted(cands, key=lambda c: -float(c[1])))
+        if self.mirostat == 1:
+            bound = min(max(self.m - 1, 0), max(n - 1, 0))
+            sum_ti_bi = sum_ti_sq = 0.0
+            for i in range(bound):
+                t_i = math.log((i + 2) / (i + 1))
+                with np.errstate(divide="ignore", invalid="ignore"):
+                    b_i = float(np.log(np.float64(cands[i][2]) / np.float64(cands[i + 1][2])))
+                sum_ti_bi += t_i * b_i
+                sum_ti_sq += t_i * t_i
+            with np.errstate(all="ignore"):
+                s_hat = np.float64(sum_ti_bi) / np.float64(sum_ti_sq)
+                eps = s_hat - 1.0
+                k = np.power((eps * np.power(2.0, np.float64(self.mu))) / (1.0 - np.power(-eps, np.float64(n))), 1.0 / s_hat)
+            keep = int(k) if np.isfinite(k) and abs(k) < 9.2e18 else (1 if not np.isfinite(k) else (2**63 - 1 if k > 0 else -(2**63)))
+            keep = min(max(keep, 1), n)
+        else:
+            cutoff = n
+            for k_, c in enumerate(cands):
+                with np.errstate(divide="ignore"):
+                    if -np.log2(c[2]) > self.mu:
+                        cutoff = k_
+                        break
+            keep = max(cutoff, 1)
+        cands = self._softmax(cands[:keep])
+        coin = f32(self.rng.next_f32())
+        cdf, sel = f32(0.0), len(cands) - 1
+        for k_, c in enumerate(cands):
+            cdf = f32(cdf + c[2])
+            if coin < cdf:
+                sel = k_
+                break
+        with np.errstate(divide="ignore"):
+            observed = f32(-np.log2(cands[sel][2]))
+        self.mu = f32(self.mu - f32(self.eta) * f32(observed - f32(self.tau)))
+        return cands[sel][0]

@@ -230,8 +230,11 @@ def test_command_line_options_follow_the_reference(tmp_path):
     assert (a["top_k"], a["min_p"], a["repeat_penalty"], a["repeat_last_n"], a["frequency_penalty"], a["presence_penalty"]) == (0, 0.0, 1.0, 64, 0.0, 0.0)  # src/main.rs:478-485
     a = parse_args(["m", "--top-k", "40", "--min-p", "0.05", "--repeat-penalty", "1.1", "--repeat-last-n", "32", "--frequency-penalty", "0.2", "--presence-penalty", "0.3"])
     assert (a["top_k"], a["min_p"], a["repeat_penalty"], a["repeat_last_n"], a["frequency_penalty"], a["presence_penalty"]) == (40, 0.05, 1.1, 32, 0.2, 0.3)
+    a = parse_args(["m", "--mirostat", "2", "--mirostat-lr", "0.2", "--mirostat-ent", "4"])
+    assert (a["mirostat"], a["mirostat_lr"], a["mirostat_ent"]) == (2, 0.2, 4.0)
+    assert (parse_args(["m"])["mirostat"], parse_args(["m"])["mirostat_lr"], parse_args(["m"])["mirostat_ent"]) == (0, 0.1, 5.0)
     with pytest.raises(SystemExit, match="unknown option"):
-        parse_args(["m", "--mirostat", "2"])  # not built
+        parse_args(["m", "--xtc-probability", "0.5"])  # not built
     assert parse_prompts("1, 2 3") == [[1, 2, 3]]
     f = tmp_path / "prompts.txt"
     f.write_text("5 6\n\n7,8,9\n")
@@ -252,10 +255,12 @@ def test_sampling_params_pick_the_chain_as_the_reference_does():
 
     assert not SamplingParams(0.8, 0.9, 1).longer_chain
     assert not SamplingParams(0.8, 0.9, 1, repeat_last_n=8).longer_chain  # a window alone changes nothing
-    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5)):
+    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5), dict(mirostat=2)):
         p = SamplingParams(0.8, 0.9, 1, **kw)
         p.validate()
         assert p.longer_chain
-    for kw in (dict(top_k=-1), dict(repeat_penalty=0.0), dict(repeat_last_n=5000), dict(min_p=float("nan"))):
+    for kw in (dict(top_k=-1), dict(repeat_penalty=0.0), dict(repeat_last_n=5000), dict(min_p=float("nan")), dict(mirostat=3)):
         with pytest.raises(ConfigError):
             SamplingParams(0.8, 0.9, 1, **kw).validate()
+    with pytest.raises(ConfigError, match="temperature"):
+        SamplingParams(0.0, 0.9, 1, mirostat=1).validate()

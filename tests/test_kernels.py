@@ -987,6 +987,50 @@ def test_sample_chain_follows_the_plain_chain(ops, n, chain):
         assert count.cpu().tolist() == [10 if s in slot_of_row else 0 for s in range(slots)]
 
 
+@pytest.mark.parametrize("n", [300, 20001])
+@pytest.mark.parametrize("mode, tau, eta, t, penalised", [(2, 3.0, 0.1, 0.8, False), (2, 6.0, 0.3, 1.2, True), (1, 3.0, 0.1, 0.9, False), (1, 5.0, 0.2, 1.0, True)])
+def test_sample_chain_mirostat_follows_the_plain_chain(ops, n, mode, tau, eta, t, penalised):
+    """Mirostat 1 and 2 (penalties -> temperature -> its own cut and draw): the same tokens as the plain chain
+    draw after draw, with the surprise ceiling mu carried from one draw to the next on the device."""
+    rows = 3
+    g = torch.Generator().manual_seed(n + mode)
+    logits = [torch.randn(rows, n, generator=g) * 3.0 for _ in range(12)]
+    seeds = [5, 2**33 + 1, 77]
+    states = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    index = torch.arange(rows, dtype=torch.int32, device=DEV)
+    history = torch.zeros(rows, 1024, dtype=torch.int32, device=DEV)
+    count = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    mu = torch.full((rows,), float("nan"), device=DEV)
+    work = torch.empty(rows * 2 * ((n + 3) // 4 * 4), device=DEV)
+    pen = dict(repeat_penalty=1.2, presence_penalty=0.3, repeat_last_n=8) if penalised else {}
+    plain = [PlainChain(temperature=t, seed=s, mirostat=mode, mirostat_lr=eta, mirostat_ent=tau, **pen) for s in seeds]
+    same = total = 0
+    for d, l in enumerate(logits):
+        got = ops.sample_chain(
+            l.to(DEV), t, 0.9, 0, 0.0, pen.get("repeat_penalty", 1.0), pen.get("repeat_last_n", 0) if penalised else 0, 0.0,
+            pen.get("presence_penalty", 0.0), states, index, history, count, work, mirostat=mode, mirostat_tau=tau, mirostat_eta=eta,
+            mirostat_mu=mu,
+        ).cpu().tolist()
+        want = [plain[r].sample(l[r].tolist()) for r in range(rows)]
+        for r in range(rows):
+            total += 1
+            if got[r] == want[r]:
+                same += 1
+            else:
+                # (mirostat 1 rounds a real number down to the count of candidates it keeps, from sums of a hundred
+                # logarithms: a count that differs by one now and then moves a draw); go on from the kernel's state
+                plain[r].mu = np.float32(mu[r].item())
+                if plain[r].ring:
+                    plain[r].ring[-1] = got[r]
+        got_mu = mu.cpu().numpy()
+        want_mu = np.array([p.mu for p in plain], dtype=np.float32)
+        for r in range(rows):
+            if got[r] == want[r]:
+                assert abs(got_mu[r] - want_mu[r]) <= 2e-4 * max(1.0, abs(want_mu[r])), f"draw {d} row {r}: mu {got_mu[r]} against {want_mu[r]}"
+    assert same >= total - (0 if mode == 2 else 3), f"{total - same} of {total} draws differ"
+    assert np.array_equal(states.cpu().numpy().view(np.uint64), np.array([p.rng.state for p in plain], dtype=np.uint64))
+
+
 def test_sample_chain_takes_equal_logits_in_index_order(ops):
     """Equal logits at the edge of top-k and inside the draw: the first by index stay, as in the plain chain's
     stable sorts."""

@@ -242,6 +242,15 @@ def test_generation_with_the_longer_sampler_chain(llms, tiny_weights):
         agree += int(got == want)
         assert len(got) == 24
     assert agree >= 2  # a draw within rounding of a boundary parts the streams
+    # mirostat keeps its surprise ceiling per sequence on the device, from the first draw of a call on
+    miro = dict(temperature=0.9, mirostat=2, mirostat_ent=3.0, mirostat_lr=0.2)
+    outs = llm.generate(prompts, max_new_tokens=24, seed=5, stop_token_ids=[], **miro)
+    assert outs == llm.generate(prompts, max_new_tokens=24, seed=5, stop_token_ids=[], **miro)
+    agree = sum(
+        int(got == plain_generate(cfg, w, p, 24, stop_token_ids=[], chain=PlainChain(seed=sequence_seed(5, i), **miro)))
+        for i, (p, got) in enumerate(zip(prompts, outs))
+    )
+    assert agree >= 2
     # greedy with a strong repetition penalty: no token twice within the window, and not the plain greedy's run
     greedy = llm.generate(prompts[0], max_new_tokens=20, temperature=0.0, stop_token_ids=[])
     pen = llm.generate(prompts[0], max_new_tokens=20, temperature=0.0, repeat_penalty=50.0, presence_penalty=100.0, repeat_last_n=4, stop_token_ids=[])
