@@ -66,6 +66,8 @@ class LLM:
         mirostat: int = 0,
         mirostat_lr: float = 0.1,
         mirostat_ent: float = 5.0,
+        xtc_probability: float = 0.0,
+        xtc_threshold: float = 0.1,
     ):
         """Token ids generated after each prompt.
 
@@ -77,7 +79,8 @@ class LLM:
         takes the wall clock.  top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty and
         presence_penalty are the reference's further knobs (`SamplingParams`); setting one selects its
         longer chain, in which the nucleus is taken before the temperature; mirostat 1 or 2 (with
-        mirostat_lr, mirostat_ent) replaces top_k, top_p and min_p.  launch_ahead=False makes the loop read every token before it
+        mirostat_lr, mirostat_ent) replaces top_k, top_p and min_p; xtc_probability > 0 (with xtc_threshold) adds
+        the "exclude top choices" stage.  launch_ahead=False makes the loop read every token before it
         starts the next step (same tokens, more idle GPU time)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         batch: List[Sequence[int]] = [prompts] if single else list(prompts)  # type: ignore[list-item]
@@ -85,7 +88,7 @@ class LLM:
             raise StepError("give max_new_tokens or steps, not both")
         params = SamplingParams(
             temperature, top_p, seed, top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty,
-            mirostat, mirostat_lr, mirostat_ent,
+            mirostat, mirostat_lr, mirostat_ent, xtc_probability, xtc_threshold,
         )
         stats = GenerationStats()
         if max_new_tokens is None:

@@ -12,8 +12,9 @@
     --top-k <int>  --min-p <float>  --repeat-penalty <float>  --repeat-last-n <int>
     --frequency-penalty <float>  --presence-penalty <float>
     --mirostat <0|1|2>  --mirostat-lr <float>  --mirostat-ent <float>
-                the reference's further sampling knobs, with its defaults (0, 0, 1.0, 64, 0, 0; 0, 0.1, 5.0;
-                src/main.rs:478-488); its XTC, DRY and grammar options are not built
+    --xtc-probability <float>  --xtc-threshold <float>
+                the reference's further sampling knobs, with its defaults (0, 0, 1.0, 64, 0, 0; 0, 0.1, 5.0; 0, 0.1;
+                src/main.rs:478-490); its DRY and grammar options, which work on token strings, are not built
 Where the reference has `-z tokenizer` and `--backend`, this program has `--dtype bfloat16|float32`
 (the second is the true 32-bit path) and `--random SEED` to run a folder that holds only a
 config.json with random weights.  Generated ids go to standard output, one line per prompt, and
@@ -51,6 +52,7 @@ def parse_args(argv: List[str]) -> dict:
         "dtype": "bfloat16", "random": None, "device": "cuda:0", "max_tokens": None,
         "top_k": 0, "min_p": 0.0, "repeat_penalty": 1.0, "repeat_last_n": 64, "frequency_penalty": 0.0,
         "presence_penalty": 0.0, "mirostat": 0, "mirostat_lr": 0.1, "mirostat_ent": 5.0,
+        "xtc_probability": 0.0, "xtc_threshold": 0.1,
     }
     flags = {
         "-t": ("temperature", float), "-p": ("top_p", float), "-s": ("seed", int), "-n": ("steps", int),
@@ -60,6 +62,7 @@ def parse_args(argv: List[str]) -> dict:
         "--repeat-last-n": ("repeat_last_n", int), "--frequency-penalty": ("frequency_penalty", float),
         "--presence-penalty": ("presence_penalty", float),
         "--mirostat": ("mirostat", int), "--mirostat-lr": ("mirostat_lr", float), "--mirostat-ent": ("mirostat_ent", float),
+        "--xtc-probability": ("xtc_probability", float), "--xtc-threshold": ("xtc_threshold", float),
     }
     i = 1
     while i < len(argv):
@@ -98,6 +101,7 @@ def main(argv=None) -> int:
         top_k=args["top_k"], min_p=args["min_p"], repeat_penalty=args["repeat_penalty"], repeat_last_n=args["repeat_last_n"],
         frequency_penalty=args["frequency_penalty"], presence_penalty=args["presence_penalty"],
         mirostat=args["mirostat"], mirostat_lr=args["mirostat_lr"], mirostat_ent=args["mirostat_ent"],
+        xtc_probability=args["xtc_probability"], xtc_threshold=args["xtc_threshold"],
     )
     dt = time.perf_counter() - t0
     n = 0

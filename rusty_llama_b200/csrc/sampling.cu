@@ -673,6 +673,7 @@ struct ChainParams {
   int top_k, last_n;
   int mirostat;             // 0, or 1 / 2: the mode that replaces top-k, top-p and min-p (src/sampler.rs:829-866)
   float mirostat_tau, mirostat_eta;
+  float xtc_probability, xtc_threshold;  // "exclude top choices", after min-p (src/sampler.rs:569-602); 0 = off
 };
 
 #define MIROSTAT_M 100  // candidates of the Zipf estimate of mirostat 1 (the reference's mirostat_m)
@@ -696,7 +697,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int n, int n_pad, ChainParams cp,
                     unsigned long long* __restrict__ rng_states, const int* __restrict__ slot_of_row,
                     int* __restrict__ history, int* __restrict__ history_count, float* __restrict__ mirostat_mu,
-                    float* __restrict__ work, int* __restrict__ out) {
+                    unsigned long long* __restrict__ xtc_states, float* __restrict__ work, int* __restrict__ out) {
   __shared__ float red[32];
   __shared__ ArgMax sh_arg[32];
   __shared__ Exchange exchange;
@@ -961,6 +962,61 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
     filtered = true;
   }
 
+  // ---- XTC: with a probability of its own, all but the least likely of the candidates above a threshold go
+  // (src/sampler.rs:569-602).  What goes is struck from the working logits (minus infinity), so the stages
+  // below need no upper bound.
+  if (cp.mirostat == 0 && !collapsed && cp.xtc_probability > 0.f && !(cp.xtc_threshold > 0.5f) && N >= 2) {
+    // its own generator, started from the same seed; one draw whether or not the filter then acts
+    if (tm.rank == 0 && threadIdx.x == 0) {
+      unsigned long long* st = xtc_states + slot;
+      unsigned long long z = *st;
+      z ^= z >> 12;
+      z ^= z << 25;
+      z ^= z >> 27;
+      *st = z;
+      exchange.f[tm.turn][2] = (float)((uint32_t)((z * 0x2545F4914F6CDD1DULL) >> 32) >> 8) / 16777216.0f;
+    }
+    tm.cluster.sync();
+    const float chance = tm.of(0)->f[tm.turn][2];
+    tm.turn ^= 1;
+    if (!(chance > cp.xtc_probability)) {
+      float sum_gt, unused;
+      team_sum2(tm, L, [&](float v, int, float& s, float&) { if (okey(v) > T) s += expf(v - mx_l); }, sum_gt, unused);
+      const float e_t = E > 0 ? expf(unkey(T) - mx_l) : 0.f;
+      const float inv = 1.0f / (sum_gt + (float)E * e_t);
+      float above_gt, unused2;
+      team_sum2(tm, L, [&](float v, int, float& s, float&) { if (okey(v) > T && expf(v - mx_l) * inv >= cp.xtc_threshold) s += 1.f; },
+                above_gt, unused2);
+      const bool t_in = E > 0 && e_t * inv >= cp.xtc_threshold;
+      const int pos_last = (int)above_gt + (t_in ? E : 0) - 1;  // how many of the leading candidates go
+      const float ninf = -INFINITY;
+      if (pos_last > 0) {
+        if (t_in) {
+          // every candidate is above the threshold: only the last of them stays
+          const int keep_idx = kth_equal(tm, L, unkey(T), E - 1, false);
+          sweep(L, tm.begin, tm.end, [&](float v, int i) { if (okey(v) > T || (okey(v) == T && i != keep_idx)) L[i] = ninf; });
+          mx_l = unkey(T);
+          E = 1;
+        } else {
+          unsigned long long above;
+          bool fell;
+          const uint32_t U = select_desc(
+              tm, L, [&](float v, int, uint32_t& key, unsigned long long& w) { const uint32_t k = okey(v); key = k > T ? k : 0u; w = 1ull; },
+              (unsigned long long)pos_last, hist, total_bins, &above, &fell);
+          const int first_kept = kth_equal(tm, L, unkey(U), pos_last - (int)above, false);
+          sweep(L, tm.begin, tm.end, [&](float v, int i) { if (okey(v) > U || (okey(v) == U && i < first_kept)) L[i] = ninf; });
+          mx_l = unkey(U);
+        }
+        __syncthreads();
+        if (T < okey(ninf)) {  // everything had survived so far: now what was struck must not
+          T = okey(ninf);
+          E = 0;
+        }
+      }
+      filtered = true;
+    }
+  }
+
   // ---- the choice: argmax (:225-228), or temperature and a draw in the candidates' order (:101-106, :190-215)
   int chosen;
   float inv_final = 0.f;
@@ -1049,13 +1105,15 @@ RL_API int rl_sample(const float* logits, long long row_stride, int n_rows, int 
 }
 
 // The longer chain.  work: n_rows * 2 * n_pad floats with n_pad = n rounded up to 4.  history: int
-// [slots][1024], history_count: int [slots] and mirostat_mu: float [slots] (may be null without mirostat),
-// all indexed by slot_of_row[r], like rng_states.
+// [slots][1024], history_count: int [slots], mirostat_mu: float [slots] (may be null without mirostat) and
+// xtc_states: the second generator's states (may be null without XTC), all indexed by slot_of_row[r], like
+// rng_states.
 RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows, int n, float temperature, float top_p,
                            int top_k, float min_p, float repeat_penalty, int last_n, float frequency_penalty,
                            float presence_penalty, int mirostat, float mirostat_tau, float mirostat_eta,
-                           unsigned long long* rng_states, const int* slot_of_row, int* history, int* history_count,
-                           float* mirostat_mu, float* work, int* out, cudaStream_t stream) {
+                           float xtc_probability, float xtc_threshold, unsigned long long* rng_states,
+                           const int* slot_of_row, int* history, int* history_count, float* mirostat_mu,
+                           unsigned long long* xtc_states, float* work, int* out, cudaStream_t stream) {
   if (n_rows <= 0 || n <= 0) RL_REFUSE(1, "sample_chain: rows=%d n=%d", n_rows, n);
   if (!(temperature >= 0.f)) RL_REFUSE(2, "sample_chain: temperature %f is negative", temperature);
   if (!rng_states || !slot_of_row || !work || !history || !history_count) RL_REFUSE(3, "sample_chain: missing random state, history or scratch");
@@ -1065,8 +1123,9 @@ RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows
   if (mirostat < 0 || mirostat > 2) RL_REFUSE(7, "sample_chain: mirostat %d is none of 0, 1, 2", mirostat);
   if (mirostat != 0 && (!(temperature > 0.f) || mirostat_mu == nullptr))
     RL_REFUSE(8, "sample_chain: mirostat needs a positive temperature (got %f) and its state", temperature);
+  if (xtc_probability > 0.f && xtc_states == nullptr) RL_REFUSE(9, "sample_chain: XTC needs its random states");
   ChainParams cp = {temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k, last_n,
-                    mirostat, mirostat_tau, mirostat_eta};
+                    mirostat, mirostat_tau, mirostat_eta, xtc_probability, xtc_threshold};
   int team = 1;
   while (team < TEAM_MAX && n / (2 * team) >= 4096) team *= 2;
   cudaLaunchConfig_t cfg = {};
@@ -1083,6 +1142,6 @@ RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows
   cfg.numAttrs = 1;
   const int n_pad = (n + 3) & ~3;
   RL_LAUNCH_CHECK(cudaLaunchKernelEx(&cfg, sample_chain_kernel, logits, row_stride, n, n_pad, cp, rng_states, slot_of_row, history,
-                                     history_count, mirostat_mu, work, out));
+                                     history_count, mirostat_mu, xtc_states, work, out));
   return 0;
 }

@@ -693,6 +693,7 @@ def sample_chain(
     last_n: int, frequency_penalty: float, presence_penalty: float, rng_states: torch.Tensor, slot_of_row: torch.Tensor,
     history: torch.Tensor, history_count: torch.Tensor, work: torch.Tensor, out: Optional[torch.Tensor] = None,
     mirostat: int = 0, mirostat_tau: float = 5.0, mirostat_eta: float = 0.1, mirostat_mu: Optional[torch.Tensor] = None,
+    xtc_probability: float = 0.0, xtc_threshold: float = 0.1, xtc_states: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One token per row through penalties -> top-k -> top-p -> min-p -> temperature -> draw (temperature 0:
     the argmax of the penalised logits, no draw).
@@ -701,7 +702,8 @@ def sample_chain(
     chosen tokens of history[slot] (int32 [slots, 1024] with history_count[slot] tokens written so far) for
     the penalties and appends its choice.  work: float32, at least rows * 2 * (vocabulary rounded up to 4).
     mirostat 1 or 2: penalties -> temperature -> mirostat's own cut and draw; mirostat_mu: float32 [slots], NaN
-    for a sequence that has not drawn yet."""
+    for a sequence that has not drawn yet.  xtc_probability > 0: the "exclude top choices" filter after min-p, with
+    a generator of its own per slot (xtc_states, int64 like rng_states)."""
     _cuda(logits, "sample_chain logits", torch.float32, contiguous=False)
     stride = _rows(logits, "sample_chain logits")
     R, n = logits.shape
@@ -723,12 +725,17 @@ def sample_chain(
         _need(mirostat_mu is not None, "sample_chain: mirostat needs its state")
         _cuda(mirostat_mu, "sample_chain mirostat_mu", torch.float32)
         _need(mirostat_mu.numel() == history_count.numel(), "sample_chain: one mirostat state per slot")
+    if xtc_probability > 0.0:
+        _need(xtc_states is not None, "sample_chain: XTC needs its random states")
+        _cuda(xtc_states, "sample_chain xtc_states", torch.int64)
+        _need(xtc_states.numel() == history_count.numel(), "sample_chain: one XTC state per slot")
     lib = build.load("sampling")
     rc = lib.rl_sample_chain(
         _p(logits), c_ll(stride), c_int(R), c_int(n), c_float(temperature), c_float(top_p), c_int(top_k), c_float(min_p),
         c_float(repeat_penalty), c_int(last_n), c_float(frequency_penalty), c_float(presence_penalty), c_int(mirostat),
-        c_float(mirostat_tau), c_float(mirostat_eta), _p(rng_states), _p(slot_of_row), _p(history), _p(history_count),
-        _p(mirostat_mu) if mirostat_mu is not None else c_void_p(0), _p(work), _p(out), _stream(),
+        c_float(mirostat_tau), c_float(mirostat_eta), c_float(xtc_probability), c_float(xtc_threshold), _p(rng_states),
+        _p(slot_of_row), _p(history), _p(history_count), _p(mirostat_mu) if mirostat_mu is not None else c_void_p(0),
+        _p(xtc_states) if xtc_states is not None else c_void_p(0), _p(work), _p(out), _stream(),
     )
     _check(lib, rc, "sample_chain")
     return out

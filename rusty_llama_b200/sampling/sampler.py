@@ -10,7 +10,7 @@ reference builds another chain, penalties -> top-k -> top-p -> min-p -> temperat
 module.  The reference keeps one chain per server slot (src/server.rs:288, :513); here the
 generator states and the penalties' token histories of all sequence slots live in device arrays
 and the kernels advance them.  Mirostat 1 and 2 are a mode of that chain (penalties -> temperature ->
-mirostat).  Not built: XTC, DRY and grammars.
+mirostat), XTC a stage of it after min-p.  Not built: DRY and grammars (they work on token strings).
 """
 
 from __future__ import annotations
@@ -58,7 +58,9 @@ class SamplingParams:
     last repeat_last_n chosen ones (default 64): the reference's `--top-k`, `--min-p`, `--repeat-penalty`,
     `--repeat-last-n`, `--frequency-penalty`, `--presence-penalty` (src/main.rs:478-485).
     mirostat 1 or 2 (`--mirostat`, with `--mirostat-lr` eta and `--mirostat-ent` tau) replaces top-k, top-p
-    and min-p by its own adaptive cut (src/sampler.rs:829-866) and needs a temperature above 0."""
+    and min-p by its own adaptive cut (src/sampler.rs:829-866) and needs a temperature above 0.
+    xtc_probability > 0 (`--xtc-probability`, `--xtc-threshold`): with that probability per token, all but the
+    least likely of the candidates whose probability reaches the threshold are dropped (src/sampler.rs:569-602)."""
 
     temperature: float = 1.0
     top_p: float = 0.9
@@ -72,6 +74,8 @@ class SamplingParams:
     mirostat: int = 0
     mirostat_lr: float = 0.1
     mirostat_ent: float = 5.0
+    xtc_probability: float = 0.0
+    xtc_threshold: float = 0.1
 
     def validate(self) -> None:
         if not (self.temperature >= 0.0) or self.temperature == float("inf"):
@@ -96,7 +100,7 @@ class SamplingParams:
     @property
     def longer_chain(self) -> bool:
         """Whether the reference would build its longer chain for these values (src/sampler.rs:868-876)."""
-        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on or self.mirostat != 0
+        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on or self.mirostat != 0 or self.xtc_probability > 0.0
 
 
 class PendingTokens:
@@ -124,6 +128,8 @@ class Sampler:
         self.history_count = torch.zeros(max_seqs, dtype=torch.int32, device=self.device)
         # mirostat's surprise ceiling per slot; NaN: not drawn yet (the kernel then starts from 2 tau)
         self.mirostat_mu = torch.full((max_seqs,), float("nan"), dtype=torch.float32, device=self.device)
+        # XTC draws from a generator of its own, started from the sequence's seed (src/sampler.rs:547-553)
+        self.xtc_states = torch.ones(max_seqs, dtype=torch.int64, device=self.device)
         self._workspace = workspace
         self._scratch: Optional[torch.Tensor] = None
         self._pinned = None
@@ -134,6 +140,7 @@ class Sampler:
         vals = np.array([s or 1 for s in seeds], dtype=np.uint64).view(np.int64)
         idx = torch.tensor(list(slots), dtype=torch.long, device=self.device)
         self.rng_states[idx] = torch.from_numpy(vals).to(self.device)
+        self.xtc_states[idx] = self.rng_states[idx]
         self.history_count[idx] = 0  # a new sequence has chosen nothing yet (src/sampler.rs:349-351)
         self.mirostat_mu[idx] = float("nan")  # (src/sampler.rs:451-453)
 
@@ -186,5 +193,6 @@ class Sampler:
             params.repeat_last_n if params.penalties_on else 0, params.frequency_penalty, params.presence_penalty,
             self.rng_states, index, self.history, self.history_count, work,
             mirostat=params.mirostat, mirostat_tau=params.mirostat_ent, mirostat_eta=params.mirostat_lr,
-            mirostat_mu=self.mirostat_mu,
+            mirostat_mu=self.mirostat_mu, xtc_probability=params.xtc_probability, xtc_threshold=params.xtc_threshold,
+            xtc_states=self.xtc_states,
         )

@@ -345,7 +345,10 @@ class PlainChain:
     sorts with an unstable sort, the stable sort here keeps equal values in index order."""
 
     def __init__(self, temperature=1.0, top_p=0.9, seed=1, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64,
-                 frequency_penalty=0.0, presence_penalty=0.0, mirostat=0, mirostat_lr=0.1, mirostat_ent=5.0, mirostat_m=100):
+                 frequency_penalty=0.0, presence_penalty=0.0, mirostat=0, mirostat_lr=0.1, mirostat_ent=5.0, mirostat_m=100,
+                 xtc_probability=0.0, xtc_threshold=0.1):
+        self.xtc_p, self.xtc_thr = xtc_probability, xtc_threshold
+        self.xtc_rng = PlainRng(seed)  # its own stream from the same seed (src/sampler.rs:547-553)
         self.mirostat, self.eta, self.tau, self.m = mirostat, mirostat_lr, mirostat_ent, mirostat_m
         self.mu = np.float32(2.0) * np.float32(mirostat_ent)  # (src/sampler.rs:379)
         self.t, self.top_p, self.top_k, self.min_p = temperature, top_p, top_k, min_p
@@ -415,6 +418,22 @@ class PlainChain:
                     break
             cands = cands[: min(max(above, 1), len(cands))]
             sorted_by_p = False
+        # XTC (src/sampler.rs:569-602)
+        if self.xtc_p > 0.0 and not (self.xtc_thr > 0.5) and len(cands) >= 2:
+            chance = f32(self.xtc_rng.next_f32())  # drawn whether or not the filter acts
+            if not (chance > f32(self.xtc_p)):
+                n = len(cands)
+                cands = self._softmax(sorted(cands, key=lambda c: -float(c[1])))
+                above = 0
+                for c in cands:
+                    if c[2] >= f32(self.xtc_thr):
+                        above += 1
+                    else:
+                        break
+                pos_last = max(above - 1, 0)
+                if pos_last > 0 and n - pos_last >= 1:
+                    cands = cands[pos_last:]
+                sorted_by_p = True
         if self.t == 0.0:
             sel = plain_argmax([float(c[1]) for c in cands])  # (src/sampler.rs:225-228)
         else:

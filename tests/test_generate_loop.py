@@ -233,8 +233,11 @@ def test_command_line_options_follow_the_reference(tmp_path):
     a = parse_args(["m", "--mirostat", "2", "--mirostat-lr", "0.2", "--mirostat-ent", "4"])
     assert (a["mirostat"], a["mirostat_lr"], a["mirostat_ent"]) == (2, 0.2, 4.0)
     assert (parse_args(["m"])["mirostat"], parse_args(["m"])["mirostat_lr"], parse_args(["m"])["mirostat_ent"]) == (0, 0.1, 5.0)
+    a = parse_args(["m", "--xtc-probability", "0.5", "--xtc-threshold", "0.2"])
+    assert (a["xtc_probability"], a["xtc_threshold"]) == (0.5, 0.2)
+    assert (parse_args(["m"])["xtc_probability"], parse_args(["m"])["xtc_threshold"]) == (0.0, 0.1)
     with pytest.raises(SystemExit, match="unknown option"):
-        parse_args(["m", "--xtc-probability", "0.5"])  # not built
+        parse_args(["m", "--dry-multiplier", "0.5"])  # not built: works on token strings
     assert parse_prompts("1, 2 3") == [[1, 2, 3]]
     f = tmp_path / "prompts.txt"
     f.write_text("5 6\n\n7,8,9\n")
@@ -255,7 +258,7 @@ def test_sampling_params_pick_the_chain_as_the_reference_does():
 
     assert not SamplingParams(0.8, 0.9, 1).longer_chain
     assert not SamplingParams(0.8, 0.9, 1, repeat_last_n=8).longer_chain  # a window alone changes nothing
-    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5), dict(mirostat=2)):
+    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5), dict(mirostat=2), dict(xtc_probability=0.3)):
         p = SamplingParams(0.8, 0.9, 1, **kw)
         p.validate()
         assert p.longer_chain
