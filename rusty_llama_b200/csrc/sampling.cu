@@ -651,8 +651,9 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
 }
 
 // ---------------------------------------------------------------- the longer chain
-// penalties -> top-k -> top-p -> min-p -> temperature -> draw (or argmax), the order of the reference's
-// chain when any of its further knobs is set (src/sampler.rs:821-931).  Every filter of that chain keeps
+// penalties -> top-k -> top-p -> min-p -> XTC -> temperature -> draw (or argmax), the order of the reference's
+// chain when any of its further knobs is set (src/sampler.rs:821-931); with mirostat, penalties ->
+// temperature -> mirostat's own cut and draw (:829-866).  Every filter of that chain keeps
 // a prefix of the candidates in descending order, so the survivors are always "all logits above a
 // threshold, and the first E (by index) of those equal to it": the kernel carries (threshold key, E)
 // from stage to stage and never sorts.  Equal logits are taken in index order where the reference's
