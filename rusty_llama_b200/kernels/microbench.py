@@ -148,6 +148,29 @@ def bench_rows(a) -> dict:
     return {"kernel": "add_rmsnorm", "rows": a.rows, "d": d, "us": round(us, 2)}
 
 
+def bench_sample(a) -> dict:
+    """One sampling call for `--rows` sequences over a vocabulary of `--vocab`: greedy, temperature,
+    temperature + top-p (the reference's default chain), and the longer chain with top-k, min-p and penalties."""
+    from ..sampling.sampler import Sampler, SamplingParams
+
+    global USE_GRAPH
+    USE_GRAPH = False  # a call uploads the rows' slot numbers, which a capture does not take: plain launches
+    dev = "cuda:0"
+    logits = [torch.randn(a.rows, a.vocab, device=dev) * 3 for _ in range(4)]
+    smp = Sampler(dev, max(a.rows, 1), a.vocab)
+    slots = list(range(a.rows))
+    smp.seed_slots(slots, [7 + i for i in slots])
+    out = {"kernel": "sample", "rows": a.rows, "vocab": a.vocab, "us": {}}
+    for name, params in (
+        ("greedy", SamplingParams(0.0)),
+        ("temperature", SamplingParams(1.0, 0.0, 7)),
+        ("temperature_top_p", SamplingParams(0.8, 0.9, 7)),
+        ("longer_chain", SamplingParams(0.8, 0.9, 7, top_k=40, min_p=0.05, repeat_penalty=1.1)),
+    ):
+        out["us"][name] = round(_time(lambda i: smp.sample(logits[i % 4], slots, params), 4, a.iters, a.warmup), 2)
+    return out
+
+
 def bench_step_trace(a) -> dict:
     """Durations of the kernels inside ONE replayed decode step (a CUDA graph with programmatic
     launches, where a profiler would serialise them): every kernel's first thread notes the time at
@@ -236,7 +259,7 @@ def bench_step_trace(a) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemv", "gemm", "attn_decode", "flash_prefill", "add_rmsnorm", "step_trace"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -248,7 +271,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--layers", type=int, default=4, help="step_trace: layers of the model")
     ap.add_argument("--ff", type=int, default=14336, help="step_trace: width of the feed-forward")
-    ap.add_argument("--vocab", type=int, default=128256, help="step_trace: vocabulary")
+    ap.add_argument("--vocab", type=int, default=128256, help="step_trace, sample: vocabulary")
     ap.add_argument("--events", action="store_true", help="step_trace: also the numbered notes inside one layer's kernels")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
     ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream", "tma", "warp"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent TMA-fed kernel; attn_decode: tma or warp = one of its two kernels")
@@ -259,7 +282,7 @@ def main(argv=None) -> int:
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
     fn = {"gemv": bench_gemv, "gemm": bench_gemm, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
-          "add_rmsnorm": bench_rows, "step_trace": bench_step_trace}[a.kernel]
+          "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace}[a.kernel]
     print(json.dumps(fn(a)))
     return 0
 
