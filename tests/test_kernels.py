@@ -1044,6 +1044,49 @@ def test_sample_chain_mirostat_follows_the_plain_chain(ops, n, mode, tau, eta, t
     assert np.array_equal(states.cpu().numpy().view(np.uint64), np.array([p.rng.state for p in plain], dtype=np.uint64))
 
 
+def test_sample_chain_on_the_reference_cases(ops):
+    """The kernel on the inputs and outcomes of the reference's own unit tests of its stages
+    (src/sampler.rs:1064-1211)."""
+
+    def run(logits, draws=1, ring=(), seed=3, **kw):
+        c = dict(temperature=1.0, top_p=0.0, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64, frequency_penalty=0.0,
+                 presence_penalty=0.0, mirostat=0, mirostat_tau=5.0, mirostat_eta=0.1, xtc_probability=0.0, xtc_threshold=0.1)
+        c.update(kw)
+        n = len(logits)
+        l = torch.tensor([logits], dtype=torch.float32, device=DEV)
+        states = torch.tensor([seed], dtype=torch.int64, device=DEV)
+        history = torch.zeros(1, 1024, dtype=torch.int32, device=DEV)
+        count = torch.zeros(1, dtype=torch.int32, device=DEV)
+        last_n = c["repeat_last_n"]
+        for t in ring:  # as the kernel itself files chosen tokens
+            history[0, int(count.item()) % last_n] = t
+            count += 1
+        mu = torch.full((1,), float("nan"), device=DEV)
+        work = torch.empty(2 * ((n + 3) // 4 * 4), device=DEV)
+        out = [
+            ops.sample_chain(
+                l, c["temperature"], c["top_p"], c["top_k"], c["min_p"], c["repeat_penalty"], last_n, c["frequency_penalty"],
+                c["presence_penalty"], states, torch.zeros(1, dtype=torch.int32, device=DEV), history, count, work,
+                mirostat=c["mirostat"], mirostat_tau=c["mirostat_tau"], mirostat_eta=c["mirostat_eta"], mirostat_mu=mu,
+                xtc_probability=c["xtc_probability"], xtc_threshold=c["xtc_threshold"], xtc_states=states.clone(),
+            ).item()
+            for _ in range(draws)
+        ]
+        return out, mu.item()
+
+    assert set(run([3.0, 1.0, 4.0, 1.0, 5.0], draws=40, top_k=2)[0]) == {2, 4}
+    assert set(run([10.0, 9.0, 2.0, 1.0], draws=20, min_p=0.5)[0]) == {0}
+    assert run([4.5, 1.0, 5.0], ring=[2], temperature=0.0, repeat_penalty=1.3)[0] == [0]
+    assert run([0.0, 0.0, 0.0], ring=[0, 1, 2], temperature=0.0, presence_penalty=5.0, repeat_last_n=2)[0] == [0]
+    assert run([0.0, 0.0, -1.5], ring=[0, 0, 1], temperature=0.0, frequency_penalty=1.0)[0] == [1]
+    assert run([0.0, 0.0, -0.5], ring=[0, 0, 1], temperature=0.0, frequency_penalty=1.0)[0] == [2]
+    got, mu = run([10.0, 0.0, 0.0], seed=1, mirostat=2, repeat_last_n=0)
+    assert got == [0] and abs(mu - 10.5) < 1e-4
+    assert run([10.0, 9.0, 0.0, -1.0], seed=7, temperature=0.0, xtc_probability=1.0, xtc_threshold=0.2)[0] == [1]
+    assert run([1.0, 2.0, 3.0, 4.0, 5.0], xtc_probability=1.0, xtc_threshold=0.0)[0] == [0]
+    assert run([10.0, 9.0, 0.0, -1.0], temperature=0.0, top_k=4, xtc_probability=0.0)[0] == [0]
+
+
 def test_sample_chain_takes_equal_logits_in_index_order(ops):
     """Equal logits at the edge of top-k and inside the draw: the first by index stay, as in the plain chain's
     stable sorts."""

@@ -120,3 +120,43 @@ def test_greedy_generation_is_reproducible(tiny_weights):
     w = {k: v.to(torch.float32) for k, v in tiny_weights["A"].items()}
     a = plain_generate(cfg, w, [1, 2, 3], 6)
     assert a == plain_generate(cfg, w, [1, 2, 3], 6) and len(a) == 6
+
+
+def test_longer_chain_stages_on_the_reference_cases():
+    """The stages of the longer chain on the inputs and outcomes of the reference's own unit tests
+    (src/sampler.rs:1064-1211)."""
+    from plain_llama import PlainChain
+
+    # top_k_keeps_k_highest: of [3, 1, 4, 1, 5] with k = 2 only ids 2 and 4 can be drawn
+    c = PlainChain(temperature=1.0, top_p=0.0, seed=3, top_k=2)
+    assert {c.sample([3.0, 1.0, 4.0, 1.0, 5.0]) for _ in range(40)} == {2, 4}
+    # min_p_drops_low_probability_tail: 10 + ln 0.5 = 9.31, only id 0 clears it
+    c = PlainChain(temperature=1.0, top_p=0.0, seed=3, min_p=0.5)
+    assert {c.sample([10.0, 9.0, 2.0, 1.0]) for _ in range(20)} == {0}
+    # penalty_demotes_repeated_token: id 2 (5.0) falls below id 0 (4.5) once it was chosen before
+    c = PlainChain(temperature=0.0, repeat_penalty=1.3)
+    c.ring = [2]
+    assert c.sample([4.5, 1.0, 5.0]) == 0
+    # penalty_ring_evicts_past_window: a window of 2 after 0, 1, 2: token 0 is no longer penalised
+    c = PlainChain(temperature=0.0, presence_penalty=5.0, repeat_last_n=2)
+    for tok in (0, 1, 2):
+        c._accept(tok)
+    assert c.ring == [1, 2] and c.sample([0.0, 0.0, 0.0]) == 0
+    # penalty_frequency_scales_with_count: seen twice costs more than seen once
+    c = PlainChain(temperature=0.0, frequency_penalty=1.0)
+    c.ring = [0, 0, 1]
+    assert c.sample([0.0, 0.0, -1.5]) == 1  # -2 (seen twice), -1 (seen once), -1.5
+    c.ring = [0, 0, 1]
+    assert c.sample([0.0, 0.0, -0.5]) == 2  # -2, -1, -0.5
+    # mirostat_v2_truncates_and_updates_mu: only token 0 survives, p = 1, mu = 10 - 0.1 * (0 - 5)
+    c = PlainChain(temperature=1.0, seed=1, mirostat=2, mirostat_ent=5.0, mirostat_lr=0.1)
+    assert float(c.mu) == 10.0 and c.sample([10.0, 0.0, 0.0]) == 0 and abs(float(c.mu) - 10.5) < 1e-4
+    # xtc_drops_leading_above_threshold_run: p = 0.73, 0.27, ...: id 0 goes, id 1 is then the largest
+    c = PlainChain(temperature=0.0, seed=7, xtc_probability=1.0, xtc_threshold=0.2)
+    assert c.sample([10.0, 9.0, 0.0, -1.0]) == 1
+    # xtc_always_keeps_at_least_one_token: threshold 0 leaves the least probable alone
+    c = PlainChain(temperature=1.0, top_p=0.0, seed=3, xtc_probability=1.0, xtc_threshold=0.0)
+    assert c.sample([1.0, 2.0, 3.0, 4.0, 5.0]) == 0
+    # xtc_zero_probability_is_noop (and draws nothing from its generator)
+    c = PlainChain(temperature=0.0, top_k=4, xtc_probability=0.0)
+    assert c.sample([10.0, 9.0, 0.0, -1.0]) == 0 and c.xtc_rng.state == c.rng.state
