@@ -68,6 +68,11 @@ class LLM:
         mirostat_ent: float = 5.0,
         xtc_probability: float = 0.0,
         xtc_threshold: float = 0.1,
+        dry_multiplier: float = 0.0,
+        dry_base: float = 1.75,
+        dry_allowed_length: int = 2,
+        dry_penalty_last_n: int = 64,
+        dry_sequence_breakers: Sequence[int] = (),
     ):
         """Token ids generated after each prompt.
 
@@ -80,7 +85,8 @@ class LLM:
         presence_penalty are the reference's further knobs (`SamplingParams`); setting one selects its
         longer chain, in which the nucleus is taken before the temperature; mirostat 1 or 2 (with
         mirostat_lr, mirostat_ent) replaces top_k, top_p and min_p; xtc_probability > 0 (with xtc_threshold) adds
-        the "exclude top choices" stage.  launch_ahead=False makes the loop read every token before it
+        the "exclude top choices" stage; dry_multiplier > 0 (with dry_base, dry_allowed_length,
+        dry_penalty_last_n, dry_sequence_breakers as token ids) adds the DRY penalty.  launch_ahead=False makes the loop read every token before it
         starts the next step (same tokens, more idle GPU time)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         batch: List[Sequence[int]] = [prompts] if single else list(prompts)  # type: ignore[list-item]
@@ -89,6 +95,7 @@ class LLM:
         params = SamplingParams(
             temperature, top_p, seed, top_k, min_p, repeat_penalty, repeat_last_n, frequency_penalty, presence_penalty,
             mirostat, mirostat_lr, mirostat_ent, xtc_probability, xtc_threshold,
+            dry_multiplier, dry_base, dry_allowed_length, dry_penalty_last_n, tuple(dry_sequence_breakers),
         )
         stats = GenerationStats()
         if max_new_tokens is None:

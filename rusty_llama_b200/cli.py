@@ -13,8 +13,10 @@
     --frequency-penalty <float>  --presence-penalty <float>
     --mirostat <0|1|2>  --mirostat-lr <float>  --mirostat-ent <float>
     --xtc-probability <float>  --xtc-threshold <float>
+    --dry-multiplier <float>  --dry-base <float>  --dry-allowed-length <int>  --dry-penalty-last-n <int>
+    --dry-sequence-breaker <id>   (may be given up to 8 times; a token id where the reference takes a string)
                 the reference's further sampling knobs, with its defaults (0, 0, 1.0, 64, 0, 0; 0, 0.1, 5.0; 0, 0.1;
-                src/main.rs:478-490); its DRY and grammar options, which work on token strings, are not built
+                0, 1.75, 2, 64, none; src/main.rs:478-495); its grammar options, which work on token strings, are not built
 Where the reference has `-z tokenizer` and `--backend`, this program has `--dtype bfloat16|float32`
 (the second is the true 32-bit path) and `--random SEED` to run a folder that holds only a
 config.json with random weights.  Generated ids go to standard output, one line per prompt, and
@@ -53,6 +55,7 @@ def parse_args(argv: List[str]) -> dict:
         "top_k": 0, "min_p": 0.0, "repeat_penalty": 1.0, "repeat_last_n": 64, "frequency_penalty": 0.0,
         "presence_penalty": 0.0, "mirostat": 0, "mirostat_lr": 0.1, "mirostat_ent": 5.0,
         "xtc_probability": 0.0, "xtc_threshold": 0.1,
+        "dry_multiplier": 0.0, "dry_base": 1.75, "dry_allowed_length": 2, "dry_penalty_last_n": 64, "dry_sequence_breakers": [],
     }
     flags = {
         "-t": ("temperature", float), "-p": ("top_p", float), "-s": ("seed", int), "-n": ("steps", int),
@@ -63,6 +66,9 @@ def parse_args(argv: List[str]) -> dict:
         "--presence-penalty": ("presence_penalty", float),
         "--mirostat": ("mirostat", int), "--mirostat-lr": ("mirostat_lr", float), "--mirostat-ent": ("mirostat_ent", float),
         "--xtc-probability": ("xtc_probability", float), "--xtc-threshold": ("xtc_threshold", float),
+        "--dry-multiplier": ("dry_multiplier", float), "--dry-base": ("dry_base", float),
+        "--dry-allowed-length": ("dry_allowed_length", int), "--dry-penalty-last-n": ("dry_penalty_last_n", int),
+        "--dry-sequence-breaker": ("dry_sequence_breakers", int),
     }
     i = 1
     while i < len(argv):
@@ -76,7 +82,10 @@ def parse_args(argv: List[str]) -> dict:
             raise SystemExit(f"missing value for '{flag}'")
         name, conv = flags[flag]
         try:
-            args[name] = conv(argv[i + 1])
+            if isinstance(args[name], list):
+                args[name].append(conv(argv[i + 1]))  # an option that may be given more than once
+            else:
+                args[name] = conv(argv[i + 1])
         except ValueError:
             raise SystemExit(f"bad value '{argv[i + 1]}' for '{flag}'")
         i += 2
@@ -102,6 +111,8 @@ def main(argv=None) -> int:
         frequency_penalty=args["frequency_penalty"], presence_penalty=args["presence_penalty"],
         mirostat=args["mirostat"], mirostat_lr=args["mirostat_lr"], mirostat_ent=args["mirostat_ent"],
         xtc_probability=args["xtc_probability"], xtc_threshold=args["xtc_threshold"],
+        dry_multiplier=args["dry_multiplier"], dry_base=args["dry_base"], dry_allowed_length=args["dry_allowed_length"],
+        dry_penalty_last_n=args["dry_penalty_last_n"], dry_sequence_breakers=args["dry_sequence_breakers"],
     )
     dt = time.perf_counter() - t0
     n = 0

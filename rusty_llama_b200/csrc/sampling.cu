@@ -651,8 +651,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int n, flo
 }
 
 // ---------------------------------------------------------------- the longer chain
-// penalties -> top-k -> top-p -> min-p -> XTC -> temperature -> draw (or argmax), the order of the reference's
-// chain when any of its further knobs is set (src/sampler.rs:821-931); with mirostat, penalties ->
+// penalties -> DRY -> top-k -> top-p -> min-p -> XTC -> temperature -> draw (or argmax), the order of the reference's
+// chain when any of its further knobs is set (src/sampler.rs:821-931); with mirostat, penalties -> DRY ->
 // temperature -> mirostat's own cut and draw (:829-866).  Every filter of that chain keeps
 // a prefix of the candidates in descending order, so the survivors are always "all logits above a
 // threshold, and the first E (by index) of those equal to it": the kernel carries (threshold key, E)
@@ -675,12 +675,17 @@ struct ChainParams {
   int mirostat;             // 0, or 1 / 2: the mode that replaces top-k, top-p and min-p (src/sampler.rs:829-866)
   float mirostat_tau, mirostat_eta;
   float xtc_probability, xtc_threshold;  // "exclude top choices", after min-p (src/sampler.rs:569-602); 0 = off
+  // DRY, after the penalties (src/sampler.rs:683-733): off when the multiplier is 0, the base below 1 or the window 0
+  float dry_multiplier, dry_base;
+  int dry_allowed_length, dry_last_n, dry_n_breakers;
+  int dry_breakers[8];  // tokens that a repeat may not cross
 };
 
 #define MIROSTAT_M 100  // candidates of the Zipf estimate of mirostat 1 (the reference's mirostat_m)
 #define MIROSTAT_LIST 128
 
-#define HISTORY_MAX 1024  // tokens of history that the penalties can look back on
+#define HISTORY_MAX 1024  // tokens of history that the penalties and DRY can look back on
+#define DRY_MAX_BREAKERS 8
 
 // f(value, index, sum, count) adds to two running sums; their totals over the whole row come back.
 template <typename F>
@@ -691,8 +696,9 @@ __device__ __forceinline__ void team_sum2(Team& tm, const float* a, F f, float& 
 }
 
 // grid: (team size, rows), clusters of (team size, 1, 1).  work: per row 2 * n_pad floats (the penalised
-// logits, then the weights of the current softmax).  history[slot][HISTORY_MAX] with history_count[slot]
-// tokens accepted so far: the ring of the last `last_n` sampled tokens (src/sampler.rs:339-347).
+// logits, then the weights of the current softmax).  history[slot][HISTORY_MAX] is a ring of the sequence's
+// chosen tokens, the p-th of them at p % HISTORY_MAX, history_count[slot] of them so far: the penalties read
+// its last `last_n` (src/sampler.rs:339-347), DRY its last `dry_last_n` (:735-743).
 // mirostat_mu[slot]: the surprise ceiling that mirostat adapts, NaN for a sequence that has not drawn yet.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int n, int n_pad, ChainParams cp,
@@ -735,10 +741,13 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
   // ---- penalties over the ring of accepted tokens (src/sampler.rs:314-337)
   sweep(row, tm.begin, tm.end, [&](float v, int i) { L[i] = v; });
   const bool penalties_on = cp.repeat_penalty != 1.f || cp.frequency_penalty != 0.f || cp.presence_penalty != 0.f;
-  const int accepted = cp.last_n > 0 ? history_count[slot] : 0;
+  const bool dry_on = cp.dry_multiplier != 0.f && !(cp.dry_base < 1.f) && cp.dry_last_n > 0;
+  const bool records = cp.last_n > 0 || dry_on;
+  const int accepted = records ? history_count[slot] : 0;
+  const int* past = history + (size_t)slot * HISTORY_MAX;
   const int valid = min(accepted, cp.last_n);
   if (penalties_on && valid > 0) {
-    for (int j = threadIdx.x; j < valid; j += blockDim.x) ring[j] = history[(size_t)slot * HISTORY_MAX + j];
+    for (int j = threadIdx.x; j < valid; j += blockDim.x) ring[j] = past[(accepted - valid + j) % HISTORY_MAX];
     __syncthreads();  // (also orders the writes of L above before the changes below)
     for (int j = threadIdx.x; j < valid; j += blockDim.x) {
       const int t = ring[j];
@@ -761,6 +770,56 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
     }
   }
   __syncthreads();
+
+  // ---- DRY: a token that would make the end of the history repeat an earlier stretch of it loses
+  // multiplier * base^(length of the repeat - allowed length) (src/sampler.rs:683-733)
+  const int dry_n = dry_on ? min(accepted, cp.dry_last_n) : 0;
+  if (dry_n > max(cp.dry_allowed_length, 1)) {
+    __shared__ int rep_limit_s;
+    const int allowed = max(cp.dry_allowed_length, 1);
+    int* rev = ring;                                 // the window, newest first
+    int* rep_len = reinterpret_cast<int*>(hist);     // [k]: length of the repeat that rev[k - 1] would complete, or 0
+    if (threadIdx.x == 0) rep_limit_s = dry_n;
+    for (int i = threadIdx.x; i < dry_n; i += blockDim.x) rev[i] = past[(accepted - 1 - i) % HISTORY_MAX];
+    __syncthreads();
+    // the window ends before the most recent breaker
+    for (int i = threadIdx.x; i < dry_n; i += blockDim.x)
+      for (int b = 0; b < cp.dry_n_breakers; ++b)
+        if (rev[i] == cp.dry_breakers[b]) atomicMin(&rep_limit_s, i);
+    __syncthreads();
+    const int limit = rep_limit_s;
+    if (limit > allowed) {
+      // z[k]: how far the window from k on agrees with the window from 0 on (the reference's Z array of
+      // the reversed window, here by direct comparison: the window has at most 1024 tokens)
+      for (int k = threadIdx.x; k < limit; k += blockDim.x) {
+        int z = 0;
+        if (k >= 1) {
+          while (k + z < limit && rev[z] == rev[k + z]) ++z;
+          rep_len[k] = (z + 1 >= allowed) ? z + 1 : 0;
+        } else {
+          rep_len[k] = 0;
+        }
+      }
+      __syncthreads();
+      for (int k = 1 + (int)threadIdx.x; k < limit; k += blockDim.x) {
+        const int len = rep_len[k];
+        const int t = rev[k - 1];  // the token that followed the earlier stretch
+        if (len == 0 || t < tm.begin || t >= tm.end) continue;
+        bool longest = true;  // of all places with this continuation, the longest repeat (the first of equals) counts
+        for (int kk = 1; kk < limit; ++kk)
+          if (rev[kk - 1] == t && (rep_len[kk] > len || (rep_len[kk] == len && kk < k))) longest = false;
+        if (longest) {
+          float pw = 1.f, b = cp.dry_base;  // base^(len - allowed) by squaring, as powi does
+          for (int e = len - allowed; e > 0; e >>= 1) {
+            if (e & 1) pw *= b;
+            b *= b;
+          }
+          L[t] -= cp.dry_multiplier * pw;
+        }
+      }
+    }
+    __syncthreads();
+  }
 
   float mx_l = -INFINITY;
   sweep(L, tm.begin, tm.end, [&](float v, int) { mx_l = fmaxf(mx_l, v); });
@@ -1070,8 +1129,8 @@ sample_chain_kernel(const float* __restrict__ logits, long long row_stride, int 
       const float p_sel = expf(L[chosen] / cp.temperature - mx_l / cp.temperature) * inv_final;
       mirostat_mu[slot] = mu - cp.mirostat_eta * (-log2f(p_sel) - cp.mirostat_tau);
     }
-    if (cp.last_n > 0) {  // the chosen token joins the ring (src/sampler.rs:339-347)
-      history[(size_t)slot * HISTORY_MAX + accepted % cp.last_n] = chosen;
+    if (records) {  // the chosen token joins the history (src/sampler.rs:339-347, :735-743)
+      history[(size_t)slot * HISTORY_MAX + accepted % HISTORY_MAX] = chosen;
       history_count[slot] = accepted + 1;
     }
   }
@@ -1112,7 +1171,9 @@ RL_API int rl_sample(const float* logits, long long row_stride, int n_rows, int 
 RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows, int n, float temperature, float top_p,
                            int top_k, float min_p, float repeat_penalty, int last_n, float frequency_penalty,
                            float presence_penalty, int mirostat, float mirostat_tau, float mirostat_eta,
-                           float xtc_probability, float xtc_threshold, unsigned long long* rng_states,
+                           float xtc_probability, float xtc_threshold, float dry_multiplier, float dry_base,
+                           int dry_allowed_length, int dry_last_n, const int* dry_breakers, int dry_n_breakers,
+                           unsigned long long* rng_states,
                            const int* slot_of_row, int* history, int* history_count, float* mirostat_mu,
                            unsigned long long* xtc_states, float* work, int* out, cudaStream_t stream) {
   if (n_rows <= 0 || n <= 0) RL_REFUSE(1, "sample_chain: rows=%d n=%d", n_rows, n);
@@ -1126,7 +1187,13 @@ RL_API int rl_sample_chain(const float* logits, long long row_stride, int n_rows
     RL_REFUSE(8, "sample_chain: mirostat needs a positive temperature (got %f) and its state", temperature);
   if (xtc_probability > 0.f && xtc_states == nullptr) RL_REFUSE(9, "sample_chain: XTC needs its random states");
   ChainParams cp = {temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k, last_n,
-                    mirostat, mirostat_tau, mirostat_eta, xtc_probability, xtc_threshold};
+                    mirostat, mirostat_tau, mirostat_eta, xtc_probability, xtc_threshold,
+                    dry_multiplier, dry_base, dry_allowed_length, dry_last_n, dry_n_breakers, {0, 0, 0, 0, 0, 0, 0, 0}};
+  if (dry_last_n < 0 || dry_last_n > HISTORY_MAX || dry_allowed_length < 0)
+    RL_REFUSE(10, "sample_chain: a DRY window of %d tokens is outside 0..%d, or its allowed length %d is negative", dry_last_n, HISTORY_MAX, dry_allowed_length);
+  if (dry_n_breakers < 0 || dry_n_breakers > DRY_MAX_BREAKERS || (dry_n_breakers > 0 && dry_breakers == nullptr))
+    RL_REFUSE(11, "sample_chain: %d DRY sequence breakers, at most %d are taken", dry_n_breakers, DRY_MAX_BREAKERS);
+  for (int b = 0; b < dry_n_breakers; ++b) cp.dry_breakers[b] = dry_breakers[b];  // (a host array)
   int team = 1;
   while (team < TEAM_MAX && n / (2 * team) >= 4096) team *= 2;
   cudaLaunchConfig_t cfg = {};

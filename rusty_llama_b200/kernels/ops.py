@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -694,6 +694,8 @@ def sample_chain(
     history: torch.Tensor, history_count: torch.Tensor, work: torch.Tensor, out: Optional[torch.Tensor] = None,
     mirostat: int = 0, mirostat_tau: float = 5.0, mirostat_eta: float = 0.1, mirostat_mu: Optional[torch.Tensor] = None,
     xtc_probability: float = 0.0, xtc_threshold: float = 0.1, xtc_states: Optional[torch.Tensor] = None,
+    dry_multiplier: float = 0.0, dry_base: float = 1.75, dry_allowed_length: int = 2, dry_last_n: int = 0,
+    dry_breakers: Sequence[int] = (),
 ) -> torch.Tensor:
     """One token per row through penalties -> top-k -> top-p -> min-p -> temperature -> draw (temperature 0:
     the argmax of the penalised logits, no draw).
@@ -703,7 +705,9 @@ def sample_chain(
     the penalties and appends its choice.  work: float32, at least rows * 2 * (vocabulary rounded up to 4).
     mirostat 1 or 2: penalties -> temperature -> mirostat's own cut and draw; mirostat_mu: float32 [slots], NaN
     for a sequence that has not drawn yet.  xtc_probability > 0: the "exclude top choices" filter after min-p, with
-    a generator of its own per slot (xtc_states, int64 like rng_states)."""
+    a generator of its own per slot (xtc_states, int64 like rng_states).  dry_multiplier > 0: the DRY penalty
+    after the other penalties, over the last dry_last_n chosen tokens, with up to 8 breaker tokens.
+    history[slot] is a ring over all 1024 places (the p-th chosen token at p % 1024), whatever the windows."""
     _cuda(logits, "sample_chain logits", torch.float32, contiguous=False)
     stride = _rows(logits, "sample_chain logits")
     R, n = logits.shape
@@ -729,11 +733,14 @@ def sample_chain(
         _need(xtc_states is not None, "sample_chain: XTC needs its random states")
         _cuda(xtc_states, "sample_chain xtc_states", torch.int64)
         _need(xtc_states.numel() == history_count.numel(), "sample_chain: one XTC state per slot")
+    breakers = (ctypes.c_int * max(len(dry_breakers), 1))(*[int(b) for b in dry_breakers])
     lib = build.load("sampling")
     rc = lib.rl_sample_chain(
         _p(logits), c_ll(stride), c_int(R), c_int(n), c_float(temperature), c_float(top_p), c_int(top_k), c_float(min_p),
         c_float(repeat_penalty), c_int(last_n), c_float(frequency_penalty), c_float(presence_penalty), c_int(mirostat),
-        c_float(mirostat_tau), c_float(mirostat_eta), c_float(xtc_probability), c_float(xtc_threshold), _p(rng_states),
+        c_float(mirostat_tau), c_float(mirostat_eta), c_float(xtc_probability), c_float(xtc_threshold),
+        c_float(dry_multiplier), c_float(dry_base), c_int(dry_allowed_length), c_int(dry_last_n), breakers, c_int(len(dry_breakers)),
+        _p(rng_states),
         _p(slot_of_row), _p(history), _p(history_count), _p(mirostat_mu) if mirostat_mu is not None else c_void_p(0),
         _p(xtc_states) if xtc_states is not None else c_void_p(0), _p(work), _p(out), _stream(),
     )

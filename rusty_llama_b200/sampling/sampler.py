@@ -10,7 +10,8 @@ reference builds another chain, penalties -> top-k -> top-p -> min-p -> temperat
 module.  The reference keeps one chain per server slot (src/server.rs:288, :513); here the
 generator states and the penalties' token histories of all sequence slots live in device arrays
 and the kernels advance them.  Mirostat 1 and 2 are a mode of that chain (penalties -> temperature ->
-mirostat), XTC a stage of it after min-p.  Not built: DRY and grammars (they work on token strings).
+mirostat), XTC a stage of it after min-p, DRY one after the penalties.  Not built: grammars (they work on
+token strings).
 """
 
 from __future__ import annotations
@@ -60,7 +61,11 @@ class SamplingParams:
     mirostat 1 or 2 (`--mirostat`, with `--mirostat-lr` eta and `--mirostat-ent` tau) replaces top-k, top-p
     and min-p by its own adaptive cut (src/sampler.rs:829-866) and needs a temperature above 0.
     xtc_probability > 0 (`--xtc-probability`, `--xtc-threshold`): with that probability per token, all but the
-    least likely of the candidates whose probability reaches the threshold are dropped (src/sampler.rs:569-602)."""
+    least likely of the candidates whose probability reaches the threshold are dropped (src/sampler.rs:569-602).
+    dry_multiplier > 0 (`--dry-multiplier`, `--dry-base`, `--dry-allowed-length`, `--dry-penalty-last-n`,
+    `--dry-sequence-breaker`): a token that would make the end of the chosen tokens repeat an earlier stretch of
+    them loses multiplier * base^(repeat length - allowed length) (src/sampler.rs:683-733).  The breakers are
+    token ids here (the reference takes strings of one token each, src/main.rs:349-360); at most 8."""
 
     temperature: float = 1.0
     top_p: float = 0.9
@@ -76,6 +81,11 @@ class SamplingParams:
     mirostat_ent: float = 5.0
     xtc_probability: float = 0.0
     xtc_threshold: float = 0.1
+    dry_multiplier: float = 0.0
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_penalty_last_n: int = 64
+    dry_sequence_breakers: Sequence[int] = ()
 
     def validate(self) -> None:
         if not (self.temperature >= 0.0) or self.temperature == float("inf"):
@@ -88,6 +98,10 @@ class SamplingParams:
             raise ConfigError(f"min_p {self.min_p} or repeat_penalty {self.repeat_penalty} out of range")
         if not (0 <= self.repeat_last_n <= ops.SAMPLE_HISTORY_MAX):
             raise ConfigError(f"repeat_last_n must lie in 0..{ops.SAMPLE_HISTORY_MAX}, got {self.repeat_last_n}")
+        if not (0 <= self.dry_penalty_last_n <= ops.SAMPLE_HISTORY_MAX) or self.dry_allowed_length < 0:
+            raise ConfigError(f"dry_penalty_last_n must lie in 0..{ops.SAMPLE_HISTORY_MAX} and dry_allowed_length be >= 0")
+        if len(self.dry_sequence_breakers) > 8:
+            raise ConfigError(f"at most 8 DRY sequence breakers are taken, got {len(self.dry_sequence_breakers)}")
         if self.mirostat not in (0, 1, 2):
             raise ConfigError(f"mirostat must be 0, 1 or 2, got {self.mirostat}")
         if self.mirostat and not (self.temperature > 0.0):
@@ -100,7 +114,7 @@ class SamplingParams:
     @property
     def longer_chain(self) -> bool:
         """Whether the reference would build its longer chain for these values (src/sampler.rs:868-876)."""
-        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on or self.mirostat != 0 or self.xtc_probability > 0.0
+        return self.top_k != 0 or self.min_p > 0.0 or self.penalties_on or self.mirostat != 0 or self.xtc_probability > 0.0 or self.dry_multiplier > 0.0
 
 
 class PendingTokens:
@@ -194,5 +208,8 @@ class Sampler:
             self.rng_states, index, self.history, self.history_count, work,
             mirostat=params.mirostat, mirostat_tau=params.mirostat_ent, mirostat_eta=params.mirostat_lr,
             mirostat_mu=self.mirostat_mu, xtc_probability=params.xtc_probability, xtc_threshold=params.xtc_threshold,
-            xtc_states=self.xtc_states,
+            xtc_states=self.xtc_states, dry_multiplier=params.dry_multiplier, dry_base=params.dry_base,
+            dry_allowed_length=params.dry_allowed_length,
+            dry_last_n=params.dry_penalty_last_n if params.dry_multiplier > 0.0 else 0,
+            dry_breakers=list(params.dry_sequence_breakers),
         )

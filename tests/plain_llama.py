@@ -346,7 +346,11 @@ class PlainChain:
 
     def __init__(self, temperature=1.0, top_p=0.9, seed=1, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64,
                  frequency_penalty=0.0, presence_penalty=0.0, mirostat=0, mirostat_lr=0.1, mirostat_ent=5.0, mirostat_m=100,
-                 xtc_probability=0.0, xtc_threshold=0.1):
+                 xtc_probability=0.0, xtc_threshold=0.1, dry_multiplier=0.0, dry_base=1.75, dry_allowed_length=2,
+                 dry_penalty_last_n=64, dry_sequence_breakers=()):
+        self.dry_mult, self.dry_base, self.dry_allowed = dry_multiplier, dry_base, max(dry_allowed_length, 1)
+        self.dry_last_n, self.dry_breakers = dry_penalty_last_n, set(dry_sequence_breakers)
+        self.dry_ring = []  # DRY's own ring of chosen tokens (src/sampler.rs:735-743)
         self.xtc_p, self.xtc_thr = xtc_probability, xtc_threshold
         self.xtc_rng = PlainRng(seed)  # its own stream from the same seed (src/sampler.rs:547-553)
         self.mirostat, self.eta, self.tau, self.m = mirostat, mirostat_lr, mirostat_ent, mirostat_m
@@ -381,6 +385,7 @@ class PlainChain:
                     l = f32(l - f32(self.present))
                 out.append((i, l, p))
             cands = out
+        cands = self._dry(cands)
         if self.mirostat:
             return self._accept(self._mirostat(cands))
         # top-k (src/sampler.rs:239-251): the k largest logits; here in descending order
@@ -455,7 +460,59 @@ class PlainChain:
             if len(self.ring) == self.last_n:
                 self.ring.pop(0)
             self.ring.append(token)
+        if self.dry_last_n > 0:
+            if len(self.dry_ring) == self.dry_last_n:
+                self.dry_ring.pop(0)
+            self.dry_ring.append(token)
         return token
+
+    @staticmethod
+    def _z_array(s):
+        """z[k]: length of the longest common prefix of s and s[k:] (src/sampler.rs:612-635); plainly."""
+        n = len(s)
+        z = [0] * n
+        if n:
+            z[0] = n
+        for k in range(1, n):
+            while k + z[k] < n and s[z[k]] == s[k + z[k]]:
+                z[k] += 1
+        return z
+
+    def _dry(self, cands):
+        """DRY (src/sampler.rs:683-733): the chain holds this stage only when the multiplier is above 0 (:889)."""
+        f32 = np.float32
+        if not (self.dry_mult > 0.0) or self.dry_base < 1.0 or self.dry_last_n == 0 or len(self.dry_ring) <= self.dry_allowed:
+            return cands
+        history = list(self.dry_ring)
+        n = len(history)
+        rep_limit = n
+        for i in range(n):
+            if history[n - i - 1] in self.dry_breakers:
+                rep_limit = i
+                break
+        if rep_limit <= self.dry_allowed:
+            return cands
+        rev = history[n - rep_limit:][::-1]
+        z = self._z_array(rev)
+        max_repeat = {}
+        for k in range(1, rep_limit):
+            repeat_len = z[k] + 1
+            if repeat_len < self.dry_allowed:
+                continue
+            cont = rev[k - 1]
+            max_repeat[cont] = max(max_repeat.get(cont, 0), repeat_len)
+        out = []
+        for i, l, p in cands:
+            if i in max_repeat:
+                pw, b, e = f32(1.0), f32(self.dry_base), max_repeat[i] - self.dry_allowed  # powi: by squaring
+                while e > 0:
+                    if e & 1:
+                        pw = f32(pw * b)
+                    b = f32(b * b)
+                    e >>= 1
+                l = f32(l - f32(self.dry_mult) * pw)
+            out.append((i, l, p))
+        return out
 
     def _mirostat(self, cands) -> int:
         """penalties (done) -> temperature -> mirostat 1 (src/sampler.rs:401-449) or 2 (:494-524)."""

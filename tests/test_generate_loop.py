@@ -236,8 +236,13 @@ def test_command_line_options_follow_the_reference(tmp_path):
     a = parse_args(["m", "--xtc-probability", "0.5", "--xtc-threshold", "0.2"])
     assert (a["xtc_probability"], a["xtc_threshold"]) == (0.5, 0.2)
     assert (parse_args(["m"])["xtc_probability"], parse_args(["m"])["xtc_threshold"]) == (0.0, 0.1)
+    a = parse_args(["m", "--dry-multiplier", "0.8", "--dry-base", "2", "--dry-allowed-length", "3", "--dry-penalty-last-n", "128",
+                    "--dry-sequence-breaker", "13", "--dry-sequence-breaker", "198"])
+    assert (a["dry_multiplier"], a["dry_base"], a["dry_allowed_length"], a["dry_penalty_last_n"], a["dry_sequence_breakers"]) == (0.8, 2.0, 3, 128, [13, 198])
+    d = parse_args(["m"])
+    assert (d["dry_multiplier"], d["dry_base"], d["dry_allowed_length"], d["dry_penalty_last_n"], d["dry_sequence_breakers"]) == (0.0, 1.75, 2, 64, [])
     with pytest.raises(SystemExit, match="unknown option"):
-        parse_args(["m", "--dry-multiplier", "0.5"])  # not built: works on token strings
+        parse_args(["m", "--grammar", "root ::= x"])  # not built: works on token strings
     assert parse_prompts("1, 2 3") == [[1, 2, 3]]
     f = tmp_path / "prompts.txt"
     f.write_text("5 6\n\n7,8,9\n")
@@ -258,7 +263,7 @@ def test_sampling_params_pick_the_chain_as_the_reference_does():
 
     assert not SamplingParams(0.8, 0.9, 1).longer_chain
     assert not SamplingParams(0.8, 0.9, 1, repeat_last_n=8).longer_chain  # a window alone changes nothing
-    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5), dict(mirostat=2), dict(xtc_probability=0.3)):
+    for kw in (dict(top_k=5), dict(min_p=0.1), dict(repeat_penalty=1.1), dict(frequency_penalty=0.5), dict(presence_penalty=-0.5), dict(mirostat=2), dict(xtc_probability=0.3), dict(dry_multiplier=0.8)):
         p = SamplingParams(0.8, 0.9, 1, **kw)
         p.validate()
         assert p.longer_chain

@@ -1044,13 +1044,59 @@ def test_sample_chain_mirostat_follows_the_plain_chain(ops, n, mode, tau, eta, t
     assert np.array_equal(states.cpu().numpy().view(np.uint64), np.array([p.rng.state for p in plain], dtype=np.uint64))
 
 
+@pytest.mark.parametrize("n", [12, 9000])
+@pytest.mark.parametrize("extra", [dict(), dict(repeat_penalty=1.1, repeat_last_n=5), dict(dry_sequence_breakers=(2,)), dict(mirostat=2, mirostat_ent=2.0)])
+def test_sample_chain_dry_follows_the_plain_chain(ops, n, extra):
+    """DRY over a history in which stretches do repeat (a handful of likely tokens), with its own window beside
+    the penalties' window, with a breaker token, and inside the mirostat mode: the plain chain's tokens draw for
+    draw, 80 draws, so the ring of 1024 places is read at many phases."""
+    rows = 2
+    g = torch.Generator().manual_seed(n)
+    seeds = [9, 2**35 + 7]
+    states = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    index = torch.arange(rows, dtype=torch.int32, device=DEV)
+    history = torch.zeros(rows, 1024, dtype=torch.int32, device=DEV)
+    count = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    mu = torch.full((rows,), float("nan"), device=DEV)
+    work = torch.empty(rows * 2 * ((n + 3) // 4 * 4), device=DEV)
+    knobs = dict(temperature=0.9, top_p=0.0, dry_multiplier=0.8, dry_base=1.75, dry_allowed_length=2, dry_penalty_last_n=16, repeat_last_n=0)
+    knobs.update(extra)
+    plain = [PlainChain(seed=s, **knobs) for s in seeds]
+    penalised = knobs.get("repeat_penalty", 1.0) != 1.0
+    same = 0
+    for d in range(80):
+        l = torch.randn(rows, n, generator=g)
+        l[:, :5] += 7.0  # five likely tokens: their stretches repeat soon
+        got = ops.sample_chain(
+            l.to(DEV), knobs["temperature"], knobs["top_p"], 0, 0.0, knobs.get("repeat_penalty", 1.0),
+            knobs["repeat_last_n"] if penalised else 0, 0.0, 0.0, states, index, history, count, work,
+            mirostat=knobs.get("mirostat", 0), mirostat_tau=knobs.get("mirostat_ent", 5.0), mirostat_eta=0.1, mirostat_mu=mu,
+            dry_multiplier=knobs["dry_multiplier"], dry_base=knobs["dry_base"], dry_allowed_length=knobs["dry_allowed_length"],
+            dry_last_n=knobs["dry_penalty_last_n"], dry_breakers=knobs.get("dry_sequence_breakers", ()),
+        ).cpu().tolist()
+        want = [plain[r].sample(l[r].tolist()) for r in range(rows)]
+        if got != want:
+            # (without a filter the walk is in index order over the whole row: a draw within rounding of a boundary
+            # may take the neighbour; the histories then go on from the kernel's token)
+            assert n > 1000 and all(abs(a - b) <= 3 for a, b in zip(got, want)), f"draw {d}: {got} against {want}"
+            for r in range(rows):
+                for ring in (plain[r].ring, plain[r].dry_ring):
+                    if ring:
+                        ring[-1] = got[r]
+        else:
+            same += 1
+    assert same >= 76
+    assert count.cpu().tolist() == [80, 80]
+
+
 def test_sample_chain_on_the_reference_cases(ops):
     """The kernel on the inputs and outcomes of the reference's own unit tests of its stages
     (src/sampler.rs:1064-1211)."""
 
     def run(logits, draws=1, ring=(), seed=3, **kw):
         c = dict(temperature=1.0, top_p=0.0, top_k=0, min_p=0.0, repeat_penalty=1.0, repeat_last_n=64, frequency_penalty=0.0,
-                 presence_penalty=0.0, mirostat=0, mirostat_tau=5.0, mirostat_eta=0.1, xtc_probability=0.0, xtc_threshold=0.1)
+                 presence_penalty=0.0, mirostat=0, mirostat_tau=5.0, mirostat_eta=0.1, xtc_probability=0.0, xtc_threshold=0.1,
+                 dry_multiplier=0.0, dry_base=1.75, dry_allowed_length=2, dry_last_n=0, dry_breakers=())
         c.update(kw)
         n = len(logits)
         l = torch.tensor([logits], dtype=torch.float32, device=DEV)
@@ -1059,7 +1105,7 @@ def test_sample_chain_on_the_reference_cases(ops):
         count = torch.zeros(1, dtype=torch.int32, device=DEV)
         last_n = c["repeat_last_n"]
         for t in ring:  # as the kernel itself files chosen tokens
-            history[0, int(count.item()) % last_n] = t
+            history[0, int(count.item()) % 1024] = t
             count += 1
         mu = torch.full((1,), float("nan"), device=DEV)
         work = torch.empty(2 * ((n + 3) // 4 * 4), device=DEV)
@@ -1069,6 +1115,8 @@ def test_sample_chain_on_the_reference_cases(ops):
                 c["presence_penalty"], states, torch.zeros(1, dtype=torch.int32, device=DEV), history, count, work,
                 mirostat=c["mirostat"], mirostat_tau=c["mirostat_tau"], mirostat_eta=c["mirostat_eta"], mirostat_mu=mu,
                 xtc_probability=c["xtc_probability"], xtc_threshold=c["xtc_threshold"], xtc_states=states.clone(),
+                dry_multiplier=c["dry_multiplier"], dry_base=c["dry_base"], dry_allowed_length=c["dry_allowed_length"],
+                dry_last_n=c["dry_last_n"], dry_breakers=c["dry_breakers"],
             ).item()
             for _ in range(draws)
         ]
@@ -1085,6 +1133,16 @@ def test_sample_chain_on_the_reference_cases(ops):
     assert run([10.0, 9.0, 0.0, -1.0], seed=7, temperature=0.0, xtc_probability=1.0, xtc_threshold=0.2)[0] == [1]
     assert run([1.0, 2.0, 3.0, 4.0, 5.0], xtc_probability=1.0, xtc_threshold=0.0)[0] == [0]
     assert run([10.0, 9.0, 0.0, -1.0], temperature=0.0, top_k=4, xtc_probability=0.0)[0] == [0]
+    # dry_short_repeat_at_allowed_length_boundary_hand_computed (src/sampler.rs:1247-1262): after A, B, A the
+    # token B would repeat "A, B": a repeat of 2 = the allowed length, so it loses the bare multiplier
+    dry = dict(temperature=0.0, repeat_last_n=0, dry_multiplier=1.0, dry_base=2.0, dry_allowed_length=2, dry_last_n=64)
+    assert run([0.0, 0.0, 0.5], ring=[1, 2, 1], **dry)[0] == [1]   # token 2 at 0.5 - 1.0 falls behind; last of the equal 0, 1
+    assert run([0.0, 0.0, 1.5], ring=[1, 2, 1], **dry)[0] == [2]   # 1.5 - 1.0 still leads
+    # dry_no_repeat_no_penalty: all different, nothing changes
+    assert run([0.0, 0.3, 0.0, 0.0, 0.0, 0.0], ring=[1, 2, 3, 4, 5], **dry)[0] == [1]
+    # a breaker between the two stretches stops the match
+    assert run([0.0, 0.0, 0.5, 0.0], ring=[1, 2, 3, 1], **dict(dry, dry_breakers=(3,)))[0] == [2]
+    assert run([0.0, 0.0, 0.5, 0.0], ring=[1, 2, 3, 1], **dry)[0] == [3]  # without it, 2 after the last 1 would repeat "1, 2"
 
 
 def test_sample_chain_takes_equal_logits_in_index_order(ops):

@@ -160,3 +160,15 @@ def test_longer_chain_stages_on_the_reference_cases():
     # xtc_zero_probability_is_noop (and draws nothing from its generator)
     c = PlainChain(temperature=0.0, top_k=4, xtc_probability=0.0)
     assert c.sample([10.0, 9.0, 0.0, -1.0]) == 0 and c.xtc_rng.state == c.rng.state
+    # DRY (src/sampler.rs:1231-1262): no repeat, no penalty; after A, B, A the token B loses the bare multiplier
+    dry = dict(temperature=0.0, repeat_last_n=0, dry_multiplier=1.0, dry_base=2.0, dry_allowed_length=2)
+    c = PlainChain(**dry)
+    c.dry_ring = [1, 2, 3, 4, 5]
+    assert c.sample([0.0, 0.3, 0.0, 0.0, 0.0, 0.0]) == 1
+    c = PlainChain(**dry)
+    c.dry_ring = [1, 2, 1]
+    assert c.sample([0.0, 0.0, 0.5]) == 1 and c.sample([0.0, 0.0, 1.5]) == 2
+    assert PlainChain._z_array([1, 2, 1, 2]) == [4, 0, 2, 0] and PlainChain._z_array([1, 2, 3, 4]) == [4, 0, 0, 0]
+    c = PlainChain(dry_sequence_breakers=(3,), **dry)
+    c.dry_ring = [1, 2, 3, 1]
+    assert c.sample([0.0, 0.0, 0.5, 0.0]) == 2  # the breaker keeps "1, 2" out of reach
