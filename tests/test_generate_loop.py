@@ -272,3 +272,20 @@ def test_sampling_params_pick_the_chain_as_the_reference_does():
             SamplingParams(0.8, 0.9, 1, **kw).validate()
     with pytest.raises(ConfigError, match="temperature"):
         SamplingParams(0.0, 0.9, 1, mirostat=1).validate()
+
+
+def test_bench_answers_for_more_gpus_and_for_the_reference_arm():
+    """`bench.py --gpus 2` says in one line that it measures one GPU and exits with 2; `--impl reference` prints
+    its `unavailable` line and exits with 0.  Neither touches a GPU."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    bench = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "bench.py")
+    two = subprocess.run([sys.executable, bench, "--gpus", "2"], capture_output=True, text=True, timeout=120)
+    assert two.returncode == 2 and len(two.stdout.strip().splitlines()) == 1 and "one GPU" in two.stdout
+    ref = subprocess.run([sys.executable, bench, "--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3"],
+                         capture_output=True, text=True, timeout=120)
+    line = json.loads(ref.stdout.strip())
+    assert ref.returncode == 0 and line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
