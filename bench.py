@@ -28,25 +28,26 @@ sys.path.insert(0, ROOT)
 METRIC = "decode_tokens_per_second_batch{batch}_ctx{ctx}"  # at the defaults: batch 8, context 4096
 
 
-def load_config(index: int = 2) -> dict:
-    """BASELINE.json's configs are prose; the sizes of configs[2] as config.json keys."""
-    return {
-        "architectures": ["LlamaForCausalLM"],
-        "hidden_size": 4096,
-        "intermediate_size": 14336,
-        "num_hidden_layers": 32,
-        "num_attention_heads": 32,
-        "num_key_value_heads": 8,
-        "head_dim": 128,
-        "vocab_size": 128256,
-        "max_position_embeddings": 131072,
-        "rms_norm_eps": 1e-5,
-        "rope_theta": 500000.0,
-        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                         "original_max_position_embeddings": 8192},
-        "tie_word_embeddings": False,
-        "torch_dtype": "bfloat16",
-    }
+SIZES = {
+    # BASELINE.json's configs are prose; their sizes as config.json keys.  "8b" is configs[2], the default run.
+    "8b": ("Llama-3.1-8B sizes (BASELINE.json configs[2])", dict(
+        hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+        head_dim=128, vocab_size=128256, max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
+        rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                      "original_max_position_embeddings": 8192})),
+    "1b": ("TinyLlama-1.1B sizes (BASELINE.json configs[3])", dict(
+        hidden_size=2048, intermediate_size=5632, num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4,
+        head_dim=64, vocab_size=32000, max_position_embeddings=2048, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None)),
+    "13b": ("Llama-2-13B sizes (BASELINE.json configs[4])", dict(
+        hidden_size=5120, intermediate_size=13824, num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=40,
+        head_dim=128, vocab_size=32000, max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None)),
+}
+
+
+def load_config(sizes: str = "8b") -> dict:
+    cfg = {"architectures": ["LlamaForCausalLM"], "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
+    cfg.update(SIZES[sizes][1])
+    return cfg
 
 
 def measured_peaks() -> dict:
@@ -123,7 +124,7 @@ def run_ours(args) -> dict:
     from rusty_llama_b200 import StepEntry
     from rusty_llama_b200.kernels import ops
 
-    cfg = load_config()
+    cfg = load_config(args.sizes)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -255,7 +256,7 @@ def run_ours(args) -> dict:
         "data": "synthetic: random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
         "config": {
-            "model": "Llama-3.1-8B sizes (BASELINE.json configs[2])",
+            "model": SIZES[args.sizes][0],
             "global_batch": batch,
             "seq_len": ctx,
             "parallelism": "single GPU",
@@ -268,7 +269,7 @@ def run_ours(args) -> dict:
             "head_dim": cfg["head_dim"],
             "vocab_size": V,
             "rope_theta": cfg["rope_theta"],
-            "rope_scaling": "llama3 factor 8 low 1 high 4 original 8192",
+            "rope_scaling": "llama3 factor 8 low 1 high 4 original 8192" if cfg["rope_scaling"] else "none",
             "rms_norm_eps": cfg["rms_norm_eps"],
             "tie_word_embeddings": False,
             "prefill_tokens": T,
@@ -302,6 +303,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="layer sizes: 8b is BASELINE.json's configs[2] (the default run), 1b and 13b its configs[3] and [4]")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in the output)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="profiling aid: run one phase only")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one")
