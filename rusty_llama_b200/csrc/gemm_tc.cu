@@ -32,13 +32,16 @@ RL_DEFINE_ERROR_TEXT()
 #define BM 128
 #define BN 256
 #define BK 64
-#define STAGES 4
+#define STAGES 4           // (5 when the rows fit a half tile of activations, see SMALL_A)
+#define MAX_STAGES 5
 #define UMMA_K 16
 #define TMEM_COLS 512  // two accumulators of BN columns
 #define NUM_THREADS 192
 #define STAGE_A_BYTES (BM * BK * 2)
 #define STAGE_B_BYTES (BN * BK * 2)
 #define STAGE_BYTES (STAGE_A_BYTES + STAGE_B_BYTES)
+#define SMALL_A_ROWS 64
+#define SMALL_A_BYTES (SMALL_A_ROWS * BK * 2)
 
 template <typename TO>
 __device__ __forceinline__ void store_row32(TO* dst, const uint32_t (&r)[32], int n_valid, bool vec);
@@ -106,7 +109,12 @@ __device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32],
 
 // SWIGLU: w's rows alternate gate and up (row 2i gate i, row 2i+1 up i); the epilogue writes
 // h[m, i] = silu(gate) * up from the 32-bit accumulators, N / 2 columns per row.
-template <typename TO, bool SWIGLU>
+// SMALL_A: at most 64 rows (a decode step of 9 to 64 sequences, bound by the weights' bytes).  A block then
+// streams 2 MB of weights through four stages of 32 KB at 49 GB/s, well under what an SM can take, so the
+// activations' half of a stage shrinks to the 64 rows that exist and a fifth stage takes the room (measured
+// at 64 x 28672 x 4096: 43.0 -> 41.0 us).  The MMA still spans 128 rows: its rows 64..127 read the first 8 KB of the
+// stage's weights as if they were activations and fill accumulator rows that are never stored.
+template <typename TO, bool SWIGLU, bool SMALL_A>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int k_splits, int bn,
@@ -114,8 +122,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   extern __shared__ unsigned char smem_dyn[];
   // the swizzled stages must start on a 1024-byte boundary
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t full_bar[STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  constexpr int N_STAGES = SMALL_A ? 5 : STAGES;
+  constexpr int A_BYTES = SMALL_A ? SMALL_A_BYTES : STAGE_A_BYTES;
+  constexpr int STG_BYTES = A_BYTES + STAGE_B_BYTES;
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_slot;
@@ -131,7 +142,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int slices_per_split = (slices_total + k_splits - 1) / k_splits;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < N_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -157,13 +168,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (lane == 0) {
       // the same walk over (unit, k block) twice: at most STAGES steps of it for the early weights, then all of it
       uint32_t early = 0;
-      for (int unit = blockIdx.x; unit < n_units && early < STAGES; unit += gridDim.x) {
+      for (int unit = blockIdx.x; unit < n_units && early < N_STAGES; unit += gridDim.x) {
         const int tile = unit % n_tiles, ks = unit / n_tiles;
         const int n0 = (tile / tiles_m) * bn;
         const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
-        for (int kb = kb0; kb < kb1 && early < STAGES; ++kb, ++early) {
-          unsigned char* b_dst = stages + (size_t)early * STAGE_BYTES + STAGE_A_BYTES;
-          mbar_expect_tx(&full_bar[early], STAGE_A_BYTES + bn * BK * 2);
+        for (int kb = kb0; kb < kb1 && early < N_STAGES; ++kb, ++early) {
+          unsigned char* b_dst = stages + (size_t)early * STG_BYTES + A_BYTES;
+          mbar_expect_tx(&full_bar[early], A_BYTES + bn * BK * 2);
           tma_load_2d(b_dst, &map_w, &full_bar[early], kb * BK, n0);
         }
       }
@@ -175,8 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
         const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t round = it / STAGES;
+          const int s = it % N_STAGES;
+          const uint32_t round = it / N_STAGES;
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
             atomicExch(status, 1);
             abort_flag = 1;
@@ -187,10 +198,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             ok = false;
             break;
           }
-          unsigned char* a_dst = stages + (size_t)s * STAGE_BYTES;
-          unsigned char* b_dst = a_dst + STAGE_A_BYTES;
+          unsigned char* a_dst = stages + (size_t)s * STG_BYTES;
+          unsigned char* b_dst = a_dst + A_BYTES;
           if (it >= early) {
-            mbar_expect_tx(&full_bar[s], STAGE_A_BYTES + bn * BK * 2);
+            mbar_expect_tx(&full_bar[s], A_BYTES + bn * BK * 2);
             tma_load_2d(b_dst, &map_w, &full_bar[s], kb * BK, n0);
           }
           tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
@@ -201,8 +212,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (!ok) {
         // (an early request for weights whose activations were never asked for cannot complete its barrier;
         // its bytes have long arrived by the time a bounded wait of a second has expired elsewhere)
-        const uint32_t first = it > STAGES ? it - STAGES : 0;
-        for (uint32_t j = first; j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
+        const uint32_t first = it > N_STAGES ? it - N_STAGES : 0;
+        for (uint32_t j = first; j < it; ++j) mbar_wait(&full_bar[j % N_STAGES], (j / N_STAGES) & 1);
       }
     }
   } else if (warp == 1) {
@@ -210,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, bn);
       // descriptors differ from stage to stage only in their address field (bytes / 16)
-      const uint64_t a_desc0 = make_smem_desc(smem_u32(stages)), b_desc0 = make_smem_desc(smem_u32(stages) + STAGE_A_BYTES);
+      const uint64_t a_desc0 = make_smem_desc(smem_u32(stages)), b_desc0 = make_smem_desc(smem_u32(stages) + A_BYTES);
       uint32_t it = 0, s = 0, phase = 0;  // slices so far; the stage and the parity of its `full` barrier
       bool ok = true;
       int local = 0;  // tiles done by this block
@@ -239,10 +250,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint64_t stage_off = (uint64_t)(s * (STAGE_BYTES >> 4));
+          const uint64_t stage_off = (uint64_t)(s * (STG_BYTES >> 4));
           umma_bf16_x4(tmem_d, a_desc0 + stage_off, b_desc0 + stage_off, idesc, kb > kb0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);
-          if (++s == STAGES) {
+          if (++s == N_STAGES) {
             s = 0;
             phase ^= 1;
           }
@@ -348,13 +359,14 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   }
   const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) * k_splits;
   CUtensorMap map_x, map_w;
-  int e1 = make_matrix_map(&map_x, x, M, K, ldx, BM), e2 = make_matrix_map(&map_w, w, N, K, ldw, bn);
+  const bool small_a = M <= SMALL_A_ROWS;
+  int e1 = make_matrix_map(&map_x, x, M, K, ldx, small_a ? SMALL_A_ROWS : BM), e2 = make_matrix_map(&map_w, w, N, K, ldw, bn);
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  const size_t smem = (small_a ? (size_t)5 * (SMALL_A_BYTES + STAGE_B_BYTES) : (size_t)STAGES * STAGE_BYTES) + 1024;
   dim3 grid((unsigned)(tiles < n_sms ? tiles : n_sms));
 #define RL_TC_LAUNCH(TOUT, SW)                                                                                      \
   do {                                                                                                            \
-    auto kern = gemm_tc_kernel<TOUT, SW>;                                                                         \
+    auto kern = small_a ? gemm_tc_kernel<TOUT, SW, true> : gemm_tc_kernel<TOUT, SW, false>;                       \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
       RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
     RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store,  \
