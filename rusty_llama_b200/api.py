@@ -20,6 +20,22 @@ from .weights import load_model, random_model
 
 DEFAULT_STEPS = 256  # the reference's `-n` default (src/main.rs:30)
 
+# Without a `max_tokens` the cache is sized for 8 sequences of the model's position limit, but never
+# for more than this share of the device memory that is free once the weights are loaded: the rest is
+# for a prompt step's activations and the sampler's scratch.
+DEFAULT_CACHE_SEQUENCES = 8
+DEFAULT_CACHE_SHARE = 0.5
+
+
+def default_max_tokens(model: Model) -> int:
+    want = DEFAULT_CACHE_SEQUENCES * model.spec.max_positions
+    per_token = model.cache_bytes_per_token()
+    if model.rt.device.type != "cuda" or per_token == 0:
+        return want
+    free, _ = torch.cuda.mem_get_info(model.rt.device)
+    fits = int(free * DEFAULT_CACHE_SHARE) // per_token // 64 * 64
+    return max(64, min(want, fits))
+
 
 class LLM:
     """A loaded model with its cache, step function and sampler."""
@@ -27,7 +43,7 @@ class LLM:
     def __init__(self, model: Model, max_tokens: Optional[int] = None, max_seqs: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         if max_tokens is None:
-            max_tokens = 8 * model.spec.max_positions
+            max_tokens = default_max_tokens(model)
         self.engine = Engine(model, max_tokens, max_seqs, use_graphs=use_graphs)
         self.sampler = Sampler(model.rt.device, self.engine.cache.max_seqs, model.spec.vocab_size, model.rt.workspace)
         self.last_stats: Optional[GenerationStats] = None
@@ -39,8 +55,9 @@ class LLM:
     def close_sequence(self, slot: int) -> None:
         self.engine.close_sequence(slot)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        return self.engine.step(entries)
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
+        """`Engine.step`: float32 logits [wanted, vocab], the caller's to keep unless `borrow`."""
+        return self.engine.step(entries, borrow=borrow)
 
     # -- generation
     def generate(

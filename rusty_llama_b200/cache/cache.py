@@ -88,6 +88,7 @@ class KVGroup:
         self.runs = list(runs)
         self.pool = PagePool(n_pages)
         shape = (len(runs), n_pages, need.num_kv_heads, PAGE_SIZE, need.head_dim)
+        dtype = need.dtype or dtype  # a need may name its own storage type; else the run's
         # zero-filled once: a page that was never written holds finite values, which the
         # attention kernels rely on when they multiply masked scores by unread rows
         self.k = torch.zeros(shape, dtype=dtype, device=device)
@@ -150,6 +151,23 @@ class Cache:
             if not isinstance(need, (KVNeed, StateNeed)):
                 raise CacheError(f"run {run} asks for {need!r}, which is neither a KVNeed nor a StateNeed")
             by_need.setdefault(need, []).append(run)
+        if self.device.type == "cuda":
+            # say so before allocating, with the numbers, instead of running out of memory half-way
+            asked = 0
+            for need, runs in by_need.items():
+                if isinstance(need, KVNeed):
+                    size = torch.empty((), dtype=need.dtype or dtype).element_size()
+                    asked += 2 * len(runs) * self.n_pages * need.num_kv_heads * PAGE_SIZE * need.head_dim * size
+                else:
+                    n = torch.empty((), dtype=need.dtype).element_size() * max_seqs * len(runs)
+                    for s in need.shape:
+                        n *= s
+                    asked += n
+            free, _ = torch.cuda.mem_get_info(self.device)
+            if asked > free:
+                raise CacheError(
+                    f"a cache of {self.max_tokens} positions needs {asked / 2**30:.1f} GiB, the device has {free / 2**30:.1f} GiB free: "
+                    f"ask for fewer positions (max_tokens)")
         self.kv_groups: List[KVGroup] = []
         self.state_groups: List[StateGroup] = []
         self._where: Dict[int, Tuple[str, int, int]] = {}  # run -> (family, group index, index in group)

@@ -19,7 +19,8 @@ from .rope_scaling import RopeScaling
 
 ARCHITECTURE = "LlamaForCausalLM"
 
-_DTYPES = ("bfloat16", "float32")
+# how the checkpoint stores its tensors; the run's own type is chosen at load (bfloat16 or float32)
+_DTYPES = ("bfloat16", "float32", "float16")
 
 
 def _positive_int(d: Mapping[str, Any], key: str) -> int:

@@ -89,7 +89,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        int fuse, bf16* __restrict__ k_pages_w, bf16* __restrict__ v_pages_w,
                        const float* __restrict__ inv_freq, int rot, int interleaved,
                        unsigned int* __restrict__ counters, bf16* __restrict__ out, int out_stride,
-                       const float* __restrict__ q_parts, int n_parts, long long part_stride) {
+                       const float* __restrict__ q_parts, int n_parts, long long part_stride, int test_role,
+                       uint32_t test_ns) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -110,6 +111,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int h0 = kh * G + g0;
   const int s = blockIdx.z;
   const bool aligned = (smem_u32(smem) & 1023u) == 0;
+  const WaitCtl ctl = {&bars.abort_flag, test_role, test_ns};
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -117,7 +119,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       mbar_init(&bars.empty[i], PRODUCT_WARPS);
     }
     bars.abort_flag = aligned ? 0 : 1;
-    if (!aligned) atomicExch(status, 56);
+    if (!aligned) give_up_code(status, 56);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // rows of the query tile past the group's heads are zero
@@ -139,8 +141,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   if (warp == PRODUCT_WARPS) {
     // ---------------- copies
+    int issued = 0;
     if (lane == 0 && !*(volatile int*)&bars.abort_flag) {
-      int issued = 0;
       bool waited = false;
       for (int tile = my_lo; tile <= my_hi; ++tile, ++issued) {
         const int st = issued % STAGES, round = issued / STAGES;
@@ -150,8 +152,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           pdl_wait();
           waited = true;
         }
-        if (round > 0 && !mbar_wait(&bars.empty[st], (round - 1) & 1)) {
-          atomicExch(status, 51);
+        if (round > 0 && !mbar_wait_role(&bars.empty[st], (round - 1) & 1, ctl, 51)) {
+          give_up_code(status, 51);
           bars.abort_flag = 1;
           break;
         }
@@ -164,11 +166,15 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tma_load_4d(dst + 2 * HALF_BYTES, &map_v, &bars.full[st], 0, 0, kh, page);
         tma_load_4d(dst + 3 * HALF_BYTES, &map_v, &bars.full[st], 64, 0, kh, page);
       }
-      // nothing may still be writing shared memory when the block ends (or when the ring is reused for
-      // the merge): if someone gave up, wait (bounded) for the copies that were started
-      if (*(volatile int*)&bars.abort_flag)
-        for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&bars.full[j % STAGES], (j / STAGES) & 1);
     }
+    // The copying warp stays until the product warps have left their loop over the pages (they arrive at
+    // this barrier without waiting).  Nothing may still be writing shared memory when the block ends, or
+    // when the ring is reused for the merge... which only happens when nobody gave up: if someone did, the
+    // copying lane now waits (bounded, with the long limit) for the copies that were started.
+    __syncwarp();
+    asm volatile("bar.sync 2, %0;" ::"n"(NUM_THREADS) : "memory");
+    if (lane == 0 && *(volatile int*)&bars.abort_flag)
+      for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&bars.full[j % STAGES], (j / STAGES) & 1);
     return;  // the product warps meet at a barrier of their own
   }
 
@@ -274,9 +280,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   int done = 0;
   for (int tile = my_lo; tile <= my_hi && ok; ++tile, ++done) {
     const int st = done % STAGES;
-    if (!mbar_wait(&bars.full[st], (done / STAGES) & 1)) {
+    if (!mbar_wait_role(&bars.full[st], (done / STAGES) & 1, ctl, 52)) {
       if (lane == 0) {
-        atomicExch(status, 52);
+        give_up_code(status, 52);
         bars.abort_flag = 1;
       }
       ok = false;
@@ -392,6 +398,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   // ---- the four warps' partial results meet in the ring's memory, which nobody reads any more once
   // every product warp is here (a warp that gave up comes here too)
+  asm volatile("bar.arrive 2, %0;" ::"n"(NUM_THREADS) : "memory");  // lets the copying warp go (see there)
   product_warps_sync();
   if (*(volatile int*)&bars.abort_flag) return;  // the same answer for all four warps: nothing changes it after the barrier
 #pragma unroll
@@ -518,12 +525,14 @@ RL_API int rl_attn_decode_tma_head_dim() { return HD; }
 // counters: null, or n_seqs * (K * groups of 8 heads) zeros in device memory: the splits are then added
 // up by the block that finishes last (no merge kernel is launched) and the counters are zeros again
 // when the kernel ends.
+// wait_test_role, wait_test_ns: 0, 0 in normal use; a test names 51 or 52 and a limit in nanoseconds, and
+// that role's waits give up after that long instead of a second.
 RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
                               const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
                               void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
                               float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
                               int interleaved, unsigned int* counters, const float* q_parts, int n_parts,
-                              long long part_stride, cudaStream_t stream) {
+                              long long part_stride, int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
   if (hd != HD) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for %d", hd, HD);
   if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
@@ -548,7 +557,8 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, SMEM_BYTES, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
                             table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
                             fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
-                            interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride));
+                            interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride, wait_test_role,
+                            (uint32_t)wait_test_ns));
   if (counters != nullptr) return 0;
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,

@@ -46,6 +46,7 @@ struct SmallItems {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_ready, pv_done[2];
   uint64_t pair_bar[4];            // the two warps of a lane quarter meet here
+  uint64_t drain_bar;              // an issuer that gives up waits here for the MMAs it has issued
   float pair_val[2][2][BMQ];       // [tile parity][column half][row]
   uint32_t tmem_slot;
   int abort_flag;
@@ -65,7 +66,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
-                        int out_stride, int H, int K, int window, float scale_log2, int* __restrict__ status) {
+                        int out_stride, int H, int K, int window, float scale_log2, int* __restrict__ status,
+                        int test_role, uint32_t test_ns) {
   // All shared memory is dynamic, so that the seven 32 KB tiles start at the block's first byte
   // (1024-byte aligned, as the 128-byte swizzle needs) and the small items fit behind them.
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -83,13 +85,16 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   uint64_t& p_ready = sm.p_ready;
   uint64_t(&pv_done)[2] = sm.pv_done;
   uint64_t(&pair_bar)[4] = sm.pair_bar;
+  uint64_t& drain_bar = sm.drain_bar;
   float(&pair_val)[2][2][BMQ] = sm.pair_val;
   uint32_t& tmem_slot = sm.tmem_slot;
   int& abort_flag = sm.abort_flag;
   if (smem_u32(smem_dyn) & 1023u) {  // uniform over the block; nothing has been set up yet
-    if (threadIdx.x == 0) atomicExch(status, 23);
+    if (threadIdx.x == 0) give_up_code(status, 23);
     return;
   }
+  const WaitCtl ctl = {&abort_flag, test_role, test_ns};
+  int issued_k = 0, issued_v = 0;  // (the producer's lane) key and value tiles whose copies were started
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s = blockIdx.x / H, h = blockIdx.x % H;
@@ -123,6 +128,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
     mbar_init(&pv_done[0], 1);
     mbar_init(&pv_done[1], 1);
+    mbar_init(&drain_bar, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -143,7 +149,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tma_load_2d(q_s + SUB_BYTES, &map_q, &q_full, h * HD + 64, tok0 + row0);
       const int* table = block_table + (size_t)s * table_width;
       bool ok = true;
-      int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t round = j / KV_STAGES;
@@ -155,8 +160,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           pages[p] = idx < table_width ? table[idx] : 0;  // a page past the sequence's end is never attended to
         }
         // K
-        if (round > 0 && !mbar_wait(&k_empty[st], (round - 1) & 1)) {
-          atomicExch(status, 11);
+        if (round > 0 && !mbar_wait_role(&k_empty[st], (round - 1) & 1, ctl, 11)) {
+          give_up_code(status, 11);
           abort_flag = 1;
           break;
         }
@@ -169,8 +174,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tma_load_4d(k_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_k, &k_full[st], 64 * b, 0, kh, pages[p]);
         issued_k = j + 1;
         // V
-        if (round > 0 && !mbar_wait(&v_empty[st], (round - 1) & 1)) {
-          atomicExch(status, 12);
+        if (round > 0 && !mbar_wait_role(&v_empty[st], (round - 1) & 1, ctl, 12)) {
+          give_up_code(status, 12);
           abort_flag = 1;
           break;
         }
@@ -182,13 +187,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tma_load_4d(v_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_v, &v_full[st], 64 * b, 0, kh, pages[p]);
         issued_v = j + 1;
       }
-      // nothing may still be writing shared memory when the block ends: if someone gave up, wait
-      // (bounded) for the copies that were started
-      if (*(volatile int*)&abort_flag) {
-        mbar_wait(&q_full, 0);
-        for (int j = max(0, issued_k - KV_STAGES); j < issued_k; ++j) mbar_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1);
-        for (int j = max(0, issued_v - KV_STAGES); j < issued_v; ++j) mbar_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1);
-      }
     }
   } else if (warp == SOFTMAX_WARPS + 1) {
     // ---------------- tensor-core issuer
@@ -196,15 +194,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const uint32_t idesc_qk = make_idesc_bf16(BMQ, BNK, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BMQ, HD, 0, 1);
       const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-      bool ok = mbar_wait(&q_full, 0);
+      bool ok = mbar_wait_role(&q_full, 0, ctl, 13);
       if (!ok) {
-        atomicExch(status, 13);
+        give_up_code(status, 13);
         abort_flag = 1;
       }
       auto issue_qk = [&](int j) -> bool {
         const int st = j % KV_STAGES;
-        if (!mbar_wait(&k_full[st], (j / KV_STAGES) & 1)) {
-          atomicExch(status, 14);
+        if (!mbar_wait_role(&k_full[st], (j / KV_STAGES) & 1, ctl, 14)) {
+          give_up_code(status, 14);
           abort_flag = 1;
           return false;
         }
@@ -225,14 +223,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);  // S of the next tile is computed while this tile's softmax runs
         if (!ok) break;
-        if (!mbar_wait(&p_ready, j & 1)) {
-          atomicExch(status, 15);
+        if (!mbar_wait_role(&p_ready, j & 1, ctl, 15)) {
+          give_up_code(status, 15);
           abort_flag = 1;
           break;
         }
         const int st = j % KV_STAGES;
-        if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1)) {
-          atomicExch(status, 16);
+        if (!mbar_wait_role(&v_full[st], (j / KV_STAGES) & 1, ctl, 16)) {
+          give_up_code(status, 16);
           abort_flag = 1;
           break;
         }
@@ -248,6 +246,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         umma_commit(&v_empty[st]);
         umma_commit(&pv_done[j & 1]);
       }
+      if (*(volatile int*)&abort_flag) {
+        // the tensor core may still be at work on what was issued before a wait failed: tensor memory is not
+        // given back, and the block does not end, before that is done (bounded like the drain)
+        umma_commit(&drain_bar);
+        mbar_wait(&drain_bar, 0);
+      }
     }
   } else {
     // ---------------- softmax and output: warps w and w + 4 own tensor-memory lanes 32(w % 4)..+31,
@@ -262,23 +266,23 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     bool ok = true;
     auto give_up = [&](int code) {
       if (lane == 0) {
-        atomicExch(status, code);
+        give_up_code(status, code);
         abort_flag = 1;
       }
       ok = false;
     };
     // both halves of a row learn the other's value: write, arrive, wait (bounded), read
-    auto exchange = [&](float mine, int parity_slot, float& other) -> bool {
+    auto exchange = [&](float mine, int parity_slot, float& other, int code) -> bool {
       pair_val[parity_slot][half][r] = mine;
       __syncwarp();
       if (lane == 0) mbar_arrive(&pair_bar[quarter]);
-      if (!mbar_wait(&pair_bar[quarter], pair_phase)) return false;
+      if (!mbar_wait_role(&pair_bar[quarter], pair_phase, ctl, code)) return false;
       pair_phase ^= 1;
       other = pair_val[parity_slot][half ^ 1][r];
       return true;
     };
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) {
+      if (!mbar_wait_role(&s_full[j & 1], (j >> 1) & 1, ctl, 17)) {
         give_up(17);
         break;
       }
@@ -308,7 +312,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int i = 0; i < HALF_COLS; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
       }
       float mx_other;
-      if (!exchange(mx, j & 1, mx_other)) {
+      if (!exchange(mx, j & 1, mx_other, 21)) {
         give_up(21);
         break;
       }
@@ -318,7 +322,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const float m_next = raise ? mx : m_run;
       if (j > 0 && __any_sync(0xffffffffu, raise && m_run != -INFINITY)) {
         // the accumulator holds sums scaled by 2^-m_run: bring this warp's rows and columns to 2^-m_next
-        if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) {
+        if (!mbar_wait_role(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, ctl, 18)) {
           give_up(18);
           break;
         }
@@ -339,7 +343,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       m_run = m_next;
       const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;  // a row past the sequence's end may see nothing
       // the P buffer of this tile was last read by the product of tile j - 2
-      if (j >= 2 && !mbar_wait(&pv_done[j & 1], ((j - 2) >> 1) & 1)) {
+      if (j >= 2 && !mbar_wait_role(&pv_done[j & 1], ((j - 2) >> 1) & 1, ctl, 19)) {
         give_up(19);
         break;
       }
@@ -366,9 +370,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
-    if (ok && !mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) give_up(20);
+    if (ok && !mbar_wait_role(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, ctl, 20)) give_up(20);
     float l_other = 0.f;
-    if (ok && !exchange(l_run, n_tiles & 1, l_other)) give_up(22);
+    if (ok && !exchange(l_run, n_tiles & 1, l_other, 22)) give_up(22);
     if (ok) {
       tc_fence_after();
       const float l_all = l_run + l_other;
@@ -396,17 +400,30 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_before();
   __syncthreads();
   if (warp == SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  // Every role is done or has given up.  Nothing may still be writing shared memory when the block ends: if
+  // someone gave up, the producer's lane waits (bounded, with the long limit) for the copies that were
+  // started.  It does so here, after the roles have met, because it may have left its loop before another
+  // role gave up.
+  if (threadIdx.x == SOFTMAX_WARPS * 32 && *(volatile int*)&abort_flag) {
+    mbar_wait(&q_full, 0);
+    for (int j = max(0, issued_k - KV_STAGES); j < issued_k; ++j) mbar_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+    for (int j = max(0, issued_v - KV_STAGES); j < issued_v; ++j) mbar_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1);
+  }
 }
 
 // ------------------------------------------------------------------ host side
 RL_API int rl_flash_prefill_tc_head_dim() { return HD; }
 
 // status: one int in device memory, 0 before the call; afterwards non-zero means that a bounded wait
-// expired (11-22: which one; 23: shared memory not aligned) and the output is not valid.
+// expired (11, 12 the producer for a free key / value stage; 13, 14, 15, 16 the tensor-core issuer for the
+// queries, a key tile, the probabilities, a value tile; 17-22 a softmax warp; 23: shared memory not aligned)
+// and the output is not valid.  wait_test_role, wait_test_ns: 0, 0 in normal use; a test names one of these
+// codes and a limit in nanoseconds, and that role's waits give up after that long instead of a second.
 RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
                                int n_pages, const int* block_table, int table_width, const int* seq_start,
                                const int* seq_pos0, void* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
-                               int hd, int page_size, int window, float scale, int* status, cudaStream_t stream) {
+                               int hd, int page_size, int window, float scale, int* status, int wait_test_role,
+                               unsigned int wait_test_ns, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || n_tokens <= 0 || n_pages <= 0)
     RL_REFUSE(1, "flash_prefill_tc: S=%d max_q=%d H=%d K=%d T=%d pages=%d", n_seqs, max_q_len, H, K, n_tokens, n_pages);
   if (hd != HD) RL_REFUSE(2, "flash_prefill_tc: head size %d, this kernel is built for %d", hd, HD);
@@ -428,6 +445,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
     RL_REFUSE(12, "flash_prefill_tc: cannot get %zu bytes of shared memory", smem);
   dim3 grid(H * n_seqs, (max_q_len + BMQ - 1) / BMQ);
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
-                            (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status));
+                            (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status, wait_test_role,
+                            (uint32_t)wait_test_ns));
   return 0;
 }

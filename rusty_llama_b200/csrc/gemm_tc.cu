@@ -118,7 +118,7 @@ template <typename TO, bool SWIGLU, bool SMALL_A>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int k_splits, int bn,
-               int* __restrict__ status) {
+               int* __restrict__ status, int test_role, uint32_t test_ns) {
   extern __shared__ unsigned char smem_dyn[];
   // the swizzled stages must start on a 1024-byte boundary
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -129,10 +129,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ __align__(8) uint64_t drain_bar;  // an issuer that gives up waits here for the MMAs it has issued
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  const WaitCtl ctl = {&abort_flag, test_role, test_ns};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t issued = 0;  // (the producer's lane) slices whose copies were started
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   const int n_tiles = tiles_m * tiles_n;
   // a unit of work is one output tile and one slice of the k range (k_splits > 1: each slice
@@ -150,6 +153,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
     }
+    mbar_init(&drain_bar, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -188,13 +192,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % N_STAGES;
           const uint32_t round = it / N_STAGES;
-          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-            atomicExch(status, 1);
+          if (round > 0 && !mbar_wait_role(&empty_bar[s], (round - 1) & 1, ctl, 1)) {
+            give_up_code(status, 1);
             abort_flag = 1;
             ok = false;
             break;
           }
-          if (*(volatile int*)&abort_flag) {
+          // (a stage whose weights were asked for early still gets its activations when the block is being
+          // abandoned: its barrier then completes and the drain below can wait for it)
+          if (*(volatile int*)&abort_flag && it >= early) {
             ok = false;
             break;
           }
@@ -207,14 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           tma_load_2d(a_dst, &map_x, &full_bar[s], kb * BK, m0);
         }
       }
-      // nothing may still be writing shared memory when the block ends: if someone gave up, wait
-      // (bounded) for the copies that were started and not consumed
-      if (!ok) {
-        // (an early request for weights whose activations were never asked for cannot complete its barrier;
-        // its bytes have long arrived by the time a bounded wait of a second has expired elsewhere)
-        const uint32_t first = it > N_STAGES ? it - N_STAGES : 0;
-        for (uint32_t j = first; j < it; ++j) mbar_wait(&full_bar[j % N_STAGES], (j / N_STAGES) & 1);
-      }
+      issued = it;
     }
   } else if (warp == 1) {
     // ---------------- tensor-core issuer (reads shared and tensor memory only: no wait of its own)
@@ -230,8 +229,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int kb0 = ks * slices_per_split, kb1 = min(slices_total, kb0 + slices_per_split);
         const int acc = local & 1;
         const uint32_t use = local >> 1;  // how often this half was used before
-        if (use > 0 && !mbar_wait(&acc_empty[acc], (use - 1) & 1)) {
-          atomicExch(status, 4);
+        if (use > 0 && !mbar_wait_role(&acc_empty[acc], (use - 1) & 1, ctl, 4)) {
+          give_up_code(status, 4);
           abort_flag = 1;
           ok = false;
           break;
@@ -243,8 +242,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          if (!mbar_wait(&full_bar[s], phase)) {
-            atomicExch(status, 2);
+          if (!mbar_wait_role(&full_bar[s], phase, ctl, 2)) {
+            give_up_code(status, 2);
             abort_flag = 1;
             ok = false;
             break;
@@ -260,6 +259,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         if (ok) umma_commit(&acc_full[acc]);  // arrives when the whole tile has been accumulated
       }
+      if (!ok) {
+        // the tensor core may still be at work on slices issued before the wait that failed: tensor memory
+        // is not given back, and the block does not end, before they are done (bounded like the drain)
+        umma_commit(&drain_bar);
+        mbar_wait(&drain_bar, 0);
+      }
     }
   } else {
     // ---------------- epilogue: warps 2..5, each on its quarter of the 128 lanes
@@ -270,10 +275,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int tile = unit % n_tiles, ks = unit / n_tiles;
       TO* out_k = out + (size_t)ks * M * ldo;
       const int acc = local & 1;
-      const bool ok = mbar_wait(&acc_full[acc], (local >> 1) & 1);
+      const bool ok = mbar_wait_role(&acc_full[acc], (local >> 1) & 1, ctl, 3);
       if (!ok) {
         if (lane == 0) {
-          atomicExch(status, 3);
+          give_up_code(status, 3);
           abort_flag = 1;
         }
         break;
@@ -305,6 +310,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  // Every role is done or has given up.  Nothing may still be writing shared memory when the block ends: if
+  // someone gave up, the producer's lane waits (bounded, with the long limit) for the copies that were
+  // started and not consumed.  It does so here, after the roles have met, because the producer may have
+  // left its loop before another role gave up.
+  if (threadIdx.x == 0 && *(volatile int*)&abort_flag) {
+    const uint32_t first = issued > N_STAGES ? issued - N_STAGES : 0;
+    for (uint32_t j = first; j < issued; ++j) mbar_wait(&full_bar[j % N_STAGES], (j / N_STAGES) & 1);
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -314,8 +327,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel).
 // k_splits > 1: the k range is cut into that many slices (rounded so that none is empty; the number
 // used is returned through *k_splits_used), out is [slices][M][ldo] float32 partial results.
+// wait_test_role, wait_test_ns: 0, 0 in normal use.  A test names one of the codes above and a limit in
+// nanoseconds: the waits of that role then give up after that long instead of a second.
 RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                      int K, int swiglu, int k_splits, int* k_splits_used, int* status, cudaStream_t stream) {
+                      int K, int swiglu, int k_splits, int* k_splits_used, int* status, int wait_test_role,
+                      unsigned int wait_test_ns, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
   if (swiglu && (N & 1)) RL_REFUSE(11, "gemm_tc: %d gate/up rows are not pairs", N);
@@ -370,7 +386,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
       RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
     RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store,  \
-                              k_splits, bn, status));                                                                 \
+                              k_splits, bn, status, wait_test_role, (uint32_t)wait_test_ns));                         \
   } while (0)
   if (out_dtype == RL_BF16 && swiglu) RL_TC_LAUNCH(bf16, true);
   else if (out_dtype == RL_BF16) RL_TC_LAUNCH(bf16, false);

@@ -93,7 +93,8 @@ __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float
 template <typename TO, bool SWIGLU, bool HI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ CUtensorMap map_w, TO* __restrict__ out, int ldo,
-                   int M, int N, int K, int slice_len, int units, int items, int* __restrict__ status) {
+                   int M, int N, int K, int slice_len, int units, int items, int* __restrict__ status, int test_role,
+                   uint32_t test_ns) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -102,14 +103,16 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
   StreamBarriers& bars = *reinterpret_cast<StreamBarriers*>(reinterpret_cast<unsigned char*>(red) + RED_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (smem_u32(smem) & 1023u) {  // uniform over the block; nothing has been set up yet
-    if (threadIdx.x == 0) atomicExch(status, 36);
+    if (threadIdx.x == 0) give_up_code(status, 36);
     return;
   }
+  const WaitCtl ctl = {&bars.abort_flag, test_role, test_ns};
 
   pdl_trigger();
   if (threadIdx.x == 32) rl_trace_event(1);  // (profiling aid, see common.cuh) block 0 is running
   if (threadIdx.x == CONSUMER_WARPS * 32)  // the copying lane: have the tensor map on its way before the barriers are set up
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+  int issued = 0;  // (the copying lane) stages whose copies were started
   const int first_item = (int)((long long)blockIdx.x * items / gridDim.x);
   const int end_item = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
 
@@ -139,8 +142,8 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
         const int kbeg = slice * slice_len, klen = min(slice_len, K - kbeg);
         for (int k0 = 0; k0 < klen; k0 += KC, ++it) {
           const int st = it % STAGES, round = it / STAGES;
-          if (round > 0 && !mbar_wait(&bars.empty[st], (round - 1) & 1)) {
-            atomicExch(status, 32);
+          if (round > 0 && !mbar_wait_role(&bars.empty[st], (round - 1) & 1, ctl, 32)) {
+            give_up_code(status, 32);
             bars.abort_flag = 1;
             ok = false;
             break;
@@ -157,10 +160,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
         }
       }
       rl_trace_event(7);  // last copy issued
-      // nothing may still be writing shared memory when the block ends: if someone gave up, wait
-      // (bounded) for the copies that were started
-      if (*(volatile int*)&bars.abort_flag)
-        for (int j = max(0, it - STAGES); j < it; ++j) mbar_wait(&bars.full[j % STAGES], (j / STAGES) & 1);
+      issued = it;
     }
   } else if (warp > CONSUMER_WARPS) {
     // ---------------- sums and stores
@@ -170,9 +170,9 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     for (int item = first_item; item < end_item; ++item, ++done_items) {
       const int slice = item / units, unit = item - slice * units;
       const int buf = done_items & 1;
-      if (!mbar_wait(&bars.red_full[buf], (done_items >> 1) & 1)) {
+      if (!mbar_wait_role(&bars.red_full[buf], (done_items >> 1) & 1, ctl, 35)) {
         if (lane == 0) {
-          atomicExch(status, 35);
+          give_up_code(status, 35);
           bars.abort_flag = 1;
         }
         break;
@@ -221,7 +221,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     bool ok = true;
     auto give_up = [&](int code) {
       if (lane == 0) {
-        atomicExch(status, code);
+        give_up_code(status, code);
         bars.abort_flag = 1;
       }
       ok = false;
@@ -251,7 +251,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
       for (int s = 0; s < SLICE_STAGES; ++s) {
         if (s * KC < klen && ok) {
           const int st = it % STAGES;
-          if (!mbar_wait(&bars.full[st], (it / STAGES) & 1)) {
+          if (!mbar_wait_role(&bars.full[st], (it / STAGES) & 1, ctl, 34)) {
             give_up(34);
           } else if (*(volatile int*)&bars.abort_flag) {
             ok = false;
@@ -275,7 +275,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
       if (!ok) break;
       // leave the partial sums to the storing warps; the buffer was last read two items ago
       const int buf = done_items & 1;
-      if (done_items >= 2 && !mbar_wait(&bars.red_free[buf], ((done_items >> 1) - 1) & 1)) {
+      if (done_items >= 2 && !mbar_wait_role(&bars.red_free[buf], ((done_items >> 1) - 1) & 1, ctl, 37)) {
         give_up(37);
         break;
       }
@@ -293,6 +293,12 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
       if (warp == 0 && lane == 0 && item == end_item - 1) rl_trace_event(6);  // last item's sums handed over
     }
   }
+  // Every role is done or has given up.  Nothing may still be writing shared memory when the block ends: if
+  // someone gave up, the copying lane waits (bounded, with the long limit) for the copies that were started.
+  // It does so here, after the roles have met, because it may have left its loop before another role gave up.
+  __syncthreads();
+  if (threadIdx.x == CONSUMER_WARPS * 32 && *(volatile int*)&bars.abort_flag)
+    for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&bars.full[j % STAGES], (j / STAGES) & 1);
 }
 
 // How the kernel cuts k: k per slice (a multiple of KC, at most MAX_SLICE) and the slices that
@@ -321,9 +327,13 @@ RL_API int rl_gemv_stream_slices(int M, int K, int k_slices) {
 // swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns.
 // k_slices > 1: out is [slices_used][M][ldo] float32 partial results that the consumer adds up.
 // status: one int in device memory, 0 before the call; non-zero afterwards means that a bounded
-// wait expired (32, 34, 35, 37: which one; 36: shared memory not aligned) and the output is not valid.
+// wait expired (32 the copying lane, 34 a product warp waiting for weights, 35 a storing warp, 37 a product
+// warp waiting for a free sum buffer; 36: shared memory not aligned) and the output is not valid.
+// wait_test_role, wait_test_ns: 0, 0 in normal use; a test names one of these codes and a limit in
+// nanoseconds, and that role's waits give up after that long instead of a second.
 RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                          int K, int swiglu, int k_slices, int* slices_used, int* status, cudaStream_t stream) {
+                          int K, int swiglu, int k_slices, int* slices_used, int* status, int wait_test_role,
+                          unsigned int wait_test_ns, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_stream: M=%d N=%d K=%d", M, N, K);
   if (M > MAX_M) RL_REFUSE(2, "gemv_stream: %d rows, this kernel takes at most %d", M, MAX_M);
   if (K % 64 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_stream: K=%d must be a multiple of 64, ldx=%d and ldw=%d of 8", K, ldx, ldw);
@@ -367,7 +377,8 @@ RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)                 \
       RL_REFUSE(14, "gemv_stream: cannot get %d bytes of shared memory", SMEM_BYTES);                                       \
     RL_LAUNCH_CHECK(rl_launch<true>(kern, dim3(blocks), NUM_THREADS, SMEM_BYTES, stream, (const bf16*)x, ldx, map_w,       \
-                                    (TO*)out, ldo, M, N, K, slice_len, units, items, status));                            \
+                                    (TO*)out, ldo, M, N, K, slice_len, units, items, status, wait_test_role,              \
+                                    (uint32_t)wait_test_ns));                                                             \
   } while (0)
 #define LAUNCH_ROWS(TO, SW)      \
   do {                           \

@@ -39,9 +39,19 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
   return a;
 }
 
-__device__ int block_argmax(const float* row, int n, float t, ArgMax* sh) {
+// The reference's argmax compares with `!(best > candidate)`, which a NaN on either side makes true: a NaN
+// takes the running maximum's place and is itself replaced by whatever follows it (src/sampler.rs:76-84, test
+// :983-988).  The result is therefore the last of the equal maxima among the elements AFTER the row's last NaN,
+// or that NaN's own index when it is the row's last element.  Only a broken model produces NaN logits, so
+// the first scan also looks for the last NaN and a second scan over the elements after it runs only then.
+__device__ int block_argmax_scan(const float* row, int lo, int n, float t, ArgMax* sh, int* last_nan_out) {
   ArgMax best = {-INFINITY, -1};
-  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+  int last_nan = -1;
+  auto see = [&](float v, int i) {
+    if (v != v) last_nan = max(last_nan, i);
+    else best = better(best, ArgMax{v / t, i});
+  };
+  if (lo == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
     // four values per load, four loads in flight: a row of 128k logits is scanned by one block,
     // which would otherwise wait for one load after the other
     const int n4 = n >> 2;
@@ -54,27 +64,28 @@ __device__ int block_argmax(const float* row, int n, float t, ArgMax* sh) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int base = 4 * (i + u * blockDim.x);
-        best = better(best, ArgMax{v[u].x / t, base});
-        best = better(best, ArgMax{v[u].y / t, base + 1});
-        best = better(best, ArgMax{v[u].z / t, base + 2});
-        best = better(best, ArgMax{v[u].w / t, base + 3});
+        see(v[u].x, base);
+        see(v[u].y, base + 1);
+        see(v[u].z, base + 2);
+        see(v[u].w, base + 3);
       }
     }
     for (; i < n4; i += blockDim.x) {
       const float4 v = r4[i];
-      best = better(best, ArgMax{v.x / t, 4 * i});
-      best = better(best, ArgMax{v.y / t, 4 * i + 1});
-      best = better(best, ArgMax{v.z / t, 4 * i + 2});
-      best = better(best, ArgMax{v.w / t, 4 * i + 3});
+      see(v.x, 4 * i);
+      see(v.y, 4 * i + 1);
+      see(v.z, 4 * i + 2);
+      see(v.w, 4 * i + 3);
     }
-    for (int j = 4 * n4 + threadIdx.x; j < n; j += blockDim.x) best = better(best, ArgMax{row[j] / t, j});
+    for (int j = 4 * n4 + threadIdx.x; j < n; j += blockDim.x) see(row[j], j);
   } else {
-    for (int i = threadIdx.x; i < n; i += blockDim.x) best = better(best, ArgMax{row[i] / t, i});
+    for (int i = lo + threadIdx.x; i < n; i += blockDim.x) see(row[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     ArgMax other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
     best = better(best, other);
+    last_nan = max(last_nan, __shfl_xor_sync(0xffffffffu, last_nan, o));
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   __syncthreads();
@@ -82,7 +93,22 @@ __device__ int block_argmax(const float* row, int n, float t, ArgMax* sh) {
   __syncthreads();
   ArgMax r = sh[0];
   for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = better(r, sh[w]);
-  return r.i < 0 ? n - 1 : r.i;  // all NaN: the reference ends on the last index
+  __syncthreads();
+  if (lane == 0) sh[warp].i = last_nan;
+  __syncthreads();
+  int ln = sh[0].i;
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) ln = max(ln, sh[w].i);
+  *last_nan_out = ln;
+  return r.i;
+}
+
+__device__ int block_argmax(const float* row, int n, float t, ArgMax* sh) {
+  int last_nan;
+  const int idx = block_argmax_scan(row, 0, n, t, sh, &last_nan);
+  if (last_nan < 0) return idx;
+  if (last_nan == n - 1) return n - 1;
+  int none;
+  return block_argmax_scan(row, last_nan + 1, n, t, sh, &none);
 }
 
 __global__ void argmax_kernel(const float* __restrict__ logits, long long row_stride, int n, int* __restrict__ out) {

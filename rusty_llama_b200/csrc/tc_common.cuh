@@ -2,9 +2,17 @@
 // kernels that use them: mbarriers with bounded waits, TMA tile loads, tensor-memory allocation,
 // tcgen05.mma / commit / ld, and the shared-memory and instruction descriptors.
 //
-// Bounded waits: mbar_wait polls for about one second and then returns false; the caller records a
-// code in its status word, tells the other roles through a flag and lets the block drain, so that a
-// mistake in a pipeline ends in an error message instead of a hung GPU.
+// Bounded waits.  A role (producer, tensor-core issuer, product or epilogue warp) waits with
+// mbar_wait_role: it polls for the role limit (about one second), looks at the block's abort flag
+// now and then, and returns false when the limit ran out or another role has given up.  The caller
+// then records its code in the status word (the first code sticks), raises the abort flag and lets the
+// block drain, so that a mistake in a pipeline ends in an error message instead of a hung GPU.
+// mbar_wait is the wait of the drain itself: it keeps a block alive until the copies it started have
+// landed, never looks at the abort flag and always has the long limit (a copy that lands in the
+// shared memory of a block that has ended is the fault all of this exists to prevent).
+// For tests, a launch may name one role code whose waits get another limit (WaitCtl.test_role,
+// test_ns): that role then polls without suspending and reads the clock before every poll, so a limit
+// of 0 runs out before the first poll and one of a few nanoseconds before any copy can have arrived.
 #pragma once
 
 #include <cuda.h>
@@ -40,7 +48,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the barrier did not flip within WAIT_LIMIT_NS.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// The drain's wait: false when the barrier did not flip within WAIT_LIMIT_NS.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   // try_wait itself suspends the thread for a while before it answers "not yet", so this is no
@@ -52,6 +73,34 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((spins & 15u) == 0 && global_ns() - t0 > WAIT_LIMIT_NS) return false;
   }
 }
+
+// What a role's waits need to know: the block's abort flag (shared memory) and the launch's test knob.
+struct WaitCtl {
+  const volatile int* abort;
+  int test_role;
+  uint32_t test_ns;
+};
+// A role's wait (see the header): false when its limit ran out or the block is being abandoned.
+__device__ __forceinline__ bool mbar_wait_role(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int role) {
+  if (role == ctl.test_role) {
+    // polls while the limit lasts: a limit of 0 has run out before the first poll, whatever has arrived
+    const uint64_t t0 = global_ns();
+    while (global_ns() - t0 < ctl.test_ns)
+      if (mbar_test_wait(bar, parity)) return true;
+    return false;
+  }
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 15u) == 0) {
+      if (*ctl.abort) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+// Records why a block gives up: the first code of a launch stays (later ones are consequences of it).
+__device__ __forceinline__ void give_up_code(int* status, int code) { atomicCAS(status, 0, code); }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(

@@ -231,11 +231,17 @@ class Engine:
         tables = [meta.dev_part(8 + g).view(S, w) for g, w in enumerate(meta.widths)]
         return step, tables
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
         """Run the entries' tokens; returns float32 logits [wanted, vocab] on the device,
-        in the order of the entries and of each entry's `want`."""
+        in the order of the entries and of each entry's `want`.
+
+        The result is the caller's to keep.  borrow=True skips the copy that makes it so: a decode
+        step that was replayed as a CUDA graph then returns the graph's own output buffer, which
+        the next decode step of the same batch size overwrites; a caller that has consumed the
+        logits before its next call (in stream order: sampling from them is enough) may ask for that."""
         if self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
-            return self._decode_graph_step(entries)
+            logits = self._decode_graph_step(entries)
+            return logits if borrow else logits.clone()
         self._validate(entries)
         slots = [e.slot for e in entries]
         q_lens = [len(e.tokens) for e in entries]
@@ -257,12 +263,19 @@ class Engine:
         self.cache.commit(slots, q_lens)
         return logits
 
+    def step_borrowed(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """`step(entries, borrow=True)`, for loops that consume a step's logits before their next call."""
+        return self.step(entries, borrow=True)
+
     # ------------------------------------------------------------------ decode through a graph
     def step_device_tokens(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         """One token for each of `slots`, taken from `tokens` (int32 [len(slots)] on the device, for
         instance what the sampler just wrote) without the host ever seeing them; logits for every
         slot.  The generation loop uses it to launch a step before it has read the previous step's
-        tokens, so that launching overlaps the GPU's work."""
+        tokens, so that launching overlaps the GPU's work.
+
+        The logits are borrowed (see `step`): they are the replayed graph's output buffer and hold
+        this step's values only until the next decode step of the same batch size is launched."""
         if tokens.dtype != torch.int32 or tokens.device != self.rt.device or tuple(tokens.shape) != (len(slots),):
             raise StepError(f"step_device_tokens wants int32 [{len(slots)}] on {self.rt.device}, got {tokens.dtype} {tuple(tokens.shape)} on {tokens.device}")
         entries = [StepEntry(int(s), [0], [0]) for s in slots]

@@ -138,6 +138,8 @@ def generate(
     ]
     stats = stats if stats is not None else GenerationStats()
     step_ahead = getattr(engine, "step_device_tokens", None) if launch_ahead else None
+    # the loop samples from a step's logits before it launches the next step, so it may borrow them
+    step_borrowing = getattr(engine, "step_borrowed", engine.step)
 
     for batch in batches:
         stats.batches += 1
@@ -211,7 +213,7 @@ def generate(
                     logits = ahead if len(kept_rows) == n_before else ahead[kept_rows]
                 else:
                     t_call = time.perf_counter()
-                    logits = engine.step([StepEntry(s.slot, [s.next_token], [0]) for s in running])
+                    logits = step_borrowing([StepEntry(s.slot, [s.next_token], [0]) for s in running])
                     stats.decode_step_call_seconds += time.perf_counter() - t_call
                     stats.decode_steps += 1
                 for s in running:
@@ -221,4 +223,7 @@ def generate(
             for s in running:
                 if s.slot >= 0:
                     engine.close_sequence(s.slot)
+    check = getattr(engine, "check_device_status", None)
+    if check is not None:
+        check()  # one synchronisation per call: a decode kernel that gave up on a wait made its step's tokens invalid
     return results  # type: ignore[return-value]

@@ -18,6 +18,7 @@ import torch
 
 from ..errors import KernelError
 from . import ops
+from .device import sm_count
 
 _library_gemm = False
 
@@ -25,10 +26,6 @@ _library_gemm = False
 # the activations for its 16 features and the L1/L2 traffic, not HBM, sets the pace; the tcgen05
 # kernel stages the activations in shared memory once per tile and streams weights at HBM rate.
 STREAM_MAX_ROWS = 8
-_SMS = 148
-# (The kernel in which two SMs share a 256-row tile, `ops.gemm_tc(pair=True)`, is not used here:
-# measured alone at 2048 rows it is within -1 .. +3 % of the single-SM kernel, and inside a prompt step
-# of the 8B sizes it was slower, 29.2 to 32.0 ms against 28.9.)
 
 
 def _streams(M: int, K: int, whole: bool) -> bool:
@@ -68,7 +65,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         if _streams(M, K, whole=True):
             return ops.gemv_stream(x, w, out_dtype)
         return ops.gemv_bf16(x, w, out_dtype)
-    if M <= 32 and ((M + 127) // 128) * ((w.shape[0] + 255) // 256) < _SMS // 2:
+    if M <= 32 and ((M + 127) // 128) * ((w.shape[0] + 255) // 256) < sm_count(x.device) // 2:
         # too few output tiles to keep the SMs busy, and nothing downstream that could add up
         # partial sums: the streaming kernel's many small blocks still win here (measured)
         return ops.gemv_bf16(x, w, out_dtype)
@@ -93,8 +90,8 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
 
 
-# blocks of the streaming kernel that fill a 148-SM part (six resident blocks per SM)
-_STREAM_TARGET_BLOCKS = 888
+# resident blocks of the register-streaming kernel per SM: its splits of k aim at filling the GPU once
+_STREAM_BLOCKS_PER_SM = 6
 
 
 def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -115,14 +112,16 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         # (for a long k the tcgen05 kernel below is faster even at one row: 25 us against 32 us
         # for the 8B down projection)
         blocks = (N + 15) // 16
-        splits = min((_STREAM_TARGET_BLOCKS + blocks - 1) // blocks, 8, max(1, K // 1024))
+        target = _STREAM_BLOCKS_PER_SM * sm_count(x.device)
+        splits = min((target + blocks - 1) // blocks, 8, max(1, K // 1024))
         if splits > 1:
             return ops.gemv_bf16(x, w, torch.float32, k_splits=splits)
         return ops.gemv_bf16(x, w)
     if _library_gemm:
         return linear(x, w)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
-    splits = min(_SMS // tiles, 8, max(1, K // 512)) if tiles <= _SMS // 2 else 1
+    sms = sm_count(x.device)
+    splits = min(sms // tiles, 8, max(1, K // 512)) if tiles <= sms // 2 else 1
     if splits > 1:
         return ops.gemm_tc(x, w, torch.float32, k_splits=splits)
     return ops.gemm_tc(x, w)

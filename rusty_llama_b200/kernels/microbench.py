@@ -79,18 +79,17 @@ def bench_gemm(a) -> dict:
     nv = min(_copies(a.n * a.k * 2), 16)
     ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
     x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
-    if a.impl in ("tc", "tc2"):
-        pair = a.impl == "tc2"
+    if a.impl == "tc":
         out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
         if a.splits > 1:
-            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.float32, k_splits=a.splits, pair=pair), nv, a.iters, a.warmup)
+            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.float32, k_splits=a.splits), nv, a.iters, a.warmup)
         else:
-            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out, pair=pair), nv, a.iters, a.warmup)
+            us = _time(lambda i: ops.gemm_tc(x, ws[i], torch.bfloat16, out=out), nv, a.iters, a.warmup)
         ops.tc_status_check()
     else:
         us = _time(lambda i: linear(x, ws[i]), nv, a.iters, a.warmup)
     flops = 2.0 * a.rows * a.n * a.k
-    return {"kernel": {"tc": "gemm_tc", "tc2": "gemm_tc2"}.get(a.impl, "linear(bf16)"), "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+    return {"kernel": "gemm_tc" if a.impl == "tc" else "linear(bf16)", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def _paged(seqs: int, ctx: int, K: int, hd: int, copies: int):

@@ -356,7 +356,7 @@ def attn_decode(
             c_int(n_splits), _p(status), c_int(fuse), _p(inv_freq) if (fuse and rotary_dim) else c_void_p(0), c_int(rotary_dim if fuse else 0),
             c_int(1 if interleaved else 0), _p(counters) if counters is not None else c_void_p(0),
             _p(q_parts) if q_parts is not None else c_void_p(0), c_int(0 if q_parts is None else q_parts.shape[0]),
-            c_ll(0 if q_parts is None else q_parts.stride(0)), _stream(),
+            c_ll(0 if q_parts is None else q_parts.stride(0)), *_wt(), _stream(),
         )
         _check(lib, rc, "attn_decode_tma", kernels=1 if counters is not None else 2)
         return out
@@ -434,7 +434,7 @@ def flash_prefill_tc(
     rc = lib.rl_flash_prefill_tc(
         _p(q), c_int(qs), c_int(T), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), _p(seq_start), _p(seq_pos0), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len),
-        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), _stream(),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), *_wt(), _stream(),
     )
     _check(lib, rc, "flash_prefill_tc")
     return out
@@ -565,7 +565,7 @@ def gemv_stream(
     lib = build.load("gemv_stream")
     rc = lib.rl_gemv_stream(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_stream out")), c_int(ldo),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), *_wt(), _stream(),
     )
     _check(lib, rc, "gemv_stream")
     _need(used.value == slices, f"gemv_stream: kernel used {used.value} slices, the wrapper planned {slices}")
@@ -573,6 +573,31 @@ def gemv_stream(
 
 
 _tc_status = {}
+_wait_test = (0, 0)  # (role code, limit in nanoseconds) handed to the launchers with bounded waits; (0, 0): none
+
+
+class short_wait:
+    """For tests of the give-up paths: inside `with ops.short_wait(code, ns):` the kernels with bounded waits
+    let the role whose status code is `code` wait `ns` nanoseconds instead of a second (every other role keeps
+    its limit, and so do the waits that keep a block alive until its copies have landed).  The codes are the
+    ones `tc_status_check` names."""
+
+    def __init__(self, role_code: int, limit_ns: int):
+        self.value = (int(role_code), int(limit_ns))
+
+    def __enter__(self):
+        global _wait_test
+        self.before, _wait_test = _wait_test, self.value
+        return self
+
+    def __exit__(self, *exc):
+        global _wait_test
+        _wait_test = self.before
+        return False
+
+
+def _wt():
+    return c_int(_wait_test[0]), ctypes.c_uint(_wait_test[1])
 
 
 def _tc_status_word(device: torch.device) -> torch.Tensor:
@@ -582,30 +607,41 @@ def _tc_status_word(device: torch.device) -> torch.Tensor:
     return _tc_status[key]
 
 
+_STATUS_NAMES = {
+    1: "gemm_tc: the TMA producer (for a free stage)", 2: "gemm_tc: the tensor-core issuer (for a stage's data)",
+    3: "gemm_tc: an epilogue warp (for a finished accumulator)", 4: "gemm_tc: the tensor-core issuer (for a free accumulator)",
+    11: "flash_prefill_tc: the TMA producer (for a free key stage)", 12: "flash_prefill_tc: the TMA producer (for a free value stage)",
+    13: "flash_prefill_tc: the tensor-core issuer (for the queries)", 14: "flash_prefill_tc: the tensor-core issuer (for a key tile)",
+    15: "flash_prefill_tc: the tensor-core issuer (for the probabilities)", 16: "flash_prefill_tc: the tensor-core issuer (for a value tile)",
+    17: "flash_prefill_tc: a softmax warp (for the scores)", 18: "flash_prefill_tc: a softmax warp (for the product before a rescale)",
+    19: "flash_prefill_tc: a softmax warp (for a free probability buffer)", 20: "flash_prefill_tc: a softmax warp (for the last product)",
+    21: "flash_prefill_tc: a softmax warp (for its partner's maximum)", 22: "flash_prefill_tc: a softmax warp (for its partner's sum)",
+    23: "flash_prefill_tc: shared memory not aligned",
+    32: "gemv_stream: the copying lane (for a free stage)", 34: "gemv_stream: a product warp (for a stage's weights)",
+    35: "gemv_stream: a storing warp (for an item's sums)", 36: "gemv_stream: shared memory not aligned",
+    37: "gemv_stream: a product warp (for a free sum buffer)",
+    51: "attn_decode_tma: the copying lane (for a free stage)", 52: "attn_decode_tma: a product warp (for a page)",
+    56: "attn_decode_tma: shared memory not aligned",
+}
+
+
 def tc_status_check() -> None:
-    """Raise if a bounded wait inside a tensor-core kernel expired since the last check (synchronises)."""
-    names = {1: "gemm_tc: the TMA producer", 2: "gemm_tc: the tensor-core issuer", 3: "gemm_tc: the epilogue",
-             4: "gemm_tc: the tensor-core issuer (for a free accumulator)",
-             41: "gemm_tc2: a TMA producer", 42: "gemm_tc2: the tensor-core issuer", 43: "gemm_tc2: an epilogue",
-             44: "gemm_tc2: the tensor-core issuer (for a free accumulator)"}
+    """Raise if a bounded wait inside a TMA / tensor-core kernel expired since the last check (synchronises);
+    the status word is zero again afterwards."""
     for word in _tc_status.values():
         code = int(word.item())
         if code:
             word.zero_()
-            who = names.get(code, f"flash_prefill_tc: a role (wait {code})" if 11 <= code <= 23 else
-                            f"gemv_stream: a role (wait {code})" if 31 <= code <= 37 else
-                            f"attn_decode_tma: a role (wait {code})" if 51 <= code <= 56 else "a role")
+            who = _STATUS_NAMES.get(code, "a role")
             raise KernelError(f"{who} gave up waiting on a barrier (code {code}); results of that step are not valid")
 
 
 def gemm_tc(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1, pair: bool = False,
+    swiglu: bool = False, k_splits: int = 1,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
 
-    pair: the kernel in which two SMs share a 256 x 256 tile (tcgen05 cta_group::2) instead of one SM
-    per 128 x 256 tile; same results, less shared-memory traffic per flop.
     swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit accumulators.
     k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (at most k_splits of
     them), for a consumer that adds them up: more blocks at work when the output has few tiles."""
@@ -631,10 +667,10 @@ def gemm_tc(
         _need(tuple(out.shape) == (M, n_out), "gemm_tc: out has the wrong shape")
         ldo = _rows(out, "gemm_tc out")
     status = _tc_status_word(x.device)
-    lib = build.load("gemm_tc2" if pair else "gemm_tc")
-    rc = (lib.rl_gemm_tc2 if pair else lib.rl_gemm_tc)(
+    lib = build.load("gemm_tc")
+    rc = lib.rl_gemm_tc(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(ldo),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), *_wt(), _stream(),
     )
     _check(lib, rc, "gemm_tc")
     if k_splits > 1:

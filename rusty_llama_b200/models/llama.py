@@ -86,6 +86,9 @@ def describe_llama(cfg: LlamaConfig) -> ModelSpec:
         ),
         stop_token_ids=cfg.eos_token_ids,
         stored_dtype=cfg.torch_dtype,
+        # Llama folders often carry the rotary tables as buffers (they are recomputed here from theta and
+        # the scaling) and, beside tied embeddings, a second copy of the matrix as lm_head.weight
+        redundant_tensors=("*.rotary_emb.inv_freq",) + (("lm_head.weight",) if cfg.tie_word_embeddings else ()),
     )
 
 

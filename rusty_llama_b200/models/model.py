@@ -37,15 +37,21 @@ class Model:
 
     # ------------------------------------------------------------------ weights
     def parts(self):
-        yield self.embedding
+        """Every part of the model, owners before what they own (`Part.children`)."""
+
+        def walk(part):
+            yield part
+            for child in part.children():
+                yield from walk(child)
+
+        yield from walk(self.embedding)
         for b in self.blocks:
-            yield b.mixer
-            if hasattr(b.mixer, "position"):
-                yield b.mixer.position
-            yield b.feed_forward
-            yield from b.norms.values()
-        yield self.final_norm
-        yield self.head
+            yield from walk(b.mixer)
+            yield from walk(b.feed_forward)
+            for n in b.norms.values():
+                yield from walk(n)
+        yield from walk(self.final_norm)
+        yield from walk(self.head)
 
     def param_infos(self) -> Dict[str, ParamInfo]:
         """Every tensor the checkpoint must hold.  A name asked for by two parts
@@ -73,6 +79,17 @@ class Model:
             if need is not None:
                 needs.append((run, need))
         return needs
+
+    def cache_bytes_per_token(self) -> int:
+        """Bytes of key/value storage that one cached position costs over all runs of the schedule."""
+        from ..parts.base import KVNeed
+
+        total = 0
+        for _, need in self.cache_needs():
+            if isinstance(need, KVNeed):
+                size = torch.empty((), dtype=need.dtype or self.rt.dtype).element_size()
+                total += 2 * need.num_kv_heads * need.head_dim * size
+        return total
 
     def new_cache(self, max_tokens: int, max_seqs: int) -> Cache:
         return Cache(self.cache_needs(), max_tokens, max_seqs, self.rt.dtype, self.rt.device)

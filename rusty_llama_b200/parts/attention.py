@@ -9,33 +9,35 @@ import torch
 
 from ..errors import ConfigError
 from ..kernels import ops
+from ..kernels.device import sm_count
 from ..kernels.linear import linear, linear_to_stream
 from ..spec import PartSpec
 from .base import MIXERS, POSITIONS, KVNeed, Mixer, ParamInfo
 
-# one-warp blocks of the decode kernel that a 148-SM part holds at once (four per SM at head size
-# 128, its shared memory's limit): measured best when the splits fill that and no more
-_DECODE_TARGET_BLOCKS = 592
+# one-warp blocks of the decode kernel that an SM holds at once (four at head size 128, its shared
+# memory's limit): measured best when the splits fill the GPU once and no more
+_DECODE_BLOCKS_PER_SM = 4
 _DECODE_HEADS_PER_BLOCK = 8
 
 
 # the four-warp kernel for head size 128: two blocks per SM; a split shorter than four pages costs
 # more in the merge than it gains (measured at one sequence of 4096: 16 splits 7.5 us, 37 splits 8.8)
 _QKV_PARTIALS_MAX_ROWS = 128
-_DECODE_TMA_TARGET_BLOCKS = 296
+_DECODE_TMA_BLOCKS_PER_SM = 2
 _DECODE_TMA_MIN_PAGES = 4
 
 
-def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int, head_dim: int = 0) -> int:
+def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int, head_dim: int = 0, sms: int = 0) -> int:
     """How many pieces to cut the key range into, from shapes only (head_dim tells which of the two
-    decode kernels will run)."""
+    decode kernels will run; sms: the GPU's multiprocessors, asked from the current device if 0)."""
+    sms = sms or sm_count()
     group = num_heads // num_kv_heads
     per_split = n_seqs * num_kv_heads * ((group + _DECODE_HEADS_PER_BLOCK - 1) // _DECODE_HEADS_PER_BLOCK)
     tiles = max(1, (kv_len + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE)
     if head_dim == ops.ATTN_DECODE_TMA_HEAD_DIM:
-        want = _DECODE_TMA_TARGET_BLOCKS // per_split
+        want = _DECODE_TMA_BLOCKS_PER_SM * sms // per_split
         return max(1, min(want, (tiles + _DECODE_TMA_MIN_PAGES - 1) // _DECODE_TMA_MIN_PAGES, 64))
-    want = _DECODE_TARGET_BLOCKS // per_split
+    want = _DECODE_BLOCKS_PER_SM * sms // per_split
     return max(1, min(want, tiles, 64))
 
 
@@ -62,8 +64,12 @@ class Attention(Mixer):
         self.window = int(self._param("window"))
         if self.H % self.K:
             raise ConfigError(f"attention: {self.H} heads are not a multiple of {self.K} kv heads")
-        if self.hd % 8 or self.hd > 256:
-            raise ConfigError(f"attention: head_dim {self.hd} must be a multiple of 8 and at most 256 for the kernels built here")
+        if self.hd > 256:
+            raise ConfigError(f"attention: head_dim {self.hd} is above 256, the most the attention kernels built here take")
+        if self.hd % 8 and runtime.dtype != torch.float32:
+            raise ConfigError(
+                f"attention: the bfloat16 kernels move a head in 16-byte pieces and need head_dim to be a multiple of 8, got {self.hd} "
+                f"(a float32 run takes any head size up to 256)")
         pos_spec = self._param("position")
         if not isinstance(pos_spec, PartSpec):
             raise ConfigError("attention: 'position' must be a PartSpec")
@@ -75,6 +81,9 @@ class Attention(Mixer):
 
     def cache_need(self):
         return KVNeed(self.K, self.hd, self.window)
+
+    def children(self):
+        return (self.position,)
 
     def param_infos(self) -> Dict[str, ParamInfo]:
         p = self.prefix

@@ -111,6 +111,7 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    dtype: Optional[torch.dtype] = None  # None: the run's activation type
 
 
 @dataclass(frozen=True)
@@ -134,6 +135,11 @@ class Part:
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         """Receive the tensors named by `param_infos`, already on the device in their run types."""
+
+    def children(self) -> Tuple["Part", ...]:
+        """Parts that this part owns (an attention mixer's position encoding, extra norms): the model
+        asks them for their tensors and loads them like its own parts."""
+        return ()
 
     def _param(self, key: str):
         try:

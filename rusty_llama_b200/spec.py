@@ -63,6 +63,10 @@ class ModelSpec:
     head: PartSpec
     stop_token_ids: Tuple[int, ...] = ()
     stored_dtype: str = "bfloat16"
+    # shell-style patterns of tensor names that checkpoints of this architecture are known to carry
+    # although no part wants them (buffers that are recomputed at load, a copy of a tied matrix): the
+    # loader passes over them with a note; any other unexpected tensor stays an error
+    redundant_tensors: Tuple[str, ...] = ()
 
     def validate(self) -> None:
         from .errors import ConfigError

@@ -53,9 +53,9 @@ def main(argv=None) -> int:
             entries.append(StepEntry(slots[rid], [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])]))
         if entries:
             logits = llm.step(entries)
+            arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+            llm.engine.check_device_status()  # every step: a kernel that gave up on a wait ends the run here
             if logits.shape[0] > 0:
-                arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
-                llm.engine.check_device_status()
                 tmp = os.path.join(args.out, f"{step_id}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(args.out, f"{step_id}.f32"))

@@ -10,7 +10,9 @@ same things tensor by tensor while parsing GGUF (src/model.rs:562-585,
 
 from __future__ import annotations
 
-from typing import Dict, Mapping, Optional, Tuple
+import fnmatch
+import sys
+from typing import Dict, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -26,11 +28,12 @@ _INT_STORED = {"I32": torch.int32, "I64": torch.int64}
 
 
 def compare_with_checkpoint(
-    wanted: Mapping[str, ParamInfo], found: Mapping[str, Tuple[str, Tuple[int, ...]]]
+    wanted: Mapping[str, ParamInfo], found: Mapping[str, Tuple[str, Tuple[int, ...]]], redundant: Sequence[str] = ()
 ) -> Optional[WeightsError]:
-    """found: name -> (stored dtype name, shape).  None when everything matches."""
+    """found: name -> (stored dtype name, shape).  None when everything matches.
+    redundant: patterns of names that may be present without being wanted (`ModelSpec.redundant_tensors`)."""
     missing = sorted(n for n in wanted if n not in found)
-    unexpected = sorted(n for n in found if n not in wanted)
+    unexpected = sorted(n for n in found if n not in wanted and not any(fnmatch.fnmatchcase(n, p) for p in redundant))
     wrong_shape, wrong_dtype = [], []
     for name, info in wanted.items():
         if name not in found:
@@ -74,9 +77,14 @@ def load_tensors(model: Model, source: Mapping[str, torch.Tensor] | Checkpoint) 
         rev = {torch.bfloat16: "BF16", torch.float32: "F32", torch.float16: "F16", torch.int32: "I32", torch.int64: "I64"}
         found = {n: (rev.get(t.dtype, str(t.dtype)), tuple(t.shape)) for n, t in source.items()}
         read = source.__getitem__
-    err = compare_with_checkpoint(wanted, found)
+    redundant = tuple(model.spec.redundant_tensors)
+    err = compare_with_checkpoint(wanted, found, redundant)
     if err is not None:
         raise err
+    passed_over = sorted(n for n in found if n not in wanted)
+    if passed_over:
+        print(f"[rusty_llama_b200] passing over {len(passed_over)} tensors the model recomputes or shares: "
+              + ", ".join(passed_over[:4]) + (" ..." if len(passed_over) > 4 else ""), file=sys.stderr)
     placed: Dict[str, torch.Tensor] = {}
     for name, info in wanted.items():
         placed[name] = place(read(name), info, model.rt)

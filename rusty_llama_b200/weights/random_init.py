@@ -22,7 +22,7 @@ from ..parts.base import ParamInfo, Runtime
 from ..registry import describe_model
 from .safetensors_io import write_safetensors
 
-_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -54,7 +54,8 @@ def random_tensors(
 def _param_infos(config_json: Mapping) -> Dict[str, ParamInfo]:
     """The tensors a configuration asks for, found by building its parts without weights."""
     spec = describe_model(config_json)
-    return Model(spec, Runtime.create("cpu", _TORCH_DTYPE.get(spec.stored_dtype, torch.float32))).param_infos()
+    # (names and shapes do not depend on the run type; a 32-bit run takes every size a configuration allows)
+    return Model(spec, Runtime.create("cpu", torch.float32)).param_infos()
 
 
 def write_random_model(model_dir: str, config_json: Mapping, seed: int, std: float = 0.02, norm_jitter: float = 0.0) -> str:

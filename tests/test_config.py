@@ -48,7 +48,7 @@ def test_round_trip_through_json():
         ({"rope_theta": float("inf")}, "finite"),
         ({"attention_bias": True}, "bias"),
         ({"hidden_act": "gelu"}, "SwiGLU"),
-        ({"torch_dtype": "float16"}, "torch_dtype"),
+        ({"torch_dtype": "int8"}, "torch_dtype"),
         ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "unsupported rope_scaling"),
         ({"rope_scaling": {"rope_type": "llama3"}}, "needs 'factor'"),
         ({"eos_token_id": 9999}, "outside the vocabulary"),

@@ -57,6 +57,26 @@ def close_bf16(got, ref):
     assert float(err.mean()) <= 2e-3 * scale, f"mean error {float(err.mean()):.3e} vs range {scale:.3e}"
 
 
+def guarded_out(M, n_out, dtype, pad_cols=8):
+    """A NaN-filled flat buffer and the [M, n_out] window inside it that a product is asked to write: rows
+    n_out + pad_cols apart (so ldo > N, and as ragged as N is), the first one on a 16-byte boundary, a row's
+    worth of guard on both sides.  `untouched` says whether everything around the window is still NaN: a
+    store past a ragged edge, or with the wrong row stride, lands there."""
+    ld = n_out + pad_cols
+    lead = (ld + 7) // 8 * 8
+    buf = torch.full((lead + (M + 1) * ld,), float("nan"), dtype=dtype, device=DEV)
+    return buf, buf[lead : lead + M * ld].view(M, ld)[:, :n_out]
+
+
+def untouched(buf, M, n_out, pad_cols=8):
+    ld = n_out + pad_cols
+    lead = (ld + 7) // 8 * 8
+    b = buf.float().cpu()
+    inside = b[lead : lead + M * ld].view(M, ld)
+    return bool(torch.isnan(b[:lead]).all() and torch.isnan(b[lead + M * ld :]).all() and torch.isnan(inside[:, n_out:]).all()
+                and not torch.isnan(inside[:, :n_out]).any())
+
+
 class PagedKV:
     """Dense keys/values of several sequences laid out in scrambled pages."""
 
@@ -631,7 +651,9 @@ def test_gemm_f32_rows_do_not_depend_on_the_batch(ops):
 def test_gemv_bf16(ops, M, N, K, out_dtype):
     x = bf16_round(torch.randn(M, K))
     w = bf16_round(torch.randn(N, K) * 0.05)
-    out = ops.gemv_bf16(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
+    buf, out = guarded_out(M, N, out_dtype)
+    ops.gemv_bf16(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype, out=out)
+    assert untouched(buf, M, N)
     if out_dtype == torch.float32:
         close_dot_f32(out, x, w)
     else:
@@ -644,16 +666,17 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
      (640, 17920, 128), (1280, 25600, 64)],  # the last two give every block several tiles: both accumulators, many rounds
 )
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("pair", [False, True])
-def test_gemm_tc(ops, M, N, K, out_dtype, pair):
-    """The tcgen05 kernels (one SM per tile, and pairs of SMs) at full tiles, at ragged edges in M, N
-    and K, and with a long K."""
+def test_gemm_tc(ops, M, N, K, out_dtype):
+    """The tcgen05 kernel at full tiles, at ragged edges in M, N and K, and with a long K; the result goes
+    into the middle of a NaN-filled buffer whose surroundings must stay as they were."""
     g = torch.Generator().manual_seed(M + N + K)
     x = bf16_round(torch.randn(M, K, generator=g))
     w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
-    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype, pair=pair)
+    buf, out = guarded_out(M, N, out_dtype)
+    ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype, out=out)
     torch.cuda.synchronize()
     ops.tc_status_check()
+    assert untouched(buf, M, N)
     if out_dtype == torch.float32:
         close_dot_f32(out, x, w)
     else:
@@ -661,12 +684,11 @@ def test_gemm_tc(ops, M, N, K, out_dtype, pair):
 
 
 @pytest.mark.parametrize("M, N, K, splits", [(64, 512, 4096, 8), (20, 300, 1000, 3), (200, 256, 640, 64), (64, 4096, 14336, 8)])
-@pytest.mark.parametrize("pair", [False, True])
-def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits, pair):
+def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits):
     g = torch.Generator().manual_seed(M + N)
     x = bf16_round(torch.randn(M, K, generator=g))
     w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
-    parts = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits, pair=pair)
+    parts = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, k_splits=splits)
     torch.cuda.synchronize()
     ops.tc_status_check()
     assert parts.dim() == 3 and parts.shape[1:] == (M, N) and 1 < parts.shape[0] <= splits
@@ -676,16 +698,15 @@ def test_gemm_tc_partial_sums_over_k_slices(ops, M, N, K, splits, pair):
         close_dot_f32(parts[i], x[:, i * per : (i + 1) * per], w[:, i * per : (i + 1) * per])
 
 
-@pytest.mark.parametrize("pair", [False, True])
-def test_gemm_tc_each_output_sees_its_own_row_and_column(ops, pair):
+def test_gemm_tc_each_output_sees_its_own_row_and_column(ops):
     """x = one-hot rows, w = distinct rows: out[m, n] must be w[n, pick(m)], which exposes any mix-up of
-    rows, columns, k slices, the swizzle, or the two halves of a pair's tile."""
+    rows, columns, k slices or the swizzle."""
     M, N, K = 512, 768, 320
     pick = torch.arange(M) * 7 % K
     x = torch.zeros(M, K)
     x[torch.arange(M), pick] = 1.0
     w = bf16_round(torch.randn(N, K, generator=torch.Generator().manual_seed(1)))
-    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32, pair=pair)
+    out = ops.gemm_tc(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), torch.float32)
     torch.cuda.synchronize()
     ops.tc_status_check()
     assert torch.equal(out.cpu(), w[:, pick].T.contiguous())
@@ -738,9 +759,11 @@ def test_gemv_stream(ops, M, N, K, out_dtype):
     g = torch.Generator().manual_seed(M * 7 + N)
     x = bf16_round(torch.randn(M, K, generator=g))
     w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
-    out = ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype)
+    buf, out = guarded_out(M, N, out_dtype)
+    ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out_dtype, out=out)
     torch.cuda.synchronize()
     ops.tc_status_check()
+    assert untouched(buf, M, N)
     if out_dtype == torch.float32:
         close_dot_f32(out, x, w)
     else:
@@ -777,10 +800,11 @@ def test_gemv_stream_fused_swiglu(ops, M, ff, K):
     wg = bf16_round(torch.randn(ff, K, generator=g) * 0.1)
     wu = bf16_round(torch.randn(ff, K, generator=g) * 0.1)
     w = torch.stack([wg, wu], dim=1).reshape(2 * ff, K)
-    out = ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), swiglu=True)
+    buf, out = guarded_out(M, ff, torch.bfloat16)
+    ops.gemv_stream(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out=out, swiglu=True)
     torch.cuda.synchronize()
     ops.tc_status_check()
-    assert out.shape == (M, ff)
+    assert untouched(buf, M, ff)
     close_bf16(out, plain_silu(x.double() @ wg.double().T) * (x.double() @ wu.double().T))
 
 
@@ -863,6 +887,67 @@ def test_argmax_last_of_ties(ops):
     out = ops.argmax(logits.to(DEV)).cpu().tolist()
     assert out == [plain_argmax(row.tolist()) for row in logits]
     assert out[0] == 999 and out[1] == 999 and out[2] == 0
+
+
+def test_argmax_with_nans_follows_the_reference(ops):
+    """The reference's comparison `!(best > x)` lets a NaN take the running maximum's place and whatever
+    follows take the NaN's (src/sampler.rs:76-84, test :983-988): the winner is the last of the equal maxima
+    among the elements after the row's last NaN, or that NaN when it ends the row."""
+    nan = float("nan")
+    small = [[1.0, nan, 0.5], [nan, 3.0, 2.0], [5.0, 1.0, nan], [nan, nan, nan], [2.0, nan, 1.0, 1.0], [nan, 9.0, nan, 0.0, -1.0]]
+    for row in small:
+        got = ops.argmax(torch.tensor([row], device=DEV)).item()
+        assert got == plain_argmax(row), f"{row}: kernel {got}, reference {plain_argmax(row)}"
+    assert plain_argmax([1.0, nan, 0.5]) == 2 and plain_argmax([5.0, 1.0, nan]) == 2  # the reference's own cases
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(6, 5003, generator=g)
+    big[0, 4000] = nan                      # the maximum before the NaN does not count
+    big[0, 100] = 50.0
+    big[1, [7, 4999]] = nan                 # two NaNs: only what follows the last one counts
+    big[2, 5002] = nan                      # a NaN at the end wins
+    big[3, 0] = nan                         # a NaN at the start changes nothing
+    big[4, 2500:] = nan                     # a tail of NaNs
+    want = [plain_argmax(r.tolist()) for r in big]
+    assert want[0] > 4000 and want[1] > 4999 and want[2] == 5002 and want[4] == 5002
+    assert ops.argmax(big.to(DEV)).cpu().tolist() == want
+
+
+@pytest.mark.parametrize("rows", [1, 8, 64])
+def test_sample_kernels_at_a_vocabulary_of_128256(ops, rows):
+    """The classifier's width in the benchmark: greedy, temperature and temperature + top-p for 1, 8 and 64 rows,
+    each row with its own seed; a few rows of each batch are replayed by the plain sampler (it is slow), all rows
+    must be valid and the same on a second run from the same states."""
+    n = 128256
+    g = torch.Generator().manual_seed(rows)
+    logits = torch.randn(rows, n, generator=g) * 3.0
+    ld = logits.to(DEV)
+    assert ops.argmax(ld).cpu().tolist() == [int(r.argmax()) for r in logits]  # (no ties in random floats)
+    seeds = [1000 + 17 * r for r in range(rows)]
+    index = torch.arange(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * n, device=DEV)
+    check = sorted({0, rows // 2, rows - 1})
+    for temperature, top_p in ((0.8, 0.0), (1.1, 0.9)):
+        states = torch.from_numpy(np.array(seeds, dtype=np.uint64).view(np.int64).copy()).to(DEV)
+        got = ops.sample(ld, temperature, top_p, states, index, scratch).cpu().tolist()
+        again_states = torch.from_numpy(np.array(seeds, dtype=np.uint64).view(np.int64).copy()).to(DEV)
+        assert ops.sample(ld, temperature, top_p, again_states, index, scratch).cpu().tolist() == got
+        assert all(0 <= t < n for t in got)
+        for r in check:
+            want = plain_sample(logits[r].tolist(), temperature, top_p, PlainRng(seeds[r]))
+            if got[r] != want:
+                # 128k probabilities summed in 32-bit in index order (the reference) and as exact fixed-point sums (the
+                # kernel) may put a draw that lands within 1e-5 of a boundary on either side of it
+                near = {plain_sample((logits[r] / s).tolist(), temperature, top_p, PlainRng(seeds[r])) for s in (1 + 1e-5, 1 - 1e-5, 1 + 1e-4, 1 - 1e-4)}
+                assert got[r] in near, f"row {r}: kernel {got[r]}, plain {want}"
+    # the longer chain on the same rows: top-k, then the nucleus, then min-p, then the draw
+    history = torch.zeros(rows, ops.SAMPLE_HISTORY_MAX, dtype=torch.int32, device=DEV)
+    count = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    work = torch.empty(rows * 2 * n, device=DEV)
+    states = torch.from_numpy(np.array(seeds, dtype=np.uint64).view(np.int64).copy()).to(DEV)
+    got = ops.sample_chain(ld, 0.9, 0.95, 50, 0.01, 1.0, 0, 0.0, 0.0, states, index, history, count, work).cpu().tolist()
+    for r in check:
+        want = PlainChain(temperature=0.9, top_p=0.95, top_k=50, min_p=0.01, seed=seeds[r]).sample(logits[r].numpy())
+        assert got[r] == want, f"row {r}: chain kernel {got[r]}, plain {want}"
 
 
 @pytest.mark.parametrize("n, temperature, top_p", [(300, 1.0, 0.9), (300, 0.7, 0.0), (5000, 1.3, 0.5), (5000, 0.8, 0.95), (8, 1.0, 0.9)])

@@ -27,6 +27,46 @@ def llms(tiny_dirs):
     return get
 
 
+class ShiftedRng:
+    """The plain generator with its draw number `at` moved by `shift` (for `parted_within_rounding`)."""
+
+    def __init__(self, seed, at, shift):
+        from plain_llama import PlainRng
+
+        self.inner, self.at, self.shift, self.n = PlainRng(seed), at, shift, 0
+
+    def next_f32(self):
+        v = self.inner.next_f32()
+        if self.n == self.at:
+            v = min(max(v + self.shift, 0.0), 0.99999994)
+        self.n += 1
+        return v
+
+
+def parted_within_rounding(cfg, w, prompt, got, want, make_sampler):
+    """Where the engine's sampled stream `got` leaves the plain stream `want`, is the engine's token what the
+    plain sampler draws when that one draw's coin, or its temperature, moves by 1e-5 or less?  The engine's
+    32-bit logits equal the plain ones to a few 1e-5 of their range, so a draw that lands that close to a
+    boundary of the cumulative distribution (or a nucleus that closes that close to top-p) may fall on either
+    side; any other parting is a fault.  make_sampler(rng) -> callable(logits) with fresh state."""
+    k = next(i for i, (a, b) in enumerate(zip(got, want)) if a != b)
+    trials = [(d, 1.0) for d in (1e-6, -1e-6, 1e-5, -1e-5)] + [(0.0, 1.0 + d) for d in (1e-5, -1e-5, 3e-5, -3e-5)]
+    for shift, t_scale in trials:
+        sampler = make_sampler(lambda seed: ShiftedRng(seed, k, shift))
+        seq = list(prompt)
+        for j in range(k + 1):
+            logits = plain_logits(cfg, w, seq)[-1].to(torch.float32).numpy()
+            tok = sampler(logits / np.float32(t_scale) if j == k else logits)
+            if j < k:
+                if tok != want[j]:
+                    break
+                seq.append(tok)
+        else:
+            if tok == got[k]:
+                return True
+    return False
+
+
 def step_all(llm, slot, tokens):
     from rusty_llama_b200 import StepEntry
 
@@ -211,11 +251,19 @@ def test_sampled_generation_follows_the_plain_sampler(llms, tiny_weights):
     assert outs == again
     alone = llm.generate(prompts[2], max_new_tokens=16, temperature=0.8, top_p=0.9, seed=sequence_seed(4242, 2), stop_token_ids=[])
     w = rounded_weights(tiny_weights[name], "float32")
+    from plain_llama import plain_sample
+
     agree = 0
     for i, (p, got) in enumerate(zip(prompts, outs)):
         want = plain_generate(cfg, w, p, 16, temperature=0.8, top_p=0.9, seed=sequence_seed(4242, i))
         agree += int(got == want)
         assert len(got) == 16
+        if got != want:  # only a draw within rounding of a boundary may part the streams
+            def make(rng_of, seed=sequence_seed(4242, i)):
+                rng = rng_of(seed)
+                return lambda logits: plain_sample(logits, 0.8, 0.9, rng)
+
+            assert parted_within_rounding(cfg, w, p, got, want, make), f"sequence {i}: {got} left {want} at a clear margin"
     assert agree >= 4
     assert alone == outs[2]  # a sequence's draws do not depend on its neighbours
 
@@ -241,15 +289,29 @@ def test_generation_with_the_longer_sampler_chain(llms, tiny_weights):
         want = plain_generate(cfg, w, p, 24, stop_token_ids=[], chain=PlainChain(seed=sequence_seed(77, i), **knobs))
         agree += int(got == want)
         assert len(got) == 24
-    assert agree >= 2  # a draw within rounding of a boundary parts the streams
+        if got != want:  # only a draw within rounding of a boundary may part the streams
+            def make(rng_of, seed=sequence_seed(77, i)):
+                chain = PlainChain(seed=seed, **knobs)
+                chain.rng = rng_of(seed)
+                return chain.sample
+
+            assert parted_within_rounding(cfg, w, p, got, want, make), f"sequence {i}: {got} left {want} at a clear margin"
+    assert agree >= 2
     # mirostat keeps its surprise ceiling per sequence on the device, from the first draw of a call on
     miro = dict(temperature=0.9, mirostat=2, mirostat_ent=3.0, mirostat_lr=0.2)
     outs = llm.generate(prompts, max_new_tokens=24, seed=5, stop_token_ids=[], **miro)
     assert outs == llm.generate(prompts, max_new_tokens=24, seed=5, stop_token_ids=[], **miro)
-    agree = sum(
-        int(got == plain_generate(cfg, w, p, 24, stop_token_ids=[], chain=PlainChain(seed=sequence_seed(5, i), **miro)))
-        for i, (p, got) in enumerate(zip(prompts, outs))
-    )
+    agree = 0
+    for i, (p, got) in enumerate(zip(prompts, outs)):
+        want = plain_generate(cfg, w, p, 24, stop_token_ids=[], chain=PlainChain(seed=sequence_seed(5, i), **miro))
+        agree += int(got == want)
+        if got != want:
+            def make(rng_of, seed=sequence_seed(5, i)):
+                chain = PlainChain(seed=seed, **miro)
+                chain.rng = rng_of(seed)
+                return chain.sample
+
+            assert parted_within_rounding(cfg, w, p, got, want, make), f"mirostat, sequence {i}: {got} left {want} at a clear margin"
     assert agree >= 2
     # greedy with a strong repetition penalty: no token twice within the window, and not the plain greedy's run
     greedy = llm.generate(prompts[0], max_new_tokens=20, temperature=0.0, stop_token_ids=[])
@@ -350,3 +412,75 @@ def test_one_layer_at_the_sizes_of_the_benchmark(tmp_path):
             llm.engine.check_device_status()
             del llm
             torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_graph_buckets_and_kept_logits(dtype, tmp_path, tiny_weights):
+    """Decode graphs are captured per (batch size, page-table width 4, 8, 16, 32, ...).  One sequence and a
+    batch of three, whose members stand on different pages, decode from below position 256 to above 1024
+    (tiny B with room for 1100 positions): every new width means a plain run, a capture and then replays,
+    and the number of key splits changes with it.  Every step's logits are kept on the device and read only
+    at the end, so a result that a later step overwrote would show; all are compared with the plain model,
+    and in 32-bit the runs with and without graphs must agree in every bit."""
+    import rusty_llama_b200 as rl
+    from conftest import read_weights
+    from rusty_llama_b200 import StepEntry
+
+    cfg = dict(TINY["B"][0], max_position_embeddings=1100)
+    model_dir = rl.write_random_model(str(tmp_path / "long_b"), cfg, seed=1, norm_jitter=0.1)
+    w = read_weights(model_dir)
+    rng = np.random.default_rng(12)
+    seqs = {"solo": rng.integers(0, cfg["vocab_size"], 1100).tolist(), "x": rng.integers(0, cfg["vocab_size"], 1050).tolist(),
+            "y": rng.integers(0, cfg["vocab_size"], 930).tolist(), "z": rng.integers(0, cfg["vocab_size"], 860).tolist()}
+    prompt = {"solo": 200, "x": 250, "y": 130, "z": 60}
+    ref = plain_all_logits(cfg, w, dtype, seqs)
+    kept = {}
+    for graphs in (True, False):
+        llm = rl.load(model_dir, dtype=dtype, max_tokens=64 * 48, max_seqs=3, use_graphs=graphs)
+        got = {n: [] for n in seqs}
+        for batch in (["solo"], ["x", "y", "z"]):
+            slots = {n: llm.open_sequence() for n in batch}
+            out = llm.step([StepEntry(slots[n], seqs[n][: prompt[n]], [prompt[n] - 1]) for n in batch])
+            for i, n in enumerate(batch):
+                got[n].append(out[i : i + 1])
+            pos = {n: prompt[n] for n in batch}
+            while True:
+                live = [n for n in batch if pos[n] < len(seqs[n])]
+                if not live:
+                    break
+                out = llm.step([StepEntry(slots[n], [seqs[n][pos[n]]], [0]) for n in live])  # stays on the device
+                for i, n in enumerate(live):
+                    got[n].append(out[i : i + 1])
+                    pos[n] += 1
+                    if pos[n] == len(seqs[n]):
+                        llm.close_sequence(slots[n])
+        llm.engine.check_device_status()
+        if graphs:
+            widths = sorted({k[1] for k in llm.engine._graphs})
+            assert widths == [4, 8, 16, 32], widths
+        kept[graphs] = {n: torch.cat(got[n]).cpu() for n in seqs}
+        for n in seqs:
+            check_logits(kept[graphs][n].numpy(), ref[n][prompt[n] - 1 :], dtype, f"{n}, graphs={graphs}")
+    if dtype == "float32":
+        for n in seqs:
+            assert torch.equal(kept[True][n], kept[False][n]), f"{n}: graphs change bits"
+
+
+def test_borrowed_logits_are_the_graphs_buffer_and_owned_ones_are_not(llms):
+    """`step` hands out logits that are the caller's to keep; `borrow=True` (what the generation loop uses) hands
+    out the replayed graph's own buffer, which the next step of the same shape overwrites."""
+    from rusty_llama_b200 import StepEntry
+
+    llm = llms("A", "bfloat16")
+    s = llm.open_sequence()
+    llm.step([StepEntry(s, [1, 2, 3], [])])
+    for t in (4, 5, 6):  # plain run, capture, replay
+        llm.step([StepEntry(s, [t], [0])])
+    own = llm.step([StepEntry(s, [7], [0])])
+    own_then = own.clone()
+    lent = llm.step([StepEntry(s, [8], [0])], borrow=True)
+    lent_then = lent.clone()
+    after = llm.step([StepEntry(s, [9], [0])], borrow=True)
+    llm.close_sequence(s)
+    assert torch.equal(own, own_then)
+    assert lent.data_ptr() == after.data_ptr() and torch.equal(lent, after) and not torch.equal(lent, lent_then)

@@ -70,3 +70,42 @@ def test_shape_runs_and_agrees_with_the_plain_model(shape, tmp_path):
         llm.engine.check_device_status()
         del llm
     torch.cuda.empty_cache()
+
+
+# head size, heads, kv heads, width, feed-forward, vocabulary, layers: head sizes that are even but no multiple of 8
+SHAPES_32_BIT_ONLY = [(12, 3, 1, 36, 40, 50, 2), (20, 4, 2, 80, 72, 90, 1), (6, 2, 2, 12, 20, 33, 1), (250, 1, 1, 250, 64, 40, 1)]
+
+
+@pytest.mark.parametrize("shape", SHAPES_32_BIT_ONLY, ids=lambda s: "hd{}_h{}k{}_d{}_ff{}_v{}".format(*s[:6]))
+def test_head_sizes_that_only_a_32_bit_run_takes(shape, tmp_path):
+    """The 32-bit kernels take every even head size up to 256; the bfloat16 kernels move heads in 16-byte pieces
+    and say so instead of computing something else."""
+    import rusty_llama_b200 as rl
+
+    hd, H, K, d, ff, V, L = shape
+    cfg = {
+        "architectures": ["LlamaForCausalLM"], "hidden_size": d, "intermediate_size": ff, "num_hidden_layers": L,
+        "num_attention_heads": H, "num_key_value_heads": K, "head_dim": hd, "vocab_size": V,
+        "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+        "tie_word_embeddings": True, "torch_dtype": "float32",
+    }
+    model_dir = rl.write_random_model(str(tmp_path / "m"), cfg, seed=hd, norm_jitter=0.1)
+    w = read_weights(model_dir)
+    rng = np.random.default_rng(hd)
+    reqs = {"a": rng.integers(0, V, 80).tolist(), "b": rng.integers(0, V, 9).tolist()}
+    refs = plain_all_logits(cfg, w, "float32", reqs)
+    llm = rl.load(model_dir, dtype="float32", max_tokens=64 * 4, max_seqs=2)
+    slots = {n: llm.open_sequence() for n in reqs}
+    cut = {n: len(reqs[n]) - 4 for n in reqs}
+    out = llm.step([rl.StepEntry(slots[n], reqs[n][: cut[n]], list(range(cut[n]))) for n in reqs]).cpu().numpy()
+    at = 0
+    for n in reqs:
+        check_logits(out[at : at + cut[n]], refs[n][: cut[n]], "float32", f"{shape}: prompt {n}")
+        at += cut[n]
+    for t in range(4):
+        out = llm.step([rl.StepEntry(slots[n], [reqs[n][cut[n] + t]], [0]) for n in reqs]).cpu().numpy()
+        for i, n in enumerate(reqs):
+            check_logits(out[i : i + 1], refs[n][[cut[n] + t]], "float32", f"{shape}: decode {n} {t}")
+    if hd % 8:
+        with pytest.raises(rl.ConfigError, match="multiple of 8"):
+            rl.load(model_dir, dtype="bfloat16", max_tokens=64)

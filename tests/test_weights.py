@@ -149,3 +149,37 @@ def test_sharded_checkpoint(tiny_weights, tmp_path):
         m = _cpu_model(TINY_A)
         load_tensors(m, c)
     assert m.loaded
+
+
+def test_known_redundant_tensors_are_passed_over_and_unknown_ones_are_not(tiny_weights, capsys):
+    """Llama folders often carry rotary tables as buffers and, beside tied embeddings, a copy of the matrix as
+    lm_head.weight: the architecture names those patterns and the loader passes over them with a note; a
+    tensor that nobody names stays an error, and so does lm_head.weight's absence in an untied model."""
+    w = dict(tiny_weights["A"])  # tied
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    w["lm_head.weight"] = w["model.embed_tokens.weight"].clone()
+    m = _cpu_model(TINY_A)
+    load_tensors(m, w)
+    assert m.loaded and m.head.weight is m.embedding.weight
+    assert "passing over 2 tensors" in capsys.readouterr().err
+    w["model.layers.0.self_attn.rotary_emb.cos_cached"] = torch.zeros(8)
+    with pytest.raises(WeightsError) as e:
+        load_tensors(_cpu_model(TINY_A), w)
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.cos_cached"]
+    b = dict(tiny_weights["B"])  # untied: lm_head.weight is wanted, not redundant
+    del b["lm_head.weight"]
+    with pytest.raises(WeightsError) as e:
+        load_tensors(_cpu_model(TINY_B), b)
+    assert e.value.missing == ["lm_head.weight"]
+
+
+def test_a_checkpoint_stored_in_float16_loads_into_either_run_type(tmp_path):
+    cfg = dict(TINY_A, torch_dtype="float16")
+    d = write_random_model(str(tmp_path / "h"), cfg, 5)
+    w = read_weights(d)
+    assert all(t.dtype == torch.float16 for t in w.values())
+    for run, want in (("bfloat16", torch.bfloat16), ("float32", torch.float32)):
+        m = _cpu_model(cfg, run)
+        load_tensors(m, w)
+        assert m.blocks[0].mixer.w_o.dtype == want
+        assert torch.equal(m.blocks[0].mixer.w_o, w["model.layers.0.self_attn.o_proj.weight"].to(want))
