@@ -92,6 +92,30 @@ def bench_gemm(a) -> dict:
     return {"kernel": "gemm_tc" if a.impl == "tc" else "linear(bf16)", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
+def bench_linear(a) -> dict:
+    """A projection as the model runs it: `linear`, `linear_swiglu` (a.swiglu: n counts gate and up rows) or
+    `linear_to_stream` (a.to_stream: the result may come as partial sums), whichever kernel the dispatch picks
+    for a.rows rows."""
+    from .linear import linear_swiglu, linear_to_stream
+
+    dev = "cuda:0"
+    wbytes = a.n * a.k * 2
+    nv = min(_copies(wbytes), 16)
+    ws = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(nv)]
+    x = torch.randn(a.rows, a.k, device=dev, dtype=torch.bfloat16)
+    out_dtype = getattr(a, "out_dtype", None)
+    if getattr(a, "swiglu", False):
+        fn = lambda i: linear_swiglu(x, ws[i])
+    elif getattr(a, "to_stream", False):
+        fn = lambda i: linear_to_stream(x, ws[i])
+    else:
+        fn = lambda i: linear(x, ws[i], out_dtype)
+    us = _time(fn, nv, a.iters, a.warmup)
+    ops.tc_status_check()
+    return {"kernel": "linear", "rows": a.rows, "n": a.n, "k": a.k, "us": round(us, 2), "GBps": round(wbytes / us / 1e3, 1),
+            "TFLOPs": round(2.0 * a.rows * a.n * a.k / us / 1e6, 1)}
+
+
 def _paged(seqs: int, ctx: int, K: int, hd: int, copies: int):
     dev = "cuda:0"
     pages_per_seq = (ctx + 63) // 64
@@ -129,12 +153,13 @@ def bench_flash_prefill(a) -> dict:
     q = torch.randn(T, (H + 2 * K) * hd, device=dev, dtype=torch.bfloat16)
     seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
     pos0 = torch.zeros(1, dtype=torch.int32, device=dev)
-    fn = ops.flash_prefill_tc if a.impl == "tc" else ops.flash_prefill
+    tc = a.impl == "tc" or (a.impl == "auto" and hd == ops.FLASH_TC_HEAD_DIM)
+    fn = ops.flash_prefill_tc if tc else ops.flash_prefill
     us = _time(lambda i: fn(q, ks[0], vs[0], table, seq_start, pos0, T, H, K, hd), 1, a.iters, a.warmup)
-    if a.impl == "tc":
+    if tc:
         ops.tc_status_check()
     flops = 4.0 * T * T * hd * H / 2
-    return {"kernel": "flash_prefill_tc" if a.impl == "tc" else "flash_prefill", "tokens": T, "H": H, "K": K, "hd": hd, "us": round(us, 2), "causal_TFLOPs": round(flops / us / 1e6, 1)}
+    return {"kernel": "flash_prefill_tc" if tc else "flash_prefill", "tokens": T, "H": H, "K": K, "hd": hd, "us": round(us, 2), "causal_TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def bench_rows(a) -> dict:
@@ -258,7 +283,7 @@ def bench_step_trace(a) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemv", "gemm", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -273,14 +298,16 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=128256, help="step_trace, sample: vocabulary")
     ap.add_argument("--events", action="store_true", help="step_trace: also the numbered notes inside one layer's kernels")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits; gemv/gemm: slices of k with float32 partial sums")
-    ap.add_argument("--impl", default="linear", choices=["linear", "tc", "tc2", "stream", "tma", "warp"], help="gemm: the dispatching linear(), the tcgen05 kernel or (tc2) its two-SM form; flash_prefill: tc = the tcgen05 kernel; gemv: stream = the persistent TMA-fed kernel; attn_decode: tma or warp = one of its two kernels")
+    ap.add_argument("--impl", default="linear", choices=["linear", "auto", "tc", "stream", "tma", "warp"], help="gemm: the dispatching linear() or the tcgen05 kernel; flash_prefill: tc = the tcgen05 kernel, auto = by head size; gemv: stream = the persistent TMA-fed kernel; attn_decode: tma or warp = one of its two kernels")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--swiglu", action="store_true", help="linear: the fused gate/up product (n counts both)")
+    ap.add_argument("--to-stream", action="store_true", help="linear: a projection into the residual stream (may split k)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed calls one by one instead of as one graph")
     a = ap.parse_args(argv)
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
-    fn = {"gemv": bench_gemv, "gemm": bench_gemm, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
+    fn = {"gemv": bench_gemv, "gemm": bench_gemm, "linear": bench_linear, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
           "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace}[a.kernel]
     print(json.dumps(fn(a)))
     return 0

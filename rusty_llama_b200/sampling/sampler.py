@@ -149,6 +149,8 @@ class Sampler:
         self._pinned = None
         self._events = None
         self._turn = 0
+        self._index_key = None
+        self._index: Optional[torch.Tensor] = None
 
     def seed_slots(self, slots: Sequence[int], seeds: Sequence[int]) -> None:
         vals = np.array([s or 1 for s in seeds], dtype=np.uint64).view(np.int64)
@@ -173,6 +175,15 @@ class Sampler:
         event.record()
         return PendingTokens(host, event)
 
+    def _slot_index(self, slots: Sequence[int]) -> torch.Tensor:
+        """The rows' slot numbers on the device.  A batch keeps its members for many steps, so the tensor
+        of the last call is kept and an upload happens only when the members change."""
+        key = tuple(slots)
+        if key != self._index_key:
+            self._index = torch.tensor(key, dtype=torch.int32, device=self.device)
+            self._index_key = key
+        return self._index
+
     def sample(self, logits: torch.Tensor, slots: Sequence[int], params: SamplingParams) -> torch.Tensor:
         """int32 [rows] on the device: one token per row of logits[rows, vocab]; row i belongs to slots[i]."""
         if params.longer_chain:
@@ -187,7 +198,7 @@ class Sampler:
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
             scratch = self._scratch
-        index = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
+        index = self._slot_index(slots)
         return ops.sample(logits, params.temperature, params.top_p, self.rng_states, index, scratch)
 
     def _sample_chain(self, logits: torch.Tensor, slots: Sequence[int], params: SamplingParams) -> torch.Tensor:
@@ -201,7 +212,7 @@ class Sampler:
             work = self._scratch
         if self.history is None:
             self.history = torch.zeros((self.max_seqs, ops.SAMPLE_HISTORY_MAX), dtype=torch.int32, device=self.device)
-        index = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
+        index = self._slot_index(slots)
         return ops.sample_chain(
             logits, params.temperature, params.top_p, params.top_k, params.min_p, params.repeat_penalty,
             params.repeat_last_n if params.penalties_on else 0, params.frequency_penalty, params.presence_penalty,
