@@ -1,4 +1,4 @@
-// Decode attention over the paged cache in bfloat16 for head size 128, the form for small batches
+// Decode attention over the paged cache in bfloat16 for head sizes 64 and 128, the form for small batches
 // whose key range is cut into splits: the same mathematics and the same scratch layout as
 // `attn_decode` (attention_decode.cu; the reference runs its scalar kernel with a single row here,
 // src/backend/cuda.rs:1189-1192), another way of feeding it.
@@ -22,7 +22,8 @@
 // into its copy of the page in shared memory (the warp that owns that row does it, nobody else
 // reads the row) and, for the next steps, into the cache.  Same formulas as rope.cu.
 // Two blocks share an SM (99 KB of shared memory each): 192 KB of keys and values in flight per SM,
-// eight product warps.
+// eight product warps.  At head size 64 a page's keys and values are half as many bytes, so the ring
+// has six stages instead of three and the same bytes are in flight.
 //
 // Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
 #include "tc_common.cuh"
@@ -30,23 +31,31 @@
 
 RL_DEFINE_ERROR_TEXT()
 
-#define HD 128
 #define HEADS 8     // query heads per block (the N of the MMA)
 #define PAGE 64     // positions per cache page = keys per tile
-#define STAGES 3
 #define PRODUCT_WARPS 4
 #define NUM_THREADS ((PRODUCT_WARPS + 1) * 32)
 #define HALF_BYTES (PAGE * 64 * 2)            // one [64 keys][64 dims] swizzled box: 8 KB
-#define STAGE_BYTES (4 * HALF_BYTES)          // K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127
-#define Q_STRIDE (HD + 8)                     // bf16 elements per row of the query tile
-#define O_STRIDE (HD + 4)                     // floats per head in the merge buffer
-#define SMEM_BYTES (STAGES * STAGE_BYTES + HEADS * Q_STRIDE * 2 + 1024)
+#define MAX_STAGES 6
+
+// What follows from the head size HD (64 or 128): a stage holds a page's keys and then its values, each as
+// HD / 64 boxes of 64 dims; the ring has 96 KB whatever the head size.
+template <int HD>
+struct Shape {
+  static constexpr int BOXES = HD / 64;                     // boxes per page of keys (and of values)
+  static constexpr int STAGE_BYTES = 2 * BOXES * HALF_BYTES;
+  static constexpr int STAGES = 3 * 128 / HD;               // 3 at head size 128, 6 at 64
+  static constexpr int Q_STRIDE = HD + 8;                   // bf16 elements per row of the query tile
+  static constexpr int O_STRIDE = HD + 4;                   // floats per head in the merge buffer
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + HEADS * Q_STRIDE * 2 + 1024;
+  static constexpr int DPL = HD / 32;                       // dims of the new key and value per lane of the patching warp
+};
 
 struct DecodeBarriers {
-  uint64_t full[STAGES], empty[STAGES];
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES];
   int abort_flag;
   int last;  // this block is the last of its group's splits to finish
-  float cs[HD / 2], sn[HD / 2];  // cosine and sine of the new position's angles (fused rotary)
+  float cs[64], sn[64];  // cosine and sine of the new position's angles (fused rotary), HD / 2 of each
 };
 static_assert(sizeof(DecodeBarriers) <= 1024, "the small items must fit their area");
 
@@ -81,6 +90,7 @@ __device__ __forceinline__ void product_warps_sync() { asm volatile("bar.sync 1,
 // byte offset, inside a [64 keys][64 dims] box, of the 16-byte piece `piece` (0..7) of row `row`
 __device__ __forceinline__ uint32_t swz(int row, int piece) { return (uint32_t)(row * 128 + ((piece ^ (row & 7)) << 4)); }
 
+template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table, int table_width,
@@ -93,6 +103,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        uint32_t test_ns) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
+  constexpr int STAGES = Shape<HD>::STAGES, STAGE_BYTES = Shape<HD>::STAGE_BYTES, BOXES = Shape<HD>::BOXES;
+  constexpr int Q_STRIDE = Shape<HD>::Q_STRIDE, O_STRIDE = Shape<HD>::O_STRIDE, DPL = Shape<HD>::DPL;
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* ring = smem;
   bf16* q_s = reinterpret_cast<bf16*>(ring + STAGES * STAGE_BYTES);  // [HEADS][Q_STRIDE]
@@ -161,10 +173,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int page = table[tile];
         unsigned char* dst = ring + (size_t)st * STAGE_BYTES;
         mbar_expect_tx(&bars.full[st], STAGE_BYTES);
-        tma_load_4d(dst, &map_k, &bars.full[st], 0, 0, kh, page);
-        tma_load_4d(dst + HALF_BYTES, &map_k, &bars.full[st], 64, 0, kh, page);
-        tma_load_4d(dst + 2 * HALF_BYTES, &map_v, &bars.full[st], 0, 0, kh, page);
-        tma_load_4d(dst + 3 * HALF_BYTES, &map_v, &bars.full[st], 64, 0, kh, page);
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) {
+          tma_load_4d(dst + b * HALF_BYTES, &map_k, &bars.full[st], 64 * b, 0, kh, page);
+          tma_load_4d(dst + (BOXES + b) * HALF_BYTES, &map_v, &bars.full[st], 64 * b, 0, kh, page);
+        }
       }
     }
     // The copying warp stays until the product warps have left their loop over the pages (they arrive at
@@ -193,8 +206,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // ---------------- products
   const int g = lane >> 2, t4 = lane & 3;
   {
-    // this block's queries: HEADS rows of 128 values, 16 bytes per thread
-    const int r = threadIdx.x >> 4, piece = threadIdx.x & 15;  // 128 threads = 8 rows x 16 pieces
+    // this block's queries: HEADS rows of HD values, 16 bytes per thread
+    constexpr int PIECES = HD / 8;
+    const int r = threadIdx.x / PIECES, piece = threadIdx.x % PIECES;  // 128 threads = 8 (or 16) rows x 16 (or 8) pieces
     if (r < n_heads) {
       const size_t at = (size_t)s * q_stride + (size_t)(h0 + r) * HD + piece * 8;
       if (n_parts == 0) {
@@ -250,27 +264,41 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int k_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), k_piece = lane >> 4;      // + 2 * kk
   const int v_row = warp * 16 + (lane & 7) + 8 * (lane >> 4), v_piece = (lane >> 3) & 1;      // + 2 * dt
   // The warp that owns the new position's row in the sequence's last page reads the new token's raw key
-  // and value now, so that the loads are long done when that page arrives: lane l takes dimensions
-  // 4 l .. 4 l + 3 of both, one 8-byte load each (or one 16-byte load per partial sum, all independent).
+  // and value now, so that the loads are long done when that page arrives: lane l takes DPL = HD / 32
+  // dimensions of both, from DPL l on, one load each (or one per partial sum, all independent).
   const bool patch_here = fuse == 2 && my_lo <= my_hi && my_hi == tile_hi && warp == ((pos & (PAGE - 1)) >> 4);
-  float new_k[4] = {0.f, 0.f, 0.f, 0.f}, new_v[4] = {0.f, 0.f, 0.f, 0.f};
+  float new_k[DPL], new_v[DPL];
+#pragma unroll
+  for (int e = 0; e < DPL; ++e) new_k[e] = new_v[e] = 0.f;
   if (patch_here) {
-    const size_t k_at = (size_t)s * q_stride + (size_t)(H + kh) * HD + 4 * lane, v_at = k_at + (size_t)K * HD;
+    const size_t k_at = (size_t)s * q_stride + (size_t)(H + kh) * HD + DPL * lane, v_at = k_at + (size_t)K * HD;
     if (n_parts == 0) {
-      const uint2 kr = __ldcg(reinterpret_cast<const uint2*>(q + k_at)), vr = __ldcg(reinterpret_cast<const uint2*>(q + v_at));
-      const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
-      const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x)), v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
-      new_k[0] = k0.x; new_k[1] = k0.y; new_k[2] = k1.x; new_k[3] = k1.y;
-      new_v[0] = v0.x; new_v[1] = v0.y; new_v[2] = v1.x; new_v[3] = v1.y;
+      if (DPL == 4) {
+        const uint2 kr = __ldcg(reinterpret_cast<const uint2*>(q + k_at)), vr = __ldcg(reinterpret_cast<const uint2*>(q + v_at));
+        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
+        const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x)), v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+        new_k[0] = k0.x; new_k[1] = k0.y; new_k[DPL - 2] = k1.x; new_k[DPL - 1] = k1.y;
+        new_v[0] = v0.x; new_v[1] = v0.y; new_v[DPL - 2] = v1.x; new_v[DPL - 1] = v1.y;
+      } else {
+        const uint32_t kr = __ldcg(reinterpret_cast<const uint32_t*>(q + k_at)), vr = __ldcg(reinterpret_cast<const uint32_t*>(q + v_at));
+        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr));
+        const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr));
+        new_k[0] = k0.x; new_k[1] = k0.y;
+        new_v[0] = v0.x; new_v[1] = v0.y;
+      }
     } else {
       for (int p = 0; p < n_parts; ++p) {
-        const float4 kp = __ldcg(reinterpret_cast<const float4*>(q_parts + (size_t)p * part_stride + k_at));
-        const float4 vp = __ldcg(reinterpret_cast<const float4*>(q_parts + (size_t)p * part_stride + v_at));
-        new_k[0] += kp.x; new_k[1] += kp.y; new_k[2] += kp.z; new_k[3] += kp.w;
-        new_v[0] += vp.x; new_v[1] += vp.y; new_v[2] += vp.z; new_v[3] += vp.w;
+        const float* kp = q_parts + (size_t)p * part_stride + k_at;
+        const float* vp = q_parts + (size_t)p * part_stride + v_at;
+#pragma unroll
+        for (int e = 0; e < DPL; e += 2) {
+          const float2 kk2 = __ldcg(reinterpret_cast<const float2*>(kp + e)), vv2 = __ldcg(reinterpret_cast<const float2*>(vp + e));
+          new_k[e] += kk2.x; new_k[e + 1] += kk2.y;
+          new_v[e] += vv2.x; new_v[e + 1] += vv2.y;
+        }
       }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {  // rounded to bfloat16 as the projection would have stored them
+      for (int e = 0; e < DPL; ++e) {  // rounded to bfloat16 as the projection would have stored them
         new_k[e] = __bfloat162float(__float2bfloat16_rn(new_k[e]));
         new_v[e] = __bfloat162float(__float2bfloat16_rn(new_v[e]));
       }
@@ -292,16 +320,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       ok = false;
       break;
     }
-    const uint32_t k_s = smem_u32(ring) + st * STAGE_BYTES, v_s = k_s + 2 * HALF_BYTES;
+    const uint32_t k_s = smem_u32(ring) + st * STAGE_BYTES, v_s = k_s + BOXES * HALF_BYTES;
     if (patch_here && tile == tile_hi) {
       // the new token's key and value (read before the loop): the key turned by the position's angles,
       // both into this block's copy of the page and (one block per kv head) into the cache
       const int row = pos & (PAGE - 1);
-      const int hq = half_rot >> 2;  // lanes between the two halves of a pair (neighbour layout)
-      float o[4];
+      const int hq = half_rot / DPL;  // lanes between the two halves of a pair (neighbour layout)
+      float o[DPL];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int d = 4 * lane + e;
+      for (int e = 0; e < DPL; ++e) {
+        const int d = DPL * lane + e;
         // the partner's raw value: from the lane that holds dimension d + half_rot or d - half_rot
         const float up = __shfl_sync(0xffffffffu, new_k[e], (lane + hq) & 31), dn = __shfl_sync(0xffffffffu, new_k[e], (lane - hq) & 31);
         float r = new_k[e];
@@ -318,17 +346,27 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         o[e] = r;
       }
-      const int d0 = 4 * lane;
+      const int d0 = DPL * lane;
       const uint32_t in_tile = (d0 >> 6) * HALF_BYTES + swz(row, (d0 & 63) >> 3) + (d0 & 7) * 2;
-      const uint2 k_packed = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
-      const uint2 v_packed = make_uint2(pack_bf16(new_v[0], new_v[1]), pack_bf16(new_v[2], new_v[3]));
       unsigned char* k_tile = ring + (size_t)st * STAGE_BYTES;
-      *reinterpret_cast<uint2*>(k_tile + in_tile) = k_packed;
-      *reinterpret_cast<uint2*>(k_tile + 2 * HALF_BYTES + in_tile) = v_packed;
-      if (g0 == 0) {
-        const size_t cache_at = (((size_t)table[tile] * K + kh) * PAGE + row) * HD + d0;
-        *reinterpret_cast<uint2*>(k_pages_w + cache_at) = k_packed;
-        *reinterpret_cast<uint2*>(v_pages_w + cache_at) = v_packed;
+      const size_t cache_at = (((size_t)table[tile] * K + kh) * PAGE + row) * HD + d0;
+      if (DPL == 4) {
+        const uint2 k_packed = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[DPL - 2], o[DPL - 1]));
+        const uint2 v_packed = make_uint2(pack_bf16(new_v[0], new_v[1]), pack_bf16(new_v[DPL - 2], new_v[DPL - 1]));
+        *reinterpret_cast<uint2*>(k_tile + in_tile) = k_packed;
+        *reinterpret_cast<uint2*>(k_tile + BOXES * HALF_BYTES + in_tile) = v_packed;
+        if (g0 == 0) {
+          *reinterpret_cast<uint2*>(k_pages_w + cache_at) = k_packed;
+          *reinterpret_cast<uint2*>(v_pages_w + cache_at) = v_packed;
+        }
+      } else {
+        const uint32_t k_packed = pack_bf16(o[0], o[1]), v_packed = pack_bf16(new_v[0], new_v[1]);
+        *reinterpret_cast<uint32_t*>(k_tile + in_tile) = k_packed;
+        *reinterpret_cast<uint32_t*>(k_tile + BOXES * HALF_BYTES + in_tile) = v_packed;
+        if (g0 == 0) {
+          *reinterpret_cast<uint32_t*>(k_pages_w + cache_at) = k_packed;
+          *reinterpret_cast<uint32_t*>(v_pages_w + cache_at) = v_packed;
+        }
       }
       __syncwarp();
     }
@@ -509,7 +547,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 }
 
 // ------------------------------------------------------------------ host side
-RL_API int rl_attn_decode_tma_head_dim() { return HD; }
+// Head sizes this kernel is built for: 64 and 128 (1 if `hd` is one of them).
+RL_API int rl_attn_decode_tma_takes(int hd) { return hd == 64 || hd == 128; }
 
 // Same arguments as rl_attn_decode (scratch: part_o of n_seqs*H*n_splits*hd floats, part_ml of
 // n_seqs*H*n_splits*2), plus the number of cache pages and a status word: one int in device memory,
@@ -527,34 +566,23 @@ RL_API int rl_attn_decode_tma_head_dim() { return HD; }
 // when the kernel ends.
 // wait_test_role, wait_test_ns: 0, 0 in normal use; a test names 51 or 52 and a limit in nanoseconds, and
 // that role's waits give up after that long instead of a second.
-RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
-                              const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
-                              void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
-                              float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
-                              int interleaved, unsigned int* counters, const float* q_parts, int n_parts,
-                              long long part_stride, int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
-  if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
-  if (hd != HD) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for %d", hd, HD);
-  if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
-  if (page_size != PAGE) RL_REFUSE(4, "attn_decode_tma: page size %d, this kernel is built for %d", page_size, PAGE);
-  if (q_stride % 8) RL_REFUSE(5, "attn_decode_tma: query row stride %d breaks 16-byte alignment", q_stride);
-  if (((n_parts > 0 ? (uintptr_t)0 : (uintptr_t)q) | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
-  if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
-  if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
-  if (fuse < 0 || fuse > 2 || rot < 0 || rot > HD || (rot & 7) || (fuse && rot > 0 && inv_freq == nullptr))
-    RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d (a multiple of 8 up to the head size)%s", fuse, rot, inv_freq ? "" : " and no angles");
-  if (n_parts < 0 || n_parts > 64 || (n_parts > 0 && (q_parts == nullptr || fuse == 0 || ((uintptr_t)q_parts & 15) || part_stride % 4 || q_stride % 4)))
-    RL_REFUSE(14, "attn_decode_tma: %d partial sums need fuse > 0 and 16-byte aligned rows", n_parts);
-  if (fuse == 2 && q_stride < (H + 2 * K) * HD) RL_REFUSE(13, "attn_decode_tma: rows of %d hold no key and value behind %d query heads", q_stride, H);
+template <int HD>
+static int launch_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
+                             const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
+                             void* out, int out_stride, int n_seqs, int H, int K, int window, float scale, int n_splits,
+                             int* status, int fuse, const float* inv_freq, int rot, int interleaved, unsigned int* counters,
+                             const float* q_parts, int n_parts, long long part_stride, int wait_test_role,
+                             unsigned int wait_test_ns, cudaStream_t stream) {
   CUtensorMap map_k, map_v;
   if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
     RL_REFUSE(10, "attn_decode_tma: cannot describe the cache pages to TMA");
-  auto kern = attn_decode_tma_kernel;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-    RL_REFUSE(11, "attn_decode_tma: cannot get %d bytes of shared memory", SMEM_BYTES);
+  auto kern = attn_decode_tma_kernel<HD>;
+  constexpr int smem = Shape<HD>::SMEM_BYTES;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    RL_REFUSE(11, "attn_decode_tma: cannot get %d bytes of shared memory", smem);
   const int G = H / K;
   dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
-  RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, SMEM_BYTES, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
+  RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, block_table,
                             table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
                             fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
                             interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride, wait_test_role,
@@ -564,4 +592,32 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
   RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
                             (bf16*)out, out_stride, H, HD, n_splits));
   return 0;
+}
+
+RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, const void* v_pages, int n_pages,
+                              const int* block_table, int table_width, const int* seq_len, float* part_o, float* part_ml,
+                              void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
+                              float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
+                              int interleaved, unsigned int* counters, const float* q_parts, int n_parts,
+                              long long part_stride, int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+  if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
+  if (!rl_attn_decode_tma_takes(hd)) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for 64 and 128", hd);
+  if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
+  if (page_size != PAGE) RL_REFUSE(4, "attn_decode_tma: page size %d, this kernel is built for %d", page_size, PAGE);
+  if (q_stride % 8) RL_REFUSE(5, "attn_decode_tma: query row stride %d breaks 16-byte alignment", q_stride);
+  if (((n_parts > 0 ? (uintptr_t)0 : (uintptr_t)q) | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) RL_REFUSE(6, "attn_decode_tma: operands must be 16-byte aligned");
+  if (n_splits <= 0 || n_splits > 64 || n_seqs > 65535) RL_REFUSE(7, "attn_decode_tma: splits=%d (1..64) seqs=%d", n_splits, n_seqs);
+  if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "attn_decode_tma: bad window or scale, or no status word");
+  if (fuse < 0 || fuse > 2 || rot < 0 || rot > hd || (rot & 7) || (fuse && rot > 0 && inv_freq == nullptr))
+    RL_REFUSE(12, "attn_decode_tma: fuse=%d with a rotary size of %d (a multiple of 8 up to the head size)%s", fuse, rot, inv_freq ? "" : " and no angles");
+  if (n_parts < 0 || n_parts > 64 || (n_parts > 0 && (q_parts == nullptr || fuse == 0 || ((uintptr_t)q_parts & 15) || part_stride % 4 || q_stride % 4)))
+    RL_REFUSE(14, "attn_decode_tma: %d partial sums need fuse > 0 and 16-byte aligned rows", n_parts);
+  if (fuse == 2 && q_stride < (H + 2 * K) * hd) RL_REFUSE(13, "attn_decode_tma: rows of %d hold no key and value behind %d query heads", q_stride, H);
+#define RL_DECODE_TMA(HDV)                                                                                                  \
+  return launch_decode_tma<HDV>(q, q_stride, k_pages, v_pages, n_pages, block_table, table_width, seq_len, part_o, part_ml, out, \
+                                out_stride, n_seqs, H, K, window, scale, n_splits, status, fuse, inv_freq, rot, interleaved,      \
+                                counters, q_parts, n_parts, part_stride, wait_test_role, wait_test_ns, stream)
+  if (hd == 64) RL_DECODE_TMA(64);
+  RL_DECODE_TMA(128);
+#undef RL_DECODE_TMA
 }

@@ -1,4 +1,4 @@
-// Causal flash attention for prompts on the 5th-generation tensor cores, head size 128, bfloat16,
+// Causal flash attention for prompts on the 5th-generation tensor cores, head sizes 64 and 128, bfloat16,
 // reading keys and values from the paged cache.  Same contract as `flash_prefill` (ragged batch,
 // positions from seq_pos0, optional window); the reference's counterpart is its scalar
 // `attention_kernel` (src/backend/cuda.rs:157-232).
@@ -29,18 +29,20 @@
 
 RL_DEFINE_ERROR_TEXT()
 
-#define HD 128
 #define BMQ 128          // query rows per block
 #define BNK 128          // keys per tile
 #define PAGE 64
 #define KV_STAGES 2
 #define SUB_BYTES (128 * 64 * 2)        // one [128 rows][64 columns] swizzled sub-tile: 16 KB
-#define TILE_BYTES (2 * SUB_BYTES)      // a 128 x 128 bf16 tile: 32 KB
+#define P_BYTES (2 * SUB_BYTES)         // the probabilities of a tile, 128 rows x 128 keys: 32 KB
 #define SOFTMAX_WARPS 8
 #define NUM_THREADS ((SOFTMAX_WARPS + 2) * 32)
 #define HALF_COLS (BNK / 2)
 #define TMEM_COLS 512                   // S0 at 0, S1 at 128, O at 256
 #define RESCALE_THRESHOLD 8.0f          // in base-2 exponents
+// A tile of queries, keys or values is 128 rows x HD columns: HD / 64 sub-tiles.
+#define TILE_BYTES_OF(HD) ((HD) / 64 * SUB_BYTES)
+#define SMEM_BYTES_OF(HD) ((1 + 2 * KV_STAGES) * TILE_BYTES_OF(HD) + 2 * P_BYTES + 3072)
 
 struct SmallItems {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
@@ -51,9 +53,8 @@ struct SmallItems {
   uint32_t tmem_slot;
   int abort_flag;
 };
-#define SMEM_BYTES ((3 + 2 * KV_STAGES) * TILE_BYTES + 3072)
 static_assert(sizeof(SmallItems) <= 3072, "the small items must fit behind the tiles");
-static_assert(SMEM_BYTES <= 227 * 1024, "more shared memory than a block can have");
+static_assert(SMEM_BYTES_OF(128) <= 227 * 1024, "more shared memory than a block can have");
 
 // 2^x for x <= 8 or so; -inf gives 0
 __device__ __forceinline__ float exp2_fast(float x) {
@@ -62,20 +63,22 @@ __device__ __forceinline__ float exp2_fast(float x) {
   return y;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
                         int out_stride, int H, int K, int window, float scale_log2, int* __restrict__ status,
                         int test_role, uint32_t test_ns) {
-  // All shared memory is dynamic, so that the seven 32 KB tiles start at the block's first byte
-  // (1024-byte aligned, as the 128-byte swizzle needs) and the small items fit behind them.
+  // All shared memory is dynamic, so that the tiles start at the block's first byte (1024-byte
+  // aligned, as the 128-byte swizzle needs) and the small items fit behind them.
+  constexpr int TILE_BYTES = TILE_BYTES_OF(HD), SUBS = HD / 64;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
-  unsigned char* q_s = smem_dyn;                           // 32 KB
-  unsigned char* k_s = q_s + TILE_BYTES;                   // KV_STAGES x 32 KB
-  unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;       // KV_STAGES x 32 KB
+  unsigned char* q_s = smem_dyn;                           // 128 rows x HD
+  unsigned char* k_s = q_s + TILE_BYTES;                   // KV_STAGES x (128 keys x HD)
+  unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;       // KV_STAGES x (128 keys x HD)
   unsigned char* p_s = v_s + KV_STAGES * TILE_BYTES;       // 2 x 32 KB
-  SmallItems& sm = *reinterpret_cast<SmallItems*>(p_s + 2 * TILE_BYTES);
+  SmallItems& sm = *reinterpret_cast<SmallItems*>(p_s + 2 * P_BYTES);
   uint64_t& q_full = sm.q_full;
   uint64_t(&k_full)[KV_STAGES] = sm.k_full;
   uint64_t(&k_empty)[KV_STAGES] = sm.k_empty;
@@ -145,8 +148,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // ---------------- TMA producer
     if (lane == 0) {
       mbar_expect_tx(&q_full, TILE_BYTES);
-      tma_load_2d(q_s, &map_q, &q_full, h * HD, tok0 + row0);
-      tma_load_2d(q_s + SUB_BYTES, &map_q, &q_full, h * HD + 64, tok0 + row0);
+#pragma unroll
+      for (int b = 0; b < SUBS; ++b) tma_load_2d(q_s + b * SUB_BYTES, &map_q, &q_full, h * HD + 64 * b, tok0 + row0);
       const int* table = block_table + (size_t)s * table_width;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -170,7 +173,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int p = 0; p < 2; ++p)
 #pragma unroll
-          for (int b = 0; b < 2; ++b)
+          for (int b = 0; b < SUBS; ++b)
             tma_load_4d(k_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_k, &k_full[st], 64 * b, 0, kh, pages[p]);
         issued_k = j + 1;
         // V
@@ -183,7 +186,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int p = 0; p < 2; ++p)
 #pragma unroll
-          for (int b = 0; b < 2; ++b)
+          for (int b = 0; b < SUBS; ++b)
             tma_load_4d(v_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_v, &v_full[st], 64 * b, 0, kh, pages[p]);
         issued_v = j + 1;
       }
@@ -210,7 +213,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t k_addr = smem_u32(k_s + (size_t)st * TILE_BYTES);
         const uint32_t tmem_s = tmem_base + (uint32_t)((j & 1) * BNK);
 #pragma unroll
-        for (int b = 0; b < 2; ++b)
+        for (int b = 0; b < SUBS; ++b)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_bf16(tmem_s, make_smem_desc(q_addr + b * SUB_BYTES + kk * 32), make_smem_desc(k_addr + b * SUB_BYTES + kk * 32),
@@ -237,7 +240,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tc_fence_after();
         const uint32_t v_addr = smem_u32(v_s + (size_t)st * TILE_BYTES);
         const uint32_t tmem_o = tmem_base + 2 * BNK;
-        const uint32_t pj_addr = p_addr + (uint32_t)((j & 1) * TILE_BYTES);
+        const uint32_t pj_addr = p_addr + (uint32_t)((j & 1) * P_BYTES);
         // O[128 rows x 128 dims] += P[128 x 128 keys] . V[128 keys x 128 dims]; a k step is 16 keys
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
@@ -348,7 +351,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         break;
       }
       float row_sum = 0.f;
-      unsigned char* p_sub = p_s + (size_t)(j & 1) * TILE_BYTES + half * SUB_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+      unsigned char* p_sub = p_s + (size_t)(j & 1) * P_BYTES + half * SUB_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
       for (int c8 = 0; c8 < HALF_COLS / 8; ++c8) {  // eight keys = one 16-byte piece of the row
         uint32_t pk[4];
@@ -412,7 +415,29 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 }
 
 // ------------------------------------------------------------------ host side
-RL_API int rl_flash_prefill_tc_head_dim() { return HD; }
+// Head sizes this kernel is built for: 64 and 128 (1 if `hd` is one of them).
+RL_API int rl_flash_prefill_tc_takes(int hd) { return hd == 64 || hd == 128; }
+
+template <int HD>
+static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
+                           const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, void* out,
+                           int out_stride, int n_seqs, int max_q_len, int H, int K, int window, float scale, int* status,
+                           int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+  CUtensorMap map_q, map_k, map_v;
+  if (make_matrix_map(&map_q, q, n_tokens, q_stride, q_stride, BMQ))
+    RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
+  if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
+    RL_REFUSE(11, "flash_prefill_tc: cannot describe the cache pages to TMA");
+  const size_t smem = SMEM_BYTES_OF(HD);
+  auto kern = flash_prefill_tc_kernel<HD>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    RL_REFUSE(12, "flash_prefill_tc: cannot get %zu bytes of shared memory", smem);
+  dim3 grid(H * n_seqs, (max_q_len + BMQ - 1) / BMQ);
+  RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
+                            (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status, wait_test_role,
+                            (uint32_t)wait_test_ns));
+  return 0;
+}
 
 // status: one int in device memory, 0 before the call; afterwards non-zero means that a bounded wait
 // expired (11, 12 the producer for a free key / value stage; 13, 14, 15, 16 the tensor-core issuer for the
@@ -426,7 +451,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
                                unsigned int wait_test_ns, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || n_tokens <= 0 || n_pages <= 0)
     RL_REFUSE(1, "flash_prefill_tc: S=%d max_q=%d H=%d K=%d T=%d pages=%d", n_seqs, max_q_len, H, K, n_tokens, n_pages);
-  if (hd != HD) RL_REFUSE(2, "flash_prefill_tc: head size %d, this kernel is built for %d", hd, HD);
+  if (!rl_flash_prefill_tc_takes(hd)) RL_REFUSE(2, "flash_prefill_tc: head size %d, this kernel is built for 64 and 128", hd);
   if (H % K) RL_REFUSE(3, "flash_prefill_tc: %d query heads are not a multiple of %d kv heads", H, K);
   if (page_size != PAGE) RL_REFUSE(4, "flash_prefill_tc: page size %d, this kernel is built for %d", page_size, PAGE);
   if (q_stride % 8 || out_stride % 8) RL_REFUSE(5, "flash_prefill_tc: strides %d/%d break 16-byte alignment", q_stride, out_stride);
@@ -434,18 +459,9 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   if ((long long)H * n_seqs > 0x7fffffffLL || (max_q_len + BMQ - 1) / BMQ > 65535)
     RL_REFUSE(7, "flash_prefill_tc: H=%d x S=%d blocks or %d query rows exceed the grid", H, n_seqs, max_q_len);
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "flash_prefill_tc: bad window or scale, or no status word");
-  CUtensorMap map_q, map_k, map_v;
-  if (make_matrix_map(&map_q, q, n_tokens, q_stride, q_stride, BMQ))
-    RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
-  if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
-    RL_REFUSE(11, "flash_prefill_tc: cannot describe the cache pages to TMA");
-  const size_t smem = SMEM_BYTES;
-  auto kern = flash_prefill_tc_kernel;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    RL_REFUSE(12, "flash_prefill_tc: cannot get %zu bytes of shared memory", smem);
-  dim3 grid(H * n_seqs, (max_q_len + BMQ - 1) / BMQ);
-  RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
-                            (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status, wait_test_role,
-                            (uint32_t)wait_test_ns));
-  return 0;
+  if (hd == 64)
+    return launch_flash_tc<64>(q, q_stride, n_tokens, k_pages, v_pages, n_pages, block_table, table_width, seq_start, seq_pos0, out,
+                               out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, stream);
+  return launch_flash_tc<128>(q, q_stride, n_tokens, k_pages, v_pages, n_pages, block_table, table_width, seq_start, seq_pos0, out,
+                              out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, stream);
 }

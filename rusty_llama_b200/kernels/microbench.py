@@ -153,7 +153,7 @@ def bench_flash_prefill(a) -> dict:
     q = torch.randn(T, (H + 2 * K) * hd, device=dev, dtype=torch.bfloat16)
     seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
     pos0 = torch.zeros(1, dtype=torch.int32, device=dev)
-    tc = a.impl == "tc" or (a.impl == "auto" and hd == ops.FLASH_TC_HEAD_DIM)
+    tc = a.impl == "tc" or (a.impl == "auto" and hd in ops.FLASH_TC_HEAD_DIMS)
     fn = ops.flash_prefill_tc if tc else ops.flash_prefill
     us = _time(lambda i: fn(q, ks[0], vs[0], table, seq_start, pos0, T, H, K, hd), 1, a.iters, a.warmup)
     if tc:
@@ -251,7 +251,7 @@ def bench_step_trace(a) -> dict:
         runs.append([(y - x) / 1000.0 for x, y in zip(t, t[1:])])
     # the kernels that call the dependency wait, in a step's order; an interval runs from the end of a
     # kernel's predecessor to its own end (the classifier product and the sampler follow the last mark)
-    fused = a.head_dim == ops.ATTN_DECODE_TMA_HEAD_DIM
+    fused = a.head_dim in ops.ATTN_DECODE_TMA_HEAD_DIMS
     one_split = decode_splits(a.seqs, a.heads, a.kv_heads, a.ctx, a.head_dim) == 1
     layer = ["norm1", "qkv"] + ([] if fused else ["rope"]) + ["attention"] + ([] if (fused and one_split) else ["merge"]) + ["o_proj", "norm2", "gate_up", "down"]
     names = ["embed"] + layer * a.layers + ["final_norm"]

@@ -270,7 +270,7 @@ def attn_generic(
     return out
 
 
-ATTN_DECODE_TMA_HEAD_DIM = 128
+ATTN_DECODE_TMA_HEAD_DIMS = (64, 128)  # head sizes the TMA-fed decode kernel is built for
 
 
 def attn_decode_scratch_floats(n_seqs: int, num_heads: int, head_dim: int, n_splits: int) -> int:
@@ -297,7 +297,7 @@ def attn_decode(
 
     scratch: float32 tensor of at least attn_decode_scratch_floats(...) elements.
     impl: "warp" = one-warp blocks that copy their own tiles, "tma" = four-warp blocks on a TMA-fed
-    ring of whole pages (head size 128 only), "auto" = "tma" where it applies, else "warp"."""
+    ring of whole pages (head sizes 64 and 128), "auto" = "tma" where it applies, else "warp"."""
     q_parts = None
     if q.dim() == 3:
         # the projection as float32 partial sums [parts, S, columns] (a product that was split over k): the
@@ -330,7 +330,7 @@ def attn_decode(
     part_ml = c_void_p(scratch.data_ptr() + 4 * n_o)
     _need(impl in ("auto", "warp", "tma"), f"attn_decode: unknown impl {impl!r}")
     if impl == "auto":
-        impl = "tma" if (head_dim == ATTN_DECODE_TMA_HEAD_DIM and act == torch.bfloat16) else "warp"
+        impl = "tma" if (head_dim in ATTN_DECODE_TMA_HEAD_DIMS and act == torch.bfloat16) else "warp"
     _need(fuse in (0, 1, 2), f"attn_decode: fuse={fuse}")
     if fuse:
         _need(impl == "tma", "attn_decode: only the TMA kernel fuses the position encoding")
@@ -403,7 +403,7 @@ def flash_prefill(
     return out
 
 
-FLASH_TC_HEAD_DIM = 128
+FLASH_TC_HEAD_DIMS = (64, 128)  # head sizes the tcgen05 prompt attention is built for
 
 
 def flash_prefill_tc(
@@ -411,8 +411,8 @@ def flash_prefill_tc(
     num_kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """`flash_prefill` on the tcgen05 tensor cores (TMA-fed, S and P V in tensor memory); head size 128 only."""
-    _need(head_dim == FLASH_TC_HEAD_DIM, f"flash_prefill_tc: head size {head_dim}, this kernel is built for {FLASH_TC_HEAD_DIM}")
+    """`flash_prefill` on the tcgen05 tensor cores (TMA-fed, S and P V in tensor memory); head sizes 64 and 128."""
+    _need(head_dim in FLASH_TC_HEAD_DIMS, f"flash_prefill_tc: head size {head_dim}, this kernel is built for {FLASH_TC_HEAD_DIMS}")
     _cuda(q, "flash_prefill_tc q", torch.bfloat16, contiguous=False)
     qs = _rows(q, "flash_prefill_tc q")
     T = q.shape[0]

@@ -20,7 +20,7 @@ _DECODE_BLOCKS_PER_SM = 4
 _DECODE_HEADS_PER_BLOCK = 8
 
 
-# the four-warp kernel for head size 128: two blocks per SM; a split shorter than four pages costs
+# the four-warp kernel for head sizes 64 and 128: two blocks per SM; a split shorter than four pages costs
 # more in the merge than it gains (measured at one sequence of 4096: 16 splits 7.5 us, 37 splits 8.8)
 _QKV_PARTIALS_MAX_ROWS = 128
 _DECODE_TMA_BLOCKS_PER_SM = 2
@@ -34,7 +34,7 @@ def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int, h
     group = num_heads // num_kv_heads
     per_split = n_seqs * num_kv_heads * ((group + _DECODE_HEADS_PER_BLOCK - 1) // _DECODE_HEADS_PER_BLOCK)
     tiles = max(1, (kv_len + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE)
-    if head_dim == ops.ATTN_DECODE_TMA_HEAD_DIM:
+    if head_dim in ops.ATTN_DECODE_TMA_HEAD_DIMS:
         want = _DECODE_TMA_BLOCKS_PER_SM * sms // per_split
         return max(1, min(want, (tiles + _DECODE_TMA_MIN_PAGES - 1) // _DECODE_TMA_MIN_PAGES, 64))
     want = _DECODE_BLOCKS_PER_SM * sms // per_split
@@ -102,10 +102,10 @@ class Attention(Mixer):
         self.w_o = tensors[p + "o_proj.weight"].contiguous()
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
-        # a decode step of a bfloat16 run at head size 128: the attention kernel turns the queries and the
+        # a decode step of a bfloat16 run at head size 64 or 128: the attention kernel turns the queries and the
         # new key and stores key and value itself, if the position encoding is one it knows how to apply
         fusion = None
-        if step.decode_only and self.rt.dtype == torch.bfloat16 and self.hd == ops.ATTN_DECODE_TMA_HEAD_DIM:
+        if step.decode_only and self.rt.dtype == torch.bfloat16 and self.hd in ops.ATTN_DECODE_TMA_HEAD_DIMS:
             fusion = self.position.decode_fusion()
         # the keys and values may be another run's: then only the queries are projected.  The fused attention
         # kernel also takes the projection as partial sums over slices of k, which lets a product with few
@@ -128,7 +128,7 @@ class Attention(Mixer):
             # second kernel adds the splits up: letting the block that finishes last do that (the kernel
             # can) measured slower at batch 1 and 8 (its serial tail costs more than the small kernel).
             counters = None
-            if self.hd == ops.ATTN_DECODE_TMA_HEAD_DIM and n_splits == 1:
+            if self.hd in ops.ATTN_DECODE_TMA_HEAD_DIMS and n_splits == 1:
                 groups = self.K * ((self.H // self.K + _DECODE_HEADS_PER_BLOCK - 1) // _DECODE_HEADS_PER_BLOCK)
                 counters = self.rt.workspace.get("attn_decode_counters", step.n_seqs * groups, torch.int32, zeroed=True)
             a = ops.attn_decode(
@@ -137,7 +137,7 @@ class Attention(Mixer):
                 **({} if fusion is None else dict(
                     fuse=1 if shared_cache else 2, inv_freq=fusion[0], rotary_dim=fusion[1], interleaved=fusion[2])),
             )
-        elif self.hd == ops.FLASH_TC_HEAD_DIM:
+        elif self.hd in ops.FLASH_TC_HEAD_DIMS:
             a = ops.flash_prefill_tc(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
                 step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,

@@ -301,7 +301,8 @@ def test_attn_decode(ops, H, K, hd, n_splits, window):
     q = bf16_round(torch.randn(S, (H + 2 * K) * hd))
     scratch = torch.full((ops.attn_decode_scratch_floats(S, H, hd, n_splits) + 7,), float("nan"), device=DEV)
     seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
-    out = ops.attn_decode(q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window)
+    out = ops.attn_decode(q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, seq_len, H, K, hd, n_splits, scratch, window=window,
+                          impl="warp")  # (the one-warp kernel, also at the head sizes that "auto" gives to the TMA kernel)
     ref = torch.cat([
         ref_attention_rows(q[s : s + 1, : H * hd].view(1, H, hd), kv, s, [lens[s] - 1], window) for s in range(S)
     ]).view(S, H * hd)
@@ -311,11 +312,11 @@ def test_attn_decode(ops, H, K, hd, n_splits, window):
 
 @pytest.mark.parametrize("H, K", [(8, 2), (4, 4), (32, 8), (24, 1), (5, 1)])
 @pytest.mark.parametrize("n_splits, window", [(1, 0), (3, 0), (8, 0), (2, 100), (64, 0), (5, 333)])
-def test_attn_decode_tma(ops, H, K, n_splits, window):
-    """The four-warp kernel on a TMA-fed ring of pages (head size 128): lengths that end at a page's
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attn_decode_tma(ops, H, K, n_splits, window, hd):
+    """The four-warp kernel on a TMA-fed ring of pages (head sizes 64 and 128): lengths that end at a page's
     first and last key and inside a warp's 16 keys, more splits than pages (empty splits), groups
     of 1, 4, 5 and 24 query heads per kv head (fewer than 8, and more than one block per kv head)."""
-    hd = 128
     lens = [1, 64, 65, 300, 128, 1000, 17]
     S = len(lens)
     kv = PagedKV(lens, K, hd, torch.bfloat16, seed=3)
@@ -334,13 +335,13 @@ def test_attn_decode_tma(ops, H, K, n_splits, window):
 
 
 @pytest.mark.parametrize("H, K", [(8, 2), (32, 8), (24, 1)])
-@pytest.mark.parametrize("rot, interleaved", [(128, False), (128, True), (64, False), (0, False)])
+@pytest.mark.parametrize("hd, rot, interleaved", [(128, 128, False), (128, 128, True), (128, 64, False), (128, 0, False),
+                                                  (64, 64, False), (64, 64, True), (64, 32, False), (64, 0, False), (64, 24, True)])
 @pytest.mark.parametrize("n_splits, window", [(1, 0), (4, 0), (3, 150)])
-def test_attn_decode_tma_with_rotary_and_cache_write_fused(ops, H, K, rot, interleaved, n_splits, window):
+def test_attn_decode_tma_with_rotary_and_cache_write_fused(ops, H, K, hd, rot, interleaved, n_splits, window):
     """fuse = 2 against the two kernels it stands for (rope_kv_write, then attention): the same keys
     and values end up in the cache, bit for bit, at a page's first and last slot and in every warp's
     quarter of a page, and the same attention comes out; fuse = 1 turns the queries only."""
-    hd = 128
     lens = [1, 64, 65, 300, 128, 1000, 17, 81, 112]
     S = len(lens)
     kv = PagedKV(lens, K, hd, torch.bfloat16, seed=9)
@@ -384,10 +385,10 @@ def test_attn_decode_tma_with_rotary_and_cache_write_fused(ops, H, K, rot, inter
 
 @pytest.mark.parametrize("H, K", [(8, 2), (32, 8), (24, 1)])
 @pytest.mark.parametrize("n_splits, window", [(1, 0), (4, 0), (64, 0), (3, 150)])
-def test_attn_decode_tma_adds_its_splits_up_itself(ops, H, K, n_splits, window):
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attn_decode_tma_adds_its_splits_up_itself(ops, H, K, n_splits, window, hd):
     """With counters the block that finishes last merges the splits: the same result as with the merge
     kernel, call after call (the counters are zeros again each time), also with splits that hold no key."""
-    hd = 128
     lens = [1, 64, 65, 300, 128, 1000, 17]
     S = len(lens)
     kv = PagedKV(lens, K, hd, torch.bfloat16, seed=6)
@@ -413,10 +414,11 @@ def test_attn_decode_tma_adds_its_splits_up_itself(ops, H, K, n_splits, window):
 
 @pytest.mark.parametrize("parts", [1, 3])
 @pytest.mark.parametrize("fuse", [1, 2])
-def test_attn_decode_tma_takes_the_projection_as_partial_sums(ops, parts, fuse):
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attn_decode_tma_takes_the_projection_as_partial_sums(ops, parts, fuse, hd):
     """The fused kernel fed with float32 partial sums [parts, S, columns] of the projection against the
     same kernel fed with their bfloat16 sum: the same cache contents and the same result, bit for bit."""
-    H, K, hd, rot = 8, 2, 128, 128
+    H, K, rot = 8, 2, hd
     lens = [1, 64, 65, 300, 128, 17]
     S = len(lens)
     kv = PagedKV(lens, K, hd, torch.bfloat16, seed=12)
@@ -445,10 +447,11 @@ def test_attn_decode_tma_takes_the_projection_as_partial_sums(ops, parts, fuse):
         ops.attn_decode(pieces, k_b, v_b, kv.table, seq_len, H, K, hd, 2, scratch, impl="tma")
 
 
-def test_attn_decode_tma_finds_a_far_key(ops):
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attn_decode_tma_finds_a_far_key(ops, hd):
     """One key far back among hundreds carries almost all the weight: a kernel that skips a page, a
     split, a warp's 16 keys or a swizzled piece returns something else entirely."""
-    H, K, hd = 4, 1, 128
+    H, K = 4, 1
     for far in (0, 15, 16, 63, 64, 127, 450, 512):
         kv = PagedKV([513], K, hd, torch.bfloat16, seed=4)
         q = bf16_round(torch.randn(1, H * hd))
@@ -481,7 +484,7 @@ def test_attn_decode_finds_a_far_key(ops):
         kv.k_pages[page, 0, slot] = boost.to(torch.bfloat16).to(DEV)
         qq = bf16_round(boost.repeat(H) * 1.0)[None]
         scratch = torch.empty(ops.attn_decode_scratch_floats(1, H, hd, 4), device=DEV)
-        out = ops.attn_decode(qq.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([513], dtype=torch.int32, device=DEV), H, K, hd, 4, scratch)
+        out = ops.attn_decode(qq.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([513], dtype=torch.int32, device=DEV), H, K, hd, 4, scratch, impl="warp")
         ref = ref_attention_rows(qq.view(1, H, hd), kv, 0, [512]).view(1, H * hd)
         close_bf16(out, ref)
         # and the weight really is on that key
@@ -513,10 +516,10 @@ def test_flash_prefill(ops, H, K, hd, window):
 
 @pytest.mark.parametrize("H, K", [(4, 2), (3, 3), (8, 1)])
 @pytest.mark.parametrize("window", [0, 200])
-def test_flash_prefill_tc(ops, H, K, window):
-    """The tcgen05 prompt-attention kernel (head size 128): whole prompts, a chunk behind cached positions,
+@pytest.mark.parametrize("hd", [128, 64])
+def test_flash_prefill_tc(ops, H, K, window, hd):
+    """The tcgen05 prompt-attention kernel (head sizes 64 and 128): whole prompts, a chunk behind cached positions,
     single rows, tile-sized and ragged lengths, several key tiles per row tile."""
-    hd = 128
     pos0 = [0, 100, 199, 0, 300]
     q_lens = [150, 77, 1, 128, 257]
     lens = [p + n for p, n in zip(pos0, q_lens)]
@@ -537,12 +540,13 @@ def test_flash_prefill_tc(ops, H, K, window):
     close_bf16(out, torch.cat(refs).view(T, H * hd))
 
 
-def test_long_context_attention_kernels_at_head_size_128(ops):
+@pytest.mark.parametrize("hd", [128, 64])
+def test_long_context_attention_kernels(ops, hd):
     """20 000 cached positions (313 pages in a scrambled table): a chunk of 200 prompt rows appended far
     into the sequence through the tcgen05 kernel, then a decode row through the TMA kernel with few and
     many key splits, with and without a window.  One key far back (position 77) is made to matter, so
     that a page skipped hundreds of pages away would show."""
-    H, K, hd = 4, 2, 128
+    H, K = 4, 2
     n, q_len = 20000, 200
     kv = PagedKV([n], K, hd, torch.bfloat16, seed=31, extra_pages=5)
     g = torch.Generator().manual_seed(7)
@@ -574,10 +578,11 @@ def test_long_context_attention_kernels_at_head_size_128(ops):
     assert float((full[0] - near[0]).abs().max()) > 0.05
 
 
-def test_flash_prefill_tc_each_key_and_dimension_lands_where_it_should(ops):
+@pytest.mark.parametrize("hd", [128, 64])
+def test_flash_prefill_tc_each_key_and_dimension_lands_where_it_should(ops, hd):
     """Values that name their own key and dimension, queries that each pick one key: any mix-up of pages,
     swizzled pieces, k steps or the transposed V operand shows as a wrong number, not as noise."""
-    H, K, hd, n = 1, 1, 128, 320
+    H, K, n = 1, 1, 320
     kv = PagedKV([n], K, hd, torch.bfloat16, seed=16)
     # keys: orthogonal-ish directions; query t points at key pick(t) <= t
     keys = bf16_round(torch.randn(n, hd, generator=torch.Generator().manual_seed(3)))
