@@ -182,7 +182,12 @@ class Cache:
                 gi = len(self.state_groups) - 1
                 for j, run in enumerate(runs):
                     self._where[run] = ("state", gi, j)
+        # Fixed-size record per sequence slot, on the device: positions held, tokens decoded, the most it may decode,
+        # flags (bit 0: open).  The host keeps its own copy of the lengths for its bookkeeping (`_length`); a decode
+        # step's kernels take theirs from here (`ops.seq_begin_decode`), so a replayed graph needs no upload of them.
+        self.seq_records = torch.zeros((max_seqs, 4), dtype=torch.int32, device=self.device)
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
+        self._record_open = torch.tensor([0, 0, 0, 1], dtype=torch.int32, device=self.device)
         self._open = np.zeros(max_seqs, dtype=bool)
         self._length = np.zeros(max_seqs, dtype=np.int64)
 
@@ -208,7 +213,13 @@ class Cache:
             g.table[slot, :] = 0
         for g in self.state_groups:
             g.state[:, slot].zero_()
+        self.seq_records[slot] = self._record_open  # nothing held, nothing decoded, no budget named, open
         return slot
+
+    def set_budget(self, slot: int, max_new: int) -> None:
+        """Note in the slot's record how many tokens its sequence may decode (0: no limit named)."""
+        self._check_open(slot)
+        self.seq_records[slot, 2] = int(max_new)
 
     def close_sequence(self, slot: int) -> None:
         self._check_open(slot)
@@ -220,6 +231,7 @@ class Cache:
         self._open[slot] = False
         self._length[slot] = 0
         self._free_slots.append(slot)
+        self.seq_records[slot, 3] = 0  # closed; what it held and decoded stays readable until the slot opens again
 
     def _check_open(self, slot: int) -> None:
         if not (isinstance(slot, (int, np.integer)) and 0 <= slot < self.max_seqs):
@@ -288,12 +300,18 @@ class Cache:
     def has_window_groups(self) -> bool:
         return any(g.need.window for g in self.kv_groups)
 
-    def reserve_one_each(self, slots: Sequence[int], lengths: np.ndarray) -> None:
+    def reserve_one_each(self, slots: Sequence[int], lengths: np.ndarray) -> bool:
         """`reserve(slots, [1] * len(slots))` for the common decode step: a page is taken only by the
-        sequences that stand at a page boundary."""
+        sequences that stand at a page boundary.  Returns whether any page list changed."""
         at_boundary = [int(s) for s, n in zip(slots, lengths) if n % PAGE_SIZE == 0]
         if at_boundary:
             self.reserve(at_boundary, [1] * len(at_boundary))
+        return bool(at_boundary)
+
+    def record(self, slot: int) -> dict:
+        """The slot's record as the device holds it (synchronises): for tests and for looking at a run."""
+        held, decoded, max_new, flags = self.seq_records[slot].tolist()
+        return {"len": held, "decoded": decoded, "max_new": max_new, "open": bool(flags & 1)}
 
     def commit_one_each(self, slots: np.ndarray) -> None:
         if self.has_window_groups():

@@ -231,6 +231,49 @@ RL_API int rl_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_pa
   RL_REFUSE(5, "add_rmsnorm: unknown dtypes act=%d w=%d", act_dtype, w_dtype);
 }
 
+// ---------------------------------------------------------------- per-sequence records
+// A sequence's fixed-size record lives on the device, one row of four integers per slot of the cache:
+// [0] positions held, [1] tokens decoded so far, [2] the most it may decode, [3] flags.  The reference keeps the
+// same as a device-side position (src/backend/cuda.rs:523-526, :1385-1387) and host-side slot fields
+// (src/server.rs:286-296).  A decode step takes its positions from here, so that a captured graph replays
+// without the host telling it where each sequence stands.
+#define SEQ_FIELDS 4
+
+// Row i of the batch belongs to slot slot_ids[i]: its new token stands at position len, the sequence holds len + 1
+// afterwards; the record moves on by one position and one decoded token.
+__global__ void seq_begin_decode_kernel(int* __restrict__ state, const int* __restrict__ slot_ids, int n_seqs,
+                                        int* __restrict__ tok_pos, int* __restrict__ seq_pos0, int* __restrict__ seq_len) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_seqs) return;
+  int* rec = state + (size_t)slot_ids[i] * SEQ_FIELDS;
+  const int len = rec[0];
+  tok_pos[i] = len;
+  seq_pos0[i] = len;
+  seq_len[i] = len + 1;
+  rec[0] = len + 1;
+  rec[1] += 1;
+}
+
+// After a step whose positions the host gave: the records of its sequences hold seq_len[i] positions.
+__global__ void seq_set_len_kernel(int* __restrict__ state, const int* __restrict__ slot_ids, const int* __restrict__ seq_len, int n_seqs) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_seqs) state[(size_t)slot_ids[i] * SEQ_FIELDS] = seq_len[i];
+}
+
+RL_API int rl_seq_begin_decode(int* state, const int* slot_ids, int n_seqs, int* tok_pos, int* seq_pos0, int* seq_len, cudaStream_t stream) {
+  if (n_seqs <= 0) RL_REFUSE(1, "seq_begin_decode: %d sequences", n_seqs);
+  RL_LAUNCH_CHECK(rl_launch(seq_begin_decode_kernel, (n_seqs + 127) / 128, 128, 0, stream, state, slot_ids, n_seqs, tok_pos, seq_pos0, seq_len));
+  return 0;
+}
+
+RL_API int rl_seq_set_len(int* state, const int* slot_ids, const int* seq_len, int n_seqs, cudaStream_t stream) {
+  if (n_seqs <= 0) RL_REFUSE(1, "seq_set_len: %d sequences", n_seqs);
+  seq_set_len_kernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(state, slot_ids, seq_len, n_seqs);
+  RL_LAUNCH_RESULT();
+}
+
 // ---------------------------------------------------------------- gated activation
 // h[t, i] = silu(g) * u with g = gu[t, i], u = gu[t, ff + i], silu(z) = z / (1 + exp(-z))
 // in 32-bit (src/math.rs:25-27, src/backend/cuda.rs:94-97).

@@ -129,6 +129,7 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.warm = 0
         self.launches = 0  # kernels of this library inside the captured graph
+        self.members = None  # the slots, in order, whose numbers and page tables the device buffers hold
 
 
 class Engine:
@@ -149,6 +150,8 @@ class Engine:
         self.use_graphs = use_graphs and self.rt.device.type == "cuda"
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self._meta = _MetaBuffers(self.rt.device)
+        self.uploads = 0  # host-to-device copies of step integers so far (a replayed decode step may need none)
+        self.upload_bytes = 0
 
     # ------------------------------------------------------------------ sequences
     def open_sequence(self) -> int:
@@ -156,6 +159,14 @@ class Engine:
 
     def close_sequence(self, slot: int) -> None:
         self.cache.close_sequence(slot)
+
+    def note_budget(self, slot: int, max_new: int) -> None:
+        """Write into the slot's record on the device how many tokens its sequence may decode."""
+        self.cache.set_budget(slot, max_new)
+
+    def sequence_record(self, slot: int) -> dict:
+        """The slot's record as the device holds it: positions held, tokens decoded, budget, open (synchronises)."""
+        return self.cache.record(slot)
 
     def check_device_status(self) -> None:
         """Raise if a kernel with bounded waits gave up since the last check.  Synchronises the device."""
@@ -258,8 +269,12 @@ class Engine:
         meta.layout(T, S, len(rows), widths)
         self._fill_meta(meta, entries, pos0, rows)
         meta.upload()
+        self.uploads += 1
+        self.upload_bytes += 4 * meta.total
         step, tables = self._context(meta, entries, pos0, len(rows), max(p + q for p, q in zip(pos0, q_lens)))
         logits = self.model.forward(step, self.cache, tables)
+        if self.rt.device.type == "cuda":
+            ops.seq_set_len(self.cache.seq_records, step.slot_ids, step.seq_len)  # the records follow a step whose positions the host gave
         self.cache.commit(slots, q_lens)
         return logits
 
@@ -306,7 +321,7 @@ class Engine:
                 if len(e.want) != 1 or int(e.want[0]) != 0:
                     raise StepError(f"slot {e.slot} wants logits at {list(e.want)} of 1 token")
                 rows.append(i)
-        self.cache.reserve_one_each(slots, pos0)
+        took_page = self.cache.reserve_one_each(slots, pos0)
         need_width = (int(pos0.max()) + PAGE_SIZE) // PAGE_SIZE
         width = 4
         while width < need_width:
@@ -323,31 +338,40 @@ class Engine:
             g.meta.host_part(7)[:] = ar[:S]
             g.host = [g.meta.host_part(i) for i in range(8 + len(self.cache.kv_groups))]
             self._graphs[key] = g
-        else:
+        # What the device buffers of this graph have to be told: the tokens, unless they lie on the device already;
+        # the slots and their page tables, unless they are the ones of this graph's last step and no sequence
+        # took a page (a window group also gives pages back, so its tables are sent every time).  The positions
+        # are never sent: the step's first kernel takes them from the records on the device.
+        members = tuple(slots.tolist())
+        if g.graph is None or device_tokens is None or g.members != members or took_page or self.cache.has_window_groups():
             g.meta.wait_for_copy()
-        h = g.host
-        h[0][:] = toks
-        h[2][:] = pos0
-        h[4][:] = pos0
-        h[5][:] = pos0 + 1
-        h[6][:] = slots
-        for gi in range(len(self.cache.kv_groups)):
-            h[8 + gi][:] = self.cache.block_table(gi, slots, width).reshape(-1)
-        g.meta.upload()
+            h = g.host
+            h[0][:] = toks
+            h[6][:] = slots
+            for gi in range(len(self.cache.kv_groups)):
+                h[8 + gi][:] = self.cache.block_table(gi, slots, width).reshape(-1)
+            g.meta.upload()
+            self.uploads += 1
+            self.upload_bytes += 4 * g.meta.total
+            g.members = members
         if device_tokens is not None:
             g.meta.dev_part(0).copy_(device_tokens, non_blocking=True)
+        meta = g.meta
+        begin = lambda: ops.seq_begin_decode(self.cache.seq_records, meta.dev_part(6), meta.dev_part(2), meta.dev_part(4), meta.dev_part(5))  # noqa: E731
         if g.graph is None:
             pos_list = pos0.tolist()
             step, tables = self._context(g.meta, entries, pos_list, S, width * PAGE_SIZE)
             if g.warm < 1:
                 # first use of this shape: run it plainly, which also sizes the workspaces
                 g.warm += 1
+                begin()
                 logits = self.model.forward(step, self.cache, tables)
             else:
                 torch.cuda.synchronize(self.rt.device)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
                 with torch.cuda.graph(graph):
+                    begin()
                     g.logits = self.model.forward(step, self.cache, tables)
                 g.launches = ops.launch_count() - before
                 g.graph = graph

@@ -145,8 +145,11 @@ def generate(
         stats.batches += 1
         running: List[_Running] = []
         try:
+            note_budget = getattr(engine, "note_budget", None)
             for r in batch:
                 running.append(_Running(r, engine.open_sequence(), 0))
+                if note_budget is not None:
+                    note_budget(running[-1].slot, budgets[r])
             sampler.seed_slots([s.slot for s in running], [sequence_seed(seed, s.request) for s in running])
             t0 = time.perf_counter()
             entries = [StepEntry(s.slot, list(prompts[s.request]), [len(prompts[s.request]) - 1]) for s in running]

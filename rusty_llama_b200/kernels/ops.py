@@ -177,6 +177,37 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
     return out
 
 
+# ------------------------------------------------------------------ per-sequence records
+SEQ_FIELDS = 4  # a record: positions held, tokens decoded, the most it may decode, flags
+SEQ_LEN, SEQ_DECODED, SEQ_MAX_NEW, SEQ_FLAGS = 0, 1, 2, 3
+
+
+def seq_begin_decode(state: torch.Tensor, slot_ids: torch.Tensor, tok_pos: torch.Tensor, seq_pos0: torch.Tensor, seq_len: torch.Tensor) -> None:
+    """A decode step's positions from the records on the device (int32 [slots, 4]): row i of the batch, which belongs
+    to slot slot_ids[i], stands at position record.len; the record moves on by one position and one decoded token."""
+    _cuda(state, "seq_begin_decode state", torch.int32)
+    _need(state.dim() == 2 and state.shape[1] == SEQ_FIELDS, f"seq_begin_decode: records must be [slots, {SEQ_FIELDS}]")
+    S = slot_ids.numel()
+    for name, t in (("slot_ids", slot_ids), ("tok_pos", tok_pos), ("seq_pos0", seq_pos0), ("seq_len", seq_len)):
+        _cuda(t, f"seq_begin_decode {name}", torch.int32)
+        _need(t.numel() == S, f"seq_begin_decode: {name} has {t.numel()} entries for {S} sequences")
+    lib = build.load("elementwise")
+    rc = lib.rl_seq_begin_decode(_p(state), _p(slot_ids), c_int(S), _p(tok_pos), _p(seq_pos0), _p(seq_len), _stream())
+    _check(lib, rc, "seq_begin_decode")
+
+
+def seq_set_len(state: torch.Tensor, slot_ids: torch.Tensor, seq_len: torch.Tensor) -> None:
+    """record.len = seq_len[i] for the sequences of a step whose positions the host gave."""
+    _cuda(state, "seq_set_len state", torch.int32)
+    _need(state.dim() == 2 and state.shape[1] == SEQ_FIELDS, f"seq_set_len: records must be [slots, {SEQ_FIELDS}]")
+    _cuda(slot_ids, "seq_set_len slot_ids", torch.int32)
+    _cuda(seq_len, "seq_set_len seq_len", torch.int32)
+    _need(slot_ids.numel() == seq_len.numel(), "seq_set_len: one length per sequence")
+    lib = build.load("elementwise")
+    rc = lib.rl_seq_set_len(_p(state), _p(slot_ids), _p(seq_len), c_int(slot_ids.numel()), _stream())
+    _check(lib, rc, "seq_set_len")
+
+
 # ------------------------------------------------------------------ position encoding + cache write
 def rope_kv_write(
     qkv: torch.Tensor,

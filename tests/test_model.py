@@ -484,3 +484,45 @@ def test_borrowed_logits_are_the_graphs_buffer_and_owned_ones_are_not(llms):
     llm.close_sequence(s)
     assert torch.equal(own, own_then)
     assert lent.data_ptr() == after.data_ptr() and torch.equal(lent, after) and not torch.equal(lent, lent_then)
+
+
+def test_sequence_records_on_the_device_follow_every_kind_of_step(llms):
+    """Each slot has a record on the device (positions held, tokens decoded, budget, open).  A decode step that is
+    replayed as a graph takes its positions from there, so once the slots and their page tables are on the device
+    a step launched on device tokens uploads nothing; the records must agree with the host's bookkeeping after
+    prompt steps, chunks, plain and replayed decode steps, and a slot that is opened again starts from zero."""
+    from rusty_llama_b200 import StepEntry
+
+    for graphs in (True, False):
+        llm = llms("B", "bfloat16", use_graphs=graphs, max_tokens=64 * 8, max_seqs=2)
+        eng = llm.engine
+        a, b = llm.open_sequence(), llm.open_sequence()
+        eng.note_budget(a, 77)
+        llm.step([StepEntry(a, [1, 2, 3, 4, 5], []), StepEntry(b, [9] * 70, [])])
+        assert eng.sequence_record(a) == {"len": 5, "decoded": 0, "max_new": 77, "open": True}
+        assert eng.sequence_record(b)["len"] == 70
+        llm.step([StepEntry(a, [6, 7], [])])  # a chunk
+        for t in range(4):
+            llm.step([StepEntry(a, [10 + t], [0]), StepEntry(b, [20 + t], [0])])
+        ra, rb = eng.sequence_record(a), eng.sequence_record(b)
+        assert (ra["len"], rb["len"]) == (11, 74) == (eng.cache.length(a), eng.cache.length(b))
+        assert ra["decoded"] == rb["decoded"] == (4 if graphs else 0)  # (the plain path's positions come from the host)
+        if graphs:
+            # steps on tokens that lie on the device: nothing is uploaded while the members and their pages stay
+            toks = torch.tensor([3, 4], dtype=torch.int32, device="cuda:0")
+            eng.step_device_tokens([a, b], toks)  # (the first one sends the slots and tables of this batch)
+            before = eng.uploads
+            for _ in range(20):
+                eng.step_device_tokens([a, b], toks)
+            assert eng.uploads == before, "a replayed step on device tokens uploaded its integers"
+            assert eng.sequence_record(a)["len"] == 11 + 21 == eng.cache.length(a)
+            for _ in range(40):  # ... until a sequence crosses into a new page (b: 74 + 21 + 40 = 135 > 128)
+                eng.step_device_tokens([a, b], toks)
+            assert eng.uploads > before
+            assert eng.sequence_record(b)["len"] == eng.cache.length(b) == 135
+        llm.close_sequence(a)
+        assert eng.sequence_record(a)["open"] is False
+        a2 = llm.open_sequence()
+        assert a2 == a and eng.sequence_record(a2) == {"len": 0, "decoded": 0, "max_new": 0, "open": True}
+        llm.close_sequence(a2)
+        llm.close_sequence(b)
