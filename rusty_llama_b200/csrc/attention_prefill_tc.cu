@@ -3,25 +3,30 @@
 // positions from seq_pos0, optional window); the reference's counterpart is its scalar
 // `attention_kernel` (src/backend/cuda.rs:157-232).
 //
-// A block owns 128 query rows of one head of one sequence and walks over key tiles of 128
-// positions (two cache pages):
-//   warp 8 (one lane)  TMA: the Q tile once, then K and V tiles (four 64 x 64 boxes each, straight
-//                      from their pages, 128-byte swizzled) into two-stage rings;
-//   warp 9 (one lane)  tcgen05.mma: S = Q K^T (128 x 128, k = head size) into one of two S buffers
-//                      in tensor memory, always one tile ahead; then O += P V (k = 128 keys) into
+// A block owns 128 query rows of one head of one sequence and walks over key tiles of 64
+// positions (one cache page):
+//   warp 4 (one lane)  TMA: the Q tile once, then K and V tiles (64 x 64 boxes straight from their
+//                      page, 128-byte swizzled) into two-stage rings;
+//   warp 5 (one lane)  tcgen05.mma: S = Q K^T (128 x 64, k = head size) into one of two S buffers
+//                      in tensor memory, always one tile ahead; then O += P V (k = 64 keys) into
 //                      the output accumulator, which stays in tensor memory for the whole block,
 //                      with V read as the M/N-contiguous operand it is;
-//   warps 0-7          two threads per query row (warps w and w + 4 share the tensor-memory lanes of
-//                      rows 32w.., each takes 64 of the 128 keys: one softmax warp per scheduler
-//                      cannot hide its own latencies, two can): read the half row of S with
-//                      tcgen05.ld (one round trip), its maximum without any shuffle, exchange the
-//                      two halves' maxima through shared memory, P = 2^(s - m) rounded to bfloat16
-//                      and written to one of two shared-memory buffers in the swizzled k-major
-//                      layout the tensor core expects.  The running maximum m is only raised when the new one
-//                      exceeds it by more than 8 (P then stays below 2^8, harmless in bfloat16 and
-//                      32-bit sums); raising it means rescaling the accumulator in tensor memory
-//                      (tcgen05.ld, multiply, tcgen05.st), which after the first tiles is rare.  At
-//                      the end the row's output is read once and divided by the row sum.
+//   warps 0-3          one thread per query row (its lane of tensor memory): read the row of S with
+//                      tcgen05.ld (one round trip), its maximum without any shuffle, P = 2^(s - m) rounded to
+//                      bfloat16 and written to shared memory in the swizzled k-major layout the tensor core
+//                      expects.  The running maximum m is only raised when the new one exceeds it by more
+//                      than 8 (P then stays below 2^8, harmless in bfloat16 and 32-bit sums); raising it
+//                      means rescaling the accumulator in tensor memory (tcgen05.ld, multiply, tcgen05.st),
+//                      which after the first tiles is rare.  At the end the row's output is read once and
+//                      divided by the row sum.
+// TWO blocks share an SM (half of its shared memory and half of its tensor memory each): the softmax of a
+// tile is a chain of latencies (tensor-memory load, exponentials, shared-memory stores, a fence) during which
+// a block's own tensor-core work is one tile ahead at most; the other block's products and softmax fill the
+// gaps.  Measured at 2048 tokens of 32 heads: one block per SM with 128-key tiles and two threads per row took
+// 57.9 us (tensor pipe busy 30 % of the time); this form 47.7 us (37 %), and 530 instead of 621 us at 8192
+// tokens; two blocks per SM with two threads per row again (sixteen softmax warps per SM, which have to exchange
+// their maxima) 53.5 us.  A prompt of 512 tokens has too few blocks for two per SM and pays for the shorter
+// tiles: 14.7 us against 10.5.
 // Softmax statistics, the accumulator and the final division are 32-bit.
 //
 // Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
@@ -30,31 +35,32 @@
 RL_DEFINE_ERROR_TEXT()
 
 #define BMQ 128          // query rows per block
-#define BNK 128          // keys per tile
+#define BNK 64           // keys per tile = one cache page
 #define PAGE 64
 #define KV_STAGES 2
-#define SUB_BYTES (128 * 64 * 2)        // one [128 rows][64 columns] swizzled sub-tile: 16 KB
-#define P_BYTES (2 * SUB_BYTES)         // the probabilities of a tile, 128 rows x 128 keys: 32 KB
-#define SOFTMAX_WARPS 8
+#define SUBQ_BYTES (128 * 64 * 2)       // a [128 rows][64 columns] swizzled sub-tile of Q or P: 16 KB
+#define SUBK_BYTES (64 * 64 * 2)        // a [64 keys][64 dims] swizzled sub-tile of K or V: 8 KB
+#define P_BYTES SUBQ_BYTES              // the probabilities of a tile, 128 rows x 64 keys
+#define SOFTMAX_WARPS 4
 #define NUM_THREADS ((SOFTMAX_WARPS + 2) * 32)
-#define HALF_COLS (BNK / 2)
-#define TMEM_COLS 512                   // S0 at 0, S1 at 128, O at 256
+#define TMEM_COLS 256                   // S0 at 0, S1 at 64, O at 128
+#define O_COL 128
 #define RESCALE_THRESHOLD 8.0f          // in base-2 exponents
-// A tile of queries, keys or values is 128 rows x HD columns: HD / 64 sub-tiles.
-#define TILE_BYTES_OF(HD) ((HD) / 64 * SUB_BYTES)
-#define SMEM_BYTES_OF(HD) ((1 + 2 * KV_STAGES) * TILE_BYTES_OF(HD) + 2 * P_BYTES + 3072)
+#define SMALL_BYTES 512
+// Q is HD / 64 sub-tiles of 16 KB; a K or V tile HD / 64 sub-tiles of 8 KB.  Two blocks must fit an SM and
+// no more (a third would wait for tensor memory): at head size 64 the request is padded to that end.
+#define SMEM_NEEDED(HD) ((HD) / 64 * SUBQ_BYTES + 2 * KV_STAGES * ((HD) / 64) * SUBK_BYTES + P_BYTES + SMALL_BYTES)
+#define SMEM_BYTES_OF(HD) (SMEM_NEEDED(HD) > 80 * 1024 ? SMEM_NEEDED(HD) : 80 * 1024)
 
 struct SmallItems {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_ready, pv_done[2];
-  uint64_t pair_bar[4];            // the two warps of a lane quarter meet here
   uint64_t drain_bar;              // an issuer that gives up waits here for the MMAs it has issued
-  float pair_val[2][2][BMQ];       // [tile parity][column half][row]
   uint32_t tmem_slot;
   int abort_flag;
 };
-static_assert(sizeof(SmallItems) <= 3072, "the small items must fit behind the tiles");
-static_assert(SMEM_BYTES_OF(128) <= 227 * 1024, "more shared memory than a block can have");
+static_assert(sizeof(SmallItems) <= SMALL_BYTES, "the small items must fit behind the tiles");
+static_assert(2 * (SMEM_BYTES_OF(128) + 1024) <= 228 * 1024, "two blocks must fit an SM's shared memory");
 
 // 2^x for x <= 8 or so; -inf gives 0
 __device__ __forceinline__ float exp2_fast(float x) {
@@ -64,7 +70,7 @@ __device__ __forceinline__ float exp2_fast(float x) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
@@ -72,13 +78,13 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         int test_role, uint32_t test_ns) {
   // All shared memory is dynamic, so that the tiles start at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs) and the small items fit behind them.
-  constexpr int TILE_BYTES = TILE_BYTES_OF(HD), SUBS = HD / 64;
+  constexpr int SUBS = HD / 64, Q_BYTES = SUBS * SUBQ_BYTES, KV_BYTES = SUBS * SUBK_BYTES;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char* q_s = smem_dyn;                           // 128 rows x HD
-  unsigned char* k_s = q_s + TILE_BYTES;                   // KV_STAGES x (128 keys x HD)
-  unsigned char* v_s = k_s + KV_STAGES * TILE_BYTES;       // KV_STAGES x (128 keys x HD)
-  unsigned char* p_s = v_s + KV_STAGES * TILE_BYTES;       // 2 x 32 KB
-  SmallItems& sm = *reinterpret_cast<SmallItems*>(p_s + 2 * P_BYTES);
+  unsigned char* k_s = q_s + Q_BYTES;                      // KV_STAGES x (64 keys x HD)
+  unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;         // KV_STAGES x (64 keys x HD)
+  unsigned char* p_s = v_s + KV_STAGES * KV_BYTES;         // 128 rows x 64 keys
+  SmallItems& sm = *reinterpret_cast<SmallItems*>(p_s + P_BYTES);
   uint64_t& q_full = sm.q_full;
   uint64_t(&k_full)[KV_STAGES] = sm.k_full;
   uint64_t(&k_empty)[KV_STAGES] = sm.k_empty;
@@ -87,9 +93,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   uint64_t(&s_full)[2] = sm.s_full;
   uint64_t& p_ready = sm.p_ready;
   uint64_t(&pv_done)[2] = sm.pv_done;
-  uint64_t(&pair_bar)[4] = sm.pair_bar;
   uint64_t& drain_bar = sm.drain_bar;
-  float(&pair_val)[2][2][BMQ] = sm.pair_val;
   uint32_t& tmem_slot = sm.tmem_slot;
   int& abort_flag = sm.abort_flag;
   if (smem_u32(smem_dyn) & 1023u) {  // uniform over the block; nothing has been set up yet
@@ -105,8 +109,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int q_len = seq_start[s + 1] - tok0;
   // Late row tiles have the most keys to visit.  Blocks are handed out in the order of blockIdx.x, then y:
   // with the row tile in y, the last row tiles of ALL heads and sequences go out first, then the ones before,
-  // and the short tiles fill the gaps at the end (with the heads outermost, the last head's longest tile
-  // started when the others were nearly done: 2048 tokens took 68 us, now 58; 8192 took 654, now 621).
+  // and the short tiles fill the gaps at the end.
   const int row0 = (int)(gridDim.y - 1 - blockIdx.y) * BMQ;
   if (row0 >= q_len) return;  // before any barrier or tensor-memory use: the whole block leaves
   const int pos0 = seq_pos0[s];
@@ -128,7 +131,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
     mbar_init(&p_ready, SOFTMAX_WARPS);  // one arrival per softmax warp
-    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
     mbar_init(&pv_done[0], 1);
     mbar_init(&pv_done[1], 1);
     mbar_init(&drain_bar, 1);
@@ -147,21 +149,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (warp == SOFTMAX_WARPS) {
     // ---------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&q_full, TILE_BYTES);
+      mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
-      for (int b = 0; b < SUBS; ++b) tma_load_2d(q_s + b * SUB_BYTES, &map_q, &q_full, h * HD + 64 * b, tok0 + row0);
+      for (int b = 0; b < SUBS; ++b) tma_load_2d(q_s + b * SUBQ_BYTES, &map_q, &q_full, h * HD + 64 * b, tok0 + row0);
       const int* table = block_table + (size_t)s * table_width;
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      for (int j = 0; j < n_tiles; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t round = j / KV_STAGES;
         const int tile = tile_lo + j;
-        int pages[2];
-#pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          const int idx = 2 * tile + p;
-          pages[p] = idx < table_width ? table[idx] : 0;  // a page past the sequence's end is never attended to
-        }
+        const int page = tile < table_width ? table[tile] : 0;  // a page past the sequence's end is never attended to
         // K
         if (round > 0 && !mbar_wait_role(&k_empty[st], (round - 1) & 1, ctl, 11)) {
           give_up_code(status, 11);
@@ -169,12 +165,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           break;
         }
         if (*(volatile int*)&abort_flag) break;
-        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        mbar_expect_tx(&k_full[st], KV_BYTES);
 #pragma unroll
-        for (int p = 0; p < 2; ++p)
-#pragma unroll
-          for (int b = 0; b < SUBS; ++b)
-            tma_load_4d(k_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_k, &k_full[st], 64 * b, 0, kh, pages[p]);
+        for (int b = 0; b < SUBS; ++b) tma_load_4d(k_s + (size_t)st * KV_BYTES + b * SUBK_BYTES, &map_k, &k_full[st], 64 * b, 0, kh, page);
         issued_k = j + 1;
         // V
         if (round > 0 && !mbar_wait_role(&v_empty[st], (round - 1) & 1, ctl, 12)) {
@@ -182,12 +175,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           abort_flag = 1;
           break;
         }
-        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        mbar_expect_tx(&v_full[st], KV_BYTES);
 #pragma unroll
-        for (int p = 0; p < 2; ++p)
-#pragma unroll
-          for (int b = 0; b < SUBS; ++b)
-            tma_load_4d(v_s + (size_t)st * TILE_BYTES + b * SUB_BYTES + p * (SUB_BYTES / 2), &map_v, &v_full[st], 64 * b, 0, kh, pages[p]);
+        for (int b = 0; b < SUBS; ++b) tma_load_4d(v_s + (size_t)st * KV_BYTES + b * SUBK_BYTES, &map_v, &v_full[st], 64 * b, 0, kh, page);
         issued_v = j + 1;
       }
     }
@@ -210,13 +200,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           return false;
         }
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_s + (size_t)st * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(k_s + (size_t)st * KV_BYTES);
         const uint32_t tmem_s = tmem_base + (uint32_t)((j & 1) * BNK);
+        // S[128 rows x 64 keys] = Q[128 x HD] . K[64 keys x HD]^T; a k step is 16 dims
 #pragma unroll
         for (int b = 0; b < SUBS; ++b)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_s, make_smem_desc(q_addr + b * SUB_BYTES + kk * 32), make_smem_desc(k_addr + b * SUB_BYTES + kk * 32),
+            umma_bf16(tmem_s, make_smem_desc(q_addr + b * SUBQ_BYTES + kk * 32), make_smem_desc(k_addr + b * SUBK_BYTES + kk * 32),
                       idesc_qk, (b > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&k_empty[st]);
         umma_commit(&s_full[j & 1]);
@@ -224,7 +215,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       };
       if (ok) ok = issue_qk(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);  // S of the next tile is computed while this tile's softmax runs
+        // S of the next tile is computed while this tile's softmax runs.  Its buffer was last read by the softmax
+        // of tile j - 1, which had finished before the product of tile j - 1 was issued.
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
         if (!mbar_wait_role(&p_ready, j & 1, ctl, 15)) {
           give_up_code(status, 15);
@@ -238,14 +231,13 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           break;
         }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_s + (size_t)st * TILE_BYTES);
-        const uint32_t tmem_o = tmem_base + 2 * BNK;
-        const uint32_t pj_addr = p_addr + (uint32_t)((j & 1) * P_BYTES);
-        // O[128 rows x 128 dims] += P[128 x 128 keys] . V[128 keys x 128 dims]; a k step is 16 keys
+        const uint32_t v_addr = smem_u32(v_s + (size_t)st * KV_BYTES);
+        const uint32_t tmem_o = tmem_base + O_COL;
+        // O[128 rows x HD dims] += P[128 x 64 keys] . V[64 keys x HD dims]; a k step is 16 keys
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem_o, make_smem_desc(pj_addr + (kk >> 2) * SUB_BYTES + (kk & 3) * 32),
-                    make_smem_desc_mn(v_addr + kk * 2048, SUB_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem_o, make_smem_desc(p_addr + kk * 32), make_smem_desc_mn(v_addr + kk * 2048, SUBK_BYTES, 1024), idesc_pv,
+                    (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&v_empty[st]);
         umma_commit(&pv_done[j & 1]);
       }
@@ -257,15 +249,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
     }
   } else {
-    // ---------------- softmax and output: warps w and w + 4 own tensor-memory lanes 32(w % 4)..+31,
-    // thread = (query row, half of the columns)
-    const int quarter = warp & 3, half = warp >> 2;
-    const int r = quarter * 32 + lane;
+    // ---------------- softmax and output: warp w owns tensor-memory lanes 32 w .. 32 w + 31, one thread a query row
+    const int r = warp * 32 + lane;
     const int qpos = first_pos + r;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t o_addr = lane_addr + 2 * BNK + half * (HD / 2);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t o_addr = lane_addr + O_COL;
     float m_run = -INFINITY, l_run = 0.f;   // m_run in units of raw scores times scale_log2
-    uint32_t pair_phase = 0;
     bool ok = true;
     auto give_up = [&](int code) {
       if (lane == 0) {
@@ -274,16 +263,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       ok = false;
     };
-    // both halves of a row learn the other's value: write, arrive, wait (bounded), read
-    auto exchange = [&](float mine, int parity_slot, float& other, int code) -> bool {
-      pair_val[parity_slot][half][r] = mine;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&pair_bar[quarter]);
-      if (!mbar_wait_role(&pair_bar[quarter], pair_phase, ctl, code)) return false;
-      pair_phase ^= 1;
-      other = pair_val[parity_slot][half ^ 1][r];
-      return true;
-    };
+    unsigned char* p_row = p_s + (r >> 3) * 1024 + (r & 7) * 128;  // this row's 128 bytes (64 keys) of the P tile
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (!mbar_wait_role(&s_full[j & 1], (j >> 1) & 1, ctl, 17)) {
         give_up(17);
@@ -294,45 +274,59 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         break;
       }
       tc_fence_after();
-      const int key0 = (tile_lo + j) * BNK + half * HALF_COLS;
-      const bool need_mask = (tile_lo + j) * BNK + BNK - 1 > first_pos || window != 0;
-      const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * BNK + half * HALF_COLS);
-      // this thread's half of the row of S in one round trip
-      uint32_t v[HALF_COLS];
+      const int key0 = (tile_lo + j) * BNK;
+      const bool need_mask = key0 + BNK - 1 > first_pos || window != 0;
+      const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * BNK);
+      // this thread's row of S in one round trip
+      uint32_t v[BNK];
 #pragma unroll
-      for (int c = 0; c < HALF_COLS / 32; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      for (int c = 0; c < BNK / 32; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
       tmem_ld_wait();
-      float mx = -INFINITY;
+      // (four running maxima and, below, four running sums: one chain of 64 dependent operations would leave the
+      // few warps of an SM waiting on their own arithmetic)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < HALF_COLS; ++i) {
+        for (int i = 0; i < BNK; ++i) {
           const int key = key0 + i;
           if (key > qpos || (window != 0 && qpos - key >= window)) v[i] = __float_as_uint(-INFINITY);
-          mx = fmaxf(mx, __uint_as_float(v[i]));
+          mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < HALF_COLS; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        for (int i = 0; i < BNK; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
       }
-      float mx_other;
-      if (!exchange(mx, j & 1, mx_other, 21)) {
-        give_up(21);
-        break;
-      }
-      mx = fmaxf(mx, mx_other) * scale_log2;   // the scale is positive: the maximum commutes with it
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      mx *= scale_log2;   // the scale is positive: the maximum commutes with it
       // raise the running maximum only when it pays (see the header); the first tile sets it
       const bool raise = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx != -INFINITY);
       const float m_next = raise ? mx : m_run;
-      if (j > 0 && __any_sync(0xffffffffu, raise && m_run != -INFINITY)) {
-        // the accumulator holds sums scaled by 2^-m_run: bring this warp's rows and columns to 2^-m_next
-        if (!mbar_wait_role(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, ctl, 18)) {
-          give_up(18);
-          break;
-        }
+      const float a = (raise && m_run != -INFINITY) ? exp2f(m_run - m_next) : 1.0f;
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, raise && m_run != -INFINITY);
+      m_run = m_next;
+      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;  // a row past the sequence's end may see nothing
+      // the probabilities, in registers: they need nothing but S
+      uint32_t pk[BNK / 2];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < BNK / 2; ++i) {
+        const float p0 = exp2_fast(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
+        const float p1 = exp2_fast(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
+        sum4[i & 3] += p0 + p1;
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+        pk[i] = *reinterpret_cast<uint32_t*>(&b2);
+      }
+      const float row_sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // the P tile (and, for a rescale, the accumulator) is free once the product of the tile before is done
+      if (j > 0 && !mbar_wait_role(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, ctl, 18)) {
+        give_up(18);
+        break;
+      }
+      if (rescale) {
+        // the accumulator holds sums scaled by 2^-m_run(old): bring this warp's rows to 2^-m_next
         tc_fence_after();
-        const float a = (raise && m_run != -INFINITY) ? exp2f(m_run - m_next) : 1.0f;
 #pragma unroll 1
-        for (int c = 0; c < HD / 64; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
           tmem_ld_32x32b_x32(o_addr + c * 32, o);
           tmem_ld_wait();
@@ -341,32 +335,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_st_32x32b_x32(o_addr + c * 32, o);
         }
         tmem_st_wait();
-        l_run *= a;
       }
-      m_run = m_next;
-      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;  // a row past the sequence's end may see nothing
-      // the P buffer of this tile was last read by the product of tile j - 2
-      if (j >= 2 && !mbar_wait_role(&pv_done[j & 1], ((j - 2) >> 1) & 1, ctl, 19)) {
-        give_up(19);
-        break;
-      }
-      float row_sum = 0.f;
-      unsigned char* p_sub = p_s + (size_t)(j & 1) * P_BYTES + half * SUB_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+      l_run = l_run * a + row_sum;
 #pragma unroll
-      for (int c8 = 0; c8 < HALF_COLS / 8; ++c8) {  // eight keys = one 16-byte piece of the row
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2_fast(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2, neg_m));
-          const float p1 = exp2_fast(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2, neg_m));
-          row_sum += p0 + p1;
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-          pk[e] = *reinterpret_cast<uint32_t*>(&b2);
-        }
-        // piece c8 of the row's 128 bytes in this half's sub-tile, swizzled
-        *reinterpret_cast<uint4*>(p_sub + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      }
-      l_run += row_sum;
+      for (int c8 = 0; c8 < BNK / 8; ++c8)  // eight keys = one 16-byte piece of the row, swizzled
+        *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
       // P is complete (and the accumulator rescaled if it had to be): hand both to the tensor core
       tc_fence_before();
       fence_async_shared();
@@ -374,15 +347,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (lane == 0) mbar_arrive(&p_ready);
     }
     if (ok && !mbar_wait_role(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, ctl, 20)) give_up(20);
-    float l_other = 0.f;
-    if (ok && !exchange(l_run, n_tiles & 1, l_other, 22)) give_up(22);
     if (ok) {
       tc_fence_after();
-      const float l_all = l_run + l_other;
-      const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-      bf16* o = out + (size_t)(tok0 + row0 + r) * out_stride + (size_t)h * HD + half * (HD / 2);
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      bf16* o = out + (size_t)(tok0 + row0 + r) * out_stride + (size_t)h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 64; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(o_addr + c * 32, v);
         tmem_ld_wait();
@@ -441,7 +411,8 @@ static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void
 
 // status: one int in device memory, 0 before the call; afterwards non-zero means that a bounded wait
 // expired (11, 12 the producer for a free key / value stage; 13, 14, 15, 16 the tensor-core issuer for the
-// queries, a key tile, the probabilities, a value tile; 17-22 a softmax warp; 23: shared memory not aligned)
+// queries, a key tile, the probabilities, a value tile; 17, 18, 20 a softmax warp for the scores, the product before,
+// the last product; 23: shared memory not aligned)
 // and the output is not valid.  wait_test_role, wait_test_ns: 0, 0 in normal use; a test names one of these
 // codes and a limit in nanoseconds, and that role's waits give up after that long instead of a second.
 RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
