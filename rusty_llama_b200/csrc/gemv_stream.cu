@@ -30,6 +30,13 @@
 //                       alternate gate and up, or as one of k_slices partial results.  (With the
 //                       sum done by the product warps themselves, every item cost them about half
 //                       a microsecond of waiting for one another.)
+// An RMSNorm between two such products can be folded into them (up to 8 rows).  The norm is
+// y = x * w / sqrt(mean(x^2) + eps): the product BEFORE it (whose sums go into the residual stream x) adds
+// them to x where it stores, writes x * w in bfloat16 beside it and leaves each block's share of the rows'
+// sums of squares; the product AFTER it takes x * w as its activations and multiplies its 32-bit sums by the
+// row's 1 / sqrt(...) before they are stored or go through the activation.  A row's scale is a scalar, so
+// scaling the sums is scaling the activations; the kernel between the two products, with its pass over the
+// stream and its two boundaries, is gone.
 // Every wait is bounded: on expiry a code goes to status[0] and the block drains.
 #include "tc_common.cuh"
 
@@ -55,6 +62,23 @@ struct StreamBarriers {
   uint64_t full[STAGES], empty[STAGES];
   uint64_t red_full[2], red_free[2];
   int abort_flag;
+  float row_scale[8];  // (a folded norm after this product) 1 / sqrt(mean(x^2) + eps) per row
+};
+
+// A norm folded into this product (see the header); all pointers null: none.
+struct Fold {
+  // the norm comes BEFORE this product: its rows' sums of squares as [scale_blocks][8] shares, the row length
+  // they were taken over, eps; the activations are x * w already
+  const float* sumsq_in;
+  int scale_blocks, norm_k;
+  float eps;
+  // the norm comes AFTER this product, whose sums belong to the residual stream: resid[m, n] += sum (32-bit, in
+  // place), xw[m, n] = bfloat16(resid[m, n] * next_w[n]), sumsq_out[block][m] = the block's share of sum(resid^2)
+  float* resid;
+  const void* next_w;
+  bf16* xw;
+  float* sumsq_out;
+  int resid_ld, xw_ld, next_w_f32;
 };
 static_assert(sizeof(StreamBarriers) <= SMALL_BYTES, "barriers must fit their area");
 
@@ -94,7 +118,7 @@ template <typename TO, bool SWIGLU, bool HI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ CUtensorMap map_w, TO* __restrict__ out, int ldo,
                    int M, int N, int K, int slice_len, int units, int items, int* __restrict__ status, int test_role,
-                   uint32_t test_ns) {
+                   uint32_t test_ns, const Fold fold) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -166,6 +190,37 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     // ---------------- sums and stores
     const int e = threadIdx.x - (CONSUMER_WARPS + 1) * 32;  // 0..127
     pdl_wait();  // the kernel before this one may still read the output buffer
+    float scale = 1.0f;  // (a folded norm before this product) this thread's row's 1 / sqrt(mean(x^2) + eps)
+    if (fold.sumsq_in != nullptr) {
+      // 8 rows x 16 threads: thread (m, t) adds the shares of blocks t, t + 16, ...; the sixteen partial sums of a
+      // row meet by shuffles in a fixed order, so every block computes the same bits
+      const int m = e >> 4, t = e & 15;
+      float part = 0.f;
+      for (int b = t; b < fold.scale_blocks; b += 16) part += __ldcg(fold.sumsq_in + (size_t)b * 8 + m);
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (t == 0) bars.row_scale[m] = 1.0f / sqrtf(part / (float)fold.norm_k + fold.eps);
+      asm volatile("bar.sync 3, %0;" ::"n"(STORE_WARPS * 32) : "memory");
+      scale = bars.row_scale[SWIGLU ? ((e >> 1) >> 2) & 7 : ((e >> 2) >> 2)];
+    }
+    // (a folded norm after this product) the stream's old values and the norm's weights at this thread's place in the
+    // block's first items, asked for before the sums are waited for
+    float x_old[4] = {0.f, 0.f, 0.f, 0.f}, w_next[4] = {0.f, 0.f, 0.f, 0.f};
+    float ss = 0.f;
+    if (!SWIGLU && fold.resid != nullptr) {
+      const int l = e >> 2, c = e & 3;
+      const int m = (l >> 2) + 8 * (c >> 1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int item = first_item + i;
+        const int n = (item % units) * UNIT_ROWS + 2 * (l & 3) + (c & 1);
+        if (item < end_item && m < M && n < N) {
+          x_old[i] = __ldcg(fold.resid + (size_t)m * fold.resid_ld + n);
+          w_next[i] = fold.next_w_f32 ? __ldg(reinterpret_cast<const float*>(fold.next_w) + n)
+                                      : __bfloat162float(reinterpret_cast<const bf16*>(fold.next_w)[n]);
+        }
+      }
+    }
     int done_items = 0;
     for (int item = first_item; item < end_item; ++item, ++done_items) {
       const int slice = item / units, unit = item - slice * units;
@@ -189,6 +244,8 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
             gate += red_f[(wq * 32 + l) * 4 + 2 * hi];
             up += red_f[(wq * 32 + l) * 4 + 2 * hi + 1];
           }
+          gate *= scale;
+          up *= scale;
           const int m = (l >> 2) + 8 * hi, col = unit * (UNIT_ROWS / 2) + (l & 3);
           if (m < M && col < (N >> 1)) store_out<TO>(out_slice + (size_t)m * ldo + col, gate * (1.0f / (1.0f + expf(-gate))) * up);
         }
@@ -197,12 +254,38 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
         float sum = 0.f;
 #pragma unroll
         for (int wq = 0; wq < CONSUMER_WARPS; ++wq) sum += red_f[(wq * 32 + l) * 4 + c];
+        sum *= scale;
         const int m = (l >> 2) + 8 * (c >> 1), n = unit * UNIT_ROWS + 2 * (l & 3) + (c & 1);
-        if (m < M && n < N) store_out<TO>(out_slice + (size_t)m * ldo + n, sum);
+        if (m < M && n < N) {
+          if (fold.resid != nullptr) {
+            float* px = fold.resid + (size_t)m * fold.resid_ld + n;
+            float old, wn;
+            if (done_items < 4) {
+              old = done_items == 0 ? x_old[0] : done_items == 1 ? x_old[1] : done_items == 2 ? x_old[2] : x_old[3];
+              wn = done_items == 0 ? w_next[0] : done_items == 1 ? w_next[1] : done_items == 2 ? w_next[2] : w_next[3];
+            } else {
+              old = __ldcg(px);
+              wn = fold.next_w_f32 ? __ldg(reinterpret_cast<const float*>(fold.next_w) + n) : __bfloat162float(reinterpret_cast<const bf16*>(fold.next_w)[n]);
+            }
+            const float v = old + sum;
+            *px = v;
+            fold.xw[(size_t)m * fold.xw_ld + n] = __float2bfloat16_rn(v * wn);
+            ss += v * v;
+          } else {
+            store_out<TO>(out_slice + (size_t)m * ldo + n, sum);
+          }
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.red_free[buf]);
       if (e == 0 && item == end_item - 1) rl_trace_event(8);  // last result stored
+    }
+    if (!SWIGLU && fold.resid != nullptr) {
+      // row m's values sit in the 16 lanes [16 (m & 1), +16) of storing warp m >> 1 (those of rows 8..15 hold zeros):
+      // added up in a fixed order, one number per row and block
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((lane & 15) == 0) fold.sumsq_out[(size_t)blockIdx.x * 8 + 2 * (e >> 5) + (lane >> 4)] = ss;
     }
   } else {
     // ---------------- products
@@ -331,9 +414,9 @@ RL_API int rl_gemv_stream_slices(int M, int K, int k_slices) {
 // warp waiting for a free sum buffer; 36: shared memory not aligned) and the output is not valid.
 // wait_test_role, wait_test_ns: 0, 0 in normal use; a test names one of these codes and a limit in
 // nanoseconds, and that role's waits give up after that long instead of a second.
-RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                          int K, int swiglu, int k_slices, int* slices_used, int* status, int wait_test_role,
-                          unsigned int wait_test_ns, cudaStream_t stream) {
+static int launch_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                              int K, int swiglu, int k_slices, int* slices_used, int* status, int wait_test_role,
+                              unsigned int wait_test_ns, const Fold& fold, int* blocks_used, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_stream: M=%d N=%d K=%d", M, N, K);
   if (M > MAX_M) RL_REFUSE(2, "gemv_stream: %d rows, this kernel takes at most %d", M, MAX_M);
   if (K % 64 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_stream: K=%d must be a multiple of 64, ldx=%d and ldw=%d of 8", K, ldx, ldw);
@@ -358,6 +441,15 @@ RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* 
   if (!sm_count[dev] && cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     RL_REFUSE(13, "gemv_stream: cannot count the SMs");
   const int blocks = items < sm_count[dev] ? items : sm_count[dev];
+  if (blocks_used) *blocks_used = blocks;
+  if (fold.sumsq_in != nullptr || fold.resid != nullptr) {
+    if (M > 8) RL_REFUSE(20, "gemv_stream: a folded norm takes at most 8 rows, got %d", M);
+    if (fold.resid != nullptr && (slices != 1 || swiglu)) RL_REFUSE(21, "gemv_stream: sums that go into the stream must be whole (k = %d comes in %d slices) and plain", K, slices);
+    if (fold.sumsq_in != nullptr && slices != 1) RL_REFUSE(22, "gemv_stream: a row scale cannot be applied to partial sums (k = %d comes in %d slices)", K, slices);
+    if (fold.sumsq_in != nullptr && (fold.scale_blocks <= 0 || fold.norm_k <= 0)) RL_REFUSE(23, "gemv_stream: a row scale needs its shares and the row length");
+    if (fold.resid != nullptr && (fold.next_w == nullptr || fold.xw == nullptr || fold.sumsq_out == nullptr || fold.resid_ld < N || fold.xw_ld < N))
+      RL_REFUSE(24, "gemv_stream: sums that go into the stream need the stream, the next norm's weight, a place for x * w and one for the sums of squares");
+  }
   // the weights as [row][k / 64][64 k]: a box of 8 x 16 x 64 is eight rows of 1024 k
   EncodeTiledFn enc = encode_tiled();
   if (!enc) RL_REFUSE(15, "gemv_stream: cuTensorMapEncodeTiled is not available");
@@ -378,7 +470,7 @@ RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* 
       RL_REFUSE(14, "gemv_stream: cannot get %d bytes of shared memory", SMEM_BYTES);                                       \
     RL_LAUNCH_CHECK(rl_launch<true>(kern, dim3(blocks), NUM_THREADS, SMEM_BYTES, stream, (const bf16*)x, ldx, map_w,       \
                                     (TO*)out, ldo, M, N, K, slice_len, units, items, status, wait_test_role,              \
-                                    (uint32_t)wait_test_ns));                                                             \
+                                    (uint32_t)wait_test_ns, fold));                                                       \
   } while (0)
 #define LAUNCH_ROWS(TO, SW)      \
   do {                           \
@@ -392,4 +484,61 @@ RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* 
 #undef LAUNCH_ROWS
 #undef LAUNCH
   return 0;
+}
+
+RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                          int K, int swiglu, int k_slices, int* slices_used, int* status, int wait_test_role,
+                          unsigned int wait_test_ns, cudaStream_t stream) {
+  const Fold none = {};
+  return launch_gemv_stream(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_slices, slices_used, status, wait_test_role,
+                            wait_test_ns, none, nullptr, stream);
+}
+
+// Blocks that a call with these sizes runs: the shares of the rows' sums of squares that `rl_gemv_stream_into_stream`
+// leaves are that many.
+RL_API int rl_gemv_stream_blocks(int N, int K) {
+  if (N <= 0 || K <= 0 || K % 64) return 0;
+  int slice_len, slices, dev = 0, sms = 0;
+  plan(K, 1, &slice_len, &slices);
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  const long long items = (long long)((N + UNIT_ROWS - 1) / UNIT_ROWS) * slices;
+  return (int)(items < sms ? items : sms);
+}
+
+// The product before a folded RMSNorm (at most 8 rows, k in one slice): resid[M, N] (32-bit, in place) += x . w^T;
+// xw[M, N] = bfloat16(resid * next_w) for the product after the norm; sumsq[blocks][8] = each block's share of the
+// rows' sum(resid^2), `blocks` being what rl_gemv_stream_blocks(N, K) says.
+RL_API int rl_gemv_stream_into_stream(const void* x, int ldx, const void* w, int ldw, float* resid, int resid_ld, const void* next_w,
+                                      int next_w_dtype, void* xw, int xw_ld, float* sumsq, int M, int N, int K, int* blocks_used,
+                                      int* status, int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+  if (next_w_dtype != RL_F32 && next_w_dtype != RL_BF16) RL_REFUSE(25, "gemv_stream: unknown norm weight dtype %d", next_w_dtype);
+  if (((uintptr_t)resid | (uintptr_t)xw) & 3) RL_REFUSE(26, "gemv_stream: the stream and x * w must be aligned to their elements");
+  Fold fold = {};
+  fold.resid = resid;
+  fold.resid_ld = resid_ld;
+  fold.next_w = next_w;
+  fold.next_w_f32 = next_w_dtype == RL_F32;
+  fold.xw = (bf16*)xw;
+  fold.xw_ld = xw_ld;
+  fold.sumsq_out = sumsq;
+  int slices = 0;
+  // (the ordinary output is not written in this form; the stream stands in for it in the argument checks)
+  return launch_gemv_stream(x, ldx, w, ldw, resid, RL_F32, resid_ld, M, N, K, 0, 1, &slices, status, wait_test_role, wait_test_ns, fold,
+                            blocks_used, stream);
+}
+
+// The product after a folded RMSNorm (at most 8 rows, k in one slice): as rl_gemv_stream with x = the `xw` left by
+// rl_gemv_stream_into_stream, every row's sums multiplied by 1 / sqrt(sum(shares) / norm_k + eps) before they are
+// stored or go through the activation.
+RL_API int rl_gemv_stream_scaled(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N, int K,
+                                 int swiglu, const float* sumsq, int scale_blocks, int norm_k, float eps, int* status,
+                                 int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+  Fold fold = {};
+  fold.sumsq_in = sumsq;
+  fold.scale_blocks = scale_blocks;
+  fold.norm_k = norm_k;
+  fold.eps = eps;
+  int slices = 0;
+  return launch_gemv_stream(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, swiglu, 1, &slices, status, wait_test_role, wait_test_ns, fold,
+                            nullptr, stream);
 }

@@ -563,16 +563,60 @@ def gemv_stream_slices(M: int, K: int, k_splits: int = 1) -> int:
     return int(lib.rl_gemv_stream_slices(c_int(M), c_int(K), c_int(k_splits)))
 
 
+def gemv_stream_into_stream(
+    x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, next_w: torch.Tensor, xw: Optional[torch.Tensor] = None,
+    sumsq: Optional[torch.Tensor] = None,
+):
+    """The product before an RMSNorm that is folded into its neighbours (at most 8 rows, k a multiple of 64 up to 4096):
+
+        resid (float32 [M, N], in place) += x[M, K] . w[N, K]^T
+        xw[M, N] = bfloat16(resid * next_w)           the activations of the product after the norm
+        sumsq[blocks, 8]                              each block's share of the rows' sum(resid^2)
+
+    Returns (xw, sumsq, blocks); hand them to `gemv_stream(xw, ..., row_scale=(sumsq, blocks, N, eps))`."""
+    _cuda(x, "gemv_stream_into_stream x", torch.bfloat16, contiguous=False)
+    _cuda(w, "gemv_stream_into_stream w", torch.bfloat16, contiguous=False)
+    _cuda(resid, "gemv_stream_into_stream resid", torch.float32, contiguous=False)
+    _cuda(next_w, "gemv_stream_into_stream next_w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and tuple(resid.shape) == (M, N) and tuple(next_w.shape) == (N,),
+          f"gemv_stream_into_stream: x{tuple(x.shape)} w{tuple(w.shape)} resid{tuple(resid.shape)} next_w{tuple(next_w.shape)} do not fit")
+    lib = build.load("gemv_stream")
+    blocks = int(lib.rl_gemv_stream_blocks(c_int(N), c_int(K)))
+    _need(blocks > 0, f"gemv_stream_into_stream: the kernel does not take N={N}, K={K}")
+    if xw is None:
+        xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if sumsq is None:
+        sumsq = torch.empty(blocks * 8, dtype=torch.float32, device=x.device)
+    _cuda(xw, "gemv_stream_into_stream xw", torch.bfloat16, contiguous=False)
+    _cuda(sumsq, "gemv_stream_into_stream sumsq", torch.float32)
+    _need(tuple(xw.shape) == (M, N) and sumsq.numel() >= blocks * 8, "gemv_stream_into_stream: xw or sumsq of the wrong size")
+    used = c_int(0)
+    status = _tc_status_word(x.device)
+    rc = lib.rl_gemv_stream_into_stream(
+        _p(x), c_int(_rows(x, "gemv_stream_into_stream x")), _p(w), c_int(_rows(w, "gemv_stream_into_stream w")), _p(resid),
+        c_int(_rows(resid, "gemv_stream_into_stream resid")), _p(next_w), c_int(_dt(next_w, "gemv_stream_into_stream next_w")), _p(xw),
+        c_int(_rows(xw, "gemv_stream_into_stream xw")), _p(sumsq), c_int(M), c_int(N), c_int(K), ctypes.byref(used), _p(status), *_wt(), _stream(),
+    )
+    _check(lib, rc, "gemv_stream_into_stream")
+    _need(used.value == blocks, f"gemv_stream_into_stream: the kernel ran {used.value} blocks, the wrapper planned {blocks}")
+    return xw, sumsq, blocks
+
+
 def gemv_stream(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1,
+    swiglu: bool = False, k_splits: int = 1, row_scale=None,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T for M <= 16 rows: the persistent weight-streaming kernel of
     decode steps (bulk copies into a ring of shared memory, one block per SM).
 
     swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums.
     k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (`gemv_stream_slices`
-    says how many: each is a multiple of 1024 and at most 4096 long), for a consumer that adds them up."""
+    says how many: each is a multiple of 1024 and at most 4096 long), for a consumer that adds them up.
+    row_scale = (sumsq, blocks, norm_k, eps), as left by `gemv_stream_into_stream`: an RMSNorm folded into this
+    product, whose x is then `xw`; every row's sums are multiplied by 1 / sqrt(sum(shares) / norm_k + eps) before
+    they are stored or go through the activation (at most 8 rows, k in one slice)."""
     _cuda(x, "gemv_stream x", torch.bfloat16, contiguous=False)
     _cuda(w, "gemv_stream w", torch.bfloat16, contiguous=False)
     ldx, ldw = _rows(x, "gemv_stream x"), _rows(w, "gemv_stream w")
@@ -594,6 +638,16 @@ def gemv_stream(
         ldo = _rows(out, "gemv_stream out")
     status = _tc_status_word(x.device)
     lib = build.load("gemv_stream")
+    if row_scale is not None:
+        sumsq, blocks, norm_k, eps = row_scale
+        _cuda(sumsq, "gemv_stream row_scale", torch.float32)
+        _need(k_splits == 1 and slices == 1 and sumsq.numel() >= blocks * 8, "gemv_stream: a row scale goes with whole sums and needs its shares")
+        rc = lib.rl_gemv_stream_scaled(
+            _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_stream out")), c_int(ldo), c_int(M), c_int(N), c_int(K),
+            c_int(1 if swiglu else 0), _p(sumsq), c_int(blocks), c_int(norm_k), c_float(eps), _p(status), *_wt(), _stream(),
+        )
+        _check(lib, rc, "gemv_stream")
+        return out
     rc = lib.rl_gemv_stream(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_stream out")), c_int(ldo),
         c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), *_wt(), _stream(),

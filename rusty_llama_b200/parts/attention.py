@@ -102,6 +102,10 @@ class Attention(Mixer):
         self.w_o = tensors[p + "o_proj.weight"].contiguous()
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
+        a, w_o = self.forward_unprojected(xn, step, cache, shared_cache)
+        return linear_to_stream(a, w_o)
+
+    def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False):
         # a decode step of a bfloat16 run at head size 64 or 128: the attention kernel turns the queries and the
         # new key and stores key and value itself, if the position encoding is one it knows how to apply
         fusion = None
@@ -147,4 +151,4 @@ class Attention(Mixer):
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
                 step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,
             )
-        return linear_to_stream(a, self.w_o)
+        return a, self.w_o

@@ -179,6 +179,12 @@ class Norm(Part):
         (all, or those named by `rows`) in the activation type."""
         raise NotImplementedError
 
+    def rms_weight(self):
+        """(weight, eps) if this norm is y = x / sqrt(mean(x^2) + eps) * weight, else None: an arrangement
+        may then fold the norm into the products around it (the weight where the product before it stores its
+        result, the row's scale where the product after it stores its own)."""
+        return None
+
 
 class PositionEncoding(Part):
     """How a mixer's queries and keys learn their positions.
@@ -222,10 +228,20 @@ class Mixer(Part):
         shared_cache: the view belongs to an earlier run of the schedule; read it, do not write it."""
         raise NotImplementedError
 
+    def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False):
+        """None, or (a[T, k], w[d, k]) such that forward(...) == a . w^T: a mixer whose last operation is a
+        projection may leave it to the caller, who can then fuse it with what follows."""
+        return None
+
 
 class FeedForward(Part):
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
         raise NotImplementedError
+
+    def gated_weights(self):
+        """None, or (w_gate_up[2 ff, d] with gate and up rows alternating, w_down[d, ff]) if this feed-forward
+        is down(silu(gate(x)) * up(x)) with its weights in that form."""
+        return None
 
 
 class Block(Part):

@@ -52,6 +52,9 @@ class GatedMLP(FeedForward):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"].contiguous()
 
+    def gated_weights(self):
+        return (self.w_gate_up, self.w_down) if self.fused else None
+
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
         if self.fused:
             h = linear_swiglu(xn, self.w_gate_up)

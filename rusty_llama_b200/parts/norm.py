@@ -28,6 +28,9 @@ class RMSNorm(Norm):
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.prefix + "weight"]
 
+    def rms_weight(self):
+        return self.weight, self.eps
+
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         delta, stream.pending = stream.pending, None
         return ops.add_rmsnorm(

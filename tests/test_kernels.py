@@ -838,6 +838,49 @@ def test_gemv_stream_refuses_what_it_cannot_do(ops):
         ops.gemv_stream(torch.zeros(16, 14336, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 14336, dtype=torch.bfloat16, device=DEV))
 
 
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("d, q_dim, ff, norm_dtype", [(256, 128, 320, torch.float32), (1024, 2048, 2752, torch.bfloat16), (4096, 4096, 14336, torch.bfloat16), (192, 64, 96, torch.float32)])
+def test_gemv_stream_with_a_folded_norm(ops, M, d, q_dim, ff, norm_dtype):
+    """An RMSNorm folded into the two products around it: the first adds its sums to the 32-bit stream, writes
+    x * w beside it and leaves the rows' sums of squares; the second takes x * w and scales its sums by the rows'
+    1 / sqrt(mean(x^2) + eps).  Against the three steps done plainly in float64 (stream, norm, gated product),
+    with roundings to bfloat16 where the kernels store bfloat16."""
+    g = torch.Generator().manual_seed(M + d)
+    a = bf16_round(torch.randn(M, q_dim, generator=g))
+    w_o = bf16_round(torch.randn(d, q_dim, generator=g) * (q_dim ** -0.5))
+    x = torch.randn(M, d, generator=g) * 2
+    nw = (1 + 0.1 * torch.randn(d, generator=g)).to(norm_dtype)
+    wg = bf16_round(torch.randn(ff, d, generator=g) * (d ** -0.5))
+    wu = bf16_round(torch.randn(ff, d, generator=g) * (d ** -0.5))
+    w_gu = torch.stack([wg, wu], dim=1).reshape(2 * ff, d)
+    eps = 1e-5
+    xd = x.to(DEV)
+    xw, sumsq, blocks = ops.gemv_stream_into_stream(a.to(torch.bfloat16).to(DEV), w_o.to(torch.bfloat16).to(DEV), xd, nw.to(DEV))
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    x_new = x.double() + a.double() @ w_o.double().T
+    close_f32(xd, x_new, 2e-6)
+    got_x = xd.cpu().double()
+    assert torch.equal(xw.cpu(), (xd.cpu() * nw.float()).to(torch.bfloat16))  # x * w from the stream as stored, rounded once
+    shares = sumsq[: blocks * 8].view(blocks, 8).cpu().double()
+    close_f32(shares.sum(dim=0)[:M], (got_x * got_x).sum(dim=1), 1e-5)
+    assert float(shares[:, M:].abs().max()) == 0.0 if M < 8 else True
+    buf, h = guarded_out(M, ff, torch.bfloat16)
+    ops.gemv_stream(xw, w_gu.to(torch.bfloat16).to(DEV), torch.bfloat16, out=h, swiglu=True, row_scale=(sumsq, blocks, d, eps))
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    assert untouched(buf, M, ff)
+    inv = 1.0 / torch.sqrt((got_x * got_x).mean(dim=1, keepdim=True) + eps)
+    xwf = xw.float().cpu().double()
+    close_bf16(h, plain_silu((xwf @ wg.double().T) * inv) * ((xwf @ wu.double().T) * inv))
+    # and that is the plain norm followed by the plain gated product, up to the roundings
+    xn = bf16_round(plain_rmsnorm(got_x, nw.double(), eps).float()).double()
+    close_bf16(h, plain_silu(xn @ wg.double().T) * (xn @ wu.double().T))
+    # a plain (not gated) product with a row scale, 32-bit out
+    out = ops.gemv_stream(xw, wg.to(torch.bfloat16).to(DEV), torch.float32, row_scale=(sumsq, blocks, d, eps))
+    close_f32(out, (xwf @ wg.double().T) * inv, 3e-5)
+
+
 def test_add_rmsnorm_takes_float32_partial_sums_in_a_bfloat16_run(ops):
     T, d = 6, 520
     x = torch.randn(T, d)
