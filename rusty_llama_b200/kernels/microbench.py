@@ -221,12 +221,12 @@ def bench_step_trace(a) -> dict:
     gen = torch.Generator().manual_seed(0)
     slots = [llm.open_sequence() for _ in range(a.seqs)]
     for s in slots:
-        llm.step([StepEntry(s, torch.randint(0, a.vocab, (a.ctx - 60,), generator=gen).tolist(), [])])  # the traced steps stay inside one page-table width
+        llm.step([StepEntry(s, torch.randint(0, a.vocab, (a.ctx - 400,), generator=gen).tolist(), [])])  # warm-up and traced steps stay inside one page-table width
 
     def decode():
         return llm.step([StepEntry(s, [5], [0]) for s in slots])
 
-    for _ in range(4):  # a plain run, the capture, replays
+    for _ in range(300):  # a plain run, the capture, and enough replays for the SM clock to have come up
         decode()
     torch.cuda.synchronize()
     cap = 8192
@@ -253,8 +253,14 @@ def bench_step_trace(a) -> dict:
     # kernel's predecessor to its own end (the classifier product and the sampler follow the last mark)
     fused = a.head_dim in ops.ATTN_DECODE_TMA_HEAD_DIMS
     one_split = decode_splits(a.seqs, a.heads, a.kv_heads, a.ctx, a.head_dim) == 1
-    layer = ["norm1", "qkv"] + ([] if fused else ["rope"]) + ["attention"] + ([] if (fused and one_split) else ["merge"]) + ["o_proj", "norm2", "gate_up", "down"]
-    names = ["embed"] + layer * a.layers + ["final_norm"]
+    import os
+
+    from .linear import STREAM_MAX_ROWS
+
+    folded = a.seqs <= STREAM_MAX_ROWS and os.environ.get("RL_FOLD_NORM", "1") != "0"  # the second norm has no kernel of its own then
+    layer = (["norm1", "qkv"] + ([] if fused else ["rope"]) + ["attention"] + ([] if (fused and one_split) else ["merge"])
+             + ["o_proj"] + ([] if folded else ["norm2"]) + ["gate_up", "down"])
+    names = ["positions", "embed"] + layer * a.layers + ["final_norm"]  # (the step's first kernel takes the positions from the sequences' records)
     if any(len(r) != len(names) for r in runs):
         raise SystemExit(f"expected {len(names)} intervals per step, got {[len(r) for r in runs]}: the step's kernel list has changed")
     per = {}
