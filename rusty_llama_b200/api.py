@@ -32,7 +32,7 @@ def default_max_tokens(model: Model) -> int:
     per_token = model.cache_bytes_per_token()
     if model.rt.device.type != "cuda" or per_token == 0:
         return want
-    free, _ = torch.cuda.mem_get_info(model.rt.device)
+    free = torch.cuda.mem_get_info(model.rt.device)[0] + torch.cuda.memory_reserved(model.rt.device) - torch.cuda.memory_allocated(model.rt.device)
     fits = int(free * DEFAULT_CACHE_SHARE) // per_token // 64 * 64
     return max(64, min(want, fits))
 

@@ -163,7 +163,8 @@ class Cache:
                     for s in need.shape:
                         n *= s
                     asked += n
-            free, _ = torch.cuda.mem_get_info(self.device)
+            # free on the device, plus what torch's allocator holds without using it (it hands that out first)
+            free = torch.cuda.mem_get_info(self.device)[0] + torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
             if asked > free:
                 raise CacheError(
                     f"a cache of {self.max_tokens} positions needs {asked / 2**30:.1f} GiB, the device has {free / 2**30:.1f} GiB free: "
