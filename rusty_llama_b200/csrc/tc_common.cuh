@@ -67,10 +67,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   // try_wait itself suspends the thread for a while before it answers "not yet", so this is no
   // busy loop (a __nanosleep here was measured to add about a microsecond to every wait); the clock
   // is read every 16 polls
-  const uint64_t t0 = global_ns();
+  // (and for the first time only then: reading it costs a waiting thread about 80 ns, which the issuing
+  // threads of a pipeline, who wait briefly all the time, cannot spare)
+  uint64_t t0 = 0;
   for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spins & 15u) == 0 && global_ns() - t0 > WAIT_LIMIT_NS) return false;
+    if ((spins & 15u) == 0) {
+      if (t0 == 0) t0 = global_ns();
+      else if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
   }
 }
 
@@ -90,12 +95,13 @@ __device__ __forceinline__ bool mbar_wait_role(uint64_t* bar, uint32_t parity, c
     return false;
   }
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
+  uint64_t t0 = 0;
   for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 15u) == 0) {
       if (*ctl.abort) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+      if (t0 == 0) t0 = global_ns();
+      else if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
     }
   }
 }
@@ -106,6 +112,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// The same with shared-memory addresses already in hand (a producer's loop adds to them instead of converting pointers).
+__device__ __forceinline__ void mbar_expect_tx_s(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
 

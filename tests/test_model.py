@@ -175,6 +175,35 @@ def test_batched_decoding_with_leavers_and_slot_reuse(dtype, llms, tiny_weights)
         assert llm.engine.cache.n_open == 0
 
 
+@pytest.mark.parametrize("name, n_seqs", [("A", 12), ("B", 40)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_of_more_than_eight_sequences(name, n_seqs, dtype, llms, tiny_weights):
+    """Batches of 12 and 40 unequal prompts: above 8 rows the bfloat16 decode step takes other kernels (the
+    tensor-core products, the norm folded into them) than the small batches of the other tests."""
+    from rusty_llama_b200 import StepEntry
+
+    cfg = TINY[name][0]
+    llm = llms(name, dtype, max_tokens=64 * 2 * n_seqs, max_seqs=n_seqs)
+    rng = np.random.default_rng(n_seqs)
+    new = 6
+    lens = [int(rng.integers(1, 70)) for _ in range(n_seqs)]
+    seqs = {i: rng.integers(0, cfg["vocab_size"], lens[i] + new).tolist() for i in range(n_seqs)}
+    ref = plain_all_logits(cfg, tiny_weights[name], dtype, seqs)
+    slots = {i: llm.open_sequence() for i in seqs}
+    got = {i: [] for i in seqs}
+    out = llm.step([StepEntry(slots[i], seqs[i][: lens[i]], [lens[i] - 1]) for i in seqs]).cpu().numpy()
+    for i in seqs:
+        got[i].append(out[i : i + 1])
+    for t in range(new):
+        out = llm.step([StepEntry(slots[i], [seqs[i][lens[i] + t]], [0]) for i in seqs]).cpu().numpy()
+        for i in seqs:
+            got[i].append(out[i : i + 1])
+    for i in seqs:
+        llm.close_sequence(slots[i])
+        check_logits(np.concatenate(got[i]), ref[i][lens[i] - 1 :], dtype, f"sequence {i} of {n_seqs}")
+    llm.engine.cache.check_consistent()
+
+
 def test_step_errors_come_before_any_launch(llms):
     from rusty_llama_b200 import CacheError, StepEntry, StepError
 
