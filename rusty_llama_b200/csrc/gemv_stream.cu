@@ -93,10 +93,10 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, uint64_t policy) {
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, uint64_t policy) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
-      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -159,28 +159,37 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     if (lane == 0) {
       const uint64_t pol_w = policy_evict_first();
       const uint32_t ring_addr = smem_u32(ring);
+      const uint32_t full0 = smem_u32(&bars.full[0]);
       int it = 0;
+      uint32_t st = 0, parity = 1, dst = ring_addr;  // the stage of copy `it`; the parity of its `empty` barrier once the ring has gone round
+      int slice = first_item / units, unit = first_item - slice * units;
       bool ok = true;
       for (int item = first_item; item < end_item && ok; ++item) {
-        const int slice = item / units, unit = item - slice * units;
         const int kbeg = slice * slice_len, klen = min(slice_len, K - kbeg);
         for (int k0 = 0; k0 < klen; k0 += KC, ++it) {
-          const int st = it % STAGES, round = it / STAGES;
-          if (round > 0 && !mbar_wait_role(&bars.empty[st], (round - 1) & 1, ctl, 32)) {
+          // (the wait looks at the abort flag itself when it has to wait; the copies of the first round, which
+          // need no wait, are issued whatever the other roles do, and the drain waits for them)
+          if (it >= STAGES && !mbar_wait_role(&bars.empty[st], parity, ctl, 32)) {
             give_up_code(status, 32);
             bars.abort_flag = 1;
             ok = false;
             break;
           }
-          if (*(volatile int*)&bars.abort_flag) {
-            ok = false;
-            break;
-          }
           // rows past N and k past K arrive as zeros and count like the rest
-          mbar_expect_tx(&bars.full[st], STAGE_BYTES);
-          tma_load_3d(ring_addr + st * STAGE_BYTES, &map_w, &bars.full[st], 0, (kbeg + k0) / 64, unit * UNIT_ROWS, pol_w);
+          mbar_expect_tx_s(full0 + 8 * st, STAGE_BYTES);
+          tma_load_3d(dst, &map_w, full0 + 8 * st, 0, (kbeg + k0) >> 6, unit * UNIT_ROWS, pol_w);
           if (it == 0) rl_trace_event(2);            // first copy issued
           if (it == STAGES - 1) rl_trace_event(3);   // the ring is full of requests
+          dst += STAGE_BYTES;
+          if (++st == STAGES) {
+            st = 0;
+            dst = ring_addr;
+            parity ^= 1;
+          }
+        }
+        if (++unit == units) {
+          unit = 0;
+          ++slice;
         }
       }
       rl_trace_event(7);  // last copy issued
@@ -300,7 +309,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
     uint4 xa[SLICE_STAGES][KB_PER_WARP], xb[HI ? SLICE_STAGES : 1][KB_PER_WARP];
-    int loaded_slice = -1, it = 0, done_items = 0;
+    int loaded_slice = -1, done_items = 0;
     bool ok = true;
     auto give_up = [&](int code) {
       if (lane == 0) {
@@ -310,8 +319,13 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
       ok = false;
     };
     pdl_wait();  // the activations are the previous kernel's output, and it may still read ours
+    // The loop over stages keeps counters and addresses (no division, no pointer conversion) and leaves the
+    // abort flag to the wait that has to wait: every instruction here is paid by every product warp for every
+    // stage, and at 16 KB a stage the SM has 640 cycles for all of them together.
+    const uint32_t full0 = smem_u32(&bars.full[0]), empty0 = smem_u32(&bars.empty[0]);
+    uint32_t st = 0, parity = 0, st_off = 0;  // the stage to consume next, the parity of its `full` barrier, its offset in the ring
+    int slice = first_item / units, unit = first_item - slice * units;
     for (int item = first_item; item < end_item && ok; ++item, ++done_items) {
-      const int slice = item / units;
       const int kbeg = slice * slice_len, klen = min(slice_len, K - kbeg);
       if (slice != loaded_slice) {
         // this lane's pieces of the activations of the slice, zero where there is no row or no k
@@ -327,21 +341,22 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
         loaded_slice = slice;
         if (warp == 0 && lane == 0 && item == first_item) rl_trace_event(4);  // activations requested
       }
+      if (++unit == units) {  // (for the next item)
+        unit = 0;
+        ++slice;
+      }
       float acc[2 * KB_PER_WARP][4];
 #pragma unroll
       for (int i = 0; i < 2 * KB_PER_WARP; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 #pragma unroll
       for (int s = 0; s < SLICE_STAGES; ++s) {
         if (s * KC < klen && ok) {
-          const int st = it % STAGES;
-          if (!mbar_wait_role(&bars.full[st], (it / STAGES) & 1, ctl, 34)) {
+          if (!mbar_wait_role_s(full0 + 8 * st, parity, ctl, 34)) {
             give_up(34);
-          } else if (*(volatile int*)&bars.abort_flag) {
-            ok = false;
           } else {
             uint4 b[KB_PER_WARP];
 #pragma unroll
-            for (int j = 0; j < KB_PER_WARP; ++j) b[j] = lds128(w_off[j] + st * STAGE_BYTES);
+            for (int j = 0; j < KB_PER_WARP; ++j) b[j] = lds128(w_off[j] + st_off);
 #pragma unroll
             for (int j = 0; j < KB_PER_WARP; ++j) {
               const uint4 lo = xa[s][j], hi = HI ? xb[s][j] : zero;
@@ -349,9 +364,14 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
               mma_bf16_16x8x16(acc[2 * j + 1], lo.z, hi.z, lo.w, hi.w, b[j].z, b[j].w);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.empty[st]);
-            if (warp == 0 && lane == 0 && it == 0) rl_trace_event(5);  // first stage consumed
-            ++it;
+            if (lane == 0) mbar_arrive_s(empty0 + 8 * st);
+            if (warp == 0 && lane == 0 && item == first_item && s == 0) rl_trace_event(5);  // first stage consumed
+            st_off += STAGE_BYTES;
+            if (++st == STAGES) {
+              st = 0;
+              st_off = 0;
+              parity ^= 1;
+            }
           }
         }
       }

@@ -105,6 +105,28 @@ __device__ __forceinline__ bool mbar_wait_role(uint64_t* bar, uint32_t parity, c
     }
   }
 }
+// The same for a caller that keeps the barrier's shared-memory address (a loop that adds to it).
+__device__ __forceinline__ bool mbar_try_wait_s(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_role_s(uint32_t bar, uint32_t parity, const WaitCtl& ctl, int role) {
+  if (role != ctl.test_role && mbar_try_wait_s(bar, parity)) return true;
+  uint64_t* p = reinterpret_cast<uint64_t*>(__cvta_shared_to_generic(bar));
+  return mbar_wait_role(p, parity, ctl, role);
+}
+__device__ __forceinline__ void mbar_arrive_s(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 // Records why a block gives up: the first code of a launch stays (later ones are consequences of it).
 __device__ __forceinline__ void give_up_code(int* status, int code) { atomicCAS(status, 0, code); }
 
