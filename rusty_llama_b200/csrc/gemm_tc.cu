@@ -285,14 +285,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int tile = unit % n_tiles, ks = unit / n_tiles;
       TO* out_k = out + (size_t)ks * M * ldo;
       const int acc = local & 1;
-      const bool ok = mbar_wait_role(&acc_full[acc], (local >> 1) & 1, ctl, 3);
-      if (!ok) {
-        if (lane == 0) {
-          give_up_code(status, 3);
-          abort_flag = 1;
-        }
-        break;
+      // One warp polls the tile's barrier and the other three wait for it at a hardware barrier, where they take
+      // no issue slots: the pollers of a whole tile's products share their SM sub-partitions with the two single
+      // threads that feed the copy engine and the tensor core.
+      if (quarter == 2 && !mbar_wait_role(&acc_full[acc], (local >> 1) & 1, ctl, 3) && lane == 0) {
+        give_up_code(status, 3);
+        abort_flag = 1;
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*(volatile int*)&abort_flag) break;
       tc_fence_after();
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
