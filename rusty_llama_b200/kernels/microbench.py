@@ -278,8 +278,9 @@ def bench_step_trace(a) -> dict:
         # requested, 5 first stage consumed, 6 last sums handed over, 7 last copy issued, 8 last result
         # stored); every note is taken after an atomic's round trip, about a microsecond late
         marks = [i for i, (_, what) in enumerate(notes) if what == 0]
-        lo, hi = marks[1 + len(layer)], marks[min(1 + 2 * len(layer) + 1, len(marks) - 1)]
-        kernel_at = {marks[1 + len(layer) + j]: nm for j, nm in enumerate(layer + layer[:1])}
+        first = 2 + len(layer)  # marks: positions, embed, the first layer's kernels, then the second layer's
+        lo, hi = marks[first], marks[min(first + len(layer) + 1, len(marks) - 1)]
+        kernel_at = {marks[first + j]: nm for j, nm in enumerate(layer + layer[:1]) if first + j < len(marks)}
         out["events_us"] = [
             [round((when - notes[lo][0]) / 1000.0, 2), ("wait returned: " + kernel_at.get(i, "?")) if what == 0 else what]
             for i, (when, what) in enumerate(notes[lo : hi + 1], start=lo)
