@@ -4,7 +4,7 @@
 // on their way in.  Counterpart of the reference's warp-per-row GEMV family
 // (src/backend/cuda.rs:354-442).
 //
-// Work: the matrix is cut into items of 8 weight rows x one slice of k (at most 4096; the whole of
+// Work: the matrix is cut into items of 8 weight rows x one slice of k (at most 4096, or 5120 when k is longer than 4096; the whole of
 // k unless the caller asks for partial sums); the items, slice by slice, are dealt out to one block
 // per SM in contiguous, equally long ranges.  In a block
 //   warp 16 (one lane)  copies stage after stage of weights, 8 rows x 1024 k = 16 KB each, into a
@@ -48,8 +48,12 @@ RL_DEFINE_ERROR_TEXT()
 #define UNIT_ROWS 8
 #define KC 1024                           // k per stage
 #define STAGE_BYTES (UNIT_ROWS * KC * 2)  // [8 rows][16 blocks of 64 k][128 bytes, swizzled]
-#define MAX_SLICE 4096                    // k per slice: what a warp keeps of the activations is MAX_SLICE / 512 fragments
-#define SLICE_STAGES (MAX_SLICE / KC)
+// k per slice: a warp keeps a slice's activations in registers, one 16-byte fragment per 512 k and row half.  Two
+// builds of the kernel: slices of up to 4096 (four stages), and of up to 5120 (five stages) for products whose k
+// is longer than 4096, which then come in fewer slices or, up to 5120, in one (the 13B sizes' width): with five
+// stages' worth of fragments the compiler is one register short, and the products of k <= 4096 measured 1 % slower.
+#define MAX_SLICE 5120
+#define SHORT_SLICE 4096
 #define KB_PER_WARP (KC / 32 / CONSUMER_WARPS)   // 2
 #define STAGES 13
 #define MAX_M 16
@@ -114,7 +118,7 @@ __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float
 
 // slice_len: k per slice, a multiple of KC and at most MAX_SLICE (the last slice may be shorter);
 // units = ceil(N / 8); items = units * slices, numbered slice by slice.  HI: more than 8 batch rows.
-template <typename TO, bool SWIGLU, bool HI>
+template <typename TO, bool SWIGLU, bool HI, int SLICE_STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ CUtensorMap map_w, TO* __restrict__ out, int ldo,
                    int M, int N, int K, int slice_len, int units, int items, int* __restrict__ status, int test_role,
@@ -410,7 +414,8 @@ static void plan(int K, int k_slices, int* slice_len, int* slices) {
   const int chunks = (K + KC - 1) / KC;
   const int want = k_slices < chunks ? k_slices : chunks;
   int per = (chunks + want - 1) / want;
-  if (per > SLICE_STAGES) per = SLICE_STAGES;
+  const int longest = (K > SHORT_SLICE ? MAX_SLICE : SHORT_SLICE) / KC;
+  if (per > longest) per = longest;
   *slice_len = per * KC;
   *slices = (chunks + per - 1) / per;
 }
@@ -419,7 +424,7 @@ RL_API int rl_gemv_stream_max_rows() { return MAX_M; }
 
 // The slices of k that a call with these arguments produces (1: a finished result; more: partial
 // sums), or 0 when the kernel does not take the shape.  A block keeps a slice of the activations in
-// registers, so a slice is at most 4096 long and longer k always comes in slices.
+// registers, so a slice is at most 5120 long and longer k always comes in slices.
 RL_API int rl_gemv_stream_slices(int M, int K, int k_slices) {
   if (M <= 0 || M > MAX_M || K <= 0 || K % 64 || k_slices < 1 || k_slices > 64) return 0;
   int slice_len, slices;
@@ -448,8 +453,9 @@ static int launch_gemv_stream(const void* x, int ldx, const void* w, int ldw, vo
   if (status == nullptr) RL_REFUSE(10, "gemv_stream: no status word");
   int slice_len, slices;
   plan(K, k_slices, &slice_len, &slices);
-  if (slices > 1 && (swiglu || out_dtype != RL_F32))
-    RL_REFUSE(8, "gemv_stream: k = %d comes in %d slices of at most %d, whose partial sums are float32 and cannot go through the activation", K, slices, MAX_SLICE);
+  // (a caller that did not ask for slices has room for one result only)
+  if (slices > 1 && (swiglu || out_dtype != RL_F32 || k_slices == 1))
+    RL_REFUSE(8, "gemv_stream: k = %d comes in %d slices of at most %d, whose partial sums are float32, cannot go through the activation and have to be asked for (k_slices > 1)", K, slices, MAX_SLICE);
   if (slices_used) *slices_used = slices;
   const int units = (N + UNIT_ROWS - 1) / UNIT_ROWS;
   const long long items_ll = (long long)units * slices;
@@ -485,7 +491,7 @@ static int launch_gemv_stream(const void* x, int ldx, const void* w, int ldw, vo
   }
 #define LAUNCH(TO, SW, HI)                                                                                                  \
   do {                                                                                                                      \
-    auto kern = gemv_stream_kernel<TO, SW, HI>;                                                                             \
+    auto kern = slice_len > SHORT_SLICE ? gemv_stream_kernel<TO, SW, HI, MAX_SLICE / KC> : gemv_stream_kernel<TO, SW, HI, SHORT_SLICE / KC>;    \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)                 \
       RL_REFUSE(14, "gemv_stream: cannot get %d bytes of shared memory", SMEM_BYTES);                                       \
     RL_LAUNCH_CHECK(rl_launch<true>(kern, dim3(blocks), NUM_THREADS, SMEM_BYTES, stream, (const bf16*)x, ldx, map_w,       \

@@ -625,7 +625,8 @@ def gemv_stream(
     _need(w.shape[1] == K, f"gemv_stream: x[{M}, {K}] against w[{N}, {w.shape[1]}]")
     n_out = N // 2 if swiglu else N
     used = c_int(1)
-    slices = gemv_stream_slices(M, K, k_splits) if k_splits > 1 else 1
+    slices = max(1, gemv_stream_slices(M, K, k_splits))  # (0: the launcher says what it does not take)
+    _need(k_splits > 1 or slices == 1, f"gemv_stream: k = {K} comes in {slices} slices, whose float32 partial sums have to be asked for (k_splits > 1)")
     if k_splits > 1 and slices > 1:
         _need(out is None and out_dtype == torch.float32 and not swiglu, "gemv_stream: partial sums over k slices are float32, without activation")
         out = torch.empty((slices, M, n_out), dtype=torch.float32, device=x.device)

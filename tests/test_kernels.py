@@ -755,7 +755,7 @@ def test_gemv_bf16_partial_sums_over_k_slices(ops, M, N, K, splits):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("N, K", [(100, 64), (48, 4096), (257, 960), (4099, 2112), (20000, 1024)])
+@pytest.mark.parametrize("N, K", [(100, 64), (48, 4096), (257, 960), (4099, 2112), (20000, 1024), (72, 5120), (40, 4160)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemv_stream(ops, M, N, K, out_dtype):
     """The persistent TMA-fed kernel: row counts on both sides of 8, feature counts that are no
@@ -775,7 +775,7 @@ def test_gemv_stream(ops, M, N, K, out_dtype):
         close_bf16(out, x.double() @ w.double().T)
 
 
-@pytest.mark.parametrize("M, N, K, splits", [(8, 100, 4096, 4), (1, 48, 960, 3), (16, 257, 3136, 2), (3, 4096, 14336, 7), (8, 24, 2048, 2), (9, 40, 14336, 2)])
+@pytest.mark.parametrize("M, N, K, splits", [(8, 100, 4096, 4), (1, 48, 960, 3), (16, 257, 3136, 2), (3, 4096, 14336, 7), (8, 24, 2048, 2), (9, 40, 14336, 2), (2, 24, 10304, 2), (8, 16, 5184, 2)])
 def test_gemv_stream_partial_sums_over_k_slices(ops, M, N, K, splits):
     x = bf16_round(torch.randn(M, K))
     w = bf16_round(torch.randn(N, K) * 0.05)
@@ -783,7 +783,7 @@ def test_gemv_stream_partial_sums_over_k_slices(ops, M, N, K, splits):
     torch.cuda.synchronize()
     ops.tc_status_check()
     chunks = (K + 1023) // 1024
-    per = min(4, (chunks + min(splits, chunks) - 1) // min(splits, chunks))
+    per = min(5 if K > 4096 else 4, (chunks + min(splits, chunks) - 1) // min(splits, chunks))  # a slice is at most 4096 long, 5120 when k is longer than that
     used = (chunks + per - 1) // per
     assert used == ops.gemv_stream_slices(M, K, splits)
     if used == 1:
@@ -798,7 +798,7 @@ def test_gemv_stream_partial_sums_over_k_slices(ops, M, N, K, splits):
 
 
 @pytest.mark.parametrize("M", [1, 8, 13])
-@pytest.mark.parametrize("ff, K", [(100, 64), (1432, 512), (7168, 1024)])
+@pytest.mark.parametrize("ff, K", [(100, 64), (1432, 512), (7168, 1024), (104, 5120)])
 def test_gemv_stream_fused_swiglu(ops, M, ff, K):
     g = torch.Generator().manual_seed(M + ff)
     x = bf16_round(torch.randn(M, K, generator=g))
@@ -832,14 +832,17 @@ def test_gemv_stream_refuses_what_it_cannot_do(ops):
     assert ops.gemv_stream_slices(2, 72) == 0
     with pytest.raises(KernelError, match="at most 16"):
         ops.gemv_stream(torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV))
-    assert ops.gemv_stream_slices(16, 14336) == 4   # a block keeps at most 4096 activations per row
+    assert ops.gemv_stream_slices(16, 4096) == 1 and ops.gemv_stream_slices(16, 5120) == 1 and ops.gemv_stream_slices(16, 5184) == 2
+    assert ops.gemv_stream_slices(16, 14336) == 3   # a block keeps at most 5120 activations per row
     assert ops.gemv_stream_slices(16, 14336, 7) == 7
-    with pytest.raises(KernelError, match="comes in 4 slices"):
+    with pytest.raises(KernelError, match="comes in 3 slices"):
         ops.gemv_stream(torch.zeros(16, 14336, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 14336, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(KernelError, match="comes in 3 slices"):  # also with a 32-bit result: there is room for one result only
+        ops.gemv_stream(torch.zeros(2, 10304, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 10304, dtype=torch.bfloat16, device=DEV), torch.float32)
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])
-@pytest.mark.parametrize("d, q_dim, ff, norm_dtype", [(256, 128, 320, torch.float32), (1024, 2048, 2752, torch.bfloat16), (4096, 4096, 14336, torch.bfloat16), (192, 64, 96, torch.float32)])
+@pytest.mark.parametrize("d, q_dim, ff, norm_dtype", [(256, 128, 320, torch.float32), (1024, 2048, 2752, torch.bfloat16), (4096, 4096, 14336, torch.bfloat16), (192, 64, 96, torch.float32), (5120, 5120, 1728, torch.bfloat16), (4608, 4160, 200, torch.float32)])
 def test_gemv_stream_with_a_folded_norm(ops, M, d, q_dim, ff, norm_dtype):
     """An RMSNorm folded into the two products around it: the first adds its sums to the 32-bit stream, writes
     x * w beside it and leaves the rows' sums of squares; the second takes x * w and scales its sums by the rows'
