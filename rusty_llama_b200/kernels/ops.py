@@ -558,7 +558,7 @@ def gemv_bf16(
 def gemv_stream_slices(M: int, K: int, k_splits: int = 1) -> int:
     """How many slices of k `gemv_stream` produces for these arguments: 1 is a finished result, more
     are float32 partial sums, 0 means that the kernel does not take the shape (more than 16 rows, k
-    no multiple of 64).  A slice is at most 4096 long, so longer k always comes in slices."""
+    no multiple of 64).  A slice is at most 4096 long, or 5120 when k is longer than 4096, so longer k always comes in slices."""
     lib = build.load("gemv_stream")
     return int(lib.rl_gemv_stream_slices(c_int(M), c_int(K), c_int(k_splits)))
 
@@ -567,7 +567,7 @@ def gemv_stream_into_stream(
     x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, next_w: torch.Tensor, xw: Optional[torch.Tensor] = None,
     sumsq: Optional[torch.Tensor] = None,
 ):
-    """The product before an RMSNorm that is folded into its neighbours (at most 8 rows, k a multiple of 64 up to 4096):
+    """The product before an RMSNorm that is folded into its neighbours (at most 8 rows, k a multiple of 64 up to 5120):
 
         resid (float32 [M, N], in place) += x[M, K] . w[N, K]^T
         xw[M, N] = bfloat16(resid * next_w)           the activations of the product after the norm
@@ -613,7 +613,7 @@ def gemv_stream(
 
     swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums.
     k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (`gemv_stream_slices`
-    says how many: each is a multiple of 1024 and at most 4096 long), for a consumer that adds them up.
+    says how many: each is a multiple of 1024 and at most 5120 long), for a consumer that adds them up.
     row_scale = (sumsq, blocks, norm_k, eps), as left by `gemv_stream_into_stream`: an RMSNorm folded into this
     product, whose x is then `xw`; every row's sums are multiplied by 1 / sqrt(sum(shares) / norm_k + eps) before
     they are stored or go through the activation (at most 8 rows, k in one slice)."""
