@@ -339,8 +339,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // used is returned through *k_splits_used), out is [slices][M][ldo] float32 partial results.
 // wait_test_role, wait_test_ns: 0, 0 in normal use.  A test names one of the codes above and a limit in
 // nanoseconds: the waits of that role then give up after that long instead of a second.
+// tile_n: 0, or the tile width the caller wants (a multiple of 16 up to 256) in the place of the launcher's choice.
 RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                      int K, int swiglu, int k_splits, int* k_splits_used, int* status, int wait_test_role,
+                      int K, int swiglu, int k_splits, int* k_splits_used, int tile_n, int* status, int wait_test_role,
                       unsigned int wait_test_ns, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
@@ -352,6 +353,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   if (status == nullptr) RL_REFUSE(7, "gemm_tc: no status word");
   if (k_splits < 1) RL_REFUSE(12, "gemm_tc: %d k slices", k_splits);
   if (k_splits > 1 && (swiglu || out_dtype != RL_F32)) RL_REFUSE(13, "gemm_tc: partial sums over k slices are float32 and cannot go through the activation");
+  if (tile_n != 0 && (tile_n < 16 || tile_n > BN || tile_n % 16)) RL_REFUSE(14, "gemm_tc: a tile width of %d (a multiple of 16 up to %d)", tile_n, BN);
   {
     const int slices = (K + BK - 1) / BK;
     if (k_splits > slices) k_splits = slices;
@@ -372,7 +374,9 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     const long long at_full_width = tiles_m * ((N + BN - 1) / BN) * k_splits;
     // (every tile reads its rows of x again, so narrower tiles cost L2 traffic: measured at 64 rows, a product
     // with 24 full tiles gains from 128 narrow ones, 29 -> 24 us, one with 112 full tiles does not)
-    if (at_full_width < n_sms / 2) {
+    if (tile_n != 0) {
+      bn = tile_n;
+    } else if (at_full_width < n_sms / 2) {
       const long long per_row = n_sms / (tiles_m * k_splits);  // tiles that one row of tiles may have
       if (per_row >= 1) {
         long long want = (N + per_row - 1) / per_row;

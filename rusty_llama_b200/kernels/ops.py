@@ -724,9 +724,11 @@ def tc_status_check() -> None:
 
 def gemm_tc(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1,
+    swiglu: bool = False, k_splits: int = 1, tile_n: int = 0,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+
+    tile_n: 0 (the launcher chooses), or the width of the output tiles, a multiple of 16 up to 256.
 
     swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit accumulators.
     k_splits > 1: returns float32 [slices, M, N] partial sums over slices of k (at most k_splits of
@@ -756,7 +758,7 @@ def gemm_tc(
     lib = build.load("gemm_tc")
     rc = lib.rl_gemm_tc(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(ldo),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), *_wt(), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), c_int(tile_n), _p(status), *_wt(), _stream(),
     )
     _check(lib, rc, "gemm_tc")
     if k_splits > 1:
