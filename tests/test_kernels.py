@@ -579,6 +579,35 @@ def test_long_context_attention_kernels(ops, hd):
 
 
 @pytest.mark.parametrize("hd", [128, 64])
+def test_flash_prefill_tc_whole_prompts_of_the_benchmarks_length(ops, hd):
+    """Two whole prompts in one call, 2113 and 700 tokens from position 0 (17 and 6 row tiles, up to 34 key tiles
+    for a row tile; blocks are handed out with the longest row tiles first): rows at tile edges, in the middle and
+    at the ends against the float64 attention, and one early key that late rows must still see."""
+    H, K = 4, 2
+    q_lens = [2113, 700]
+    kv = PagedKV(q_lens, K, hd, torch.bfloat16, seed=41)
+    T = sum(q_lens)
+    q = bf16_round(torch.randn(T, (H + 2 * K) * hd, generator=torch.Generator().manual_seed(8)))
+    far = 3
+    boost = bf16_round(q[2100, :hd] * 0.7)  # along row 2100's first head
+    kv.k[0][far, 0] = boost
+    kv.k_pages[int(kv.table[0, far // PAGE]), 0, far % PAGE] = boost.to(torch.bfloat16).to(DEV)
+    out = ops.flash_prefill_tc(
+        q.to(torch.bfloat16).to(DEV), kv.k_pages, kv.v_pages, kv.table, torch.tensor([0, q_lens[0], T], dtype=torch.int32, device=DEV),
+        torch.tensor([0, 0], dtype=torch.int32, device=DEV), max(q_lens), H, K, hd,
+    )
+    torch.cuda.synchronize()
+    ops.tc_status_check()
+    for s, (start, rows) in enumerate([(0, [0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 2047, 2048, 2100, 2111, 2112]), (q_lens[0], [0, 64, 639, 640, 699])]):
+        qr = q[[start + r for r in rows], : H * hd].view(len(rows), H, hd)
+        ref = ref_attention_rows(qr, kv, s, rows).view(len(rows), H * hd)
+        close_bf16(out[[start + r for r in rows]], ref)
+    # the early key carries visible weight in row 2100's first head (so a row tile that skipped its first key tile fails above)
+    scores = (kv.k[0][:2101, 0].double() @ q[2100, :hd].double()) / math.sqrt(hd)
+    assert float(torch.softmax(scores, dim=0)[far]) > 0.05
+
+
+@pytest.mark.parametrize("hd", [128, 64])
 def test_flash_prefill_tc_each_key_and_dimension_lands_where_it_should(ops, hd):
     """Values that name their own key and dimension, queries that each pick one key: any mix-up of pages,
     swizzled pieces, k steps or the transposed V operand shows as a wrong number, not as noise."""
