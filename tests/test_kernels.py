@@ -589,7 +589,7 @@ def test_flash_prefill_tc_whole_prompts_of_the_benchmarks_length(ops, hd):
     T = sum(q_lens)
     q = bf16_round(torch.randn(T, (H + 2 * K) * hd, generator=torch.Generator().manual_seed(8)))
     far = 3
-    boost = bf16_round(q[2100, :hd] * 0.7)  # along row 2100's first head
+    boost = bf16_round(q[2100, :hd] * 1.0)  # along row 2100's first head
     kv.k[0][far, 0] = boost
     kv.k_pages[int(kv.table[0, far // PAGE]), 0, far % PAGE] = boost.to(torch.bfloat16).to(DEV)
     out = ops.flash_prefill_tc(
@@ -604,7 +604,7 @@ def test_flash_prefill_tc_whole_prompts_of_the_benchmarks_length(ops, hd):
         close_bf16(out[[start + r for r in rows]], ref)
     # the early key carries visible weight in row 2100's first head (so a row tile that skipped its first key tile fails above)
     scores = (kv.k[0][:2101, 0].double() @ q[2100, :hd].double()) / math.sqrt(hd)
-    assert float(torch.softmax(scores, dim=0)[far]) > 0.05
+    assert float(torch.softmax(scores, dim=0)[far]) > 0.2
 
 
 @pytest.mark.parametrize("hd", [128, 64])
