@@ -105,6 +105,66 @@ __device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32],
   }
 }
 
+// ------------------------------------------------------------------ the epilogue's way out for bfloat16
+// A thread of the epilogue holds a ROW of the accumulator (its lane of tensor memory), so stores straight from
+// its registers put 16 bytes into each of 32 different lines per instruction.  For whole groups of columns the
+// warp turns its 32 x 64 (or, after SwiGLU, 32 x 32) piece through 4 KB of shared memory instead and writes whole
+// 128-byte (64-byte) rows, eight (four) lanes to a row.  Pieces of 16 bytes are swizzled by the row so that
+// neither the row-wise writes nor the line-wise reads conflict.
+#define OUT_STAGE_BYTES 4096  // per epilogue warp
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+// 64 columns of this lane's row (two tensor-memory loads) -> out[rows of the warp][col0 .. col0 + 63]
+__device__ __forceinline__ void store_rows64_bf16(bf16* out_tile, int ldo, int rows_valid, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
+                                                  uint32_t stage, int lane) {
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const uint32_t* r = p < 4 ? r0 : r1;
+    const int b = (p & 3) * 8;
+    const uint32_t x = pack2(__uint_as_float(r[b]), __uint_as_float(r[b + 1])), y = pack2(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]));
+    const uint32_t z = pack2(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5])), w = pack2(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]));
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + ((p ^ (lane & 7)) << 4)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3), pc = lane & 7;
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + rr * 128 + ((pc ^ (rr & 7)) << 4)));
+    if (rr < rows_valid) *reinterpret_cast<uint4*>(out_tile + (size_t)rr * ldo + pc * 8) = v;
+  }
+  __syncwarp();
+}
+// the same after SwiGLU: 64 accumulator columns (gate and up alternating) -> 32 outputs = 64 bytes a row
+__device__ __forceinline__ void store_rows32_swiglu_bf16(bf16* out_tile, int ldo, int rows_valid, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
+                                                         uint32_t stage, int lane) {
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint32_t* r = p < 2 ? r0 : r1;
+    const int b = (p & 1) * 16;
+    float h[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float g = __uint_as_float(r[b + 2 * i]), u = __uint_as_float(r[b + 2 * i + 1]);
+      h[i] = __fdividef(g, 1.0f + __expf(-g)) * u;  // (as in store_swiglu16)
+    }
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 64 + ((p ^ ((lane >> 1) & 3)) << 4)), "r"(pack2(h[0], h[1])),
+                 "r"(pack2(h[2], h[3])), "r"(pack2(h[4], h[5])), "r"(pack2(h[6], h[7]))
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int rr = it * 8 + (lane >> 2), pc = lane & 3;
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4)));
+    if (rr < rows_valid) *reinterpret_cast<uint4*>(out_tile + (size_t)rr * ldo + pc * 8) = v;
+  }
+  __syncwarp();
+}
+
 // ------------------------------------------------------------------ the kernel
 
 // SWIGLU: w's rows alternate gate and up (row 2i gate i, row 2i+1 up i); the epilogue writes
@@ -280,6 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---------------- epilogue: warps 2..5, each on its quarter of the 128 lanes
     pdl_wait();  // the kernel before this one may still read the output buffer
     const int quarter = warp & 3;
+    const uint32_t out_stage = smem_u32(stages) + (uint32_t)(N_STAGES * STG_BYTES) + (uint32_t)(quarter * OUT_STAGE_BYTES);
     int local = 0;
     for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++local) {
       const int tile = unit % n_tiles, ks = unit / n_tiles;
@@ -297,10 +358,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tc_fence_after();
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * bn;
       const int row = m0 + quarter * 32 + lane;
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      int c = 0;
+      if (sizeof(TO) == 2 && vec_store) {
+        // whole groups of 64 accumulator columns go out through shared memory as whole rows (see above)
+        const int rows_valid = min(32, M - (m0 + quarter * 32));  // (may be <= 0: nothing is written then)
 #pragma unroll 1
-      for (int c = 0; c < (bn + 31) / 32; ++c) {
+        for (; (c + 2) * 32 <= bn && n0 + (c + 2) * 32 <= N; c += 2) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32), r0);
+          tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32 + 32), r1);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          bf16* tile_out = reinterpret_cast<bf16*>(out_k) + (size_t)(m0 + quarter * 32) * ldo + (SWIGLU ? (col >> 1) : col);
+          if (SWIGLU)
+            store_rows32_swiglu_bf16(tile_out, ldo, rows_valid, r0, r1, out_stage, lane);
+          else
+            store_rows64_bf16(tile_out, ldo, rows_valid, r0, r1, out_stage, lane);
+        }
+      }
+#pragma unroll 1
+      for (; c < (bn + 31) / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+        tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32), r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
         const int n_valid = min(N - col, bn - c * 32);  // columns of this piece that belong to the tile and the matrix
@@ -392,7 +472,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   const bool small_a = M <= SMALL_A_ROWS;
   int e1 = make_matrix_map(&map_x, x, M, K, ldx, small_a ? SMALL_A_ROWS : BM), e2 = make_matrix_map(&map_w, w, N, K, ldw, bn);
   if (e1 || e2) RL_REFUSE(9, "gemm_tc: cuTensorMapEncodeTiled unavailable or failed (%d, %d)", e1, e2);
-  const size_t smem = (small_a ? (size_t)5 * (SMALL_A_BYTES + STAGE_B_BYTES) : (size_t)STAGES * STAGE_BYTES) + 1024;
+  const size_t smem = (small_a ? (size_t)5 * (SMALL_A_BYTES + STAGE_B_BYTES) : (size_t)STAGES * STAGE_BYTES) + 4 * OUT_STAGE_BYTES + 1024;
   dim3 grid((unsigned)(tiles < n_sms ? tiles : n_sms));
 #define RL_TC_LAUNCH(TOUT, SW)                                                                                      \
   do {                                                                                                            \
