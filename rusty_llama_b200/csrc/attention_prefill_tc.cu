@@ -60,6 +60,7 @@ struct SmallItems {
   int abort_flag;
 };
 static_assert(sizeof(SmallItems) <= SMALL_BYTES, "the small items must fit behind the tiles");
+static_assert(SOFTMAX_WARPS * ROW_STAGE_BYTES <= P_BYTES, "the output's way out uses the probabilities' buffer");
 static_assert(2 * (SMEM_BYTES_OF(128) + 1024) <= 228 * 1024, "two blocks must fit an SM's shared memory");
 
 // 2^x for x <= 8 or so; -inf gives 0
@@ -347,26 +348,27 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (lane == 0) mbar_arrive(&p_ready);
     }
     if (ok && !mbar_wait_role(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, ctl, 20)) give_up(20);
+    ok = __all_sync(0xffffffffu, ok);  // (the way out below works as a warp)
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      bf16* o = out + (size_t)(tok0 + row0 + r) * out_stride + (size_t)h * HD;
+      // This thread holds a row of the output; the warp turns 64 dims of its 32 rows at a time through the
+      // probabilities' buffer, which the last product has read, and writes whole 128-byte rows (see tc_common.cuh).
+      const uint32_t stage = smem_u32(p_s) + (uint32_t)(warp * ROW_STAGE_BYTES);
+      const int rows_valid = rows_here - warp * 32;  // (may be <= 0: nothing is written then)
+      bf16* o = out + (size_t)(tok0 + row0 + warp * 32) * out_stride + (size_t)h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(o_addr + c * 32, v);
+      for (int c = 0; c < HD / 64; ++c) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(o_addr + c * 64, v0);
+        tmem_ld_32x32b_x32(o_addr + c * 64 + 32, v1);
         tmem_ld_wait();
-        if (r < rows_here) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(o + c * 32 + i) = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
-                                                                   *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
-          }
+        for (int i = 0; i < 32; ++i) {
+          v0[i] = __float_as_uint(__uint_as_float(v0[i]) * inv);
+          v1[i] = __float_as_uint(__uint_as_float(v1[i]) * inv);
         }
+        store_rows64_bf16(o + c * 64, out_stride, rows_valid, v0, v1, stage, lane);
       }
     }
   }

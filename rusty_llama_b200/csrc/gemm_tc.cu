@@ -111,32 +111,7 @@ __device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32],
 // warp turns its 32 x 64 (or, after SwiGLU, 32 x 32) piece through 4 KB of shared memory instead and writes whole
 // 128-byte (64-byte) rows, eight (four) lanes to a row.  Pieces of 16 bytes are swizzled by the row so that
 // neither the row-wise writes nor the line-wise reads conflict.
-#define OUT_STAGE_BYTES 4096  // per epilogue warp
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&p);
-}
-// 64 columns of this lane's row (two tensor-memory loads) -> out[rows of the warp][col0 .. col0 + 63]
-__device__ __forceinline__ void store_rows64_bf16(bf16* out_tile, int ldo, int rows_valid, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
-                                                  uint32_t stage, int lane) {
-#pragma unroll
-  for (int p = 0; p < 8; ++p) {
-    const uint32_t* r = p < 4 ? r0 : r1;
-    const int b = (p & 3) * 8;
-    const uint32_t x = pack2(__uint_as_float(r[b]), __uint_as_float(r[b + 1])), y = pack2(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]));
-    const uint32_t z = pack2(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5])), w = pack2(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]));
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + ((p ^ (lane & 7)) << 4)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-  }
-  __syncwarp();
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int rr = it * 4 + (lane >> 3), pc = lane & 7;
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + rr * 128 + ((pc ^ (rr & 7)) << 4)));
-    if (rr < rows_valid) *reinterpret_cast<uint4*>(out_tile + (size_t)rr * ldo + pc * 8) = v;
-  }
-  __syncwarp();
-}
+#define OUT_STAGE_BYTES ROW_STAGE_BYTES  // per epilogue warp (pack2 and store_rows64_bf16 live in tc_common.cuh)
 // the same for float32 results (partial sums over a slice of k): 32 columns are a row's 128 bytes
 __device__ __forceinline__ void store_rows32_f32(float* out_tile, int ldo, int rows_valid, const uint32_t (&r)[32], uint32_t stage, int lane) {
 #pragma unroll

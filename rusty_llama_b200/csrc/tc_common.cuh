@@ -229,6 +229,38 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---- results that a thread holds by the ROW (tcgen05.ld gives a lane one row of the accumulator), on their way out.
+// Stores straight from such registers put 16 bytes into each of 32 different lines per instruction.  A warp turns
+// its 32 rows x 64 bfloat16 columns through ROW_STAGE_BYTES of shared memory instead (1024-byte aligned; 16-byte
+// pieces swizzled by the row, so that neither the row-wise writes nor the line-wise reads conflict) and writes whole
+// 128-byte rows, eight lanes to a row.
+#define ROW_STAGE_BYTES 4096
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+// 64 columns of this lane's row (two tensor-memory loads) -> out[rows of the warp][col0 .. col0 + 63]
+__device__ __forceinline__ void store_rows64_bf16(bf16* out_tile, int ldo, int rows_valid, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
+                                                  uint32_t stage, int lane) {
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const uint32_t* r = p < 4 ? r0 : r1;
+    const int b = (p & 3) * 8;
+    const uint32_t x = pack2(__uint_as_float(r[b]), __uint_as_float(r[b + 1])), y = pack2(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]));
+    const uint32_t z = pack2(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5])), w = pack2(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]));
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + ((p ^ (lane & 7)) << 4)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3), pc = lane & 7;
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + rr * 128 + ((pc ^ (rr & 7)) << 4)));
+    if (rr < rows_valid) *reinterpret_cast<uint4*>(out_tile + (size_t)rr * ldo + pc * 8) = v;
+  }
+  __syncwarp();
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) and 128-byte
 // swizzled, as TMA writes it: start address, stride between 8-row groups = 1024 bytes, descriptor
 // version 1, layout type 2 (128-byte swizzle).  The leading-dimension field is not used by this layout.
