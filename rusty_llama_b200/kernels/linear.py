@@ -125,9 +125,11 @@ def linear_to_stream(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         # take the same time as tiles of 256 (measured at 64 rows: QKV 12.9 against 14.0 us, output 10.3 against
         # 10.1, down 24.5 against 24.5) and leave half the partial sums for the next kernel to add up (a layer of a
         # decode step: 254 against 258 us at 64 sequences, 395 against 408 at 128; at 16 sequences it loses 2 %).
+        # Only where that still gives most SMs a unit of work: with the short k of the 1.1B sizes it does not (32 units
+        # of 16 k slices each), and a layer at 64 sequences took 71 instead of 66 us.
         tiles = (N + 127) // 128
         splits = min(sms // tiles, 8, max(1, K // 1024)) if tiles <= sms // 2 else 1
-        if splits > 1:
+        if splits > 1 and tiles * splits * 5 >= sms * 4:
             return ops.gemm_tc(x, w, torch.float32, k_splits=splits, tile_n=128)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     splits = min(sms // tiles, 8, max(1, K // 512)) if tiles <= sms // 2 else 1
