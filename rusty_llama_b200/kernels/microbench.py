@@ -288,9 +288,83 @@ def bench_step_trace(a) -> dict:
     return out
 
 
+def bench_probe_stream(a) -> dict:
+    """What HBM delivers to a bare ring of TMA copies (csrc/probe_pipeline.cu), nothing done with the data: 1 GiB
+    read once by one block per SM, for stages of several shapes and rings of several depths."""
+    import ctypes
+
+    from . import build as kbuild
+
+    lib = kbuild.load("probe_pipeline")
+    nbytes = 1 << 30
+    buf = torch.zeros(nbytes // 2, dtype=torch.bfloat16, device="cuda:0")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    rows_out = []
+    K = a.k
+    # (rows, k per stage, walk): the streaming product's stage, the same bytes as fewer and longer rows, a GEMM operand's tile
+    shapes = [(8, 1024, 0), (4, 2048, 0), (2, 4096, 0), (256, 64, 1), (128, 128, 1), (64, 256, 1)]
+    for rows, kc, walk in shapes:
+        if kc > K:
+            continue
+        for stages in (6, 13) if rows * kc * 2 == 16384 else (6,):
+            ms = []
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 6  # (the first launch of a burst waits for the host; it is not timed)
+                for i in range(reps):
+                    if i == 1:
+                        e0.record()
+                    rc = lib.rl_probe_tma_stream(ctypes.c_void_p(buf.data_ptr()), ctypes.c_longlong(nbytes), ctypes.c_int(K), ctypes.c_int(rows),
+                                                 ctypes.c_int(kc), ctypes.c_int(stages), ctypes.c_int(walk), ctypes.c_int(256),
+                                                 ctypes.c_void_p(err.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                    if rc != 0:
+                        raise SystemExit(f"probe_tma_stream refused or failed: {rc} {lib.rl_error_text().decode()}")
+                e1.record()
+                torch.cuda.synchronize()
+                ms.append(e0.elapsed_time(e1) / (reps - 1))
+            if int(err.item()):
+                raise SystemExit("probe_tma_stream: a wait ran out")
+            rows_out.append({"rows": rows, "bytes_per_row": kc * 2, "stage_KB": rows * kc * 2 // 1024, "stages": stages,
+                             "walk": "gemm operand" if walk else "rows along k", "GBps": round(nbytes / (min(ms) * 1e-3) / 1e9, 0)})
+    return {"kernel": "probe_tma_stream", "k": K, "results": rows_out}
+
+
+def bench_probe_handshake(a) -> dict:
+    """What one trip of a producer / consumer pair of single threads costs (csrc/probe_pipeline.cu), in nanoseconds
+    per stage: 128 blocks, 512 stages each, the slowest block."""
+    import ctypes
+
+    from . import build as kbuild
+
+    lib = kbuild.load("probe_pipeline")
+    k_blocks, n_blocks, n_iters = 256, 128, 512
+    buf = torch.zeros(64 * k_blocks * 64, dtype=torch.bfloat16, device="cuda:0")
+    out = torch.zeros(n_blocks, dtype=torch.int64, device="cuda:0")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    modes = [(0, "arrival only, counters"), (4, "arrival only, divisions by the ring's depth"), (8, "arrival only, counters, the timer read per wait"),
+             (1, "one TMA box, counters"), (3, "two TMA boxes, counters"), (5, "one TMA box, divisions"), (9, "one TMA box, counters, the timer read per wait")]
+    res = []
+    for mode, what in modes:
+        for stages in (4, 16):
+            best = None
+            for _ in range(3):
+                rc = lib.rl_probe_handshake(ctypes.c_void_p(buf.data_ptr()), ctypes.c_int(k_blocks), ctypes.c_int(mode), ctypes.c_int(stages),
+                                            ctypes.c_int(n_iters), ctypes.c_int(n_blocks), ctypes.c_void_p(out.data_ptr()),
+                                            ctypes.c_void_p(err.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                torch.cuda.synchronize()
+                if rc != 0:
+                    raise SystemExit(f"probe_handshake refused or failed: {rc} {lib.rl_error_text().decode()}")
+                worst = int(out.max().item())
+                best = worst if best is None else min(best, worst)
+            if int(err.item()):
+                raise SystemExit("probe_handshake: a wait ran out")
+            res.append({"what": what, "stages": stages, "ns_per_stage": round(best / n_iters, 1)})
+    return {"kernel": "probe_handshake", "results": res}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace", "probe_stream", "probe_handshake"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -315,7 +389,8 @@ def main(argv=None) -> int:
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
     fn = {"gemv": bench_gemv, "gemm": bench_gemm, "linear": bench_linear, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
-          "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace}[a.kernel]
+          "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace, "probe_stream": bench_probe_stream,
+          "probe_handshake": bench_probe_handshake}[a.kernel]
     print(json.dumps(fn(a)))
     return 0
 
