@@ -1377,3 +1377,37 @@ def test_sample_empty_nucleus_collapses_to_argmax(ops):
     states = torch.tensor([7], dtype=torch.int64, device=DEV)
     out = ops.sample(logits, 1.0, 0.1, states, torch.zeros(1, dtype=torch.int32, device=DEV), torch.empty(4, device=DEV))
     assert out.item() == 3 and states.item() != 7  # the coin is still drawn
+
+
+def test_pipeline_probes_run():
+    """The two measuring aids of csrc/probe_pipeline.cu on a small buffer: no wait runs out, and the handshake's
+    consumer reports a time for every block."""
+    import ctypes
+
+    from rusty_llama_b200.kernels import build
+
+    lib = build.load("probe_pipeline")
+    lib.rl_error_text.restype = ctypes.c_char_p
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    nbytes = 64 << 20
+    buf = torch.zeros(nbytes // 2, dtype=torch.bfloat16, device=DEV)
+    for rows, kc, stages, walk in [(8, 1024, 13, 0), (2, 4096, 6, 0), (256, 64, 6, 1), (64, 256, 3, 1)]:
+        rc = lib.rl_probe_tma_stream(ctypes.c_void_p(buf.data_ptr()), ctypes.c_longlong(nbytes), ctypes.c_int(4096), ctypes.c_int(rows),
+                                     ctypes.c_int(kc), ctypes.c_int(stages), ctypes.c_int(walk), ctypes.c_int(256), ctypes.c_void_p(err.data_ptr()), stream)
+        assert rc == 0, lib.rl_error_text().decode()
+    rc = lib.rl_probe_tma_stream(ctypes.c_void_p(buf.data_ptr()), ctypes.c_longlong(nbytes), ctypes.c_int(4096), ctypes.c_int(8), ctypes.c_int(1000),
+                                 ctypes.c_int(6), ctypes.c_int(0), ctypes.c_int(256), ctypes.c_void_p(err.data_ptr()), stream)
+    assert rc < 0  # k per stage must be a multiple of 64
+    out = torch.zeros(16, dtype=torch.int64, device=DEV)
+    small = torch.zeros(64 * 16 * 64, dtype=torch.bfloat16, device=DEV)
+    for mode in (0, 1, 3, 4, 5, 8, 9):
+        out.zero_()
+        rc = lib.rl_probe_handshake(ctypes.c_void_p(small.data_ptr()), ctypes.c_int(16), ctypes.c_int(mode), ctypes.c_int(4), ctypes.c_int(64),
+                                    ctypes.c_int(16), ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(err.data_ptr()), stream)
+        assert rc == 0, lib.rl_error_text().decode()
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0 and int(out.min().item()) > 0
+    assert lib.rl_probe_handshake(ctypes.c_void_p(small.data_ptr()), ctypes.c_int(16), ctypes.c_int(2), ctypes.c_int(4), ctypes.c_int(64),
+                                  ctypes.c_int(16), ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(err.data_ptr()), stream) < 0
+
