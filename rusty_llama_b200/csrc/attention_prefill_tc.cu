@@ -10,23 +10,40 @@
 //   warp 5 (one lane)  tcgen05.mma: S = Q K^T (128 x 64, k = head size) into one of two S buffers
 //                      in tensor memory, always one tile ahead; then O += P V (k = 64 keys) into
 //                      the output accumulator, which stays in tensor memory for the whole block,
-//                      with V read as the M/N-contiguous operand it is;
+//                      with P read from tensor memory and V as the M/N-contiguous operand it is;
 //   warps 0-3          one thread per query row (its lane of tensor memory): read the row of S with
 //                      tcgen05.ld (one round trip), its maximum without any shuffle, P = 2^(s - m) rounded to
-//                      bfloat16 and written to shared memory in the swizzled k-major layout the tensor core
-//                      expects.  The running maximum m is only raised when the new one exceeds it by more
-//                      than 8 (P then stays below 2^8, harmless in bfloat16 and 32-bit sums); raising it
-//                      means rescaling the accumulator in tensor memory (tcgen05.ld, multiply, tcgen05.st),
-//                      which after the first tiles is rare.  At the end the row's output is read once and
-//                      divided by the row sum.
-// TWO blocks share an SM (half of its shared memory and half of its tensor memory each): the softmax of a
-// tile is a chain of latencies (tensor-memory load, exponentials, shared-memory stores, a fence) during which
-// a block's own tensor-core work is one tile ahead at most; the other block's products and softmax fill the
-// gaps.  Measured at 2048 tokens of 32 heads: one block per SM with 128-key tiles and two threads per row took
-// 57.9 us (tensor pipe busy 30 % of the time); this form 47.7 us (37 %), and 530 instead of 621 us at 8192
-// tokens; two blocks per SM with two threads per row again (sixteen softmax warps per SM, which have to exchange
-// their maxima) 53.5 us.  A prompt of 512 tokens has too few blocks for two per SM and pays for the shorter
-// tiles: 14.7 us against 10.5.
+//                      bfloat16 and written BACK INTO TENSOR MEMORY with tcgen05.st, two to a column over the first
+//                      half of the row of S it came from; P V takes its A operand from there (no shared-memory round
+//                      trip, no proxy fence, and the tensor core reads 16 KB less shared memory per tile).  The running
+//                      maximum m is only raised when the new one exceeds it by more than 8 (P then stays below 2^8,
+//                      harmless in bfloat16 and 32-bit sums); raising it means rescaling the accumulator in tensor
+//                      memory (tcgen05.ld, multiply, tcgen05.st), which after the first tiles is rare.  At the end the
+//                      row's output is read once and divided by the row sum.
+// TWO blocks share an SM (half of its tensor memory each): the softmax of a tile is a chain of latencies
+// (tensor-memory load, maxima, exponentials, tensor-memory store) during which a block's own tensor-core work is one
+// tile ahead at most; the other block's products and softmax fill the gaps.
+//
+// Measured at 2048 tokens of 32 heads of 128 (8192 tokens in brackets):
+//   one block per SM, 128-key tiles, two threads per row                          57.9 us (621)
+//   this form with P through shared memory                                        44.6 us (530)
+//   this form                                                                     43.0 us (510)
+//   this form alone on its SM (shared memory padded)                              70.6 us (877)
+//   two blocks per SM, two threads per row (sixteen softmax warps exchanging maxima)   53.5 us
+//   the probabilities taken with the standing maximum, beside the search for the new one   45.3 us
+//   256 rows to a block alone on its SM: two query tiles A and B that share every key and value tile, key tiles of
+//   128, S_A S_B O_A O_B filling tensor memory, P over S, one softmax group per query tile working while the tensor
+//   core does the other tile's products                                          52.2 us (560)
+// Notes taken with the SM's clock inside the roles say why.  Per key tile, a block of this form spends 1950 cycles,
+// and its issuing thread is never idle in them: about 800 to get the eight MMAs of S accepted, 520 for the four of
+// P V, 420 in three waits that succeed at once, 200 around the loop.  An MMA of 128 x 64 x 16 takes 32 cycles of
+// tensor-core time but fetches 6 KB of operands from shared memory (Q again for every 64 keys), and what the tensor
+// core gets from shared memory here is 60 to 90 bytes a cycle, with TMA and the other block using it too: the two
+// blocks' products fill the period.  A softmax thread needs about 1500 of the 1950 cycles for its own chain; the
+// SM's exponential unit is busy for 1024 of them.  The form with 256 rows reads Q once per 128 keys, but each query
+// tile's chain there is serial (its S is single: softmax 2000 cycles, then P V and the next S, 1500 to 1800 of
+// issue), so it ends at 4400 cycles per tile of 128 keys for both query tiles, no better per key.  A prompt of 512
+// tokens has too few blocks for two per SM and pays for the short tiles: 13.1 us against 10.5.
 // Softmax statistics, the accumulator and the final division are 32-bit.
 //
 // Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
@@ -38,9 +55,8 @@ RL_DEFINE_ERROR_TEXT()
 #define BNK 64           // keys per tile = one cache page
 #define PAGE 64
 #define KV_STAGES 2
-#define SUBQ_BYTES (128 * 64 * 2)       // a [128 rows][64 columns] swizzled sub-tile of Q or P: 16 KB
+#define SUBQ_BYTES (128 * 64 * 2)       // a [128 rows][64 columns] swizzled sub-tile of Q: 16 KB
 #define SUBK_BYTES (64 * 64 * 2)        // a [64 keys][64 dims] swizzled sub-tile of K or V: 8 KB
-#define P_BYTES SUBQ_BYTES              // the probabilities of a tile, 128 rows x 64 keys
 #define SOFTMAX_WARPS 4
 #define NUM_THREADS ((SOFTMAX_WARPS + 2) * 32)
 #define TMEM_COLS 256                   // S0 at 0, S1 at 64, O at 128
@@ -49,7 +65,7 @@ RL_DEFINE_ERROR_TEXT()
 #define SMALL_BYTES 512
 // Q is HD / 64 sub-tiles of 16 KB; a K or V tile HD / 64 sub-tiles of 8 KB.  Two blocks must fit an SM and
 // no more (a third would wait for tensor memory): at head size 64 the request is padded to that end.
-#define SMEM_NEEDED(HD) ((HD) / 64 * SUBQ_BYTES + 2 * KV_STAGES * ((HD) / 64) * SUBK_BYTES + P_BYTES + SMALL_BYTES)
+#define SMEM_NEEDED(HD) ((HD) / 64 * SUBQ_BYTES + 2 * KV_STAGES * ((HD) / 64) * SUBK_BYTES + SMALL_BYTES)
 #define SMEM_BYTES_OF(HD) (SMEM_NEEDED(HD) > 80 * 1024 ? SMEM_NEEDED(HD) : 80 * 1024)
 
 struct SmallItems {
@@ -60,7 +76,7 @@ struct SmallItems {
   int abort_flag;
 };
 static_assert(sizeof(SmallItems) <= SMALL_BYTES, "the small items must fit behind the tiles");
-static_assert(SOFTMAX_WARPS * ROW_STAGE_BYTES <= P_BYTES, "the output's way out uses the probabilities' buffer");
+static_assert(SOFTMAX_WARPS * ROW_STAGE_BYTES <= SUBQ_BYTES, "the output's way out uses the queries' buffer");
 static_assert(2 * (SMEM_BYTES_OF(128) + 1024) <= 228 * 1024, "two blocks must fit an SM's shared memory");
 
 // 2^x for x <= 8 or so; -inf gives 0
@@ -84,8 +100,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   unsigned char* q_s = smem_dyn;                           // 128 rows x HD
   unsigned char* k_s = q_s + Q_BYTES;                      // KV_STAGES x (64 keys x HD)
   unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;         // KV_STAGES x (64 keys x HD)
-  unsigned char* p_s = v_s + KV_STAGES * KV_BYTES;         // 128 rows x 64 keys
-  SmallItems& sm = *reinterpret_cast<SmallItems*>(p_s + P_BYTES);
+  SmallItems& sm = *reinterpret_cast<SmallItems*>(v_s + KV_STAGES * KV_BYTES);
   uint64_t& q_full = sm.q_full;
   uint64_t(&k_full)[KV_STAGES] = sm.k_full;
   uint64_t(&k_empty)[KV_STAGES] = sm.k_empty;
@@ -187,7 +202,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc_bf16(BMQ, BNK, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BMQ, HD, 0, 1);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const uint32_t q_addr = smem_u32(q_s);
       bool ok = mbar_wait_role(&q_full, 0, ctl, 13);
       if (!ok) {
         give_up_code(status, 13);
@@ -233,12 +248,12 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         tc_fence_after();
         const uint32_t v_addr = smem_u32(v_s + (size_t)st * KV_BYTES);
-        const uint32_t tmem_o = tmem_base + O_COL;
-        // O[128 rows x HD dims] += P[128 x 64 keys] . V[64 keys x HD dims]; a k step is 16 keys
+        const uint32_t tmem_o = tmem_base + O_COL, tmem_p = tmem_base + (uint32_t)((j & 1) * BNK);
+        // O[128 rows x HD dims] += P[128 x 64 keys] . V[64 keys x HD dims]; a k step is 16 keys = 8 columns of P
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_o, make_smem_desc(p_addr + kk * 32), make_smem_desc_mn(v_addr + kk * 2048, SUBK_BYTES, 1024), idesc_pv,
-                    (j > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem_o, tmem_p + kk * 8, make_smem_desc_mn(v_addr + kk * 2048, SUBK_BYTES, 1024), idesc_pv,
+                       (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&v_empty[st]);
         umma_commit(&pv_done[j & 1]);
       }
@@ -264,7 +279,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       ok = false;
     };
-    unsigned char* p_row = p_s + (r >> 3) * 1024 + (r & 7) * 128;  // this row's 128 bytes (64 keys) of the P tile
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (!mbar_wait_role(&s_full[j & 1], (j >> 1) & 1, ctl, 17)) {
         give_up(17);
@@ -306,25 +320,13 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const bool rescale = j > 0 && __any_sync(0xffffffffu, raise && m_run != -INFINITY);
       m_run = m_next;
       const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;  // a row past the sequence's end may see nothing
-      // the probabilities, in registers: they need nothing but S
-      uint32_t pk[BNK / 2];
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int i = 0; i < BNK / 2; ++i) {
-        const float p0 = exp2_fast(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
-        const float p1 = exp2_fast(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
-        sum4[i & 3] += p0 + p1;
-        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-        pk[i] = *reinterpret_cast<uint32_t*>(&b2);
-      }
-      const float row_sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // the P tile (and, for a rescale, the accumulator) is free once the product of the tile before is done
-      if (j > 0 && !mbar_wait_role(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, ctl, 18)) {
-        give_up(18);
-        break;
-      }
       if (rescale) {
-        // the accumulator holds sums scaled by 2^-m_run(old): bring this warp's rows to 2^-m_next
+        // the accumulator holds sums scaled by 2^-m_run(old): bring this warp's rows to 2^-m_next, once the product
+        // of the tile before is done
+        if (!mbar_wait_role(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, ctl, 18)) {
+          give_up(18);
+          break;
+        }
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
@@ -335,15 +337,24 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * a);
           tmem_st_32x32b_x32(o_addr + c * 32, o);
         }
-        tmem_st_wait();
       }
-      l_run = l_run * a + row_sum;
+      // The probabilities, rounded to bfloat16, go back into tensor memory two to a column, over the first half of
+      // this row of S, and the product reads them there.  (The S buffer's next product comes after this tile's P V in
+      // the issuing thread's order, and the tensor core keeps that order.)
+      uint32_t pk[BNK / 2];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c8 = 0; c8 < BNK / 8; ++c8)  // eight keys = one 16-byte piece of the row, swizzled
-        *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) * 16)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
+      for (int i = 0; i < BNK / 2; ++i) {
+        const float p0 = exp2_fast(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
+        const float p1 = exp2_fast(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
+        sum4[i & 3] += p0 + p1;
+        pk[i] = pack2(p0, p1);
+      }
+      tmem_st_32x32b_x32(s_addr, pk);
+      l_run = l_run * a + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      tmem_st_wait();
       // P is complete (and the accumulator rescaled if it had to be): hand both to the tensor core
       tc_fence_before();
-      fence_async_shared();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
@@ -353,8 +364,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       // This thread holds a row of the output; the warp turns 64 dims of its 32 rows at a time through the
-      // probabilities' buffer, which the last product has read, and writes whole 128-byte rows (see tc_common.cuh).
-      const uint32_t stage = smem_u32(p_s) + (uint32_t)(warp * ROW_STAGE_BYTES);
+      // queries' buffer, which no product reads any more, and writes whole 128-byte rows (see tc_common.cuh).
+      const uint32_t stage = smem_u32(q_s) + (uint32_t)(warp * ROW_STAGE_BYTES);
       const int rows_valid = rows_here - warp * 32;  // (may be <= 0: nothing is written then)
       bf16* o = out + (size_t)(tok0 + row0 + warp * 32) * out_stride + (size_t)h * HD;
 #pragma unroll 1
@@ -413,8 +424,8 @@ static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void
 
 // status: one int in device memory, 0 before the call; afterwards non-zero means that a bounded wait
 // expired (11, 12 the producer for a free key / value stage; 13, 14, 15, 16 the tensor-core issuer for the
-// queries, a key tile, the probabilities, a value tile; 17, 18, 20 a softmax warp for the scores, the product before,
-// the last product; 23: shared memory not aligned)
+// queries, a key tile, the probabilities, a value tile; 17, 18, 20 a softmax warp for the scores, the product before
+// a rescale, the last product; 23: shared memory not aligned)
 // and the output is not valid.  wait_test_role, wait_test_ns: 0, 0 in normal use; a test names one of these
 // codes and a limit in nanoseconds, and that role's waits give up after that long instead of a second.
 RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,

@@ -167,6 +167,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
       "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand is read from tensor memory, a row to a lane, two bfloat16 to a
+// column (a k step of 16 is 8 columns), so it costs no shared-memory bandwidth.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // The four MMAs of a 64-wide k slice in one go: operands are k-major with 128-byte rows, so a k step
 // of 16 bfloat16 moves both descriptors' address fields (bytes / 16) by 2.  Only the first one's
 // accumulate flag varies.  The thread that issues MMAs is alone in feeding the tensor core, and every

@@ -700,8 +700,7 @@ _STATUS_NAMES = {
     13: "flash_prefill_tc: the tensor-core issuer (for the queries)", 14: "flash_prefill_tc: the tensor-core issuer (for a key tile)",
     15: "flash_prefill_tc: the tensor-core issuer (for the probabilities)", 16: "flash_prefill_tc: the tensor-core issuer (for a value tile)",
     17: "flash_prefill_tc: a softmax warp (for the scores)", 18: "flash_prefill_tc: a softmax warp (for the product before a rescale)",
-    19: "flash_prefill_tc: a softmax warp (for a free probability buffer)", 20: "flash_prefill_tc: a softmax warp (for the last product)",
-    21: "flash_prefill_tc: a softmax warp (for its partner's maximum)", 22: "flash_prefill_tc: a softmax warp (for its partner's sum)",
+    20: "flash_prefill_tc: a softmax warp (for the last product)",
     23: "flash_prefill_tc: shared memory not aligned",
     32: "gemv_stream: the copying lane (for a free stage)", 34: "gemv_stream: a product warp (for a stage's weights)",
     35: "gemv_stream: a storing warp (for an item's sums)", 36: "gemv_stream: shared memory not aligned",
