@@ -34,13 +34,14 @@
 //   256 rows to a block alone on its SM: two query tiles A and B that share every key and value tile, key tiles of
 //   128, S_A S_B O_A O_B filling tensor memory, P over S, one softmax group per query tile working while the tensor
 //   core does the other tile's products                                          52.2 us (560)
-// Notes taken with the SM's clock inside the roles say why.  Per key tile, a block of this form spends 1950 cycles,
-// and its issuing thread is never idle in them: about 800 to get the eight MMAs of S accepted, 520 for the four of
-// P V, 420 in three waits that succeed at once, 200 around the loop.  An MMA of 128 x 64 x 16 takes 32 cycles of
-// tensor-core time but fetches 6 KB of operands from shared memory (Q again for every 64 keys), and what the tensor
-// core gets from shared memory here is 60 to 90 bytes a cycle, with TMA and the other block using it too: the two
-// blocks' products fill the period.  A softmax thread needs about 1500 of the 1950 cycles for its own chain; the
-// SM's exponential unit is busy for 1024 of them.  The form with 256 rows reads Q once per 128 keys, but each query
+// Notes taken with the SM's clock inside the roles say where a tile's time goes.  Per key tile, a block of this form
+// spends 1950 cycles, and its issuing thread is never idle in them: about 800 until the eight MMAs of S are accepted
+// (100 each for 32 cycles of tensor-core work at 128 x 64 x 16, with the other block's products in the same queue),
+// 520 for the four of P V, 420 in three waits that succeed at once, 200 around the loop.  A softmax thread needs
+// about 1500 of the 1950 cycles for its own chain (wait and load 260, maxima 290, exponentials 650 to 990, store and
+// arrive 100); the SM's exponential unit is busy for 1024 of them.  The profiler's counters for the same launch: tensor
+// pipe 39 % active, issue slots 43 % used, the tensor core's operand reads 35 % of the shared-memory data pipe: no
+// unit is full, the roles wait on one another.  The form with 256 rows reads Q once per 128 keys, but each query
 // tile's chain there is serial (its S is single: softmax 2000 cycles, then P V and the next S, 1500 to 1800 of
 // issue), so it ends at 4400 cycles per tile of 128 keys for both query tiles, no better per key.  A prompt of 512
 // tokens has too few blocks for two per SM and pays for the short tiles: 13.1 us against 10.5.
