@@ -26,25 +26,27 @@
 //
 // Measured at 2048 tokens of 32 heads of 128 (8192 tokens in brackets):
 //   one block per SM, 128-key tiles, two threads per row                          57.9 us (621)
-//   this form with P through shared memory                                        44.6 us (530)
-//   this form                                                                     43.0 us (510)
-//   this form alone on its SM (shared memory padded)                              70.6 us (877)
+//   this form with P through shared memory and a wait, MMAs, commit in turn        44.6 us (530)
+//   the same with P in tensor memory                                              43.0 us (510)
+//   this form (the issuing thread's work in two blocks of instructions a tile)    41.2 us (494)
+//   the form before alone on its SM (shared memory padded)                        70.6 us (877)
 //   two blocks per SM, two threads per row (sixteen softmax warps exchanging maxima)   53.5 us
-//   the probabilities taken with the standing maximum, beside the search for the new one   45.3 us
+//   the probabilities taken with the standing maximum, beside the search for the new one   45.3 us (against 43.0)
 //   256 rows to a block alone on its SM: two query tiles A and B that share every key and value tile, key tiles of
 //   128, S_A S_B O_A O_B filling tensor memory, P over S, one softmax group per query tile working while the tensor
-//   core does the other tile's products                                          52.2 us (560)
-// Notes taken with the SM's clock inside the roles say where a tile's time goes.  Per key tile, a block of this form
-// spends 1950 cycles, and its issuing thread is never idle in them: about 800 until the eight MMAs of S are accepted
-// (100 each for 32 cycles of tensor-core work at 128 x 64 x 16, with the other block's products in the same queue),
-// 520 for the four of P V, 420 in three waits that succeed at once, 200 around the loop.  A softmax thread needs
-// about 1500 of the 1950 cycles for its own chain (wait and load 260, maxima 290, exponentials 650 to 990, store and
-// arrive 100); the SM's exponential unit is busy for 1024 of them.  The profiler's counters for the same launch: tensor
-// pipe 39 % active, issue slots 43 % used, the tensor core's operand reads 35 % of the shared-memory data pipe: no
-// unit is full, the roles wait on one another.  The form with 256 rows reads Q once per 128 keys, but each query
-// tile's chain there is serial (its S is single: softmax 2000 cycles, then P V and the next S, 1500 to 1800 of
-// issue), so it ends at 4400 cycles per tile of 128 keys for both query tiles, no better per key.  A prompt of 512
-// tokens has too few blocks for two per SM and pays for the short tiles: 13.1 us against 10.5.
+//   core does the other tile's products                                          52.2 us (560) (against 43.0)
+// Notes taken with the SM's clock inside the roles said where a tile's 1950 cycles went in the form with 43.0 us.  The
+// issuing thread was never idle in them: about 800 until the eight MMAs of S were accepted, 520 for the four of P V,
+// 420 in three waits that succeeded at once, 200 around the loop; `probe_mma_rate` then showed that such a thread
+// pays 45 cycles per MMA, 170 per commit and 190 per wait whose answer it reads at once, while the tensor core
+// itself takes its nominal 32 cycles for 128 x 64 x 16 (see the issuer below for what was done about it).  A softmax
+// thread needs about 1500 cycles a tile for its own chain (wait and load 260, maxima 290, exponentials 650 to 990,
+// store and arrive 100), the SM's exponential unit is busy for 1024 of them, and with the issuer out of the way that
+// chain is what a tile costs.  The profiler's counters: tensor pipe 39 % active, issue slots 43 % used, the tensor
+// core's operand reads 35 % of the shared-memory data pipe: no unit is full.  The form with 256 rows reads Q once per
+// 128 keys, but each query tile's chain there is serial (its S is single: softmax 2000 cycles, then P V and the next
+// S), so it ends at 4400 cycles per tile of 128 keys for both query tiles, no better per key.  A prompt of 512
+// tokens has too few blocks for two per SM and pays for the short tiles: 12.3 us against 10.5.
 // Softmax statistics, the accumulator and the final division are 32-bit.
 //
 // Every mbarrier wait is bounded; on expiry a code goes to status[0] and the block drains.
@@ -55,7 +57,7 @@ RL_DEFINE_ERROR_TEXT()
 #define BMQ 128          // query rows per block
 #define BNK 64           // keys per tile = one cache page
 #define PAGE 64
-#define KV_STAGES 2
+#define KV_STAGES 2          // (two, like the S buffers: the kernel uses one barrier for "S complete" and "key stage free")
 #define SUBQ_BYTES (128 * 64 * 2)       // a [128 rows][64 columns] swizzled sub-tile of Q: 16 KB
 #define SUBK_BYTES (64 * 64 * 2)        // a [64 keys][64 dims] swizzled sub-tile of K or V: 8 KB
 #define SOFTMAX_WARPS 4
@@ -70,7 +72,7 @@ RL_DEFINE_ERROR_TEXT()
 #define SMEM_BYTES_OF(HD) (SMEM_NEEDED(HD) > 80 * 1024 ? SMEM_NEEDED(HD) : 80 * 1024)
 
 struct SmallItems {
-  uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES];
   uint64_t s_full[2], p_ready, pv_done[2];
   uint64_t drain_bar;              // an issuer that gives up waits here for the MMAs it has issued
   uint32_t tmem_slot;
@@ -85,6 +87,109 @@ __device__ __forceinline__ float exp2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// The MMAs of S = Q K^T for one key tile (a k step is 16 dims; Q and K lie in sub-tiles of 64 dims: 16 KB and 8 KB
+// apart, in the descriptors' units of 16 bytes 1024 and 512), their commit, and a question about another barrier asked
+// first and read last.  Returns 1 if that barrier's phase `peek_parity` is complete.
+template <int HD>
+__device__ __forceinline__ uint32_t qk_block(uint32_t tmem_s, uint64_t q_desc, uint64_t k_desc, uint32_t idesc, uint32_t commit_bar,
+                                             uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ready;
+  if (HD == 128) {
+    asm volatile(
+        "{\n"
+        ".reg .pred t, f, q;\n"
+        ".reg .b64 a1, a2, a3, a4, a5, a6, a7, b1, b2, b3, b4, b5, b6, b7;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%6], %7;\n"
+        "setp.eq.b32 t, 0, 0;\n"
+        "setp.ne.b32 f, 0, 0;\n"
+        "add.u64 a1, %2, 2;\n"
+        "add.u64 b1, %3, 2;\n"
+        "add.u64 a2, %2, 4;\n"
+        "add.u64 b2, %3, 4;\n"
+        "add.u64 a3, %2, 6;\n"
+        "add.u64 b3, %3, 6;\n"
+        "add.u64 a4, %2, 1024;\n"
+        "add.u64 b4, %3, 512;\n"
+        "add.u64 a5, %2, 1026;\n"
+        "add.u64 b5, %3, 514;\n"
+        "add.u64 a6, %2, 1028;\n"
+        "add.u64 b6, %3, 516;\n"
+        "add.u64 a7, %2, 1030;\n"
+        "add.u64 b7, %3, 518;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, f;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a4, b4, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a5, b5, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a6, b6, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a7, b7, %4, t;\n"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n"
+        "selp.u32 %0, 1, 0, q;\n"
+        "}\n"
+        : "=r"(ready)
+        : "r"(tmem_s), "l"(q_desc), "l"(k_desc), "r"(idesc), "r"(commit_bar), "r"(peek_bar), "r"(peek_parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred t, f, q;\n"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%6], %7;\n"
+        "setp.eq.b32 t, 0, 0;\n"
+        "setp.ne.b32 f, 0, 0;\n"
+        "add.u64 a1, %2, 2;\n"
+        "add.u64 b1, %3, 2;\n"
+        "add.u64 a2, %2, 4;\n"
+        "add.u64 b2, %3, 4;\n"
+        "add.u64 a3, %2, 6;\n"
+        "add.u64 b3, %3, 6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, f;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, t;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, t;\n"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n"
+        "selp.u32 %0, 1, 0, q;\n"
+        "}\n"
+        : "=r"(ready)
+        : "r"(tmem_s), "l"(q_desc), "l"(k_desc), "r"(idesc), "r"(commit_bar), "r"(peek_bar), "r"(peek_parity)
+        : "memory");
+  }
+  return ready;
+}
+// The same for O (+)= P V: four MMAs of 16 keys each, P from tensor memory (8 columns a step), V as the M/N-contiguous
+// operand (2048 bytes = 128 units a step).
+template <int HD>
+__device__ __forceinline__ uint32_t pv_block(uint32_t tmem_o, uint32_t tmem_p, uint64_t v_desc, uint32_t idesc, uint32_t accumulate_first,
+                                             uint32_t commit_bar, uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n"
+      ".reg .pred t, p, q;\n"
+      ".reg .b64 b1, b2, b3;\n"
+      ".reg .b32 a1, a2, a3;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%7], %8;\n"
+      "setp.eq.b32 t, 0, 0;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "add.u32 a1, %2, 8;\n"
+      "add.u64 b1, %3, 128;\n"
+      "add.u32 a2, %2, 16;\n"
+      "add.u64 b2, %3, 256;\n"
+      "add.u32 a3, %2, 24;\n"
+      "add.u64 b3, %3, 384;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %4, t;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %4, t;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %4, t;\n"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(ready)
+      : "r"(tmem_o), "r"(tmem_p), "l"(v_desc), "r"(idesc), "r"(accumulate_first), "r"(commit_bar), "r"(peek_bar), "r"(peek_parity)
+      : "memory");
+  return ready;
 }
 
 template <int HD>
@@ -104,9 +209,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   SmallItems& sm = *reinterpret_cast<SmallItems*>(v_s + KV_STAGES * KV_BYTES);
   uint64_t& q_full = sm.q_full;
   uint64_t(&k_full)[KV_STAGES] = sm.k_full;
-  uint64_t(&k_empty)[KV_STAGES] = sm.k_empty;
   uint64_t(&v_full)[KV_STAGES] = sm.v_full;
-  uint64_t(&v_empty)[KV_STAGES] = sm.v_empty;
   uint64_t(&s_full)[2] = sm.s_full;
   uint64_t& p_ready = sm.p_ready;
   uint64_t(&pv_done)[2] = sm.pv_done;
@@ -141,9 +244,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     mbar_init(&q_full, 1);
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
     }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
@@ -176,7 +277,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int tile = tile_lo + j;
         const int page = tile < table_width ? table[tile] : 0;  // a page past the sequence's end is never attended to
         // K
-        if (round > 0 && !mbar_wait_role(&k_empty[st], (round - 1) & 1, ctl, 11)) {
+        // (a key stage is free when the S it fed is complete, a value stage when its P V is: with two stages and two S
+        // buffers, tile j's stage and its S buffer have the same index, and one commit serves both waiters)
+        if (round > 0 && !mbar_wait_role(&s_full[st], (round - 1) & 1, ctl, 11)) {
           give_up_code(status, 11);
           abort_flag = 1;
           break;
@@ -187,7 +290,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int b = 0; b < SUBS; ++b) tma_load_4d(k_s + (size_t)st * KV_BYTES + b * SUBK_BYTES, &map_k, &k_full[st], 64 * b, 0, kh, page);
         issued_k = j + 1;
         // V
-        if (round > 0 && !mbar_wait_role(&v_empty[st], (round - 1) & 1, ctl, 12)) {
+        if (round > 0 && !mbar_wait_role(&pv_done[st], (round - 1) & 1, ctl, 12)) {
           give_up_code(status, 12);
           abort_flag = 1;
           break;
@@ -209,54 +312,51 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         give_up_code(status, 13);
         abort_flag = 1;
       }
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j % KV_STAGES;
-        if (!mbar_wait_role(&k_full[st], (j / KV_STAGES) & 1, ctl, 14)) {
-          give_up_code(status, 14);
-          abort_flag = 1;
-          return false;
-        }
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_s + (size_t)st * KV_BYTES);
-        const uint32_t tmem_s = tmem_base + (uint32_t)((j & 1) * BNK);
-        // S[128 rows x 64 keys] = Q[128 x HD] . K[64 keys x HD]^T; a k step is 16 dims
-#pragma unroll
-        for (int b = 0; b < SUBS; ++b)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_s, make_smem_desc(q_addr + b * SUBQ_BYTES + kk * 32), make_smem_desc(k_addr + b * SUBK_BYTES + kk * 32),
-                      idesc_qk, (b > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&k_empty[st]);
-        umma_commit(&s_full[j & 1]);
-        return true;
+      // Everything this thread asks of the barriers costs it a round trip when it reads the answer at once (190
+      // cycles for a wait that succeeds, 170 for a commit, 45 for an MMA: measured with `probe_mma_rate`), and twelve
+      // MMAs, four commits and three waits a tile kept it busy for all of a tile's 1950 cycles.  So a tile's products
+      // go out as two blocks of instructions (qk_block, pv_block), each with ONE commit and with a question about
+      // data that is needed later (mbarrier.test_wait, which never suspends) asked before its MMAs and read after them.
+      const uint64_t q_desc = make_smem_desc(q_addr);
+      uint32_t v_ready = 0, k_ready = 0;  // the answers: value tile j, key tile j + 2 (for the S after next) have landed
+      auto wait_for = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        if (mbar_wait_role(bar, parity, ctl, code)) return true;
+        give_up_code(status, code);
+        abort_flag = 1;
+        return false;
       };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        // S of the next tile is computed while this tile's softmax runs.  Its buffer was last read by the softmax
-        // of tile j - 1, which had finished before the product of tile j - 1 was issued.
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-        if (!ok) break;
-        if (!mbar_wait_role(&p_ready, j & 1, ctl, 15)) {
-          give_up_code(status, 15);
-          abort_flag = 1;
-          break;
-        }
+      // S(j) = Q K(j)^T into S buffer j & 1; asks for value tile `jv` (used by the P V that comes next)
+      auto issue_qk = [&](int j, int jv) {
         const int st = j % KV_STAGES;
-        if (!mbar_wait_role(&v_full[st], (j / KV_STAGES) & 1, ctl, 16)) {
-          give_up_code(status, 16);
-          abort_flag = 1;
-          break;
-        }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_s + (size_t)st * KV_BYTES);
-        const uint32_t tmem_o = tmem_base + O_COL, tmem_p = tmem_base + (uint32_t)((j & 1) * BNK);
-        // O[128 rows x HD dims] += P[128 x 64 keys] . V[64 keys x HD dims]; a k step is 16 keys = 8 columns of P
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ts(tmem_o, tmem_p + kk * 8, make_smem_desc_mn(v_addr + kk * 2048, SUBK_BYTES, 1024), idesc_pv,
-                       (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&v_empty[st]);
-        umma_commit(&pv_done[j & 1]);
+        v_ready = qk_block<HD>(tmem_base + (uint32_t)((j & 1) * BNK), q_desc, make_smem_desc(smem_u32(k_s + (size_t)st * KV_BYTES)), idesc_qk,
+                               smem_u32(&s_full[j & 1]), smem_u32(&v_full[jv % KV_STAGES]), (uint32_t)((jv / KV_STAGES) & 1));
+      };
+      if (ok) ok = wait_for(&k_full[0], 0, 14);
+      if (ok) issue_qk(0, 0);
+      if (ok && n_tiles > 1) {
+        ok = wait_for(&k_full[1], 0, 14);
+        if (ok) issue_qk(1, 0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        // S of tile j + 1 was issued before this tile's softmax began (above, or at the end of the trip before).  Its
+        // buffer was last read by the P V of tile j - 1, which stands before it in this thread's order.
+        if (!(ok = wait_for(&p_ready, j & 1, 15))) break;
+        const int st = j % KV_STAGES;
+        if (!v_ready && !(ok = wait_for(&v_full[st], (j / KV_STAGES) & 1, 16))) break;
+        tc_fence_after();
+        // O += P(j) V(j); asks for key tile j + 2
+        const int jk = j + 2;
+        k_ready = pv_block<HD>(tmem_base + O_COL, tmem_base + (uint32_t)((j & 1) * BNK),
+                               make_smem_desc_mn(smem_u32(v_s + (size_t)st * KV_BYTES), SUBK_BYTES, 1024), idesc_pv, j > 0 ? 1u : 0u,
+                               smem_u32(&pv_done[j & 1]), smem_u32(&k_full[jk % KV_STAGES]), (uint32_t)((jk / KV_STAGES) & 1));
+        if (jk < n_tiles) {
+          // S of tile j + 2 goes into the buffer whose P this product has just been told to read
+          if (!k_ready && !(ok = wait_for(&k_full[jk % KV_STAGES], (jk / KV_STAGES) & 1, 14))) break;
+          issue_qk(jk, j + 1);
+        } else {
+          v_ready = 0;  // (nobody asked about value tile j + 1)
+        }
       }
       if (*(volatile int*)&abort_flag) {
         // the tensor core may still be at work on what was issued before a wait failed: tensor memory is not

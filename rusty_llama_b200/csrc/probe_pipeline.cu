@@ -9,6 +9,11 @@
 // or without a TMA copy per stage, with counters or with divisions by the ring's depth, with or without a read of
 // the global timer per wait: what one trip of such a single-thread loop costs.
 //
+// rl_probe_mma_rate: one thread per block issues a run of tcgen05.mma (M 128, N n, K 16, bfloat16) on operands that
+// already lie in shared memory (or, for A, in tensor memory), and notes the SM's cycles from the first issue to
+// the arrival of the commit: what the tensor core takes per instruction, by N, with one accumulator or two in
+// turn, with A from shared or from tensor memory, with or without TMA copies landing in the same shared memory.
+//
 // Every wait gives up after 2^22 polls and sets *err.
 #include "tc_common.cuh"
 
@@ -231,5 +236,118 @@ RL_API int rl_probe_handshake(const void* buf, int k_blocks, int mode, int stage
       RL_REFUSE(4, "probe_handshake: mode %d is not one of 0, 1, 3, 4, 5, 8, 9", mode);
   }
 #undef RL_PROBE_MODE
+  return 0;
+}
+
+
+// form bit 0: two accumulators in turn (else one); bit 1: A from tensor memory (n <= 128); bit 2: a second thread keeps
+// three TMA copies of 32 KB in flight into the block's shared memory meanwhile (what a GEMM's producer does); bits 3
+// and 4 (with A from shared memory and one accumulator): a commit after every fourth instruction, a wait and a fence
+// before every fourth (bit 5: the wait without the fence); bit 6: the slice as `umma_bf16_x4_commit_peek` issues it.
+__global__ void __launch_bounds__(128, 1)
+probe_mma_kernel(const __grid_constant__ CUtensorMap map, int k_blocks, int n, int form, int n_mma, long long* out_cycles, int* err) {
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  unsigned char* a_s = base;               // 128 rows x 64 k, 16 KB
+  unsigned char* b_s = base + 16 * 1024;   // 256 rows x 64 k, 32 KB
+  unsigned char* ring = base + 48 * 1024;  // 3 x 32 KB for the copies
+  __shared__ __align__(8) uint64_t done_bar, copy_bar[3], slice_bar, ready_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int stop;
+  for (int i = threadIdx.x; i < 48 * 1024 / 16; i += blockDim.x) reinterpret_cast<uint4*>(base)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    mbar_init(&done_bar, 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&copy_bar[i], 1);
+    mbar_init(&slice_bar, 1);
+    mbar_init(&ready_bar, 1);
+    mbar_arrive(&ready_bar);  // its first phase is complete from the start
+    stop = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  fence_async_shared();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (warp == 0 && lane == 0) {
+    const uint32_t idesc = make_idesc_bf16(128, n, 0, 0);
+    const uint32_t acc1 = (form & 2) ? 128u : 256u, a_tmem = tmem_base + 256;
+    const uint64_t a_desc = make_smem_desc(smem_u32(a_s)), b_desc = make_smem_desc(smem_u32(b_s));
+    long long t0, t1;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t0)::"memory");
+    // (eight at a time with everything but the instruction itself hoisted: the loop must not be what is measured)
+    const uint32_t d0 = tmem_base, d1 = tmem_base + ((form & 1) ? acc1 : 0u);
+    if (form & 2) {
+      for (int i = 0; i < n_mma; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) umma_bf16_ts((u & 1) ? d1 : d0, a_tmem + (u & 3) * 8, b_desc + 2 * (u & 3), idesc, 1u);
+      }
+    } else if (form & 64) {
+      // the same slice with the question about the next stage asked before the MMAs and read after the commit
+      uint32_t not_ready = 0;
+      const uint32_t slice_b = smem_u32(&slice_bar), ready_b = smem_u32(&ready_bar);
+      for (int i = 0; i < n_mma; i += 4) not_ready += 1u - umma_bf16_x4_commit_peek(d0, a_desc, b_desc, idesc, 1u, slice_b, ready_b, 0u);
+      if (not_ready) *err = 3;
+    } else if (form & 56) {
+      // what a GEMM's issuer does between two k slices, after every fourth instruction: bit 3 a commit (to a barrier
+      // nobody waits on), bit 4 a wait on a barrier that is complete and the fence that follows it
+      uint32_t spins = 0;
+      for (int i = 0; i < n_mma; i += 4) {
+        if (form & 16) {
+          while (!mbar_try_wait(&ready_bar, 0) && ++spins < (1u << 22)) {
+          }
+          if (!(form & 32)) tc_fence_after();
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) umma_bf16(d0, a_desc + 2 * u, b_desc + 2 * u, idesc, 1u);
+        if (form & 8) umma_commit(&slice_bar);
+      }
+      if (spins >= (1u << 22)) *err = 1;
+    } else {
+      for (int i = 0; i < n_mma; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) umma_bf16((u & 1) ? d1 : d0, a_desc + 2 * (u & 3), b_desc + 2 * (u & 3), idesc, 1u);
+      }
+    }
+    umma_commit(&done_bar);
+    probe_wait(&done_bar, 0, err);
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t1)::"memory");
+    out_cycles[blockIdx.x] = t1 - t0;
+    *(volatile int*)&stop = 1;
+  } else if (warp == 1 && lane == 0 && (form & 4)) {
+    // copies of 256 rows x 64 k (32 KB) each, three in flight, until the issuer is done (and at most 2^16 of them)
+    int kx = blockIdx.x % k_blocks, issued = 0;
+    for (int i = 0; i < (1 << 16) && !*(volatile int*)&stop; ++i) {
+      const int st = i % 3;
+      if (i >= 3 && !probe_wait(&copy_bar[st], ((i / 3) - 1) & 1, err)) break;
+      mbar_expect_tx(&copy_bar[st], 32 * 1024);
+      tma_load_2d(ring + st * 32 * 1024, &map, &copy_bar[st], kx * 64, 0);
+      issued = i + 1;
+      if (++kx == k_blocks) kx = 0;
+    }
+    // nothing may still be landing in shared memory when the block ends
+    for (int i = issued > 3 ? issued - 3 : 0; i < issued; ++i) probe_wait(&copy_bar[i % 3], (i / 3) & 1, err);
+    out_cycles[gridDim.x + blockIdx.x] = issued;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+// buf: at least 256 rows x k_blocks * 64 bfloat16 (row stride k_blocks * 64); out_cycles: 2 x n_blocks values, each block's
+// cycles and then each block's count of copies.
+RL_API int rl_probe_mma_rate(const void* buf, int k_blocks, int n, int form, int n_mma, int n_blocks, long long* out_cycles, int* err,
+                             cudaStream_t stream) {
+  if (buf == nullptr || out_cycles == nullptr || err == nullptr || k_blocks < 1 || n < 16 || n > 256 || n % 16 || form < 0 || form > 127 ||
+      n_mma < 8 || n_mma % 8 || n_blocks < 1 || ((form & 2) && n > 128))
+    RL_REFUSE(1, "probe_mma_rate: k_blocks=%d n=%d form=%d MMAs=%d blocks=%d", k_blocks, n, form, n_mma, n_blocks);
+  CUtensorMap map;
+  if (make_matrix_map(&map, buf, 256, k_blocks * 64, k_blocks * 64, 256)) RL_REFUSE(2, "probe_mma_rate: cannot describe the buffer to TMA");
+  const size_t smem = (48 + 96 + 1) * 1024;
+  if (cudaFuncSetAttribute(probe_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    RL_REFUSE(3, "probe_mma_rate: cannot get %zu bytes of shared memory", smem);
+  RL_LAUNCH_CHECK(rl_launch<false>(probe_mma_kernel, dim3(n_blocks), 128, smem, stream, map, k_blocks, n, form, n_mma, out_cycles, err));
   return 0;
 }

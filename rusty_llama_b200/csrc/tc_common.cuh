@@ -208,6 +208,42 @@ __device__ __forceinline__ void umma_bf16_x4_pair(uint32_t tmem_d, uint64_t a_de
   RL_UMMA_X4("2");
 }
 
+// A k slice of a GEMM as its issuing thread sees it, in one piece: ask whether the NEXT stage's data has landed
+// (mbarrier.test_wait, which never suspends), issue this stage's four MMAs, commit them to this stage's `empty`
+// barrier, and only then read the answer.  The thread waits some 190 cycles for the answer of a wait and 170 for a
+// commit when it asks and reads in one go (measured with `probe_mma_rate`), on top of 45 per MMA: 650 cycles for
+// a slice whose products take the tensor core 512.  Asked a slice ahead, the answer arrives while the MMAs are issued.
+// Returns 1 when the next stage is ready (0: the caller waits for it in the ordinary way).
+__device__ __forceinline__ uint32_t umma_bf16_x4_commit_peek(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                             uint32_t accumulate_first, uint32_t empty_bar, uint32_t next_full_bar,
+                                                             uint32_t next_parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, t, q;\n"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%7], %8;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "setp.eq.b32 t, 0, 0;\n"
+      "add.u64 a1, %2, 2;\n"
+      "add.u64 b1, %3, 2;\n"
+      "add.u64 a2, %2, 4;\n"
+      "add.u64 b2, %3, 4;\n"
+      "add.u64 a3, %2, 6;\n"
+      "add.u64 b3, %3, 6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, t;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, t;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, t;\n"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(ready)
+      : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(empty_bar), "r"(next_full_bar), "r"(next_parity)
+      : "memory");
+  return ready;
+}
+
 // The barrier receives one arrival when every tcgen05.mma issued before by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

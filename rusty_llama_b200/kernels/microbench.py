@@ -362,9 +362,60 @@ def bench_probe_handshake(a) -> dict:
     return {"kernel": "probe_handshake", "results": res}
 
 
+def bench_probe_mma(a) -> dict:
+    """What the tensor core takes per tcgen05.mma of M 128, N n, K 16 when one thread issues a long run of them on
+    operands that lie still (csrc/probe_pipeline.cu): SM cycles per instruction (the slowest block) against the
+    n / 2 cycles of the nominal rate, on one SM and on all of them."""
+    import ctypes
+
+    from . import build as kbuild
+
+    lib = kbuild.load("probe_pipeline")
+    k_blocks, n_mma = 64, 4096
+    buf = torch.zeros(256 * k_blocks * 64, dtype=torch.bfloat16, device="cuda:0")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    forms = [(0, "A and B from shared memory, one accumulator"), (1, "the same, two accumulators in turn"),
+             (2, "A from tensor memory, one accumulator"), (3, "A from tensor memory, two accumulators in turn"),
+             (4, "A and B from shared memory, one accumulator, TMA copies landing meanwhile"),
+             (6, "A from tensor memory, one accumulator, TMA copies landing meanwhile"),
+             (8, "A and B from shared memory, a commit after every fourth"),
+             (16, "A and B from shared memory, a wait that succeeds and a fence before every fourth"),
+             (48, "A and B from shared memory, a wait that succeeds before every fourth, no fence"),
+             (56, "A and B from shared memory, wait, four instructions, commit, no fence"),
+             (24, "A and B from shared memory, wait, fence, four instructions, commit: a GEMM's k slice"),
+             (28, "the same with TMA copies landing meanwhile"),
+             (64, "the slice with the wait's question asked before its four instructions and read after the commit"),
+             (68, "the same with TMA copies landing meanwhile")]
+    res = []
+    for n in (16, 32, 64, 128, 256):
+        for form, what in forms:
+            if (form & 2) and n > 128:
+                continue
+            for n_blocks in (148,):
+                out = torch.zeros(2 * n_blocks, dtype=torch.int64, device="cuda:0")
+                best = None
+                for _ in range(3):
+                    rc = lib.rl_probe_mma_rate(ctypes.c_void_p(buf.data_ptr()), ctypes.c_int(k_blocks), ctypes.c_int(n), ctypes.c_int(form),
+                                               ctypes.c_int(n_mma), ctypes.c_int(n_blocks), ctypes.c_void_p(out.data_ptr()),
+                                               ctypes.c_void_p(err.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                    torch.cuda.synchronize()
+                    if rc != 0:
+                        raise SystemExit(f"probe_mma_rate refused or failed: {rc} {lib.rl_error_text().decode()}")
+                    worst = int(out[:n_blocks].max().item())
+                    if best is None or worst < best[0]:
+                        best = (worst, int(out[n_blocks:].min().item()))
+                if int(err.item()):
+                    raise SystemExit("probe_mma_rate: a wait ran out")
+                row = {"n": n, "what": what, "blocks": n_blocks, "cycles_per_mma": round(best[0] / n_mma, 1), "nominal": n // 2}
+                if form & 4:
+                    row["copied_bytes_per_cycle"] = round(best[1] * 32768 / best[0], 1)
+                res.append(row)
+    return {"kernel": "probe_mma_rate", "mmas": n_mma, "results": res}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace", "probe_stream", "probe_handshake"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace", "probe_stream", "probe_handshake", "probe_mma"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -390,7 +441,7 @@ def main(argv=None) -> int:
     USE_GRAPH = not a.no_graph
     fn = {"gemv": bench_gemv, "gemm": bench_gemm, "linear": bench_linear, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
           "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace, "probe_stream": bench_probe_stream,
-          "probe_handshake": bench_probe_handshake}[a.kernel]
+          "probe_handshake": bench_probe_handshake, "probe_mma": bench_probe_mma}[a.kernel]
     print(json.dumps(fn(a)))
     return 0
 

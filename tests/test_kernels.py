@@ -1380,8 +1380,8 @@ def test_sample_empty_nucleus_collapses_to_argmax(ops):
 
 
 def test_pipeline_probes_run():
-    """The two measuring aids of csrc/probe_pipeline.cu on a small buffer: no wait runs out, and the handshake's
-    consumer reports a time for every block."""
+    """The measuring aids of csrc/probe_pipeline.cu on small buffers: no wait runs out, the handshake's consumer
+    reports a time for every block, the tensor core is not faster than its nominal rate."""
     import ctypes
 
     from rusty_llama_b200.kernels import build
@@ -1410,4 +1410,18 @@ def test_pipeline_probes_run():
         assert int(err.item()) == 0 and int(out.min().item()) > 0
     assert lib.rl_probe_handshake(ctypes.c_void_p(small.data_ptr()), ctypes.c_int(16), ctypes.c_int(2), ctypes.c_int(4), ctypes.c_int(64),
                                   ctypes.c_int(16), ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(err.data_ptr()), stream) < 0
+    # the tensor core's rate per instruction: every form runs, no wait runs out, a long run of 128 x 256 x 16 takes at
+    # least its nominal 128 cycles an instruction
+    rows256 = torch.zeros(256 * 16 * 64, dtype=torch.bfloat16, device=DEV)
+    cycles = torch.zeros(2 * 4, dtype=torch.int64, device=DEV)
+    for n, form in [(256, 0), (256, 1), (128, 2), (64, 3), (256, 4), (128, 6), (256, 8), (256, 24), (256, 56), (256, 64), (128, 68)]:
+        cycles.zero_()
+        rc = lib.rl_probe_mma_rate(ctypes.c_void_p(rows256.data_ptr()), ctypes.c_int(16), ctypes.c_int(n), ctypes.c_int(form), ctypes.c_int(512),
+                                   ctypes.c_int(4), ctypes.c_void_p(cycles.data_ptr()), ctypes.c_void_p(err.data_ptr()), stream)
+        assert rc == 0, lib.rl_error_text().decode()
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0, f"form {form}: a wait ran out"
+        assert int(cycles[:4].min().item()) >= 512 * (n // 2) * 0.98, f"n {n} form {form}: {cycles[:4].tolist()} cycles for 512 instructions"
+    assert lib.rl_probe_mma_rate(ctypes.c_void_p(rows256.data_ptr()), ctypes.c_int(16), ctypes.c_int(256), ctypes.c_int(2), ctypes.c_int(512),
+                                 ctypes.c_int(4), ctypes.c_void_p(cycles.data_ptr()), ctypes.c_void_p(err.data_ptr()), stream) < 0  # A in tensor memory: n <= 128
 
