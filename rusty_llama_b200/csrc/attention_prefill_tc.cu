@@ -79,6 +79,7 @@ struct SmallItems {
   int abort_flag;
 };
 static_assert(sizeof(SmallItems) <= SMALL_BYTES, "the small items must fit behind the tiles");
+static_assert(KV_STAGES == 2, "tile j's key / value stage and its S buffer / product barrier share the index j & 1");
 static_assert(SOFTMAX_WARPS * ROW_STAGE_BYTES <= SUBQ_BYTES, "the output's way out uses the queries' buffer");
 static_assert(2 * (SMEM_BYTES_OF(128) + 1024) <= 228 * 1024, "two blocks must fit an SM's shared memory");
 
