@@ -32,6 +32,7 @@
 //   the form before alone on its SM (shared memory padded)                        70.6 us (877)
 //   two blocks per SM, two threads per row (sixteen softmax warps exchanging maxima)   53.5 us
 //   the probabilities taken with the standing maximum, beside the search for the new one   45.3 us (against 43.0)
+//   this form with the softmax threads' question about the next S asked a tile ahead       41.5 us (against 41.2)
 //   256 rows to a block alone on its SM: two query tiles A and B that share every key and value tile, key tiles of
 //   128, S_A S_B O_A O_B filling tensor memory, P over S, one softmax group per query tile working while the tensor
 //   core does the other tile's products                                          52.2 us (560) (against 43.0)
