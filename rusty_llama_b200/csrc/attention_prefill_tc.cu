@@ -345,7 +345,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // buffer was last read by the P V of tile j - 1, which stands before it in this thread's order.
         if (!(ok = wait_for(&p_ready, j & 1, 15))) break;
         const int st = j % KV_STAGES;
-        if (!v_ready && !(ok = wait_for(&v_full[st], (j / KV_STAGES) & 1, 16))) break;
+        if (!(ok = wait_for(&v_full[st], (j / KV_STAGES) & 1, 16))) break;
         tc_fence_after();
         // O += P(j) V(j); asks for key tile j + 2
         const int jk = j + 2;
@@ -354,7 +354,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                                smem_u32(&pv_done[j & 1]), smem_u32(&k_full[jk % KV_STAGES]), (uint32_t)((jk / KV_STAGES) & 1));
         if (jk < n_tiles) {
           // S of tile j + 2 goes into the buffer whose P this product has just been told to read
-          if (!k_ready && !(ok = wait_for(&k_full[jk % KV_STAGES], (jk / KV_STAGES) & 1, 14))) break;
+          if (!(ok = wait_for(&k_full[jk % KV_STAGES], (jk / KV_STAGES) & 1, 14))) break;
           issue_qk(jk, j + 1);
         } else {
           v_ready = 0;  // (nobody asked about value tile j + 1)

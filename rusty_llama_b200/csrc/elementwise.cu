@@ -79,6 +79,47 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   const int t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * d;
   float ss = 0.f;
+  if (VEC && d <= (int)blockDim.x * 4) {
+    // One round (what the launcher arranges up to 4096 values): the row stays in registers, the parts are asked for
+    // four at a time and added in their order, and the norm weight is asked for BEFORE the block adds up its squares,
+    // so that no trip to L2 stands between the sum and the stores (the kernel is a chain of such trips and little else).
+    const int i = threadIdx.x * 4;
+    const bool mine = i < d;
+    float v[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (mine) {
+      load4_g<float>(xr + i, v);
+      if (w != nullptr) load4_g<TW>(w + i, wv);
+      const TD* dp = delta + (size_t)t * d + i;
+      int p = 0;
+      for (; p + 4 <= n_parts; p += 4) {
+        float dv[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) load4_g<TD>(dp + (size_t)(p + u) * part_stride, dv[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] += dv[u][e];
+      }
+      for (; p < n_parts; ++p) {
+        float dv[4];
+        load4_g<TD>(dp + (size_t)p * part_stride, dv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] += dv[e];
+      }
+      if (write_x) store4<float>(xr + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+    }
+    if (w == nullptr) return;
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)d + eps);
+    if (mine) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * wv[e];
+      store4<TA>(out + (size_t)r * d + i, v);
+    }
+    return;
+  }
   if (VEC) {
     for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
       float v[4];
@@ -144,7 +185,34 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, int
     if (i < d) load4_g<float>(xr + i, v[c]);
     else v[c][0] = v[c][1] = v[c][2] = v[c][3] = 0.f;
   }
-  for (int p = 0; p < n_parts; ++p) {
+  // the norm weight is asked for here, long before it is used (see add_rmsnorm_kernel)
+  float wv[CHUNKS][4];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = (threadIdx.x + c * 256) * 4;
+    if (w != nullptr && i < d) load4_g<TW>(w + i, wv[c]);
+    else wv[c][0] = wv[c][1] = wv[c][2] = wv[c][3] = 0.f;
+  }
+  // the parts two at a time (all their loads in flight together), added in their order
+  int p = 0;
+  for (; p + 2 <= n_parts; p += 2) {
+    float dv[2][CHUNKS][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int i = (threadIdx.x + c * 256) * 4;
+        if (i < d) load4_g<TD>(delta + (size_t)(p + u) * part_stride + (size_t)t * d + i, dv[u][c]);
+        else dv[u][c][0] = dv[u][c][1] = dv[u][c][2] = dv[u][c][3] = 0.f;
+      }
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[c][e] += dv[u][c][e];
+  }
+  for (; p < n_parts; ++p) {
     float dv[CHUNKS][4];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
@@ -173,10 +241,9 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, int
   for (int c = 0; c < CHUNKS; ++c) {
     const int i = (threadIdx.x + c * 256) * 4;
     if (i < d) {
-      float wv[4], y[4];
-      load4_g<TW>(w + i, wv);
+      float y[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) y[e] = v[c][e] * inv * wv[e];
+      for (int e = 0; e < 4; ++e) y[e] = v[c][e] * inv * wv[c][e];
       store4<TA>(o + i, y);
     }
   }
