@@ -28,11 +28,12 @@
 //   one block per SM, 128-key tiles, two threads per row                          57.9 us (621)
 //   this form with P through shared memory and a wait, MMAs, commit in turn        44.6 us (530)
 //   the same with P in tensor memory                                              43.0 us (510)
-//   this form (the issuing thread's work in two blocks of instructions a tile)    41.2 us (494)
+//   this form (the issuing thread's work in two blocks of instructions a tile, two commits instead of four)   42.0 us (501)
 //   the form before alone on its SM (shared memory padded)                        70.6 us (877)
 //   two blocks per SM, two threads per row (sixteen softmax warps exchanging maxima)   53.5 us
 //   the probabilities taken with the standing maximum, beside the search for the new one   45.3 us (against 43.0)
-//   this form with the softmax threads' question about the next S asked a tile ahead       41.5 us (against 41.2)
+//   with the key and value waits skipped when a question asked a tile ahead said yes: 41.2 us (494), withdrawn (see the issuer)
+//   the same with the softmax threads' question about the next S asked a tile ahead        41.5 us
 //   256 rows to a block alone on its SM: two query tiles A and B that share every key and value tile, key tiles of
 //   128, S_A S_B O_A O_B filling tensor memory, P over S, one softmax group per query tile working while the tensor
 //   core does the other tile's products                                          52.2 us (560) (against 43.0)
@@ -317,8 +318,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       // Everything this thread asks of the barriers costs it a round trip when it reads the answer at once (190
       // cycles for a wait that succeeds, 170 for a commit, 45 for an MMA: measured with `probe_mma_rate`), and twelve
       // MMAs, four commits and three waits a tile kept it busy for all of a tile's 1950 cycles.  So a tile's products
-      // go out as two blocks of instructions (qk_block, pv_block), each with ONE commit and with a question about
-      // data that is needed later (mbarrier.test_wait, which never suspends) asked before its MMAs and read after them.
+      // go out as two blocks of instructions (qk_block, pv_block), each with ONE commit.  Each block also asks about
+      // data that is needed later (mbarrier.test_wait, before its MMAs, read after them); the answers are NOT used
+      // to skip the waits below: the tensor-core GEMM's issuer, built the same way, gave up on a stage about once in
+      // 10^5 launches when it skipped its wait after a yes, and until that is understood every tile is waited for.
       const uint64_t q_desc = make_smem_desc(q_addr);
       uint32_t v_ready = 0, k_ready = 0;  // the answers: value tile j, key tile j + 2 (for the S after next) have landed
       auto wait_for = [&](uint64_t* bar, uint32_t parity, int code) -> bool {

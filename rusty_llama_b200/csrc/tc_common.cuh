@@ -208,11 +208,13 @@ __device__ __forceinline__ void umma_bf16_x4_pair(uint32_t tmem_d, uint64_t a_de
   RL_UMMA_X4("2");
 }
 
-// A k slice of a GEMM as its issuing thread sees it, in one piece: ask whether the NEXT stage's data has landed
+// A k slice of a GEMM as its issuing thread could send it, in one piece: ask whether the NEXT stage's data has landed
 // (mbarrier.test_wait, which never suspends), issue this stage's four MMAs, commit them to this stage's `empty`
 // barrier, and only then read the answer.  The thread waits some 190 cycles for the answer of a wait and 170 for a
-// commit when it asks and reads in one go (measured with `probe_mma_rate`), on top of 45 per MMA: 650 cycles for
-// a slice whose products take the tensor core 512.  Asked a slice ahead, the answer arrives while the MMAs are issued.
+// commit when it asks and reads in one go (measured with `probe_mma_rate`, which uses this function), on top of 45
+// per MMA: 650 cycles for a slice whose products take the tensor core 512.  Asked a slice ahead, the answer arrives
+// while the MMAs are issued.  `gemm_tc` issued its slices this way for a while (0.975 instead of 0.785 of the nominal
+// rate on a single SM) and went back to wait, issue, commit: see its issuer.
 // Returns 1 when the next stage is ready (0: the caller waits for it in the ordinary way).
 __device__ __forceinline__ uint32_t umma_bf16_x4_commit_peek(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                              uint32_t accumulate_first, uint32_t empty_bar, uint32_t next_full_bar,
