@@ -14,6 +14,8 @@ from 2,048-token prompts to 4,096).  `prefill` is one step of 2,048 tokens.  `e2
 the Python entry point `LLM.generate`, host token lists in and out, timed on the host per token over
 at least 512 steps.  `kernels` times the step's main kernels alone at this configuration's shapes.
 Inputs are larger than L2 (a decode step reads every weight: 16 GB), so no explicit L2 flush.
+If a kernel reports that one of its bounded waits ran out, the run is discarded and measured once more
+(`measured_again` in the line then holds the report).
 With `--workload`, the unequal-prompt workloads that BASELINE.json names for the 1b and 13b sizes run
 through `LLM.generate` instead.
 """
@@ -490,10 +492,35 @@ def main() -> int:
             return 2
         print(json.dumps(run_workload(args)))
         return 0
-    out = run_ours(args)
+    out = measured_again_if_a_kernel_gave_up(lambda: run_ours(args))
     if out is not None:
         print(json.dumps(out))
     return 0
+
+
+def measured_again_if_a_kernel_gave_up(run):
+    """run() once; if a kernel of the library reported that one of its bounded waits ran out (a KernelError: that
+    run's numbers are not valid), say so on stderr, give the device memory back and measure once more from the
+    start.  A second failure is raised.  The line of a repeated run says so under `measured_again`."""
+    from rusty_llama_b200.errors import KernelError
+
+    try:
+        return run()
+    except KernelError as e:
+        why = str(e)
+    print(f"[bench] this run is discarded: {why}; measuring once more", file=sys.stderr, flush=True)
+    import gc
+
+    import torch
+
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+    out = run()
+    if isinstance(out, dict):
+        out["measured_again"] = why
+    return out
 
 
 if __name__ == "__main__":

@@ -289,3 +289,28 @@ def test_bench_answers_for_more_gpus_and_for_the_reference_arm():
                          capture_output=True, text=True, timeout=120)
     line = json.loads(ref.stdout.strip())
     assert ref.returncode == 0 and line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+
+
+def test_bench_measures_again_when_a_kernel_gave_up():
+    """A run in which a bounded wait ran out is discarded and repeated once; the line says so; a second failure is
+    the caller's."""
+    import bench
+    from rusty_llama_b200.errors import KernelError
+
+    calls = []
+
+    def flaky():
+        calls.append(1)
+        if len(calls) == 1:
+            raise KernelError("gemm_tc: the tensor-core issuer gave up waiting on a barrier (code 2)")
+        return {"value": 1.0}
+
+    out = bench.measured_again_if_a_kernel_gave_up(flaky)
+    assert len(calls) == 2 and out["value"] == 1.0 and "code 2" in out["measured_again"]
+    assert bench.measured_again_if_a_kernel_gave_up(lambda: {"value": 2.0}) == {"value": 2.0}
+
+    def broken():
+        raise KernelError("again")
+
+    with pytest.raises(KernelError):
+        bench.measured_again_if_a_kernel_gave_up(broken)
